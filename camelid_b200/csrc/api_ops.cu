@@ -1,0 +1,240 @@
+// Operator-level C ABI: the kernels of the decode path on caller-owned device buffers.
+// Used by the microbenchmarks and the kernel-level parity tests; all work runs on the
+// calling thread's current device, default stream, and returns after completion.
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+
+namespace cmld {
+int32_t weight_alloc(Weight &w, int32_t qt, int64_t rows, int64_t cols);
+void weight_free(Weight &w);
+int32_t weight_upload(Weight &w, int32_t qt, int64_t rows, int64_t cols, const void *wire, uint64_t nbytes, cudaStream_t s);
+}  // namespace cmld
+
+using namespace cmld;
+
+static int32_t sync_ok(const char *what) {
+  cudaError_t ce = cudaStreamSynchronize(nullptr);
+  if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
+  return CMLD_OK;
+}
+
+extern "C" {
+
+int32_t cmld_weight_create(int32_t qtype, int64_t rows, int64_t cols, const void *wire, uint64_t nbytes, cmld_weight **out) {
+  if (!out) return fail(CMLD_ERR_INVALID, "null out pointer");
+  *out = nullptr;
+  cmld_weight *w = new cmld_weight();
+  int32_t rc = weight_upload(*w, qtype, rows, cols, wire, nbytes, nullptr);
+  if (rc != CMLD_OK) {
+    weight_free(*w);
+    delete w;
+    return rc;
+  }
+  *out = w;
+  return CMLD_OK;
+}
+
+int32_t cmld_weight_synth(int32_t qtype, uint64_t seed, uint64_t stream, int64_t row0, int64_t rows, int64_t cols,
+                          float sigma, cmld_weight **out) {
+  if (!out) return fail(CMLD_ERR_INVALID, "null out pointer");
+  *out = nullptr;
+  if (qtype == CMLD_Q8_0_HOST36) return fail(CMLD_ERR_UNSUPPORTED, "synthetic weights are generated in wire types only");
+  cmld_weight *w = new cmld_weight();
+  int32_t rc = weight_alloc(*w, qtype, rows, cols);
+  if (rc == CMLD_OK) rc = launch_synth(*w, seed, stream, row0, sigma, nullptr);
+  if (rc == CMLD_OK) rc = sync_ok("weight_synth");
+  if (rc != CMLD_OK) {
+    weight_free(*w);
+    delete w;
+    return rc;
+  }
+  *out = w;
+  return CMLD_OK;
+}
+
+int32_t cmld_weight_destroy(cmld_weight *w) {
+  if (!w) return CMLD_OK;
+  weight_free(*w);
+  delete w;
+  return CMLD_OK;
+}
+
+int64_t cmld_weight_wire_bytes(const cmld_weight *w) { return w ? wire_row_bytes(w->qt, w->cols) * w->rows : 0; }
+
+int32_t cmld_weight_export_wire(const cmld_weight *w, void *wire_out_host) {
+  if (!w || !wire_out_host) return fail(CMLD_ERR_INVALID, "null weight or output");
+  const int64_t n = cmld_weight_wire_bytes(w);
+  if (w->qt == CMLD_F32) {
+    CMLD_CUDA(cudaMemcpy(wire_out_host, w->data, (size_t)n, cudaMemcpyDeviceToHost));
+    return CMLD_OK;
+  }
+  uint8_t *tmp = nullptr;
+  CMLD_CUDA(cudaMalloc(&tmp, (size_t)n));
+  int32_t rc = launch_unpack_to_wire(*w, tmp, nullptr);
+  if (rc == CMLD_OK && cudaMemcpy(wire_out_host, tmp, (size_t)n, cudaMemcpyDeviceToHost) != cudaSuccess)
+    rc = fail(CMLD_ERR_CUDA, "export copy failed");
+  cudaFree(tmp);
+  return rc;
+}
+
+int32_t cmld_weight_dequant(const cmld_weight *w, int64_t row0, int64_t nrows, float *out_dev) {
+  if (!w || !out_dev) return fail(CMLD_ERR_INVALID, "null weight or output");
+  if (row0 < 0 || nrows < 0 || row0 + nrows > w->rows) return fail(CMLD_ERR_INVALID, "rows %lld+%lld out of range", (long long)row0, (long long)nrows);
+  CMLD_TRY(launch_dequant(*w, row0, nrows, out_dev, nullptr));
+  return sync_ok("weight_dequant");
+}
+
+int64_t cmld_act_row_bytes(int64_t cols) { return act_row_stride(cols); }
+
+int32_t cmld_act_quantize(int32_t act_kind, const float *x_dev, int64_t cols, int32_t batch, void *act_dev) {
+  if (!x_dev || !act_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  if (act_kind != CMLD_ACT_Q8_0 && act_kind != CMLD_ACT_Q8_K) return fail(CMLD_ERR_INVALID, "unknown activation format %d", act_kind);
+  NormQuantArgs a{};
+  a.x = x_dev;
+  a.cols = cols;
+  a.batch = batch;
+  a.act = static_cast<uint8_t *>(act_dev);
+  a.act2 = a.act;
+  a.act_q8_0 = act_kind == CMLD_ACT_Q8_0;
+  a.act_q8_k = act_kind == CMLD_ACT_Q8_K;
+  CMLD_TRY(launch_norm_quant(a, nullptr));
+  return sync_ok("act_quantize");
+}
+
+int32_t cmld_act_export(int32_t act_kind, const void *act_dev, int64_t cols, int32_t batch, int8_t *codes_out, float *scales_out) {
+  if (!act_dev || !codes_out || !scales_out) return fail(CMLD_ERR_INVALID, "null buffer");
+  const int64_t stride = act_row_stride(cols);
+  const int64_t nsc = act_kind == CMLD_ACT_Q8_0 ? cols / 32 : cols / 256;
+  const uint8_t *a = static_cast<const uint8_t *>(act_dev);
+  for (int b = 0; b < batch; ++b) {
+    CMLD_CUDA(cudaMemcpy(codes_out + (int64_t)b * cols, a + b * stride, (size_t)cols, cudaMemcpyDeviceToHost));
+    CMLD_CUDA(cudaMemcpy(scales_out + (int64_t)b * nsc, a + b * stride + act_scale_off(cols), (size_t)nsc * 4, cudaMemcpyDeviceToHost));
+  }
+  return CMLD_OK;
+}
+
+int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, float *y_dev, const float *residual_dev) {
+  if (!w || !act_dev || !y_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  if (w->qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "gemv over f32 weights is not part of this path");
+  if (batch < 1) return fail(CMLD_ERR_INVALID, "batch %d", batch);
+  GemvJob j{w->data, w->qt, w->rows, w->cols, w->stride, y_dev, residual_dev, w->rows};
+  CMLD_TRY(launch_gemv(&j, 1, static_cast<const uint8_t *>(act_dev), batch, nullptr));
+  return sync_ok("gemv");
+}
+
+int32_t cmld_gemv_time(cmld_weight *const *copies, int32_t n_copies, const void *act_dev, int32_t batch, float *y_dev,
+                       int32_t warmup, int32_t iters, float *ms_per_launch_out) {
+  if (!copies || n_copies < 1 || !act_dev || !y_dev || !ms_per_launch_out || iters < 1) return fail(CMLD_ERR_INVALID, "bad arguments");
+  for (int i = 0; i < n_copies; ++i)
+    if (!copies[i] || copies[i]->qt == CMLD_F32) return fail(CMLD_ERR_INVALID, "bad weight %d", i);
+  cudaEvent_t e0, e1;
+  CMLD_CUDA(cudaEventCreate(&e0));
+  CMLD_CUDA(cudaEventCreate(&e1));
+  int32_t rc = CMLD_OK;
+  for (int it = -warmup; it < iters && rc == CMLD_OK; ++it) {
+    if (it == 0) cudaEventRecord(e0, nullptr);
+    const cmld_weight *w = copies[((it % n_copies) + n_copies) % n_copies];
+    GemvJob j{w->data, w->qt, w->rows, w->cols, w->stride, y_dev, nullptr, w->rows};
+    rc = launch_gemv(&j, 1, static_cast<const uint8_t *>(act_dev), batch, nullptr);
+  }
+  cudaEventRecord(e1, nullptr);
+  if (rc == CMLD_OK) rc = sync_ok("gemv_time");
+  float ms = 0.0f;
+  if (rc == CMLD_OK) cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *ms_per_launch_out = ms / (float)iters;
+  return rc;
+}
+
+int32_t cmld_rms_norm(const float *x_dev, const float *w_dev, int64_t cols, int32_t batch, float eps, float *out_dev,
+                      int32_t act_kind, void *act_dev) {
+  if (!x_dev || !w_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  NormQuantArgs a{};
+  a.x = x_dev;
+  a.weight = w_dev;
+  a.eps = eps;
+  a.cols = cols;
+  a.batch = batch;
+  a.out = out_dev;
+  a.act = a.act2 = static_cast<uint8_t *>(act_dev);
+  a.act_q8_0 = act_dev && act_kind == CMLD_ACT_Q8_0;
+  a.act_q8_k = act_dev && act_kind == CMLD_ACT_Q8_K;
+  CMLD_TRY(launch_norm_quant(a, nullptr));
+  return sync_ok("rms_norm");
+}
+
+int32_t cmld_silu_mul(const float *g_dev, const float *u_dev, int64_t cols, int32_t batch, float *out_dev, int32_t act_kind,
+                      void *act_dev) {
+  if (!g_dev || !u_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  NormQuantArgs a{};
+  a.x = g_dev;
+  a.x2 = u_dev;
+  a.cols = cols;
+  a.batch = batch;
+  a.out = out_dev;
+  a.act = a.act2 = static_cast<uint8_t *>(act_dev);
+  a.act_q8_0 = act_dev && act_kind == CMLD_ACT_Q8_0;
+  a.act_q8_k = act_dev && act_kind == CMLD_ACT_Q8_K;
+  CMLD_TRY(launch_norm_quant(a, nullptr));
+  return sync_ok("silu_mul");
+}
+
+int32_t cmld_argmax(const float *x_dev, int64_t n, int32_t batch, uint32_t *idx_out_host) {
+  if (!x_dev || !idx_out_host || n < 1 || batch < 1) return fail(CMLD_ERR_INVALID, "bad arguments");
+  const int nb = argmax_blocks();
+  uint8_t *scratch = nullptr;
+  const size_t bytes = (size_t)batch * nb * 8 + (size_t)batch * 8 + (size_t)batch * 4;
+  CMLD_CUDA(cudaMalloc(&scratch, bytes));
+  cudaMemset(scratch, 0, bytes);
+  float *pv = reinterpret_cast<float *>(scratch);
+  int32_t *pi = reinterpret_cast<int32_t *>(scratch + (size_t)batch * nb * 4);
+  uint32_t *ticket = reinterpret_cast<uint32_t *>(scratch + (size_t)batch * nb * 8);
+  int32_t *out = reinterpret_cast<int32_t *>(scratch + (size_t)batch * nb * 8 + (size_t)batch * 8);
+  int32_t rc = launch_argmax(x_dev, n, batch, pv, pi, ticket, out, nullptr, nullptr, nullptr, nullptr);
+  std::vector<int32_t> host(batch);
+  if (rc == CMLD_OK && cudaMemcpy(host.data(), out, (size_t)batch * 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+    rc = fail(CMLD_ERR_CUDA, "argmax copy failed");
+  cudaFree(scratch);
+  for (int i = 0; i < batch && rc == CMLD_OK; ++i) idx_out_host[i] = (uint32_t)host[i];
+  return rc;
+}
+
+int32_t cmld_attention_decode(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev, int32_t n_heads,
+                              int32_t n_kv_heads, int32_t head_dim, int64_t max_pos, int64_t n_pos, float scale, float *out_dev) {
+  if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  if (n_pos < 1 || n_pos > max_pos) return fail(CMLD_ERR_INVALID, "n_pos %lld out of range", (long long)n_pos);
+  const int n_splits = (int)std::max<int64_t>(1, std::min<int64_t>(37, max_pos / 32));
+  const size_t part_bytes = (size_t)n_heads * n_splits * (head_dim + 2) * 4;
+  uint8_t *scratch = nullptr;
+  CMLD_CUDA(cudaMalloc(&scratch, part_bytes + (size_t)n_kv_heads * 4 + 8));
+  cudaMemset(scratch, 0, part_bytes + (size_t)n_kv_heads * 4 + 8);
+  int32_t *pos_slot = reinterpret_cast<int32_t *>(scratch + part_bytes + (size_t)n_kv_heads * 4);
+  const int32_t ps[2] = {(int32_t)(n_pos - 1), 0};
+  cudaMemcpy(pos_slot, ps, 8, cudaMemcpyHostToDevice);
+  AttnArgs a{};
+  a.q = q_dev;
+  a.k_cache = static_cast<const __half *>(k_cache_dev);
+  a.v_cache = static_cast<const __half *>(v_cache_dev);
+  a.positions = pos_slot;
+  a.slots = pos_slot + 1;
+  a.n_heads = n_heads;
+  a.n_kv_heads = n_kv_heads;
+  a.head_dim = head_dim;
+  a.batch = 1;
+  a.n_splits = n_splits;
+  a.max_pos = max_pos;
+  a.scale = scale;
+  a.part = reinterpret_cast<float *>(scratch);
+  a.tickets = reinterpret_cast<uint32_t *>(scratch + part_bytes);
+  a.out = out_dev;
+  a.q_stride = (int64_t)n_heads * head_dim;
+  int32_t rc = launch_attention(a, nullptr);
+  if (rc == CMLD_OK) rc = sync_ok("attention_decode");
+  cudaFree(scratch);
+  return rc;
+}
+
+}  // extern "C"

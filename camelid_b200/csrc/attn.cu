@@ -1,0 +1,225 @@
+// Single-query grouped-query attention over the f16 KV cache (decode step).
+//
+// CPU form (attention_context_for_head_into_with_kernels, src/inference.rs:30287-30466 in the
+// Camelid tree): score_p = dot(q, K_p) * scale; softmax over the cached positions; out =
+// sum_p prob_p * V_p.  Here the positions of one (sequence, kv head) are cut into n_splits
+// ranges handled by separate CTAs (flash-decoding): every CTA serves all n_heads/n_kv_heads
+// query heads of its kv head so each K/V row is read once, keeps a running (max, sum, acc)
+// per head, and the CTA that finishes last merges the ranges.  The result agrees with the
+// CPU's sequential sums up to f32 reassociation.
+#include "common.cuh"
+
+namespace cmld {
+
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kAttnChunk = 256;  // positions per softmax chunk
+constexpr int kMaxGroup = 8;     // query heads per kv head
+constexpr int kMaxPer = 8;       // head_dim / 32
+
+// PER consecutive f16 values of a cache row, widened to f32 (one 2/4/8-byte load).
+template <int PER>
+__device__ __forceinline__ void load_halves(const __half *p, float (&out)[PER]) {
+  if constexpr (PER == 4) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const __half2 h0 = *reinterpret_cast<const __half2 *>(&raw.x), h1 = *reinterpret_cast<const __half2 *>(&raw.y);
+    out[0] = __low2float(h0);
+    out[1] = __high2float(h0);
+    out[2] = __low2float(h1);
+    out[3] = __high2float(h1);
+  } else if constexpr (PER == 2) {
+    const __half2 h0 = *reinterpret_cast<const __half2 *>(p);
+    out[0] = __low2float(h0);
+    out[1] = __high2float(h0);
+  } else {
+#pragma unroll
+    for (int e = 0; e < PER; ++e) out[e] = __half2float(p[e]);
+  }
+}
+
+template <int G, int PER>
+__global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
+  uint32_t *tickets = a.tickets;
+  constexpr int HD = PER * 32;
+  const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_pos = a.positions[b] + 1;
+  const int slot = a.slots[b];
+  const int len = (n_pos + a.n_splits - 1) / a.n_splits;
+  const int lo = split * len, hi = min(n_pos, lo + len);
+
+  __shared__ float s_q[G][HD];
+  __shared__ float s_sc[G][kAttnChunk];
+  __shared__ float s_red[kAttnWarps][G];
+  __shared__ float s_acc[kAttnWarps][G][HD];
+  __shared__ bool s_last;
+
+  const float *q = a.q + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
+  for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) s_q[i / HD][i % HD] = q[i];
+  __syncthreads();
+  float qr[G][PER];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < PER; ++e) qr[g][e] = s_q[g][lane * PER + e];
+
+  const __half *kbase = a.k_cache + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
+  const __half *vbase = a.v_cache + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
+
+  float m_run[G], l_run[G], acc[G][PER];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m_run[g] = -INFINITY;
+    l_run[g] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) acc[g][e] = 0.0f;
+  }
+
+  for (int c0 = lo; c0 < hi; c0 += kAttnChunk) {
+    const int cn = min(kAttnChunk, hi - c0);
+    // scores of this chunk
+    for (int p = warp; p < cn; p += kAttnWarps) {
+      const __half *kr = kbase + (int64_t)(c0 + p) * HD + lane * PER;
+      float kv[PER];
+      load_halves<PER>(kr, kv);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.0f;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) d = __fmaf_rn(qr[g][e], kv[e], d);
+        d = warp_sum(d);
+        if (lane == 0) s_sc[g][p] = __fmul_rn(d, a.scale);
+      }
+    }
+    __syncthreads();
+    // chunk maximum per head
+    float cm[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float v = -INFINITY;
+      for (int p = threadIdx.x; p < cn; p += kAttnThreads) v = fmaxf(v, s_sc[g][p]);
+      v = warp_max(v);
+      if (lane == 0) s_red[warp][g] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float v = s_red[0][g];
+#pragma unroll
+      for (int w = 1; w < kAttnWarps; ++w) v = fmaxf(v, s_red[w][g]);
+      cm[g] = fmaxf(m_run[g], v);
+    }
+    __syncthreads();
+    // probabilities in place, running sums
+    float ls[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.0f;
+      for (int p = threadIdx.x; p < cn; p += kAttnThreads) {
+        const float e = expf(s_sc[g][p] - cm[g]);
+        s_sc[g][p] = e;
+        s += e;
+      }
+      s = warp_sum(s);
+      if (lane == 0) s_red[warp][g] = s;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) s += s_red[w][g];
+      ls[g] = s;
+      const float corr = m_run[g] == -INFINITY ? 0.0f : expf(m_run[g] - cm[g]);
+      l_run[g] = l_run[g] * corr + ls[g];
+#pragma unroll
+      for (int e = 0; e < PER; ++e) acc[g][e] *= corr;
+      m_run[g] = cm[g];
+    }
+    // weighted values: warp w takes positions w, w+8, ...
+    for (int p = warp; p < cn; p += kAttnWarps) {
+      const __half *vr = vbase + (int64_t)(c0 + p) * HD + lane * PER;
+      float vv[PER];
+      load_halves<PER>(vr, vv);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pr = s_sc[g][p];
+#pragma unroll
+        for (int e = 0; e < PER; ++e) acc[g][e] = __fmaf_rn(pr, vv[e], acc[g][e]);
+      }
+    }
+    __syncthreads();
+  }
+
+  // Each warp accumulated a subset of the positions against the shared (m_run, l_run);
+  // add the warps' accumulators.
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < PER; ++e) s_acc[warp][g][lane * PER + e] = acc[g][e];
+  __syncthreads();
+  float *part = a.part + (((int64_t)b * a.n_heads + (int64_t)kvh * G) * a.n_splits) * (HD + 2);
+  for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
+    const int g = i / HD, d = i % HD;
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) s += s_acc[w][g][d];
+    part[((int64_t)g * a.n_splits + split) * (HD + 2) + d] = s;
+  }
+  if (threadIdx.x < G) {
+    part[((int64_t)threadIdx.x * a.n_splits + split) * (HD + 2) + HD] = m_run[threadIdx.x];
+    part[((int64_t)threadIdx.x * a.n_splits + split) * (HD + 2) + HD + 1] = l_run[threadIdx.x];
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&tickets[b * a.n_kv_heads + kvh], 1u) == (unsigned)a.n_splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // merge the ranges: out = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
+  float *out = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
+  for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
+    const int g = i / HD, d = i % HD;
+    const float *pg = part + (int64_t)g * a.n_splits * (HD + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(pg + (int64_t)s * (HD + 2) + HD));
+    float L = 0.0f, o = 0.0f;
+    for (int s = 0; s < a.n_splits; ++s) {
+      const float ms = __ldcg(pg + (int64_t)s * (HD + 2) + HD);
+      const float w = ms == -INFINITY ? 0.0f : expf(ms - M);
+      L = __fmaf_rn(__ldcg(pg + (int64_t)s * (HD + 2) + HD + 1), w, L);
+      o = __fmaf_rn(__ldcg(pg + (int64_t)s * (HD + 2) + d), w, o);
+    }
+    out[i] = __fdiv_rn(o, L);
+  }
+  if (threadIdx.x == 0) tickets[b * a.n_kv_heads + kvh] = 0;
+}
+
+template <int G>
+static int32_t launch_g(const AttnArgs &a, cudaStream_t s) {
+  dim3 grid((unsigned)a.n_kv_heads, (unsigned)a.n_splits, (unsigned)a.batch);
+  switch (a.head_dim) {
+    case 32: attn_decode_kernel<G, 1><<<grid, kAttnThreads, 0, s>>>(a); break;
+    case 64: attn_decode_kernel<G, 2><<<grid, kAttnThreads, 0, s>>>(a); break;
+    case 128: attn_decode_kernel<G, 4><<<grid, kAttnThreads, 0, s>>>(a); break;
+    default: return fail(CMLD_ERR_SHAPE, "attention: head_dim %d not in {32,64,128}", a.head_dim);
+  }
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+// `part` holds [batch][n_heads][n_splits][head_dim+2] floats; `tickets` batch*n_kv_heads
+// counters that are zero before the launch (the merging CTA zeroes them again).
+int32_t launch_attention(const AttnArgs &a, cudaStream_t s) {
+  if (a.n_heads % a.n_kv_heads != 0) return fail(CMLD_ERR_SHAPE, "attention: n_heads %% n_kv_heads != 0");
+  switch (a.n_heads / a.n_kv_heads) {
+    case 1: return launch_g<1>(a, s);
+    case 2: return launch_g<2>(a, s);
+    case 3: return launch_g<3>(a, s);
+    case 4: return launch_g<4>(a, s);
+    case 8: return launch_g<8>(a, s);
+    default: return fail(CMLD_ERR_SHAPE, "attention: %d query heads per kv head not supported", a.n_heads / a.n_kv_heads);
+  }
+}
+
+}  // namespace cmld

@@ -1,0 +1,210 @@
+// Shared internals of the sm_100a decode library: status plumbing, device layouts of the
+// quantised formats, and small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/camelid_b200.h"
+
+namespace cmld {
+
+// ------------------------------------------------------------------ errors
+
+void set_error(const char *fmt, ...);
+int32_t fail(int32_t code, const char *fmt, ...);
+
+#define CMLD_CUDA(expr)                                                                         \
+  do {                                                                                          \
+    cudaError_t err__ = (expr);                                                                 \
+    if (err__ != cudaSuccess)                                                                   \
+      return ::cmld::fail(err__ == cudaErrorMemoryAllocation ? CMLD_ERR_OOM : CMLD_ERR_CUDA,    \
+                          "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, \
+                          __LINE__);                                                            \
+  } while (0)
+
+#define CMLD_TRY(expr)               \
+  do {                               \
+    int32_t rc__ = (expr);           \
+    if (rc__ != CMLD_OK) return rc__; \
+  } while (0)
+
+// ------------------------------------------------------------------ device layouts
+//
+// A quantised matrix keeps exactly its GGUF wire bytes, permuted within each row so that
+// every field streams as 16-byte aligned vectors ("structure of arrays per row"):
+//   Q8_0: [codes: cols x i8][scales: cols/32 x f16]
+//   Q4_K: [nibbles: nsb x 128][meta: nsb x 16 = f16 d, f16 dmin, 12 scale bytes]
+//   Q6_K: [ql: nsb x 128][qh: nsb x 64][scales: nsb x 16 x i8][d: nsb x f16]
+// with the row stride rounded up to 16 bytes.
+
+constexpr int kWarp = 32;
+
+__host__ __device__ inline int64_t round_up16(int64_t v) { return (v + 15) & ~int64_t(15); }
+
+__host__ __device__ inline int64_t wire_row_bytes(int qt, int64_t cols) {
+  switch (qt) {
+    case CMLD_Q8_0: return cols / 32 * 34;
+    case CMLD_Q4_K: return cols / 256 * 144;
+    case CMLD_Q6_K: return cols / 256 * 210;
+    case CMLD_Q8_0_HOST36: return cols / 32 * 36;
+    case CMLD_F32: return cols * 4;
+    default: return -1;
+  }
+}
+
+__host__ __device__ inline int64_t dev_row_stride(int qt, int64_t cols) {
+  switch (qt) {
+    case CMLD_Q8_0: return round_up16(cols + cols / 32 * 2);
+    case CMLD_Q4_K: return cols / 256 * 144;
+    case CMLD_Q6_K: return round_up16(cols / 256 * 210);
+    case CMLD_F32: return cols * 4;
+    default: return -1;
+  }
+}
+
+// Quantised activation row: [codes: cols x i8][scales: cols/32 x f32][bsum16: cols/16 x i16],
+// stride rounded to 16 bytes.  Q8_K uses the first cols/256 scales; bsum16[j] is the sum of
+// codes 16j..16j+15 (what ggml's Q8_K block carries as bsums).
+__host__ __device__ inline int64_t act_scale_off(int64_t cols) { return round_up16(cols); }
+__host__ __device__ inline int64_t act_bsum_off(int64_t cols) { return round_up16(cols) + round_up16(cols / 32 * 4); }
+__host__ __device__ inline int64_t act_row_stride(int64_t cols) {
+  return act_bsum_off(cols) + round_up16(cols / 16 * 2);
+}
+
+struct Weight {
+  int32_t qt = 0;  // CMLD_Q8_0 / Q4_K / Q6_K / F32
+  int64_t rows = 0, cols = 0, stride = 0;
+  uint8_t *data = nullptr;  // device
+  bool owned = true;
+};
+
+}  // namespace cmld
+
+struct cmld_weight : cmld::Weight {};
+
+namespace cmld {
+
+// ------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ uint16_t f32_to_f16_bits(float f) { return __half_as_ushort(__float2half_rn(f)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Q4_K 6-bit (scale, min) of group g from the 12 packed bytes held as three words
+// (q4_k_scale_min, src/tensor/mod.rs:5997-6006 in the Camelid tree).
+__device__ __forceinline__ void q4k_scale_min(int g, uint32_t s0, uint32_t s1, uint32_t s2, int &sc, int &m) {
+  // bytes 0..3 = s0, 4..7 = s1, 8..11 = s2
+  if (g < 4) {
+    sc = (s0 >> (8 * g)) & 63;
+    m = (s1 >> (8 * g)) & 63;
+  } else {
+    int k = g - 4;
+    uint32_t b8 = (s2 >> (8 * k)) & 0xff;
+    sc = (b8 & 0x0f) | (((s0 >> (8 * k + 6)) & 3) << 4);
+    m = (b8 >> 4) | (((s1 >> (8 * k + 6)) & 3) << 4);
+  }
+}
+
+// 128-bit read-only streaming load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ld_stream16(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+#endif  // __CUDACC__
+
+// ------------------------------------------------------------------ kernel launchers (host)
+
+// formats.cu
+int32_t launch_repack(int qt_in, const uint8_t *wire_dev, int64_t rows, int64_t cols, uint8_t *dst, cudaStream_t s);
+int32_t launch_unpack_to_wire(const Weight &w, uint8_t *wire_dev, cudaStream_t s);
+int32_t launch_dequant(const Weight &w, int64_t row0, int64_t nrows, float *out, cudaStream_t s);
+int32_t launch_synth(const Weight &w, uint64_t seed, uint64_t stream_id, int64_t row0, float sigma, cudaStream_t s);
+int32_t launch_embed_gather(const Weight &w, const int32_t *tokens_dev, int32_t batch, float *out, cudaStream_t s);
+
+// gemv.cu
+struct GemvJob {
+  const uint8_t *w;
+  int32_t qt;
+  int64_t rows, cols, stride;
+  float *y;               // [batch][y_stride]
+  const float *residual;  // may be null, same layout as y
+  int64_t y_stride;
+};
+int32_t launch_gemv(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, cudaStream_t s);
+
+// ops.cu
+struct NormQuantArgs {
+  const float *x;       // [batch][cols]
+  const float *x2;      // second operand for SwiGLU (u), else null
+  const float *weight;  // RMSNorm weight or null (no norm)
+  float eps;
+  int64_t cols;
+  int32_t batch;
+  float *out;           // f32 result or null
+  uint8_t *act;         // quantised result or null
+  int32_t act_q8_0, act_q8_k;  // which formats to emit; both allowed: Q8_K at act, Q8_0 at act2
+  uint8_t *act2;
+};
+int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s);
+int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx,
+                      uint32_t *ticket, int32_t *out_idx, int32_t *next_tokens, int32_t *positions,
+                      int32_t *history, cudaStream_t s);
+int argmax_blocks();
+
+struct RopeKvArgs {
+  float *q;        // [batch][n_heads*hd], rotated in place
+  const float *k;  // [batch][n_kv*hd]
+  const float *v;
+  const float *cos_tab, *sin_tab;  // [rows][rope_dim/2]
+  int32_t index_by_position;       // 1: row = positions[b]; 0: row = b
+  const int32_t *positions;        // [batch]
+  const int32_t *slots;            // [batch] KV slot per row
+  __half *k_cache, *v_cache;       // this layer: [slot][kv_head][max_pos][hd]
+  int32_t n_heads, n_kv_heads, head_dim, rope_dim, split_half, batch;
+  int64_t max_pos;
+  int64_t q_stride, kv_stride;     // floats between batch rows of q and of k/v
+};
+int32_t launch_rope_kv(const RopeKvArgs &a, cudaStream_t s);
+
+// attn.cu
+struct AttnArgs {
+  const float *q;  // [batch][n_heads*hd]
+  const __half *k_cache, *v_cache;
+  const int32_t *positions, *slots;  // n_pos = positions[b] + 1
+  int32_t n_heads, n_kv_heads, head_dim, batch, n_splits;
+  int64_t max_pos;
+  float scale;
+  float *part;  // [batch][n_heads][n_splits][hd + 2]
+  uint32_t *tickets;  // [batch][n_kv_heads], zero between launches
+  float *out;   // [batch][n_heads*hd]
+  int64_t q_stride;
+};
+int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
+
+}  // namespace cmld

@@ -1,0 +1,1034 @@
+// The resident decode engine behind the C ABI: owns weights, KV cache and scratch on one
+// B200 and runs the per-token layer stack.  Host-side mirror of Camelid's
+// `CudaResidentDecode` (src/cuda_resident.rs:15093 in the Camelid tree): same call surface,
+// same argument meaning, errors as status codes instead of Result<_, String>.
+#include <cmath>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace cmld {
+
+// ------------------------------------------------------------------ errors
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int32_t fail(int32_t code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+const char *last_error() { return g_err; }
+
+// ------------------------------------------------------------------ weights
+
+int32_t weight_alloc(Weight &w, int32_t qt, int64_t rows, int64_t cols) {
+  const int qd = qt == CMLD_Q8_0_HOST36 ? CMLD_Q8_0 : qt;
+  if (qd != CMLD_Q8_0 && qd != CMLD_Q4_K && qd != CMLD_Q6_K && qd != CMLD_F32)
+    return fail(CMLD_ERR_UNSUPPORTED, "tensor type %d is not one of F32/Q8_0/Q4_K/Q6_K", qt);
+  if (rows <= 0 || cols <= 0) return fail(CMLD_ERR_SHAPE, "empty tensor %lld x %lld", (long long)rows, (long long)cols);
+  const int blk = qd == CMLD_F32 ? 1 : (qd == CMLD_Q8_0 ? 32 : 256);
+  if (cols % blk != 0)
+    return fail(CMLD_ERR_SHAPE, "row length %lld is not a multiple of the %d-value block of type %d", (long long)cols, blk, qd);
+  w.qt = qd;
+  w.rows = rows;
+  w.cols = cols;
+  w.stride = dev_row_stride(qd, cols);
+  w.owned = true;
+  CMLD_CUDA(cudaMalloc(&w.data, (size_t)(rows * w.stride)));
+  return CMLD_OK;
+}
+
+void weight_free(Weight &w) {
+  if (w.data && w.owned) cudaFree(w.data);
+  w.data = nullptr;
+}
+
+// Upload GGUF wire bytes (host or device memory) and re-lay them out.
+int32_t weight_upload(Weight &w, int32_t qt, int64_t rows, int64_t cols, const void *wire, uint64_t nbytes, cudaStream_t s) {
+  if (!wire) return fail(CMLD_ERR_INVALID, "tensor data is null");
+  const int64_t need = wire_row_bytes(qt, cols) * rows;
+  if (need < 0) return fail(CMLD_ERR_UNSUPPORTED, "tensor type %d is not one of F32/Q8_0/Q4_K/Q6_K", qt);
+  if ((int64_t)nbytes != need)
+    return fail(CMLD_ERR_SHAPE, "tensor of type %d and shape %lld x %lld needs %lld bytes, got %llu", qt, (long long)rows,
+                (long long)cols, (long long)need, (unsigned long long)nbytes);
+  weight_free(w);
+  CMLD_TRY(weight_alloc(w, qt, rows, cols));
+  if (w.qt == CMLD_F32) {
+    CMLD_CUDA(cudaMemcpyAsync(w.data, wire, (size_t)need, cudaMemcpyDefault, s));
+    CMLD_CUDA(cudaStreamSynchronize(s));
+    return CMLD_OK;
+  }
+  // Stage in slabs so a 128256 x 4096 table does not need a second full-size buffer.
+  const int64_t wrb = wire_row_bytes(qt, cols);
+  const int64_t slab_rows = std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)(256ll << 20) / wrb));
+  uint8_t *stage = nullptr;
+  CMLD_CUDA(cudaMalloc(&stage, (size_t)(slab_rows * wrb)));
+  int32_t rc = CMLD_OK;
+  for (int64_t r0 = 0; r0 < rows && rc == CMLD_OK; r0 += slab_rows) {
+    const int64_t nr = std::min(slab_rows, rows - r0);
+    cudaError_t ce = cudaMemcpyAsync(stage, static_cast<const uint8_t *>(wire) + r0 * wrb, (size_t)(nr * wrb), cudaMemcpyDefault, s);
+    if (ce != cudaSuccess) {
+      rc = fail(CMLD_ERR_CUDA, "weight upload copy failed: %s", cudaGetErrorString(ce));
+      break;
+    }
+    rc = launch_repack(qt, stage, nr, cols, w.data + r0 * w.stride, s);
+    if (rc == CMLD_OK && cudaStreamSynchronize(s) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "weight re-layout failed");
+  }
+  cudaFree(stage);
+  return rc;
+}
+
+// ------------------------------------------------------------------ engine
+
+struct LayerW {
+  Weight proj[7];  // q k v o gate up down
+  float *attn_norm = nullptr, *ffn_norm = nullptr;
+  bool dense_set = false;
+  // Mixtral
+  float *router = nullptr;
+  Weight exps[3];  // gate, up, down slabs: rows = n_experts * rows_per_expert
+  bool moe_set = false;
+};
+
+}  // namespace cmld
+
+using namespace cmld;
+
+struct cmld_engine {
+  cmld_config cfg{};
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int32_t max_rows = 0;  // scratch rows (sequences per step)
+  int32_t n_splits = 1;
+  int32_t q_width = 0, kv_width = 0;
+  std::vector<LayerW> layers;
+  Weight output, token_embd;
+  float *final_norm = nullptr;
+  bool has_output = false, has_embd = false;
+  __half *kcache = nullptr, *vcache = nullptr;
+  int64_t kv_layer_elems = 0;  // halfs per layer per side
+  float *cos_all = nullptr, *sin_all = nullptr, *cos_step = nullptr, *sin_step = nullptr;
+  float *h = nullptr, *normed = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *gate = nullptr,
+        *up = nullptr, *logits = nullptr, *taps = nullptr;
+  uint8_t *act_k = nullptr, *act_0 = nullptr;  // Q8_K and Q8_0 operand buffers (widest row)
+  float *attn_part = nullptr;
+  uint32_t *attn_tickets = nullptr;
+  float *am_val = nullptr;
+  int32_t *am_idx = nullptr;
+  uint32_t *am_ticket = nullptr;  // [2*max_rows]: tickets, then history lengths
+  int32_t *out_idx = nullptr, *d_tokens = nullptr, *d_positions = nullptr, *d_slots = nullptr, *d_history = nullptr;
+  int64_t history_cap = 0;
+  int32_t *moe_sel_idx = nullptr, *moe_counts = nullptr, *moe_lists = nullptr;
+  float *moe_sel_w = nullptr, *moe_g = nullptr, *moe_u = nullptr, *moe_act = nullptr, *moe_down = nullptr;
+  int64_t filled = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float last_ms = 0.0f;
+  int64_t last_launches = 0, launches = 0;
+  std::vector<void *> allocs;
+};
+
+namespace cmld {
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) ok = false;
+    if (ok && prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+#define CMLD_ENGINE_ENTER(e)                                              \
+  if (!(e)) return fail(CMLD_ERR_INVALID, "engine handle is null");       \
+  DeviceGuard guard__((e)->device);                                       \
+  if (!guard__.ok) return fail(CMLD_ERR_CUDA, "cannot select CUDA device %d", (e)->device)
+
+template <typename T>
+static int32_t dev_alloc(cmld_engine *e, T **p, int64_t count, bool zero = true) {
+  void *raw = nullptr;
+  const size_t bytes = (size_t)std::max<int64_t>(count, 1) * sizeof(T);
+  CMLD_CUDA(cudaMalloc(&raw, bytes));
+  e->allocs.push_back(raw);
+  if (zero) CMLD_CUDA(cudaMemsetAsync(raw, 0, bytes, e->stream));
+  *p = static_cast<T *>(raw);
+  return CMLD_OK;
+}
+
+static int32_t validate_config(const cmld_config &c) {
+  if (c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.hidden <= 0 || c.ffn_dim <= 0 ||
+      c.max_pos <= 0 || c.vocab <= 0)
+    return fail(CMLD_ERR_SHAPE, "engine dimensions must be positive");
+  // resident_decode_eligible (src/inference.rs:3503-3529 in the Camelid tree)
+  if (c.hidden % 32 || c.ffn_dim % 32 || (c.n_heads * c.head_dim) % 32)
+    return fail(CMLD_ERR_SHAPE, "hidden, ffn_dim and n_heads*head_dim must be multiples of 32");
+  if (c.n_heads % c.n_kv_heads) return fail(CMLD_ERR_SHAPE, "n_heads must be a multiple of n_kv_heads");
+  if (c.head_dim != 32 && c.head_dim != 64 && c.head_dim != 128)
+    return fail(CMLD_ERR_SHAPE, "head_dim %d not in {32,64,128}", c.head_dim);
+  const int g = c.n_heads / c.n_kv_heads;
+  if (!(g == 1 || g == 2 || g == 3 || g == 4 || g == 8))
+    return fail(CMLD_ERR_SHAPE, "%d query heads per kv head not supported", g);
+  if (c.rope_dim <= 0 || c.rope_dim > c.head_dim || c.rope_dim % 2)
+    return fail(CMLD_ERR_SHAPE, "rope_dim %d must be even and within head_dim", c.rope_dim);
+  if (c.n_experts < 0 || (c.n_experts > 0 && (c.n_experts_used <= 0 || c.n_experts_used > c.n_experts)))
+    return fail(CMLD_ERR_SHAPE, "bad expert counts %d/%d", c.n_experts_used, c.n_experts);
+  if (c.max_pos > (1 << 24)) return fail(CMLD_ERR_SHAPE, "max_pos too large");
+  return CMLD_OK;
+}
+
+static int32_t engine_init(cmld_engine *e) {
+  const cmld_config &c = e->cfg;
+  CMLD_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+  CMLD_CUDA(cudaEventCreate(&e->ev0));
+  CMLD_CUDA(cudaEventCreate(&e->ev1));
+  const int seqs = std::max(1, c.max_seqs);
+  e->max_rows = std::max(seqs, 16);
+  e->q_width = c.n_heads * c.head_dim;
+  e->kv_width = c.n_kv_heads * c.head_dim;
+  e->layers.resize(c.n_layers);
+  // KV cache: [layer][slot][kv_head][max_pos][head_dim] f16, K and V
+  e->kv_layer_elems = (int64_t)seqs * c.n_kv_heads * c.max_pos * c.head_dim;
+  CMLD_TRY(dev_alloc(e, &e->kcache, e->kv_layer_elems * c.n_layers));
+  CMLD_TRY(dev_alloc(e, &e->vcache, e->kv_layer_elems * c.n_layers));
+  // RoPE tables for every position, computed with the host libm exactly as the reference's
+  // resident_decode_rope_tables does per token (src/inference/rope.rs:600-655).
+  const int half = c.rope_dim / 2;
+  {
+    std::vector<float> ct((size_t)c.max_pos * half), st((size_t)c.max_pos * half);
+    const float base = c.rope_theta > 0.0f ? c.rope_theta : 10000.0f;
+    std::vector<float> theta(half);
+    for (int i = 0; i < half; ++i) theta[i] = powf(base, -((float)i * 2.0f) / (float)c.rope_dim);
+    for (int64_t p = 0; p < c.max_pos; ++p)
+      for (int i = 0; i < half; ++i) {
+        const float ang = (float)p * theta[i];
+        st[(size_t)p * half + i] = sinf(ang);
+        ct[(size_t)p * half + i] = cosf(ang);
+      }
+    CMLD_TRY(dev_alloc(e, &e->cos_all, (int64_t)c.max_pos * half, false));
+    CMLD_TRY(dev_alloc(e, &e->sin_all, (int64_t)c.max_pos * half, false));
+    CMLD_CUDA(cudaMemcpyAsync(e->cos_all, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice, e->stream));
+    CMLD_CUDA(cudaMemcpyAsync(e->sin_all, st.data(), st.size() * 4, cudaMemcpyHostToDevice, e->stream));
+    CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  }
+  const int64_t R = e->max_rows;
+  CMLD_TRY(dev_alloc(e, &e->cos_step, R * half));
+  CMLD_TRY(dev_alloc(e, &e->sin_step, R * half));
+  CMLD_TRY(dev_alloc(e, &e->h, R * c.hidden));
+  CMLD_TRY(dev_alloc(e, &e->normed, R * c.hidden));
+  CMLD_TRY(dev_alloc(e, &e->q, R * e->q_width));
+  CMLD_TRY(dev_alloc(e, &e->k, R * e->kv_width));
+  CMLD_TRY(dev_alloc(e, &e->v, R * e->kv_width));
+  CMLD_TRY(dev_alloc(e, &e->attn, R * e->q_width));
+  CMLD_TRY(dev_alloc(e, &e->gate, R * c.ffn_dim));
+  CMLD_TRY(dev_alloc(e, &e->up, R * c.ffn_dim));
+  CMLD_TRY(dev_alloc(e, &e->logits, R * c.vocab));
+  CMLD_TRY(dev_alloc(e, &e->taps, (int64_t)c.n_layers * R * c.hidden));
+  const int64_t widest = std::max<int64_t>(std::max(c.hidden, c.ffn_dim), e->q_width);
+  CMLD_TRY(dev_alloc(e, &e->act_k, R * act_row_stride(widest)));
+  CMLD_TRY(dev_alloc(e, &e->act_0, R * act_row_stride(widest)));
+  // flash-decoding splits: enough CTAs to cover the SMs twice at batch 1
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
+  e->n_splits = std::max(1, std::min<int>(64, (2 * sms + c.n_kv_heads - 1) / c.n_kv_heads));
+  e->n_splits = (int)std::min<int64_t>(e->n_splits, std::max<int64_t>(1, c.max_pos / 32));
+  CMLD_TRY(dev_alloc(e, &e->attn_part, R * c.n_heads * e->n_splits * (c.head_dim + 2)));
+  CMLD_TRY(dev_alloc(e, &e->attn_tickets, R * c.n_kv_heads));
+  CMLD_TRY(dev_alloc(e, &e->am_val, R * argmax_blocks()));
+  CMLD_TRY(dev_alloc(e, &e->am_idx, R * argmax_blocks()));
+  CMLD_TRY(dev_alloc(e, &e->am_ticket, 2 * R));
+  CMLD_TRY(dev_alloc(e, &e->out_idx, R));
+  CMLD_TRY(dev_alloc(e, &e->d_tokens, R));
+  CMLD_TRY(dev_alloc(e, &e->d_positions, R));
+  CMLD_TRY(dev_alloc(e, &e->d_slots, R));
+  if (c.n_experts > 0) {
+    const int64_t na = R * c.n_experts_used;
+    CMLD_TRY(dev_alloc(e, &e->moe_sel_idx, na));
+    CMLD_TRY(dev_alloc(e, &e->moe_sel_w, na));
+    CMLD_TRY(dev_alloc(e, &e->moe_counts, c.n_experts));
+    CMLD_TRY(dev_alloc(e, &e->moe_lists, (int64_t)c.n_experts * na));
+    CMLD_TRY(dev_alloc(e, &e->moe_g, na * c.ffn_dim));
+    CMLD_TRY(dev_alloc(e, &e->moe_u, na * c.ffn_dim));
+    CMLD_TRY(dev_alloc(e, &e->moe_act, na * c.ffn_dim));
+    CMLD_TRY(dev_alloc(e, &e->moe_down, na * c.hidden));
+  }
+  e->history_cap = 4096;
+  CMLD_TRY(dev_alloc(e, &e->d_history, e->history_cap * R));
+  CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  return CMLD_OK;
+}
+
+static void engine_free(cmld_engine *e) {
+  for (auto &L : e->layers) {
+    for (auto &w : L.proj) weight_free(w);
+    for (auto &w : L.exps) weight_free(w);
+    cudaFree(L.attn_norm);
+    cudaFree(L.ffn_norm);
+    cudaFree(L.router);
+  }
+  weight_free(e->output);
+  weight_free(e->token_embd);
+  cudaFree(e->final_norm);
+  for (void *p : e->allocs) cudaFree(p);
+  if (e->ev0) cudaEventDestroy(e->ev0);
+  if (e->ev1) cudaEventDestroy(e->ev1);
+  if (e->stream) cudaStreamDestroy(e->stream);
+}
+
+static int32_t upload_f32(float **dst, const float *src, int64_t n, cudaStream_t s) {
+  if (!src) return fail(CMLD_ERR_INVALID, "norm weights are null");
+  if (!*dst) CMLD_CUDA(cudaMalloc(dst, (size_t)n * 4));
+  CMLD_CUDA(cudaMemcpyAsync(*dst, src, (size_t)n * 4, cudaMemcpyDefault, s));
+  CMLD_CUDA(cudaStreamSynchronize(s));
+  return CMLD_OK;
+}
+
+// Which operand formats a group of matrices reading the same activation needs.
+static void act_kinds(const Weight *const *ws, int n, bool &need_0, bool &need_k) {
+  need_0 = need_k = false;
+  for (int i = 0; i < n; ++i) {
+    if (ws[i]->qt == CMLD_Q8_0) need_0 = true;
+    else need_k = true;
+  }
+}
+
+struct Proj {
+  const Weight *w;
+  float *y;
+  const float *residual;
+  int64_t y_stride;
+};
+
+// Matvecs that share one activation row: one launch per operand format.
+static int32_t run_gemv_group(cmld_engine *e, const Proj *p, int n, int32_t batch) {
+  for (int pass = 0; pass < 2; ++pass) {
+    GemvJob jobs[4];
+    int nj = 0;
+    for (int i = 0; i < n; ++i) {
+      const bool is0 = p[i].w->qt == CMLD_Q8_0;
+      if (is0 != (pass == 0)) continue;
+      jobs[nj++] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
+    }
+    if (nj == 0) continue;
+    CMLD_TRY(launch_gemv(jobs, nj, pass == 0 ? e->act_0 : e->act_k, batch, e->stream));
+    e->launches += (batch + 7) / 8;
+  }
+  return CMLD_OK;
+}
+
+static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, const float *weight, int64_t cols,
+                              int32_t batch, float *out, bool need_0, bool need_k) {
+  NormQuantArgs a{};
+  a.x = x;
+  a.x2 = x2;
+  a.weight = weight;
+  a.eps = e->cfg.eps;
+  a.cols = cols;
+  a.batch = batch;
+  a.out = out;
+  a.act_q8_0 = need_0;
+  a.act_q8_k = need_k;
+  a.act = need_k ? e->act_k : e->act_0;
+  a.act2 = e->act_0;
+  CMLD_TRY(launch_norm_quant(a, e->stream));
+  e->launches += 1;
+  return CMLD_OK;
+}
+
+struct StepOpts {
+  int32_t batch = 1;
+  bool from_tokens = false;    // gather embeddings of d_tokens, else h holds them
+  bool rope_by_position = true;  // index the engine's all-position table, else cos_step/sin_step rows
+  float scale = 0.0f;
+  bool logits = true;
+  bool argmax = true;
+  bool feed_back = false;  // argmax writes next token / position / history
+  bool taps = false;
+};
+
+// moe.cu
+int32_t moe_route(const float *normed, const float *router, int hidden, int n_exp, int k, int batch, int32_t *sel_idx,
+                  float *sel_w, int32_t *counts, int32_t *lists, cudaStream_t s);
+int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
+                        const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
+                        int n_assign, cudaStream_t s);
+int32_t moe_combine(float *h, const float *down, const float *sel_w, const int32_t *sel_idx, int hidden, int k, int batch,
+                    int first_expert, int expert_step, bool add_residual, cudaStream_t s);
+
+static int ep_size(const cmld_engine *e) { return std::max(1, e->cfg.ep_size); }
+
+// Mixtral FFN on e->normed (f32): route, expert gate/up, SwiGLU, expert down, weighted sum.
+static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
+  const cmld_config &c = e->cfg;
+  const int k = c.n_experts_used, na = B * k;
+  const int n_local = c.n_experts / ep_size(e), first = ep_size(e) > 1 ? c.ep_rank : 0, step = ep_size(e);
+  CMLD_TRY(moe_route(e->normed, L.router, c.hidden, c.n_experts, k, B, e->moe_sel_idx, e->moe_sel_w, e->moe_counts,
+                     e->moe_lists, e->stream));
+  CMLD_TRY(moe_expert_gemv(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts,
+                           e->moe_lists, na, e->stream));
+  CMLD_TRY(moe_expert_gemv(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts,
+                           e->moe_lists, na, e->stream));
+  NormQuantArgs a{};
+  a.x = e->moe_g;
+  a.x2 = e->moe_u;
+  a.cols = c.ffn_dim;
+  a.batch = na;
+  a.out = e->moe_act;
+  CMLD_TRY(launch_norm_quant(a, e->stream));
+  CMLD_TRY(moe_expert_gemv(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts,
+                           e->moe_lists, na, e->stream));
+  CMLD_TRY(moe_combine(e->h, e->moe_down, e->moe_sel_w, e->moe_sel_idx, c.hidden, k, B, first, step, true, e->stream));
+  e->launches += 7;
+  return CMLD_OK;
+}
+
+static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
+  const cmld_config &c = e->cfg;
+  const int32_t B = o.batch;
+  if (B < 1 || B > e->max_rows) return fail(CMLD_ERR_INVALID, "step of %d rows exceeds the engine's %d", B, e->max_rows);
+  if (o.from_tokens) {
+    if (!e->has_embd) return fail(CMLD_ERR_STATE, "token embedding table not set");
+    CMLD_TRY(launch_embed_gather(e->token_embd, e->d_tokens, B, e->h, e->stream));
+    e->launches += 1;
+  }
+  for (int32_t li = 0; li < c.n_layers; ++li) {
+    LayerW &L = e->layers[li];
+    bool n0, nk;
+    {
+      const Weight *g[3] = {&L.proj[0], &L.proj[1], &L.proj[2]};
+      act_kinds(g, 3, n0, nk);
+      CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.attn_norm, c.hidden, B, nullptr, n0, nk));
+      const Proj p[3] = {{&L.proj[0], e->q, nullptr, e->q_width},
+                         {&L.proj[1], e->k, nullptr, e->kv_width},
+                         {&L.proj[2], e->v, nullptr, e->kv_width}};
+      CMLD_TRY(run_gemv_group(e, p, 3, B));
+    }
+    {
+      RopeKvArgs r{};
+      r.q = e->q;
+      r.k = e->k;
+      r.v = e->v;
+      r.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
+      r.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
+      r.index_by_position = o.rope_by_position;
+      r.positions = e->d_positions;
+      r.slots = e->d_slots;
+      r.k_cache = e->kcache + (int64_t)li * e->kv_layer_elems;
+      r.v_cache = e->vcache + (int64_t)li * e->kv_layer_elems;
+      r.n_heads = c.n_heads;
+      r.n_kv_heads = c.n_kv_heads;
+      r.head_dim = c.head_dim;
+      r.rope_dim = c.rope_dim;
+      r.split_half = c.split_half_pairing;
+      r.batch = B;
+      r.max_pos = c.max_pos;
+      r.q_stride = e->q_width;
+      r.kv_stride = e->kv_width;
+      CMLD_TRY(launch_rope_kv(r, e->stream));
+      AttnArgs a{};
+      a.q = e->q;
+      a.k_cache = r.k_cache;
+      a.v_cache = r.v_cache;
+      a.positions = e->d_positions;
+      a.slots = e->d_slots;
+      a.n_heads = c.n_heads;
+      a.n_kv_heads = c.n_kv_heads;
+      a.head_dim = c.head_dim;
+      a.batch = B;
+      a.n_splits = e->n_splits;
+      a.max_pos = c.max_pos;
+      a.scale = o.scale;
+      a.part = e->attn_part;
+      a.tickets = e->attn_tickets;
+      a.out = e->attn;
+      a.q_stride = e->q_width;
+      CMLD_TRY(launch_attention(a, e->stream));
+      e->launches += 2;
+    }
+    {
+      const Weight *g[1] = {&L.proj[3]};
+      act_kinds(g, 1, n0, nk);
+      CMLD_TRY(run_norm_quant(e, e->attn, nullptr, nullptr, e->q_width, B, nullptr, n0, nk));
+      const Proj p[1] = {{&L.proj[3], e->h, e->h, c.hidden}};
+      CMLD_TRY(run_gemv_group(e, p, 1, B));
+    }
+    if (L.moe_set) {
+      CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.ffn_norm, c.hidden, B, e->normed, false, false));
+      CMLD_TRY(moe_ffn_step(e, L, B));
+    } else {
+      const Weight *g[2] = {&L.proj[4], &L.proj[5]};
+      act_kinds(g, 2, n0, nk);
+      CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.ffn_norm, c.hidden, B, nullptr, n0, nk));
+      const Proj p[2] = {{&L.proj[4], e->gate, nullptr, c.ffn_dim}, {&L.proj[5], e->up, nullptr, c.ffn_dim}};
+      CMLD_TRY(run_gemv_group(e, p, 2, B));
+      const Weight *gd[1] = {&L.proj[6]};
+      act_kinds(gd, 1, n0, nk);
+      CMLD_TRY(run_norm_quant(e, e->gate, e->up, nullptr, c.ffn_dim, B, nullptr, n0, nk));
+      const Proj pd[1] = {{&L.proj[6], e->h, e->h, c.hidden}};
+      CMLD_TRY(run_gemv_group(e, pd, 1, B));
+    }
+    if (o.taps) {
+      CMLD_CUDA(cudaMemcpyAsync(e->taps + (int64_t)li * e->max_rows * c.hidden, e->h, (size_t)B * c.hidden * 4,
+                                cudaMemcpyDeviceToDevice, e->stream));
+    }
+  }
+  if (o.logits) {
+    if (!e->has_output) return fail(CMLD_ERR_STATE, "output weights not set");
+    bool n0, nk;
+    const Weight *g[1] = {&e->output};
+    act_kinds(g, 1, n0, nk);
+    CMLD_TRY(run_norm_quant(e, e->h, nullptr, e->final_norm, c.hidden, B, nullptr, n0, nk));
+    const Proj p[1] = {{&e->output, e->logits, nullptr, c.vocab}};
+    CMLD_TRY(run_gemv_group(e, p, 1, B));
+    if (o.argmax) {
+      CMLD_TRY(launch_argmax(e->logits, c.vocab, B, e->am_val, e->am_idx, e->am_ticket, e->out_idx,
+                             o.feed_back ? e->d_tokens : nullptr, e->d_positions, e->d_history, e->stream));
+      e->launches += 1;
+    }
+  }
+  return CMLD_OK;
+}
+
+static int32_t require_weights(const cmld_engine *e, bool need_output) {
+  for (size_t i = 0; i < e->layers.size(); ++i) {
+    const LayerW &L = e->layers[i];
+    if (!L.dense_set) return fail(CMLD_ERR_STATE, "layer %zu has no weights", i);
+    if (e->cfg.n_experts > 0 && !L.moe_set) return fail(CMLD_ERR_STATE, "layer %zu has no expert weights", i);
+  }
+  if (need_output && !e->has_output) return fail(CMLD_ERR_STATE, "output weights not set");
+  return CMLD_OK;
+}
+
+// Rows of one step: tokens (or none), positions and KV slots to the device.
+static int32_t stage_rows(cmld_engine *e, int32_t n, const int32_t *tokens, const int32_t *positions, const int32_t *slots) {
+  if (tokens) CMLD_CUDA(cudaMemcpyAsync(e->d_tokens, tokens, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->d_positions, positions, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->d_slots, slots, (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+  return CMLD_OK;
+}
+
+static int32_t finish(cmld_engine *e, const char *what) {
+  cudaError_t ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
+  return CMLD_OK;
+}
+
+// One sequence-0 row fed by an embedding vector: the forward_token family.
+static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, const float *cosv, const float *sinv,
+                                      int64_t position0, int32_t n_rows, float scale, bool logits, bool argmax, bool taps) {
+  const cmld_config &c = e->cfg;
+  if (!embeddings || !cosv || !sinv) return fail(CMLD_ERR_INVALID, "embedding / cos / sin pointer is null");
+  if (position0 < 0 || position0 + n_rows > c.max_pos)
+    return fail(CMLD_ERR_STATE, "positions %lld..%lld exceed max_pos %d", (long long)position0,
+                (long long)(position0 + n_rows - 1), c.max_pos);
+  CMLD_TRY(require_weights(e, logits));
+  const int half = c.rope_dim / 2;
+  CMLD_CUDA(cudaMemcpyAsync(e->h, embeddings, (size_t)n_rows * c.hidden * 4, cudaMemcpyDefault, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->cos_step, cosv, (size_t)n_rows * half * 4, cudaMemcpyDefault, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->sin_step, sinv, (size_t)n_rows * half * 4, cudaMemcpyDefault, e->stream));
+  std::vector<int32_t> pos(n_rows), slots(n_rows, 0);
+  for (int i = 0; i < n_rows; ++i) pos[i] = (int32_t)(position0 + i);
+  CMLD_TRY(stage_rows(e, n_rows, nullptr, pos.data(), slots.data()));
+  StepOpts o;
+  o.batch = n_rows;
+  o.from_tokens = false;
+  o.rope_by_position = false;
+  o.scale = scale;
+  o.logits = logits;
+  o.argmax = argmax;
+  o.taps = taps;
+  return engine_step(e, o);
+}
+
+}  // namespace cmld
+
+// ====================================================================== C ABI
+
+extern "C" {
+
+const char *cmld_last_error(void) { return cmld::last_error(); }
+const char *cmld_version(void) { return "camelid_b200 0.1 (sm_100a)"; }
+
+int32_t cmld_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int32_t cmld_malloc(void **dev_ptr, uint64_t nbytes) {
+  if (!dev_ptr) return fail(CMLD_ERR_INVALID, "null out pointer");
+  CMLD_CUDA(cudaMalloc(dev_ptr, (size_t)std::max<uint64_t>(nbytes, 1)));
+  return CMLD_OK;
+}
+int32_t cmld_free(void *dev_ptr) {
+  if (dev_ptr) CMLD_CUDA(cudaFree(dev_ptr));
+  return CMLD_OK;
+}
+int32_t cmld_memcpy_h2d(void *dst_dev, const void *src_host, uint64_t nbytes) {
+  CMLD_CUDA(cudaMemcpy(dst_dev, src_host, (size_t)nbytes, cudaMemcpyHostToDevice));
+  return CMLD_OK;
+}
+int32_t cmld_memcpy_d2h(void *dst_host, const void *src_dev, uint64_t nbytes) {
+  CMLD_CUDA(cudaMemcpy(dst_host, src_dev, (size_t)nbytes, cudaMemcpyDeviceToHost));
+  return CMLD_OK;
+}
+int32_t cmld_memset(void *dst_dev, int32_t value, uint64_t nbytes) {
+  CMLD_CUDA(cudaMemset(dst_dev, value, (size_t)nbytes));
+  return CMLD_OK;
+}
+int32_t cmld_device_synchronize(void) {
+  CMLD_CUDA(cudaDeviceSynchronize());
+  return CMLD_OK;
+}
+int32_t cmld_mem_info(uint64_t *free_bytes, uint64_t *total_bytes) {
+  size_t f = 0, t = 0;
+  CMLD_CUDA(cudaMemGetInfo(&f, &t));
+  if (free_bytes) *free_bytes = f;
+  if (total_bytes) *total_bytes = t;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_create(const cmld_config *cfg, cmld_engine **out) {
+  if (!cfg || !out) return fail(CMLD_ERR_INVALID, "config or out pointer is null");
+  *out = nullptr;
+  CMLD_TRY(validate_config(*cfg));
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
+    cudaGetLastError();
+    return fail(CMLD_ERR_CUDA, "no CUDA device: this engine has no CPU path");
+  }
+  int dev = cfg->device;
+  if (dev < 0) CMLD_CUDA(cudaGetDevice(&dev));
+  if (dev >= ndev) return fail(CMLD_ERR_INVALID, "device %d out of range (%d present)", dev, ndev);
+  cudaDeviceProp prop{};
+  CMLD_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10) return fail(CMLD_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev, prop.major, prop.minor);
+  // capacity check (the reference sizes VRAM in build_resident_cuda_engine, src/inference.rs:16455-16720)
+  const int seqs = std::max(1, cfg->max_seqs);
+  const double kv_bytes = 2.0 * 2.0 * cfg->n_layers * seqs * (double)cfg->n_kv_heads * cfg->max_pos * cfg->head_dim;
+  DeviceGuard guard(dev);
+  if (!guard.ok) return fail(CMLD_ERR_CUDA, "cannot select CUDA device %d", dev);
+  size_t free_b = 0, total_b = 0;
+  CMLD_CUDA(cudaMemGetInfo(&free_b, &total_b));
+  if (kv_bytes > 0.95 * (double)free_b)
+    return fail(CMLD_ERR_OOM, "KV cache of %.1f GiB does not fit in %.1f GiB free", kv_bytes / (1 << 30), (double)free_b / (1 << 30));
+  cmld_engine *e = new cmld_engine();
+  e->cfg = *cfg;
+  e->device = dev;
+  int32_t rc = engine_init(e);
+  if (rc != CMLD_OK) {
+    engine_free(e);
+    delete e;
+    return rc;
+  }
+  *out = e;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_destroy(cmld_engine *e) {
+  if (!e) return CMLD_OK;
+  DeviceGuard guard(e->device);
+  cudaStreamSynchronize(e->stream);
+  engine_free(e);
+  delete e;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_set_layer(cmld_engine *e, int32_t layer, const cmld_tensor projs[7], const float *attn_norm,
+                              const float *ffn_norm) {
+  CMLD_ENGINE_ENTER(e);
+  const cmld_config &c = e->cfg;
+  if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "set_layer: layer %d out of range", layer);
+  if (!projs) return fail(CMLD_ERR_INVALID, "set_layer: projections are null");
+  LayerW &L = e->layers[layer];
+  const int64_t shapes[7][2] = {{e->q_width, c.hidden},  {e->kv_width, c.hidden}, {e->kv_width, c.hidden}, {c.hidden, e->q_width},
+                                {c.ffn_dim, c.hidden},   {c.ffn_dim, c.hidden},   {c.hidden, c.ffn_dim}};
+  static const char *names[7] = {"q", "k", "v", "o", "gate", "up", "down"};
+  for (int i = 0; i < 7; ++i) {
+    if (i >= 4 && c.n_experts > 0 && !projs[i].data) continue;  // MoE layer: dense FFN absent
+    int32_t rc = weight_upload(L.proj[i], projs[i].qtype, shapes[i][0], shapes[i][1], projs[i].data, projs[i].nbytes, e->stream);
+    if (rc != CMLD_OK) {
+      std::string msg = cmld_last_error();
+      return fail(rc, "set_layer(%d).%s: %s", layer, names[i], msg.c_str());
+    }
+    if (L.proj[i].qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "set_layer(%d).%s: f32 projections are not supported", layer, names[i]);
+  }
+  CMLD_TRY(upload_f32(&L.attn_norm, attn_norm, c.hidden, e->stream));
+  CMLD_TRY(upload_f32(&L.ffn_norm, ffn_norm, c.hidden, e->stream));
+  L.dense_set = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_set_layer_moe(cmld_engine *e, int32_t layer, const float *router, const cmld_tensor *gate_exps,
+                                  const cmld_tensor *up_exps, const cmld_tensor *down_exps) {
+  CMLD_ENGINE_ENTER(e);
+  const cmld_config &c = e->cfg;
+  if (c.n_experts <= 0) return fail(CMLD_ERR_STATE, "set_layer_moe: engine was created without experts");
+  if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "set_layer_moe: layer %d out of range", layer);
+  if (!router || !gate_exps || !up_exps || !down_exps) return fail(CMLD_ERR_INVALID, "set_layer_moe: null tensor");
+  if (c.n_experts % ep_size(e)) return fail(CMLD_ERR_SHAPE, "n_experts %d not divisible by ep_size %d", c.n_experts, ep_size(e));
+  if (c.hidden % 256 || c.ffn_dim % 256) return fail(CMLD_ERR_SHAPE, "expert matrices need hidden and ffn_dim to be multiples of 256");
+  LayerW &L = e->layers[layer];
+  const int64_t n_local = c.n_experts / ep_size(e);
+  const cmld_tensor *ts[3] = {gate_exps, up_exps, down_exps};
+  const int64_t shapes[3][2] = {{n_local * c.ffn_dim, c.hidden}, {n_local * c.ffn_dim, c.hidden}, {n_local * c.hidden, c.ffn_dim}};
+  for (int i = 0; i < 3; ++i) {
+    if (ts[i]->qtype != CMLD_Q4_K && ts[i]->qtype != CMLD_Q6_K)
+      return fail(CMLD_ERR_UNSUPPORTED, "set_layer_moe: expert tensors must be Q4_K or Q6_K (got type %d)", ts[i]->qtype);
+    CMLD_TRY(weight_upload(L.exps[i], ts[i]->qtype, shapes[i][0], shapes[i][1], ts[i]->data, ts[i]->nbytes, e->stream));
+  }
+  CMLD_TRY(upload_f32(&L.router, router, (int64_t)c.n_experts * c.hidden, e->stream));
+  L.moe_set = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_set_output(cmld_engine *e, const float *final_norm, const cmld_tensor *output) {
+  CMLD_ENGINE_ENTER(e);
+  if (!output) return fail(CMLD_ERR_INVALID, "set_output: tensor is null");
+  CMLD_TRY(weight_upload(e->output, output->qtype, e->cfg.vocab, e->cfg.hidden, output->data, output->nbytes, e->stream));
+  if (e->output.qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "set_output: f32 output weights are not supported");
+  CMLD_TRY(upload_f32(&e->final_norm, final_norm, e->cfg.hidden, e->stream));
+  e->has_output = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_set_token_embd(cmld_engine *e, const cmld_tensor *t) {
+  CMLD_ENGINE_ENTER(e);
+  if (!t) return fail(CMLD_ERR_INVALID, "set_token_embd: tensor is null");
+  CMLD_TRY(weight_upload(e->token_embd, t->qtype, e->cfg.vocab, e->cfg.hidden, t->data, t->nbytes, e->stream));
+  e->has_embd = true;
+  return CMLD_OK;
+}
+
+static int32_t adopt(Weight &dst, cmld_weight *src, int64_t rows, int64_t cols, const char *what, bool allow_f32 = false) {
+  if (src->rows != rows || src->cols != cols)
+    return fail(CMLD_ERR_SHAPE, "%s: weight is %lld x %lld, expected %lld x %lld", what, (long long)src->rows, (long long)src->cols,
+                (long long)rows, (long long)cols);
+  if (src->qt == CMLD_F32 && !allow_f32) return fail(CMLD_ERR_UNSUPPORTED, "%s: f32 weights are not supported here", what);
+  weight_free(dst);
+  dst = *src;
+  src->data = nullptr;
+  delete src;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_adopt_layer(cmld_engine *e, int32_t layer, cmld_weight *const projs[7], const float *attn_norm,
+                                const float *ffn_norm) {
+  CMLD_ENGINE_ENTER(e);
+  const cmld_config &c = e->cfg;
+  if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "adopt_layer: layer %d out of range", layer);
+  if (!projs) return fail(CMLD_ERR_INVALID, "adopt_layer: projections are null");
+  LayerW &L = e->layers[layer];
+  const int64_t shapes[7][2] = {{e->q_width, c.hidden},  {e->kv_width, c.hidden}, {e->kv_width, c.hidden}, {c.hidden, e->q_width},
+                                {c.ffn_dim, c.hidden},   {c.ffn_dim, c.hidden},   {c.hidden, c.ffn_dim}};
+  for (int i = 0; i < 7; ++i)  // validate everything before consuming anything
+    if (projs[i] && (projs[i]->rows != shapes[i][0] || projs[i]->cols != shapes[i][1] || projs[i]->qt == CMLD_F32))
+      return fail(CMLD_ERR_SHAPE, "adopt_layer(%d): projection %d has the wrong shape or type", layer, i);
+  for (int i = 0; i < 7; ++i)
+    if (projs[i]) CMLD_TRY(adopt(L.proj[i], projs[i], shapes[i][0], shapes[i][1], "adopt_layer"));
+  CMLD_TRY(upload_f32(&L.attn_norm, attn_norm, c.hidden, e->stream));
+  CMLD_TRY(upload_f32(&L.ffn_norm, ffn_norm, c.hidden, e->stream));
+  L.dense_set = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_adopt_layer_moe(cmld_engine *e, int32_t layer, cmld_weight *router_f32, cmld_weight *gate_exps,
+                                    cmld_weight *up_exps, cmld_weight *down_exps) {
+  CMLD_ENGINE_ENTER(e);
+  const cmld_config &c = e->cfg;
+  if (c.n_experts <= 0) return fail(CMLD_ERR_STATE, "adopt_layer_moe: engine was created without experts");
+  if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "adopt_layer_moe: layer %d out of range", layer);
+  if (!router_f32 || !gate_exps || !up_exps || !down_exps) return fail(CMLD_ERR_INVALID, "adopt_layer_moe: null weight");
+  if (c.n_experts % ep_size(e)) return fail(CMLD_ERR_SHAPE, "n_experts %d not divisible by ep_size %d", c.n_experts, ep_size(e));
+  const int64_t n_local = c.n_experts / ep_size(e);
+  LayerW &L = e->layers[layer];
+  cmld_weight *ts[3] = {gate_exps, up_exps, down_exps};
+  const int64_t shapes[3][2] = {{n_local * c.ffn_dim, c.hidden}, {n_local * c.ffn_dim, c.hidden}, {n_local * c.hidden, c.ffn_dim}};
+  if (router_f32->qt != CMLD_F32 || router_f32->rows != c.n_experts || router_f32->cols != c.hidden)
+    return fail(CMLD_ERR_SHAPE, "adopt_layer_moe: router must be f32 [n_experts][hidden]");
+  for (int i = 0; i < 3; ++i)
+    if (ts[i]->rows != shapes[i][0] || ts[i]->cols != shapes[i][1] || (ts[i]->qt != CMLD_Q4_K && ts[i]->qt != CMLD_Q6_K))
+      return fail(CMLD_ERR_SHAPE, "adopt_layer_moe: expert tensor %d has the wrong shape or type", i);
+  for (int i = 0; i < 3; ++i) CMLD_TRY(adopt(L.exps[i], ts[i], shapes[i][0], shapes[i][1], "adopt_layer_moe"));
+  cudaFree(L.router);
+  L.router = reinterpret_cast<float *>(router_f32->data);
+  router_f32->data = nullptr;
+  delete router_f32;
+  L.moe_set = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_adopt_output(cmld_engine *e, const float *final_norm, cmld_weight *output) {
+  CMLD_ENGINE_ENTER(e);
+  if (!output) return fail(CMLD_ERR_INVALID, "adopt_output: weight is null");
+  CMLD_TRY(adopt(e->output, output, e->cfg.vocab, e->cfg.hidden, "adopt_output"));
+  CMLD_TRY(upload_f32(&e->final_norm, final_norm, e->cfg.hidden, e->stream));
+  e->has_output = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_adopt_token_embd(cmld_engine *e, cmld_weight *token_embd) {
+  CMLD_ENGINE_ENTER(e);
+  if (!token_embd) return fail(CMLD_ERR_INVALID, "adopt_token_embd: weight is null");
+  CMLD_TRY(adopt(e->token_embd, token_embd, e->cfg.vocab, e->cfg.hidden, "adopt_token_embd", true));
+  e->has_embd = true;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_weights_ready(const cmld_engine *e) {
+  if (!e) return 0;
+  for (const auto &L : e->layers)
+    if (!L.dense_set || (e->cfg.n_experts > 0 && !L.moe_set)) return 0;
+  return e->has_output ? 1 : 0;
+}
+int64_t cmld_engine_filled(const cmld_engine *e) { return e ? e->filled : 0; }
+int32_t cmld_engine_set_filled(cmld_engine *e, int64_t filled) {
+  if (!e) return fail(CMLD_ERR_INVALID, "engine handle is null");
+  if (filled < 0 || filled > e->cfg.max_pos) return fail(CMLD_ERR_INVALID, "filled %lld out of range", (long long)filled);
+  e->filled = filled;
+  return CMLD_OK;
+}
+int64_t cmld_engine_max_pos(const cmld_engine *e) { return e ? e->cfg.max_pos : 0; }
+int32_t cmld_engine_n_layers(const cmld_engine *e) { return e ? e->cfg.n_layers : 0; }
+
+int32_t cmld_engine_forward_token(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
+                                  int64_t position, float scale, int32_t compute_logits, uint32_t *token_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (compute_logits && !token_out) return fail(CMLD_ERR_INVALID, "token_out is null");
+  CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, compute_logits != 0, compute_logits != 0, false));
+  int32_t tok = 0;
+  if (compute_logits) CMLD_CUDA(cudaMemcpyAsync(&tok, e->out_idx, 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "forward_token"));
+  if (compute_logits) *token_out = (uint32_t)tok;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_forward_token_logits(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
+                                         int64_t position, float scale, float *logits_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (!logits_out) return fail(CMLD_ERR_INVALID, "logits_out is null");
+  CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, true, false, false));
+  CMLD_CUDA(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+  return finish(e, "forward_token_logits");
+}
+
+int32_t cmld_engine_forward_token_hidden(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
+                                         int64_t position, float scale, float *hidden_out, float *layer_taps) {
+  CMLD_ENGINE_ENTER(e);
+  if (!hidden_out) return fail(CMLD_ERR_INVALID, "hidden_out is null");
+  CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, false, false, layer_taps != nullptr));
+  CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (layer_taps)
+    CMLD_CUDA(cudaMemcpy2DAsync(layer_taps, (size_t)e->cfg.hidden * 4, e->taps, (size_t)e->max_rows * e->cfg.hidden * 4,
+                                (size_t)e->cfg.hidden * 4, e->cfg.n_layers, cudaMemcpyDeviceToHost, e->stream));
+  return finish(e, "forward_token_hidden");
+}
+
+int32_t cmld_engine_prefill_from(cmld_engine *e, const float *embeddings, const float *cos_all, const float *sin_all,
+                                 int64_t n, float scale, int64_t start) {
+  CMLD_ENGINE_ENTER(e);
+  if (n < 0 || start < 0 || start > n) return fail(CMLD_ERR_INVALID, "prefill: start=%lld exceeds n=%lld", (long long)start, (long long)n);
+  const int half = e->cfg.rope_dim / 2;
+  const int chunk = 8;
+  for (int64_t i = start; i < n; i += chunk) {
+    const int rows = (int)std::min<int64_t>(chunk, n - i);
+    CMLD_TRY(forward_embedding_rows(e, embeddings + i * e->cfg.hidden, cos_all + i * half, sin_all + i * half, i, rows, scale,
+                                    false, false, false));
+  }
+  return finish(e, "prefill");
+}
+
+int32_t cmld_engine_verify_batch(cmld_engine *e, const float *embeddings, const float *cos_all, const float *sin_all,
+                                 int64_t base_position, int32_t k, float scale, uint32_t *tokens_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (k < 1 || k > e->max_rows) return fail(CMLD_ERR_INVALID, "verify_batch: k=%d out of 1..=%d", k, e->max_rows);
+  if (!tokens_out) return fail(CMLD_ERR_INVALID, "tokens_out is null");
+  CMLD_TRY(forward_embedding_rows(e, embeddings, cos_all, sin_all, base_position, k, scale, true, true, false));
+  std::vector<int32_t> toks(k);
+  CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)k * 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "verify_batch"));
+  for (int i = 0; i < k; ++i) tokens_out[i] = (uint32_t)toks[i];
+  return CMLD_OK;
+}
+
+// KV import/export, slot 0: f32 [kv_head][n_positions][head_dim] <-> f16 cache rows.
+__global__ void kv_convert_kernel(__half *cache, float *host_layout, int n_kv, int64_t max_pos, int64_t n_pos, int hd,
+                                  bool to_cache) {
+  const int64_t total = (int64_t)n_kv * n_pos * hd;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t kh = i / (n_pos * hd), rem = i % (n_pos * hd);
+    const int64_t ci = kh * max_pos * hd + rem;
+    if (to_cache) cache[ci] = __float2half_rn(host_layout[i]);
+    else host_layout[i] = __half2float(cache[ci]);
+  }
+}
+
+static int32_t kv_transfer(cmld_engine *e, int32_t layer, float *ck, float *cv, int64_t n_pos, bool to_cache) {
+  const cmld_config &c = e->cfg;
+  if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "layer %d out of range", layer);
+  if (n_pos < 0 || n_pos > c.max_pos) return fail(CMLD_ERR_INVALID, "n_positions %lld out of range", (long long)n_pos);
+  if (n_pos == 0) return CMLD_OK;
+  if (!ck || !cv) return fail(CMLD_ERR_INVALID, "KV buffer is null");
+  const int64_t n = (int64_t)c.n_kv_heads * n_pos * c.head_dim;
+  float *tmp = nullptr;
+  CMLD_CUDA(cudaMalloc(&tmp, (size_t)n * 4));
+  int32_t rc = CMLD_OK;
+  for (int side = 0; side < 2 && rc == CMLD_OK; ++side) {
+    float *hostp = side == 0 ? ck : cv;
+    __half *cache = (side == 0 ? e->kcache : e->vcache) + (int64_t)layer * e->kv_layer_elems;
+    const unsigned blocks = (unsigned)std::min<int64_t>((n + 255) / 256, 4096);
+    if (to_cache) {
+      if (cudaMemcpyAsync(tmp, hostp, (size_t)n * 4, cudaMemcpyDefault, e->stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "KV upload failed");
+      kv_convert_kernel<<<blocks, 256, 0, e->stream>>>(cache, tmp, c.n_kv_heads, c.max_pos, n_pos, c.head_dim, true);
+    } else {
+      kv_convert_kernel<<<blocks, 256, 0, e->stream>>>(cache, tmp, c.n_kv_heads, c.max_pos, n_pos, c.head_dim, false);
+      if (cudaMemcpyAsync(hostp, tmp, (size_t)n * 4, cudaMemcpyDefault, e->stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "KV download failed");
+    }
+    if (rc == CMLD_OK && cudaStreamSynchronize(e->stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "KV transfer failed");
+  }
+  cudaFree(tmp);
+  return rc;
+}
+
+int32_t cmld_engine_seed_layer(cmld_engine *e, int32_t layer, const float *ck, const float *cv, int64_t n_positions) {
+  CMLD_ENGINE_ENTER(e);
+  return kv_transfer(e, layer, const_cast<float *>(ck), const_cast<float *>(cv), n_positions, true);
+}
+
+int32_t cmld_engine_read_kv_layer(cmld_engine *e, int32_t layer, int64_t n_positions, float *ck_out, float *cv_out) {
+  CMLD_ENGINE_ENTER(e);
+  return kv_transfer(e, layer, ck_out, cv_out, n_positions, false);
+}
+
+// ---------------------------------------------------------------- token-id driven calls
+
+static int32_t check_rows(cmld_engine *e, int32_t n, const int32_t *seqs, const int32_t *tokens, const int64_t *positions,
+                          int64_t extra_steps, std::vector<int32_t> &pos32) {
+  const cmld_config &c = e->cfg;
+  if (n < 1 || n > e->max_rows) return fail(CMLD_ERR_INVALID, "%d rows exceed the engine's %d", n, e->max_rows);
+  if (!seqs || !tokens || !positions) return fail(CMLD_ERR_INVALID, "seqs / tokens / positions pointer is null");
+  pos32.resize(n);
+  const int slots = std::max(1, c.max_seqs);
+  for (int i = 0; i < n; ++i) {
+    if (seqs[i] < 0 || seqs[i] >= slots) return fail(CMLD_ERR_INVALID, "sequence slot %d out of range (max_seqs %d)", seqs[i], slots);
+    if (tokens[i] < 0 || tokens[i] >= c.vocab) return fail(CMLD_ERR_INVALID, "token id %d out of range", tokens[i]);
+    if (positions[i] < 0 || positions[i] + extra_steps > c.max_pos)
+      return fail(CMLD_ERR_STATE, "position %lld (+%lld steps) exceeds max_pos %d", (long long)positions[i], (long long)extra_steps, c.max_pos);
+    pos32[i] = (int32_t)positions[i];
+  }
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *seqs, const int32_t *tokens_in,
+                               const int64_t *positions, uint32_t *tokens_out, float *logits_out, float *hidden_out) {
+  CMLD_ENGINE_ENTER(e);
+  std::vector<int32_t> pos32;
+  CMLD_TRY(check_rows(e, n_seqs, seqs, tokens_in, positions, 1, pos32));
+  CMLD_TRY(require_weights(e, true));
+  CMLD_TRY(stage_rows(e, n_seqs, tokens_in, pos32.data(), seqs));
+  e->launches = 0;
+  CMLD_CUDA(cudaEventRecord(e->ev0, e->stream));
+  StepOpts o;
+  o.batch = n_seqs;
+  o.from_tokens = true;
+  o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
+  CMLD_TRY(engine_step(e, o));
+  CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
+  std::vector<int32_t> toks(n_seqs);
+  CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (logits_out) CMLD_CUDA(cudaMemcpyAsync(logits_out, e->logits, (size_t)n_seqs * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (hidden_out) CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)n_seqs * e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "step_batch"));
+  cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
+  e->last_launches = e->launches;
+  if (tokens_out)
+    for (int i = 0; i < n_seqs; ++i) tokens_out[i] = (uint32_t)toks[i];
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *tokens, int64_t n, int64_t start_pos,
+                                   uint32_t *next_token_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (n < 1 || !tokens) return fail(CMLD_ERR_INVALID, "prefill_tokens: no tokens");
+  CMLD_TRY(require_weights(e, true));
+  const int chunk = 8;
+  e->launches = 0;
+  CMLD_CUDA(cudaEventRecord(e->ev0, e->stream));
+  int last_rows = 0;
+  for (int64_t i = 0; i < n; i += chunk) {
+    const int rows = (int)std::min<int64_t>(chunk, n - i);
+    std::vector<int32_t> seqs(rows, seq), pos32;
+    std::vector<int64_t> pos(rows);
+    for (int r = 0; r < rows; ++r) pos[r] = start_pos + i + r;
+    CMLD_TRY(check_rows(e, rows, seqs.data(), tokens + i, pos.data(), 1, pos32));
+    CMLD_TRY(stage_rows(e, rows, tokens + i, pos32.data(), seqs.data()));
+    StepOpts o;
+    o.batch = rows;
+    o.from_tokens = true;
+    o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
+    o.logits = o.argmax = (i + chunk >= n);
+    CMLD_TRY(engine_step(e, o));
+    last_rows = rows;
+  }
+  CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
+  int32_t tok = 0;
+  CMLD_CUDA(cudaMemcpyAsync(&tok, e->out_idx + (last_rows - 1), 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "prefill_tokens"));
+  cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
+  e->last_launches = e->launches;
+  if (next_token_out) *next_token_out = (uint32_t)tok;
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_decode_greedy(cmld_engine *e, int32_t n_seqs, const int32_t *seqs, const int32_t *tokens_in,
+                                  const int64_t *positions, int32_t n_steps, uint32_t *tokens_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (n_steps < 1 || n_steps > e->history_cap) return fail(CMLD_ERR_INVALID, "decode_greedy: n_steps %d out of 1..=%lld", n_steps, (long long)e->history_cap);
+  if (!tokens_out) return fail(CMLD_ERR_INVALID, "tokens_out is null");
+  std::vector<int32_t> pos32;
+  CMLD_TRY(check_rows(e, n_seqs, seqs, tokens_in, positions, n_steps, pos32));
+  CMLD_TRY(require_weights(e, true));
+  CMLD_TRY(stage_rows(e, n_seqs, tokens_in, pos32.data(), seqs));
+  CMLD_CUDA(cudaMemsetAsync(e->am_ticket, 0, (size_t)2 * e->max_rows * 4, e->stream));
+  e->launches = 0;
+  CMLD_CUDA(cudaEventRecord(e->ev0, e->stream));
+  StepOpts o;
+  o.batch = n_seqs;
+  o.from_tokens = true;
+  o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
+  o.feed_back = true;
+  for (int s = 0; s < n_steps; ++s) CMLD_TRY(engine_step(e, o));
+  CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
+  std::vector<int32_t> hist((size_t)n_steps * n_seqs);
+  CMLD_CUDA(cudaMemcpyAsync(hist.data(), e->d_history, hist.size() * 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "decode_greedy"));
+  cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
+  e->last_launches = e->launches;
+  for (size_t i = 0; i < hist.size(); ++i) tokens_out[i] = (uint32_t)hist[i];
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_last_timing(const cmld_engine *e, float *ms_out, int64_t *launches_out) {
+  if (!e) return fail(CMLD_ERR_INVALID, "engine handle is null");
+  if (ms_out) *ms_out = e->last_ms;
+  if (launches_out) *launches_out = e->last_launches;
+  return CMLD_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,324 @@
+// Mixtral-style top-k mixture-of-experts FFN for the decode step.
+//
+// CPU form (mixtral_moe_ffn, src/inference.rs:14142-14280 in the Camelid tree): router logits =
+// f32 router . normed hidden; softmax_top_k (src/inference.rs:13940-13991): order by (logit
+// desc, index asc), keep k, softmax over the kept logits, re-order by (weight desc, index asc);
+// each selected expert runs gate/up -> SwiGLU -> down and `out += expert_out * weight` in that
+// order; then the residual add.  Expert matrices that are not Q8_0 are multiplied as
+// dequantised f32 weights against the *unquantised* f32 activation (the reference loads
+// them as f32, src/inference.rs:832-846, and uses the plain dot of expert_matrix_view,
+// :14109-14123) — so the expert matvec here keeps f32 activations: sum_i x_i * w_i is
+// evaluated per 32- or 16-value group as scale * sum(x_i * code_i) - min * sum(x_i), which
+// is the same real number with different f32 rounding points.
+#include <algorithm>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace cmld {
+
+int32_t weight_upload(Weight &w, int32_t qt, int64_t rows, int64_t cols, const void *wire, uint64_t nbytes, cudaStream_t s);
+void weight_free(Weight &w);
+
+constexpr int kMaxExperts = 64;
+constexpr int kMoeCols = 4;  // activation columns per pass of the expert matvec
+constexpr int kMoeRows = 2;
+constexpr int kMoeWarps = 4;
+
+// total_cmp key of an f32 (Rust f32::total_cmp).
+__device__ __forceinline__ int total_key(float f) {
+  const int b = __float_as_int(f);
+  return b ^ (int)(((unsigned)(b >> 31)) >> 1);
+}
+
+// One CTA per token row: router logits, then top-k selection by thread 0.
+__global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ x, const float *__restrict__ router, int hidden,
+                                                        int n_exp, int k, int32_t *__restrict__ sel_idx, float *__restrict__ sel_w) {
+  __shared__ float logits[kMaxExperts];
+  const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float *xr = x + (int64_t)b * hidden;
+  for (int e = warp; e < n_exp; e += 8) {
+    const float *r = router + (int64_t)e * hidden;
+    float s = 0.0f;
+    for (int i = lane; i < hidden; i += 32) s = __fmaf_rn(xr[i], r[i], s);
+    s = warp_sum(s);
+    if (lane == 0) logits[e] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  int idx[kMaxExperts];
+  float w[kMaxExperts];
+  bool used[kMaxExperts];
+  for (int e = 0; e < n_exp; ++e) used[e] = false;
+  for (int s = 0; s < k; ++s) {  // selection sort: largest total_cmp key, lowest index on ties
+    int best = -1;
+    for (int e = 0; e < n_exp; ++e)
+      if (!used[e] && (best < 0 || total_key(logits[e]) > total_key(logits[best]))) best = e;
+    used[best] = true;
+    idx[s] = best;
+  }
+  float mx = -INFINITY;
+  for (int s = 0; s < k; ++s) mx = fmaxf(mx, logits[idx[s]]);
+  float sum = 0.0f;
+  for (int s = 0; s < k; ++s) {
+    const float v = logits[idx[s]];
+    w[s] = isfinite(v) ? expf(v - mx) : 0.0f;
+    sum += w[s];
+  }
+  for (int s = 0; s < k; ++s) w[s] = sum > 0.0f ? __fdiv_rn(w[s], sum) : __fdiv_rn(1.0f, (float)k);
+  for (int s = 1; s < k; ++s) {  // stable insertion by (weight desc, index asc)
+    const int ci = idx[s];
+    const float cw = w[s];
+    int j = s - 1;
+    while (j >= 0 && (total_key(w[j]) < total_key(cw) || (total_key(w[j]) == total_key(cw) && idx[j] > ci))) {
+      idx[j + 1] = idx[j];
+      w[j + 1] = w[j];
+      --j;
+    }
+    idx[j + 1] = ci;
+    w[j + 1] = cw;
+  }
+  for (int s = 0; s < k; ++s) {
+    sel_idx[b * k + s] = idx[s];
+    sel_w[b * k + s] = w[s];
+  }
+}
+
+// Bucket the batch*k assignments by expert, in ascending assignment order.
+__global__ void moe_group_kernel(const int32_t *__restrict__ sel_idx, int n_assign, int n_exp, int32_t *__restrict__ counts,
+                                 int32_t *__restrict__ lists) {
+  const int e = threadIdx.x;
+  if (e >= n_exp) return;
+  int n = 0;
+  for (int a = 0; a < n_assign; ++a)
+    if (sel_idx[a] == e) lists[e * n_assign + n++] = a;
+  counts[e] = n;
+}
+
+// float(code) of byte `sel` of w without an int->float conversion: place the byte in the
+// mantissa of 2^23 and subtract 2^23 (exact for 0..255).
+__device__ __forceinline__ float byte_to_float(uint32_t w, int sel) {
+  return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 | sel)) - 8388608.0f;
+}
+
+struct MoeGemvArgs {
+  const uint8_t *w;  // expert slabs, device layout, rows_per_expert rows each
+  int32_t qt;
+  int64_t rows_per_expert, cols, stride;
+  const float *x;   // activation rows
+  int64_t x_stride;
+  int32_t x_div;    // activation row of assignment a is a / x_div (k for gate/up, 1 for down)
+  float *y;         // [n_assign][rows_per_expert]
+  const int32_t *counts, *lists;
+  int32_t n_assign;
+  int32_t first_expert, expert_step;  // experts held locally: first_expert + i*expert_step
+};
+
+template <int QT>
+__global__ void __launch_bounds__(kMoeWarps * 32) moe_gemv_kernel(MoeGemvArgs a) {
+  const int e_local = blockIdx.y;
+  const int e = a.first_expert + e_local * a.expert_step;
+  const int n = a.counts[e];
+  if (n == 0) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t r0 = ((int64_t)blockIdx.x * kMoeWarps + warp) * kMoeRows;
+  if (r0 >= a.rows_per_expert) return;
+  const uint8_t *row[kMoeRows];
+#pragma unroll
+  for (int r = 0; r < kMoeRows; ++r)
+    row[r] = a.w + ((int64_t)e_local * a.rows_per_expert + (r0 + r < a.rows_per_expert ? r0 + r : r0)) * a.stride;
+  const int nsb = (int)(a.cols >> 8);
+  const int units = nsb * 8;
+  for (int c0 = 0; c0 < n; c0 += kMoeCols) {
+    const float *xc[kMoeCols];
+    int asg[kMoeCols];
+#pragma unroll
+    for (int c = 0; c < kMoeCols; ++c) {
+      asg[c] = a.lists[e * a.n_assign + min(c0 + c, n - 1)];
+      xc[c] = a.x + (int64_t)(asg[c] / a.x_div) * a.x_stride;
+    }
+    float acc[kMoeRows][kMoeCols];
+#pragma unroll
+    for (int r = 0; r < kMoeRows; ++r)
+#pragma unroll
+      for (int c = 0; c < kMoeCols; ++c) acc[r][c] = 0.0f;
+    for (int u = lane; u < units; u += 32) {
+      const int sb = u >> 3, t = u & 7;
+      uint4 wq[kMoeRows];
+#pragma unroll
+      for (int r = 0; r < kMoeRows; ++r) wq[r] = ld_stream16(row[r] + (int64_t)u * 16);
+      if (QT == CMLD_Q4_K) {
+        const int j = t >> 1, h = t & 1;
+        const int xo = sb * 256 + 64 * j + 16 * h;
+        float dl[kMoeRows], dh[kMoeRows], ml[kMoeRows], mh[kMoeRows];
+#pragma unroll
+        for (int r = 0; r < kMoeRows; ++r) {
+          const uint4 meta = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)nsb * 128) + sb);
+          const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
+          int s0, m0, s1, m1;
+          q4k_scale_min(2 * j, meta.y, meta.z, meta.w, s0, m0);
+          q4k_scale_min(2 * j + 1, meta.y, meta.z, meta.w, s1, m1);
+          dl[r] = __fmul_rn(d, (float)s0);
+          dh[r] = __fmul_rn(d, (float)s1);
+          ml[r] = __fmul_rn(dmin, (float)m0);
+          mh[r] = __fmul_rn(dmin, (float)m1);
+        }
+        float dotl[kMoeRows][kMoeCols], doth[kMoeRows][kMoeCols], sxl[kMoeCols], sxh[kMoeCols];
+#pragma unroll
+        for (int c = 0; c < kMoeCols; ++c) {
+          sxl[c] = sxh[c] = 0.0f;
+#pragma unroll
+          for (int r = 0; r < kMoeRows; ++r) dotl[r][c] = doth[r][c] = 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float fl[kMoeRows][4], fh[kMoeRows][4];
+#pragma unroll
+          for (int r = 0; r < kMoeRows; ++r) {
+            const uint32_t w = k == 0 ? wq[r].x : (k == 1 ? wq[r].y : (k == 2 ? wq[r].z : wq[r].w));
+            const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              fl[r][i] = byte_to_float(lo, i);
+              fh[r][i] = byte_to_float(hi, i);
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < kMoeCols; ++c) {
+            const float4 xl = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo + 4 * k));
+            const float4 xh = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo + 32 + 4 * k));
+            sxl[c] += (xl.x + xl.y) + (xl.z + xl.w);
+            sxh[c] += (xh.x + xh.y) + (xh.z + xh.w);
+#pragma unroll
+            for (int r = 0; r < kMoeRows; ++r) {
+              dotl[r][c] = __fmaf_rn(fl[r][0], xl.x, __fmaf_rn(fl[r][1], xl.y, __fmaf_rn(fl[r][2], xl.z, __fmaf_rn(fl[r][3], xl.w, dotl[r][c]))));
+              doth[r][c] = __fmaf_rn(fh[r][0], xh.x, __fmaf_rn(fh[r][1], xh.y, __fmaf_rn(fh[r][2], xh.z, __fmaf_rn(fh[r][3], xh.w, doth[r][c]))));
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kMoeRows; ++r)
+#pragma unroll
+          for (int c = 0; c < kMoeCols; ++c)
+            acc[r][c] += (dl[r] * dotl[r][c] - ml[r] * sxl[c]) + (dh[r] * doth[r][c] - mh[r] * sxh[c]);
+      } else {  // Q6_K
+        const int h = t >> 2, sp = (t >> 1) & 1, cc = t & 1;
+        const int jlo = 8 * h + 2 * sp + cc;
+        const int xo = sb * 256 + jlo * 16;
+        float dl[kMoeRows], dh[kMoeRows];
+        uint4 qh4[kMoeRows];
+#pragma unroll
+        for (int r = 0; r < kMoeRows; ++r) {
+          qh4[r] = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)nsb * 128 + sb * 64 + 32 * h + 16 * cc));
+          const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row[r] + (int64_t)nsb * 208) + sb));
+          const int8_t *sc = reinterpret_cast<const int8_t *>(row[r] + (int64_t)nsb * 192 + sb * 16);
+          dl[r] = __fmul_rn(d, (float)__ldg(sc + jlo));
+          dh[r] = __fmul_rn(d, (float)__ldg(sc + jlo + 4));
+        }
+        float dotl[kMoeRows][kMoeCols], doth[kMoeRows][kMoeCols], sxl[kMoeCols], sxh[kMoeCols];
+#pragma unroll
+        for (int c = 0; c < kMoeCols; ++c) {
+          sxl[c] = sxh[c] = 0.0f;
+#pragma unroll
+          for (int r = 0; r < kMoeRows; ++r) dotl[r][c] = doth[r][c] = 0.0f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float fl[kMoeRows][4], fh[kMoeRows][4];
+#pragma unroll
+          for (int r = 0; r < kMoeRows; ++r) {
+            const uint32_t w = k == 0 ? wq[r].x : (k == 1 ? wq[r].y : (k == 2 ? wq[r].z : wq[r].w));
+            const uint32_t q = k == 0 ? qh4[r].x : (k == 1 ? qh4[r].y : (k == 2 ? qh4[r].z : qh4[r].w));
+            const uint32_t lo = (w & 0x0f0f0f0fu) | (((q >> (2 * sp)) & 0x03030303u) << 4);
+            const uint32_t hi = ((w >> 4) & 0x0f0f0f0fu) | (((q >> (2 * sp + 4)) & 0x03030303u) << 4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              fl[r][i] = byte_to_float(lo, i);
+              fh[r][i] = byte_to_float(hi, i);
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < kMoeCols; ++c) {
+            const float4 xl = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo + 4 * k));
+            const float4 xh = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo + 64 + 4 * k));
+            sxl[c] += (xl.x + xl.y) + (xl.z + xl.w);
+            sxh[c] += (xh.x + xh.y) + (xh.z + xh.w);
+#pragma unroll
+            for (int r = 0; r < kMoeRows; ++r) {
+              dotl[r][c] = __fmaf_rn(fl[r][0], xl.x, __fmaf_rn(fl[r][1], xl.y, __fmaf_rn(fl[r][2], xl.z, __fmaf_rn(fl[r][3], xl.w, dotl[r][c]))));
+              doth[r][c] = __fmaf_rn(fh[r][0], xh.x, __fmaf_rn(fh[r][1], xh.y, __fmaf_rn(fh[r][2], xh.z, __fmaf_rn(fh[r][3], xh.w, doth[r][c]))));
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kMoeRows; ++r)
+#pragma unroll
+          for (int c = 0; c < kMoeCols; ++c)
+            acc[r][c] += dl[r] * (dotl[r][c] - 32.0f * sxl[c]) + dh[r] * (doth[r][c] - 32.0f * sxh[c]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kMoeRows; ++r)
+#pragma unroll
+      for (int c = 0; c < kMoeCols; ++c) {
+        const float v = warp_sum(acc[r][c]);
+        if (lane == 0 && r0 + r < a.rows_per_expert && c0 + c < n) a.y[(int64_t)asg[c] * a.rows_per_expert + r0 + r] = v;
+      }
+  }
+}
+
+// h[b] += sum_s down[b*k+s] * w[b][s], accumulated in selection order from zero, as the CPU does.
+__global__ void moe_combine_kernel(float *__restrict__ h, const float *__restrict__ down, const float *__restrict__ sel_w,
+                                   const int32_t *__restrict__ sel_idx, int hidden, int k, int first_expert, int expert_step,
+                                   int add_residual) {
+  const int b = blockIdx.y;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < hidden; c += gridDim.x * blockDim.x) {
+    float out = 0.0f;
+    for (int s = 0; s < k; ++s) {
+      const int e = sel_idx[b * k + s];
+      if (expert_step > 1 && (e - first_expert) % expert_step != 0) continue;  // expert held by another rank
+      out = __fadd_rn(out, __fmul_rn(down[((int64_t)b * k + s) * hidden + c], sel_w[b * k + s]));
+    }
+    h[(int64_t)b * hidden + c] = add_residual ? __fadd_rn(h[(int64_t)b * hidden + c], out) : out;
+  }
+}
+
+}  // namespace cmld
+
+using namespace cmld;
+
+namespace cmld {
+
+int32_t moe_route(const float *normed, const float *router, int hidden, int n_exp, int k, int batch, int32_t *sel_idx,
+                  float *sel_w, int32_t *counts, int32_t *lists, cudaStream_t s) {
+  if (n_exp > kMaxExperts) return fail(CMLD_ERR_SHAPE, "more than %d experts", kMaxExperts);
+  moe_route_kernel<<<batch, 256, 0, s>>>(normed, router, hidden, n_exp, k, sel_idx, sel_w);
+  CMLD_CUDA(cudaGetLastError());
+  moe_group_kernel<<<1, kMaxExperts, 0, s>>>(sel_idx, batch * k, n_exp, counts, lists);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
+                        const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
+                        int n_assign, cudaStream_t s) {
+  MoeGemvArgs a{slab.data, slab.qt, rows_per_expert, slab.cols, slab.stride, x, x_stride, x_div, y, counts, lists, n_assign,
+                first_expert, expert_step};
+  dim3 grid((unsigned)((rows_per_expert + kMoeRows * kMoeWarps - 1) / (kMoeRows * kMoeWarps)), (unsigned)n_local_experts);
+  if (slab.qt == CMLD_Q4_K) moe_gemv_kernel<CMLD_Q4_K><<<grid, kMoeWarps * 32, 0, s>>>(a);
+  else if (slab.qt == CMLD_Q6_K) moe_gemv_kernel<CMLD_Q6_K><<<grid, kMoeWarps * 32, 0, s>>>(a);
+  else return fail(CMLD_ERR_UNSUPPORTED, "expert tensors must be Q4_K or Q6_K");
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+int32_t moe_combine(float *h, const float *down, const float *sel_w, const int32_t *sel_idx, int hidden, int k, int batch,
+                    int first_expert, int expert_step, bool add_residual, cudaStream_t s) {
+  dim3 grid((unsigned)((hidden + 255) / 256), (unsigned)batch);
+  moe_combine_kernel<<<grid, 256, 0, s>>>(h, down, sel_w, sel_idx, hidden, k, first_expert, expert_step, add_residual ? 1 : 0);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+}  // namespace cmld

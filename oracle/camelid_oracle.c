@@ -932,6 +932,20 @@ ORACLE_API void orc_model_set_token_embd(orc_model *m, int32_t qt, const uint8_t
   m->token_embd = mk_tensor(qt, data, m->vocab, m->hidden);
 }
 
+/* K and V rows of one layer as [kv_head][n_pos][head_dim] (the layout of the reference's
+ * read_kv_layer, src/cuda_resident.rs:17448). */
+ORACLE_API int orc_model_read_kv(const orc_model *m, int32_t layer, int64_t n_pos, float *ck, float *cv) {
+  if (layer < 0 || layer >= m->n_layers || n_pos < 0 || n_pos > m->max_pos) return -1;
+  int32_t hd = m->head_dim;
+  const float *kc = m->kcache + (size_t)layer * m->n_kv_heads * m->max_pos * hd;
+  const float *vc = m->vcache + (size_t)layer * m->n_kv_heads * m->max_pos * hd;
+  for (int32_t kh = 0; kh < m->n_kv_heads; ++kh) {
+    memcpy(ck + (size_t)kh * n_pos * hd, kc + (size_t)kh * m->max_pos * hd, (size_t)n_pos * hd * 4);
+    memcpy(cv + (size_t)kh * n_pos * hd, vc + (size_t)kh * m->max_pos * hd, (size_t)n_pos * hd * 4);
+  }
+  return 0;
+}
+
 /* src/tensor/mod.rs:2899-3216 (embedding_lookup): dequantise one row. */
 ORACLE_API int orc_embedding(const orc_model *m, int32_t token, float *out) {
   if (token < 0 || token >= m->vocab || !m->token_embd.data) return -1;
@@ -1043,8 +1057,27 @@ ORACLE_API int orc_forward(orc_model *m, const float *x_in, int64_t position, fl
 }
 
 /* Greedy generation from token ids: prompt positions then n_gen tokens; returns ids. */
+static float top2_gap(const float *x, int64_t n) {
+  float a = -INFINITY, b = -INFINITY;
+  for (int64_t i = 0; i < n; ++i) {
+    if (x[i] > a) { b = a; a = x[i]; }
+    else if (x[i] > b) b = x[i];
+  }
+  return a - b;
+}
+
+/* gaps, if non-NULL, receives for every generated token the difference between the largest
+ * and second-largest logit it was chosen from (how close the greedy choice was to a tie). */
+ORACLE_API int orc_generate_gaps(orc_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_gen, int64_t start_pos,
+                                 int32_t *out_tokens, float *last_logits, float *gaps);
+
 ORACLE_API int orc_generate(orc_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_gen, int64_t start_pos,
                             int32_t *out_tokens, float *last_logits) {
+  return orc_generate_gaps(m, prompt, n_prompt, n_gen, start_pos, out_tokens, last_logits, NULL);
+}
+
+ORACLE_API int orc_generate_gaps(orc_model *m, const int32_t *prompt, int32_t n_prompt, int32_t n_gen, int64_t start_pos,
+                                 int32_t *out_tokens, float *last_logits, float *gaps) {
   float *emb = (float *)malloc((size_t)m->hidden * 4);
   float *logits = (float *)malloc((size_t)m->vocab * 4);
   int64_t pos = start_pos;
@@ -1058,6 +1091,7 @@ ORACLE_API int orc_generate(orc_model *m, const int32_t *prompt, int32_t n_promp
   for (int32_t i = 0; i < n_gen && rc == 0; ++i) {
     tok = orc_argmax(logits, m->vocab);
     out_tokens[i] = tok;
+    if (gaps) gaps[i] = top2_gap(logits, m->vocab);
     if (i + 1 == n_gen) break;
     rc = orc_embedding(m, tok, emb);
     if (rc) break;

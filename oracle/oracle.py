@@ -74,8 +74,10 @@ def lib(path: str | os.PathLike | None = None):
         "orc_model_set_output": (None, [vp, vp, i32, vp]),
         "orc_model_set_token_embd": (None, [vp, i32, vp]),
         "orc_embedding": (C.c_int, [vp, i32, vp]),
+        "orc_model_read_kv": (C.c_int, [vp, i32, i64, vp, vp]),
         "orc_forward": (C.c_int, [vp, vp, i64, vp, vp, vp]),
         "orc_generate": (C.c_int, [vp, vp, i32, i32, i64, vp, vp]),
+        "orc_generate_gaps": (C.c_int, [vp, vp, i32, i32, i64, vp, vp, vp]),
         "orc_num_threads": (C.c_int, []),
         "orc_set_num_threads": (None, [C.c_int]),
     }
@@ -269,6 +271,12 @@ class OracleModel:
         assert lib().orc_embedding(self._h, token, _p(out)) == 0
         return out
 
+    def read_kv_layer(self, layer: int, n_positions: int):
+        shape = (self.cfg["n_kv_heads"], n_positions, self.cfg["head_dim"])
+        ck, cv = np.empty(shape, np.float32), np.empty(shape, np.float32)
+        assert lib().orc_model_read_kv(self._h, layer, n_positions, _p(ck), _p(cv)) == 0
+        return ck, cv
+
     def forward(self, x, position: int, want_logits=True, want_taps=False):
         x = _f32(x)
         c = self.cfg
@@ -280,10 +288,11 @@ class OracleModel:
         assert rc == 0, f"oracle forward failed rc={rc}"
         return logits, hidden, taps
 
-    def generate(self, prompt, n_gen: int, start_pos: int = 0):
+    def generate(self, prompt, n_gen: int, start_pos: int = 0, want_gaps: bool = False):
         prompt = np.ascontiguousarray(prompt, dtype=np.int32)
         out = np.empty(n_gen, np.int32)
         logits = np.empty(self.cfg["vocab"], np.float32)
-        rc = lib().orc_generate(self._h, _p(prompt), prompt.size, n_gen, start_pos, _p(out), _p(logits))
+        gaps = np.empty(n_gen, np.float32)
+        rc = lib().orc_generate_gaps(self._h, _p(prompt), prompt.size, n_gen, start_pos, _p(out), _p(logits), _p(gaps))
         assert rc == 0
-        return out, logits
+        return (out, logits, gaps) if want_gaps else (out, logits)
