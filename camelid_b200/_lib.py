@@ -100,6 +100,8 @@ def lib():
         "cmld_act_quantize": (i32, [i32, vp, i64, i32, vp]),
         "cmld_act_export": (i32, [i32, vp, i64, i32, vp, vp]),
         "cmld_gemv": (i32, [vp, vp, i32, vp, vp]),
+        "cmld_gemv_select_kernel": (i32, [i32]),
+        "cmld_gemv_fused": (i32, [vp, i32, vp, vp, vp, f32, i32, vp, vp]),
         "cmld_rms_norm": (i32, [vp, vp, i64, i32, f32, vp, i32, vp]),
         "cmld_silu_mul": (i32, [vp, vp, i64, i32, vp, i32, vp]),
         "cmld_argmax": (i32, [vp, i64, i32, vp]),

@@ -20,6 +20,55 @@ static int32_t sync_ok(const char *what) {
   return CMLD_OK;
 }
 
+// Status word for the staged kernel's bounded waits, one per device, made on first use.
+static int32_t *op_status(void) {
+  static int32_t *words[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], 4) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, 4);
+  }
+  return words[dev];
+}
+
+static int32_t check_op_status(const char *what) {
+  int32_t *w = op_status(), st = 0;
+  if (!w) return CMLD_OK;
+  if (cudaMemcpy(&st, w, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return fail(CMLD_ERR_CUDA, "%s: status read failed", what);
+  if (st != 0) {
+    cudaMemset(w, 0, 4);
+    return fail(st, "%s: a bounded device-side wait gave up (status %d)", what, st);
+  }
+  return CMLD_OK;
+}
+
+static int g_gemv_pdl = 0;            // cmld_gemv_time: chain its launches with programmatic dependent launch
+static int g_gemv_kernel_choice = 0;  // 0 auto (staged when the shape fits), 1 direct-load only
+
+// One matvec launch on the default stream: staged kernel if it takes the shape, else direct-load.
+static int32_t gemv_launch(const cmld_weight *w, const uint8_t *act, int32_t batch, float *y, const float *residual,
+                           cudaStream_t stream = nullptr, bool pdl = false) {
+  GemvJob probe{w->data, w->qt, w->rows, w->cols, w->stride, y, residual, w->rows};
+  const int fit = g_gemv_kernel_choice == 0 ? gemv_pipe_fit_batch(&probe, 1) : 0;
+  const int pass = fit > 0 ? fit : 8;
+  for (int b0 = 0; b0 < batch; b0 += pass) {
+    const int nb = std::min(pass, batch - b0);
+    GemvJob j{w->data, w->qt, w->rows, w->cols, w->stride, y + (int64_t)b0 * w->rows, residual ? residual + (int64_t)b0 * w->rows : nullptr, w->rows};
+    const uint8_t *a = act + (int64_t)b0 * act_row_stride(w->cols);
+    int32_t rc = CMLD_ERR_UNSUPPORTED;
+    if (fit > 0) {
+      GemvPrologue pro{};
+      pro.mode = 0;
+      pro.act_k = pro.act_0 = a;
+      rc = launch_gemv_pipe(&j, 1, nb, pro, op_status(), stream, pdl);
+    }
+    if (rc == CMLD_ERR_UNSUPPORTED) rc = launch_gemv(&j, 1, a, nb, stream);
+    CMLD_TRY(rc);
+  }
+  return CMLD_OK;
+}
+
 extern "C" {
 
 int32_t cmld_weight_create(int32_t qtype, int64_t rows, int64_t cols, const void *wire, uint64_t nbytes, cmld_weight **out) {
@@ -119,9 +168,38 @@ int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, floa
   if (!w || !act_dev || !y_dev) return fail(CMLD_ERR_INVALID, "null buffer");
   if (w->qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "gemv over f32 weights is not part of this path");
   if (batch < 1) return fail(CMLD_ERR_INVALID, "batch %d", batch);
+  CMLD_TRY(gemv_launch(w, static_cast<const uint8_t *>(act_dev), batch, y_dev, residual_dev));
+  CMLD_TRY(sync_ok("gemv"));
+  return check_op_status("gemv");
+}
+
+int32_t cmld_gemv_select_kernel(int32_t choice) {
+  if (choice < 0 || choice > 3) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
+  g_gemv_kernel_choice = choice & 1;
+  g_gemv_pdl = (choice >> 1) & 1;
+  return CMLD_OK;
+}
+
+int32_t cmld_gemv_fused(const cmld_weight *w, int32_t mode, const float *x_dev, const float *x2_dev, const float *norm_w_dev,
+                        float eps, int32_t batch, float *y_dev, const float *residual_dev) {
+  if (!w || !x_dev || !y_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  if (mode < 1 || mode > 3) return fail(CMLD_ERR_INVALID, "mode %d not in 1..3", mode);
+  if ((mode == 1 && !norm_w_dev) || (mode == 3 && !x2_dev)) return fail(CMLD_ERR_INVALID, "missing operand for mode %d", mode);
+  if (w->qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "gemv over f32 weights is not part of this path");
+  if (batch < 1 || batch > 8) return fail(CMLD_ERR_INVALID, "batch %d not in 1..8", batch);
   GemvJob j{w->data, w->qt, w->rows, w->cols, w->stride, y_dev, residual_dev, w->rows};
-  CMLD_TRY(launch_gemv(&j, 1, static_cast<const uint8_t *>(act_dev), batch, nullptr));
-  return sync_ok("gemv");
+  GemvPrologue pro{};
+  pro.mode = mode;
+  pro.x = x_dev;
+  pro.x2 = x2_dev;
+  pro.norm_w = norm_w_dev;
+  pro.x_stride = w->cols;
+  pro.eps = eps;
+  const int32_t rc = launch_gemv_pipe(&j, 1, batch, pro, op_status(), nullptr, false);
+  if (rc == CMLD_ERR_UNSUPPORTED) return fail(rc, "the staged kernel does not take a %lld x %lld matrix at batch %d", (long long)w->rows, (long long)w->cols, batch);
+  CMLD_TRY(rc);
+  CMLD_TRY(sync_ok("gemv_fused"));
+  return check_op_status("gemv_fused");
 }
 
 int32_t cmld_gemv_time(cmld_weight *const *copies, int32_t n_copies, const void *act_dev, int32_t batch, float *y_dev,
@@ -129,22 +207,41 @@ int32_t cmld_gemv_time(cmld_weight *const *copies, int32_t n_copies, const void 
   if (!copies || n_copies < 1 || !act_dev || !y_dev || !ms_per_launch_out || iters < 1) return fail(CMLD_ERR_INVALID, "bad arguments");
   for (int i = 0; i < n_copies; ++i)
     if (!copies[i] || copies[i]->qt == CMLD_F32) return fail(CMLD_ERR_INVALID, "bad weight %d", i);
-  cudaEvent_t e0, e1;
+  // The launches are captured into one CUDA graph so that the host's enqueue rate is not what
+  // is measured; the graph is replayed once untimed (with the warm-up launches) and once timed.
+  cudaStream_t st = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  CMLD_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
   CMLD_CUDA(cudaEventCreate(&e0));
   CMLD_CUDA(cudaEventCreate(&e1));
+  op_status();  // make the status word before capture
   int32_t rc = CMLD_OK;
-  for (int it = -warmup; it < iters && rc == CMLD_OK; ++it) {
-    if (it == 0) cudaEventRecord(e0, nullptr);
-    const cmld_weight *w = copies[((it % n_copies) + n_copies) % n_copies];
-    GemvJob j{w->data, w->qt, w->rows, w->cols, w->stride, y_dev, nullptr, w->rows};
-    rc = launch_gemv(&j, 1, static_cast<const uint8_t *>(act_dev), batch, nullptr);
+  const uint8_t *act = static_cast<const uint8_t *>(act_dev);
+  for (int it = 0; it < warmup && rc == CMLD_OK; ++it) rc = gemv_launch(copies[it % n_copies], act, batch, y_dev, nullptr, st, false);
+  if (rc == CMLD_OK && cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "graph capture failed to start");
+  if (rc == CMLD_OK) {
+    for (int it = 0; it < iters && rc == CMLD_OK; ++it) rc = gemv_launch(copies[it % n_copies], act, batch, y_dev, nullptr, st, g_gemv_pdl != 0);
+    cudaError_t ce = cudaStreamEndCapture(st, &graph);
+    if (rc == CMLD_OK && ce != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce));
   }
-  cudaEventRecord(e1, nullptr);
-  if (rc == CMLD_OK) rc = sync_ok("gemv_time");
+  if (rc == CMLD_OK && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "graph instantiate failed");
+  if (rc == CMLD_OK) {
+    cudaGraphLaunch(exec, st);
+    cudaEventRecord(e0, st);
+    cudaGraphLaunch(exec, st);
+    cudaEventRecord(e1, st);
+    if (cudaStreamSynchronize(st) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "gemv_time: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  if (rc == CMLD_OK) rc = check_op_status("gemv_time");
   float ms = 0.0f;
   if (rc == CMLD_OK) cudaEventElapsedTime(&ms, e0, e1);
+  if (exec) cudaGraphExecDestroy(exec);
+  if (graph) cudaGraphDestroy(graph);
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
+  cudaStreamDestroy(st);
   *ms_per_launch_out = ms / (float)iters;
   return rc;
 }

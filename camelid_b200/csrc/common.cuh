@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -36,12 +37,13 @@ int32_t fail(int32_t code, const char *fmt, ...);
 
 // ------------------------------------------------------------------ device layouts
 //
-// A quantised matrix keeps exactly its GGUF wire bytes, permuted within each row so that
-// every field streams as 16-byte aligned vectors ("structure of arrays per row"):
-//   Q8_0: [codes: cols x i8][scales: cols/32 x f16]
-//   Q4_K: [nibbles: nsb x 128][meta: nsb x 16 = f16 d, f16 dmin, 12 scale bytes]
-//   Q6_K: [ql: nsb x 128][qh: nsb x 64][scales: nsb x 16 x i8][d: nsb x f16]
-// with the row stride rounded up to 16 bytes.
+// A quantised matrix keeps exactly its GGUF wire bytes; rows are contiguous, and within a row
+// the bytes are arranged so that every field can be read as 16-byte aligned vectors:
+//   Q8_0: [codes: cols x i8][scales: cols/32 x f16]                  (wire blocks are 34 B: 2-byte aligned)
+//   Q4_K: the wire superblocks themselves, 144 B each = [f16 d, f16 dmin, 12 scale bytes | 128 nibble bytes]
+//   Q6_K: [nsb x 208 B = ql 128 | qh 64 | 16 x i8 scales][d: nsb x f16]  (wire superblocks are 210 B)
+// with the row stride rounded up to 16 bytes.  A tile of consecutive rows is therefore one
+// contiguous, 16-byte aligned byte range: exactly what one bulk asynchronous copy moves.
 
 constexpr int kWarp = 32;
 
@@ -157,6 +159,21 @@ struct GemvJob {
   int64_t y_stride;
 };
 int32_t launch_gemv(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, cudaStream_t s);
+
+// gemv_pipe.cu: the staged kernel.  How its consumers obtain the quantised activation:
+struct GemvPrologue {
+  int32_t mode;            // 0: quantised rows given (act_k / act_0); 1: RMSNorm(x)*norm_w; 2: x as is; 3: SwiGLU(x, x2)
+  const float *x, *x2, *norm_w;
+  int64_t x_stride;        // floats between batch rows of x and x2
+  float eps;
+  const uint8_t *act_k, *act_0;  // mode 0: Q8_K rows / Q8_0 rows in the global activation layout
+  float *norm_out;         // optional: f32 copy of the prologue's result [batch][cols]
+};
+// Returns CMLD_ERR_UNSUPPORTED, leaving the error message untouched, when the shape does not fit.
+// Largest batch (<= 8) the staged kernel takes for these matrices in one launch; 0 = none.
+int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs);
+int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
+                         cudaStream_t s, bool pdl);
 
 // ops.cu
 struct NormQuantArgs {

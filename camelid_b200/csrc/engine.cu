@@ -132,6 +132,7 @@ struct cmld_engine {
   int64_t history_cap = 0;
   int32_t *moe_sel_idx = nullptr, *moe_counts = nullptr, *moe_lists = nullptr;
   float *moe_sel_w = nullptr, *moe_g = nullptr, *moe_u = nullptr, *moe_act = nullptr, *moe_down = nullptr;
+  int32_t *d_status = nullptr;  // set by a kernel whose bounded wait gave up
   int64_t filled = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = 0.0f;
@@ -267,6 +268,7 @@ static int32_t engine_init(cmld_engine *e) {
   }
   e->history_cap = 4096;
   CMLD_TRY(dev_alloc(e, &e->d_history, e->history_cap * R));
+  CMLD_TRY(dev_alloc(e, &e->d_status, 1));
   CMLD_CUDA(cudaStreamSynchronize(e->stream));
   return CMLD_OK;
 }
@@ -312,7 +314,7 @@ struct Proj {
   int64_t y_stride;
 };
 
-// Matvecs that share one activation row: one launch per operand format.
+// Matvecs that share one activation row, direct-load kernel: one launch per operand format.
 static int32_t run_gemv_group(cmld_engine *e, const Proj *p, int n, int32_t batch) {
   for (int pass = 0; pass < 2; ++pass) {
     GemvJob jobs[4];
@@ -346,6 +348,48 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
   CMLD_TRY(launch_norm_quant(a, e->stream));
   e->launches += 1;
   return CMLD_OK;
+}
+
+// One sublayer's matvecs: y_i = W_i . quantise(f(x)) (+ residual), f = RMSNorm / identity / SwiGLU.
+// Fast path: the staged kernel with f and the quantiser fused into its prologue (batch in passes
+// of 8 columns).  Shapes it does not take fall back to quantise-kernel + direct-load kernel.
+static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
+                          const float *norm_w, int64_t cols) {
+  if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3) {
+    GemvJob jobs[3];
+    for (int i = 0; i < n; ++i)
+      jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
+    const int fit = gemv_pipe_fit_batch(jobs, n);  // columns per pass: the same for every batch size, so
+    bool ok = fit > 0;                            // a row's result does not depend on who shares its step
+    for (int b0 = 0; b0 < batch && ok; b0 += fit) {
+      const int nb = std::min(fit, batch - b0);
+      for (int i = 0; i < n; ++i) {
+        jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y + (int64_t)b0 * p[i].y_stride,
+                          p[i].residual ? p[i].residual + (int64_t)b0 * p[i].y_stride : nullptr, p[i].y_stride};
+      }
+      GemvPrologue pro{};
+      pro.mode = mode;
+      pro.x = x + (int64_t)b0 * cols;
+      pro.x2 = x2 ? x2 + (int64_t)b0 * cols : nullptr;
+      pro.norm_w = norm_w;
+      pro.x_stride = cols;
+      pro.eps = e->cfg.eps;
+      const int32_t rc = launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, !(e->cfg.flags & CMLD_FLAG_NO_PDL));
+      if (rc == CMLD_ERR_UNSUPPORTED && b0 == 0) {
+        ok = false;
+        break;
+      }
+      CMLD_TRY(rc);
+      e->launches += 1;
+    }
+    if (ok) return CMLD_OK;
+  }
+  bool n0, nk;
+  const Weight *ws[4];
+  for (int i = 0; i < n; ++i) ws[i] = p[i].w;
+  act_kinds(ws, n, n0, nk);
+  CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
+  return run_gemv_group(e, p, n, batch);
 }
 
 struct StepOpts {
@@ -406,15 +450,11 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   }
   for (int32_t li = 0; li < c.n_layers; ++li) {
     LayerW &L = e->layers[li];
-    bool n0, nk;
     {
-      const Weight *g[3] = {&L.proj[0], &L.proj[1], &L.proj[2]};
-      act_kinds(g, 3, n0, nk);
-      CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.attn_norm, c.hidden, B, nullptr, n0, nk));
       const Proj p[3] = {{&L.proj[0], e->q, nullptr, e->q_width},
                          {&L.proj[1], e->k, nullptr, e->kv_width},
                          {&L.proj[2], e->v, nullptr, e->kv_width}};
-      CMLD_TRY(run_gemv_group(e, p, 3, B));
+      CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden));
     }
     {
       RopeKvArgs r{};
@@ -459,26 +499,17 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       e->launches += 2;
     }
     {
-      const Weight *g[1] = {&L.proj[3]};
-      act_kinds(g, 1, n0, nk);
-      CMLD_TRY(run_norm_quant(e, e->attn, nullptr, nullptr, e->q_width, B, nullptr, n0, nk));
       const Proj p[1] = {{&L.proj[3], e->h, e->h, c.hidden}};
-      CMLD_TRY(run_gemv_group(e, p, 1, B));
+      CMLD_TRY(gemv_fused(e, p, 1, B, 2, e->attn, nullptr, nullptr, e->q_width));
     }
     if (L.moe_set) {
       CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.ffn_norm, c.hidden, B, e->normed, false, false));
       CMLD_TRY(moe_ffn_step(e, L, B));
     } else {
-      const Weight *g[2] = {&L.proj[4], &L.proj[5]};
-      act_kinds(g, 2, n0, nk);
-      CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.ffn_norm, c.hidden, B, nullptr, n0, nk));
       const Proj p[2] = {{&L.proj[4], e->gate, nullptr, c.ffn_dim}, {&L.proj[5], e->up, nullptr, c.ffn_dim}};
-      CMLD_TRY(run_gemv_group(e, p, 2, B));
-      const Weight *gd[1] = {&L.proj[6]};
-      act_kinds(gd, 1, n0, nk);
-      CMLD_TRY(run_norm_quant(e, e->gate, e->up, nullptr, c.ffn_dim, B, nullptr, n0, nk));
+      CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden));
       const Proj pd[1] = {{&L.proj[6], e->h, e->h, c.hidden}};
-      CMLD_TRY(run_gemv_group(e, pd, 1, B));
+      CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim));
     }
     if (o.taps) {
       CMLD_CUDA(cudaMemcpyAsync(e->taps + (int64_t)li * e->max_rows * c.hidden, e->h, (size_t)B * c.hidden * 4,
@@ -487,12 +518,8 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   }
   if (o.logits) {
     if (!e->has_output) return fail(CMLD_ERR_STATE, "output weights not set");
-    bool n0, nk;
-    const Weight *g[1] = {&e->output};
-    act_kinds(g, 1, n0, nk);
-    CMLD_TRY(run_norm_quant(e, e->h, nullptr, e->final_norm, c.hidden, B, nullptr, n0, nk));
     const Proj p[1] = {{&e->output, e->logits, nullptr, c.vocab}};
-    CMLD_TRY(run_gemv_group(e, p, 1, B));
+    CMLD_TRY(gemv_fused(e, p, 1, B, 1, e->h, nullptr, e->final_norm, c.hidden));
     if (o.argmax) {
       CMLD_TRY(launch_argmax(e->logits, c.vocab, B, e->am_val, e->am_idx, e->am_ticket, e->out_idx,
                              o.feed_back ? e->d_tokens : nullptr, e->d_positions, e->d_history, e->stream));
@@ -521,8 +548,14 @@ static int32_t stage_rows(cmld_engine *e, int32_t n, const int32_t *tokens, cons
 }
 
 static int32_t finish(cmld_engine *e, const char *what) {
-  cudaError_t ce = cudaStreamSynchronize(e->stream);
+  int32_t st = 0;
+  cudaError_t ce = cudaMemcpyAsync(&st, e->d_status, 4, cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
+  if (st != 0) {
+    cudaMemsetAsync(e->d_status, 0, 4, e->stream);
+    return fail(st, "%s: a bounded device-side wait gave up (status %d); results of this call are invalid", what, st);
+  }
   return CMLD_OK;
 }
 

@@ -46,30 +46,21 @@ __global__ void relayout_kernel(int qt_wire, uint8_t *__restrict__ wire, uint8_t
     }
   } else if (qt_wire == CMLD_Q4_K) {
     uint4 *w = reinterpret_cast<uint4 *>(wire + (r * bpr + b) * 144);
-    uint4 *dq = reinterpret_cast<uint4 *>(drow + b * 128);
-    uint4 *dm = reinterpret_cast<uint4 *>(drow + bpr * 128 + b * 16);
+    uint4 *d = reinterpret_cast<uint4 *>(drow + b * 144);
     if (!TO_WIRE) {
-      *dm = w[0];
-      for (int i = 0; i < 8; ++i) dq[i] = w[1 + i];
+      for (int i = 0; i < 9; ++i) d[i] = w[i];
     } else {
-      w[0] = *dm;
-      for (int i = 0; i < 8; ++i) w[1 + i] = dq[i];
+      for (int i = 0; i < 9; ++i) w[i] = d[i];
     }
   } else {  // Q6_K: ql[128] qh[64] scales[16] d[2]
     uint16_t *w = reinterpret_cast<uint16_t *>(wire + (r * bpr + b) * 210);
-    uint16_t *dql = reinterpret_cast<uint16_t *>(drow + b * 128);
-    uint16_t *dqh = reinterpret_cast<uint16_t *>(drow + bpr * 128 + b * 64);
-    uint16_t *dsc = reinterpret_cast<uint16_t *>(drow + bpr * 192 + b * 16);
+    uint16_t *dblk = reinterpret_cast<uint16_t *>(drow + b * 208);
     uint16_t *dd = reinterpret_cast<uint16_t *>(drow + bpr * 208) + b;
     if (!TO_WIRE) {
-      for (int i = 0; i < 64; ++i) dql[i] = w[i];
-      for (int i = 0; i < 32; ++i) dqh[i] = w[64 + i];
-      for (int i = 0; i < 8; ++i) dsc[i] = w[96 + i];
+      for (int i = 0; i < 104; ++i) dblk[i] = w[i];
       *dd = w[104];
     } else {
-      for (int i = 0; i < 64; ++i) w[i] = dql[i];
-      for (int i = 0; i < 32; ++i) w[64 + i] = dqh[i];
-      for (int i = 0; i < 8; ++i) w[96 + i] = dsc[i];
+      for (int i = 0; i < 104; ++i) w[i] = dblk[i];
       w[104] = *dd;
     }
   }
@@ -109,11 +100,11 @@ __device__ __forceinline__ float dequant_element(const uint8_t *row, int qt, int
   const int64_t nsb = cols >> 8, sb = i >> 8;
   const int e = (int)(i & 255);
   if (qt == CMLD_Q4_K) {
-    const uint32_t *meta = reinterpret_cast<const uint32_t *>(row + nsb * 128 + sb * 16);
+    const uint32_t *meta = reinterpret_cast<const uint32_t *>(row + sb * 144);
     const uint32_t dm = meta[0];
     const float d = f16_bits_to_f32((uint16_t)(dm & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(dm >> 16));
     const int p = e >> 6, hi = (e >> 5) & 1, l = e & 31;
-    const uint8_t byte = row[sb * 128 + 32 * p + l];
+    const uint8_t byte = row[sb * 144 + 16 + 32 * p + l];
     const int nib = hi ? (byte >> 4) : (byte & 15);
     int sc, m;
     q4k_scale_min(2 * p + hi, meta[1], meta[2], meta[3], sc, m);
@@ -123,12 +114,12 @@ __device__ __forceinline__ float dequant_element(const uint8_t *row, int qt, int
   }
   // Q6_K
   const int h = e >> 7, stream = (e >> 5) & 3, l = e & 31;
-  const uint8_t *ql = row + sb * 128 + 64 * h;
-  const uint8_t qh = row[nsb * 128 + sb * 64 + 32 * h + l];
+  const uint8_t *ql = row + sb * 208 + 64 * h;
+  const uint8_t qh = row[sb * 208 + 128 + 32 * h + l];
   const uint8_t lb = ql[(stream & 1) * 32 + l];
   const int lo = (stream & 2) ? (lb >> 4) : (lb & 15);
   const int q = (lo | (((qh >> (2 * stream)) & 3) << 4)) - 32;
-  const int sc = reinterpret_cast<const int8_t *>(row + nsb * 192 + sb * 16)[8 * h + (l >> 4) + 2 * stream];
+  const int sc = reinterpret_cast<const int8_t *>(row + sb * 208 + 192)[8 * h + (l >> 4) + 2 * stream];
   const float d = f16_bits_to_f32(reinterpret_cast<const uint16_t *>(row + nsb * 208)[sb]);
   return d * (float)sc * (float)q;
 }
@@ -276,7 +267,7 @@ __device__ void quantize_store_q8_0(const float *src, uint8_t *row, int64_t cols
 }
 
 // quantize_block_q4_k (src/quantize.rs:152-244).
-__device__ void quantize_store_q4_k(const float *src, uint8_t *row, int64_t nsb, int64_t sb) {
+__device__ void quantize_store_q4_k(const float *src, uint8_t *row, int64_t sb) {
   float mins[8], maxs[8];
   for (int g = 0; g < 8; ++g) {
     float mn = INFINITY, mx = -INFINITY;
@@ -306,7 +297,7 @@ __device__ void quantize_store_q4_k(const float *src, uint8_t *row, int64_t nsb,
     sc[g] = (uint8_t)clampf(roundf(gs * id), 0.0f, 63.0f);
     m[g] = (uint8_t)clampf(roundf(fmaxf(-mins[g], 0.0f) * idmin), 0.0f, 63.0f);
   }
-  uint8_t *meta = row + nsb * 128 + sb * 16;
+  uint8_t *meta = row + sb * 144;
   reinterpret_cast<uint16_t *>(meta)[0] = f32_to_f16_bits(d);
   reinterpret_cast<uint16_t *>(meta)[1] = f32_to_f16_bits(dmin);
   uint8_t ps[12];
@@ -321,7 +312,7 @@ __device__ void quantize_store_q4_k(const float *src, uint8_t *row, int64_t nsb,
     ps[g + 4] = (uint8_t)((sc[g] & 0x0f) | ((m[g] & 0x0f) << 4));
   }
   for (int g = 0; g < 12; ++g) meta[4 + g] = ps[g];
-  uint8_t *qs = row + sb * 128;
+  uint8_t *qs = row + sb * 144 + 16;
   for (int p = 0; p < 4; ++p) {
     const float d0 = d * (float)sc[2 * p], d1 = d * (float)sc[2 * p + 1];
     const float m0 = -(dmin * (float)m[2 * p]), m1 = -(dmin * (float)m[2 * p + 1]);
@@ -347,8 +338,8 @@ __device__ void quantize_store_q6_k(const float *src, uint8_t *row, int64_t nsb,
   }
   const float d = smax / 127.0f;
   const float id = d != 0.0f ? 1.0f / d : 0.0f;
-  uint8_t *ql = row + sb * 128, *qh = row + nsb * 128 + sb * 64;
-  int8_t *scp = reinterpret_cast<int8_t *>(row + nsb * 192 + sb * 16);
+  uint8_t *ql = row + sb * 208, *qh = row + sb * 208 + 128;
+  int8_t *scp = reinterpret_cast<int8_t *>(row + sb * 208 + 192);
   reinterpret_cast<uint16_t *>(row + nsb * 208)[sb] = f32_to_f16_bits(d);
   float sub_id[16];
   for (int j = 0; j < 16; ++j) {
@@ -393,7 +384,7 @@ __global__ void synth_kernel(uint8_t *__restrict__ data, int qt, int64_t rows, i
   }
   float v[256];
   for (int i = 0; i < 256; ++i) v[i] = synth_normal(seed, stream, base + i, sigma);
-  if (qt == CMLD_Q4_K) quantize_store_q4_k(v, row, bpr, b);
+  if (qt == CMLD_Q4_K) quantize_store_q4_k(v, row, b);
   else quantize_store_q6_k(v, row, bpr, b);
 }
 

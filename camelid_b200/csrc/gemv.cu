@@ -9,11 +9,11 @@
 // a warp shuffle tree, so a result can differ from the CPU's block-ordered sum in the last
 // bits (never in the integer parts).
 //
-// Mapping: HBM-bound, no tensor cores.  One warp owns kRows consecutive output rows; a lane
-// owns 16-byte units of the row's code stream (unit u of every row sits at byte 16u, so a
-// warp load is 512 contiguous bytes), issues kUnroll independent 128-bit streaming loads per
-// row before touching them, unpacks in registers and feeds dp4a.
-#include "common.cuh"
+// This file holds the direct-load kernel: one warp owns kRows consecutive output rows, a lane
+// owns 16-byte units of the row's code stream, issues kUnroll independent 128-bit streaming
+// loads per row before touching them, unpacks in registers and feeds dp4a.  It accepts every
+// shape; the staged kernel in gemv_pipe.cu is the fast path for the shapes it supports.
+#include "gemv_rows.cuh"
 
 namespace cmld {
 
@@ -28,180 +28,6 @@ struct GemvJobs {
   int32_t first_block[kMaxJobs + 1];
   int32_t n;
 };
-
-__device__ __forceinline__ int dot16(const uint4 &a, const int4 &b) {
-  int s = __dp4a((int)a.x, b.x, 0);
-  s = __dp4a((int)a.y, b.y, s);
-  s = __dp4a((int)a.z, b.z, s);
-  return __dp4a((int)a.w, b.w, s);
-}
-
-template <int B>
-__device__ __forceinline__ void rows_q8_0(const uint8_t *const (&row)[kRows], int64_t cols, const uint8_t *act,
-                                          int64_t act_stride, int lane, float (&acc)[kRows][B]) {
-  const int units = (int)(cols >> 4);
-  const int64_t sc_off = act_scale_off(cols);
-  for (int u0 = 0; u0 < units; u0 += 32 * kUnroll) {
-    uint4 wv[kRows][kUnroll];
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      const int u = u0 + i * 32 + lane;
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) wv[r][i] = u < units ? ld_stream16(row[r] + (int64_t)u * 16) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      const int u = u0 + i * 32 + lane;
-      if (u >= units) continue;
-      const int blk = u >> 1;
-      float ws[kRows];
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) ws[r] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row[r] + cols) + blk));
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const uint8_t *a = act + b * act_stride;
-        const int4 xv = __ldg(reinterpret_cast<const int4 *>(a) + u);
-        const float xs = __ldg(reinterpret_cast<const float *>(a + sc_off) + blk);
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-          const int isum = dot16(wv[r][i], xv);
-          acc[r][b] = __fadd_rn(acc[r][b], __fmul_rn(__fmul_rn((float)isum, ws[r]), xs));
-        }
-      }
-    }
-  }
-}
-
-template <int B>
-__device__ __forceinline__ void rows_q4_k(const uint8_t *const (&row)[kRows], int64_t cols, const uint8_t *act,
-                                          int64_t act_stride, int lane, float (&acc)[kRows][B]) {
-  const int nsb = (int)(cols >> 8);
-  const int units = nsb * 8;
-  const int64_t sc_off = act_scale_off(cols), bs_off = act_bsum_off(cols);
-  for (int u0 = 0; u0 < units; u0 += 32 * kUnroll) {
-    uint4 wv[kRows][kUnroll];
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      const int u = u0 + i * 32 + lane;
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) wv[r][i] = u < units ? ld_stream16(row[r] + (int64_t)u * 16) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      const int u = u0 + i * 32 + lane;
-      if (u >= units) continue;
-      const int sb = u >> 3, t = u & 7, j = t >> 1, h = t & 1;
-      // This lane's 16 bytes hold values 64j+16h.. (low nibbles) and 64j+32+16h.. (high nibbles)
-      // of superblock sb; for the mins term the lane owns 32-value group t.
-      float dw[kRows], dmw[kRows];
-      int scl[kRows], sch[kRows], mt[kRows];
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        const uint4 meta = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)nsb * 128) + sb);
-        dw[r] = f16_bits_to_f32((uint16_t)(meta.x & 0xffff));
-        dmw[r] = f16_bits_to_f32((uint16_t)(meta.x >> 16));
-        int m_unused;
-        q4k_scale_min(2 * j, meta.y, meta.z, meta.w, scl[r], m_unused);
-        q4k_scale_min(2 * j + 1, meta.y, meta.z, meta.w, sch[r], m_unused);
-        int sc_unused;
-        q4k_scale_min(t, meta.y, meta.z, meta.w, sc_unused, mt[r]);
-      }
-      uint4 lo[kRows], hi[kRows];
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        const uint4 w = wv[r][i];
-        lo[r] = make_uint4(w.x & 0x0f0f0f0fu, w.y & 0x0f0f0f0fu, w.z & 0x0f0f0f0fu, w.w & 0x0f0f0f0fu);
-        hi[r] = make_uint4((w.x >> 4) & 0x0f0f0f0fu, (w.y >> 4) & 0x0f0f0f0fu, (w.z >> 4) & 0x0f0f0f0fu,
-                           (w.w >> 4) & 0x0f0f0f0fu);
-      }
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const uint8_t *a = act + b * act_stride;
-        const int4 xlo = __ldg(reinterpret_cast<const int4 *>(a + sb * 256 + 64 * j + 16 * h));
-        const int4 xhi = __ldg(reinterpret_cast<const int4 *>(a + sb * 256 + 64 * j + 32 + 16 * h));
-        const float xd = __ldg(reinterpret_cast<const float *>(a + sc_off) + sb);
-        const int bs2 = __ldg(reinterpret_cast<const int *>(a + bs_off) + sb * 8 + t);  // two i16 sums of group t
-        const int bsum = (int)(short)(bs2 & 0xffff) + (bs2 >> 16);
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-          const int s = dot16(lo[r], xlo) * scl[r] + dot16(hi[r], xhi) * sch[r];
-          const int p = bsum * mt[r];
-          const float d = __fmul_rn(xd, dw[r]), dmin = __fmul_rn(xd, dmw[r]);
-          acc[r][b] = __fmaf_rn(d, (float)s, __fmaf_rn(-dmin, (float)p, acc[r][b]));
-        }
-      }
-    }
-  }
-}
-
-template <int B>
-__device__ __forceinline__ void rows_q6_k(const uint8_t *const (&row)[kRows], int64_t cols, const uint8_t *act,
-                                          int64_t act_stride, int lane, float (&acc)[kRows][B]) {
-  const int nsb = (int)(cols >> 8);
-  const int units = nsb * 8;
-  const int64_t sc_off = act_scale_off(cols), bs_off = act_bsum_off(cols);
-  for (int u0 = 0; u0 < units; u0 += 32 * kUnroll) {
-    uint4 wl[kRows][kUnroll], wh[kRows][kUnroll];
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      const int u = u0 + i * 32 + lane;
-      const int sb = u >> 3, t = u & 7;
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        if (u < units) {
-          wl[r][i] = ld_stream16(row[r] + (int64_t)u * 16);
-          // qh bytes for l = 16c.. of half h: shared by the two lanes s' = 0,1
-          wh[r][i] = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)nsb * 128 + sb * 64 + 32 * (t >> 2) + 16 * (t & 1)));
-        } else {
-          wl[r][i] = wh[r][i] = make_uint4(0, 0, 0, 0);
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kUnroll; ++i) {
-      const int u = u0 + i * 32 + lane;
-      if (u >= units) continue;
-      // unit t of superblock sb: half h, ql sub-run s' (streams s' and s'+2), l = 16c..16c+15
-      const int sb = u >> 3, t = u & 7, h = t >> 2, sp = (t >> 1) & 1, c = t & 1;
-      const int jlo = 8 * h + 2 * sp + c;  // 16-value group of the low-nibble stream; high stream is jlo + 4
-      float dw[kRows];
-      int slo[kRows], shi[kRows];
-      uint4 qlo[kRows], qhi[kRows];
-#pragma unroll
-      for (int r = 0; r < kRows; ++r) {
-        dw[r] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row[r] + (int64_t)nsb * 208) + sb));
-        const int8_t *sc = reinterpret_cast<const int8_t *>(row[r] + (int64_t)nsb * 192 + sb * 16);
-        slo[r] = __ldg(sc + jlo);
-        shi[r] = __ldg(sc + jlo + 4);
-        const uint4 l4 = wl[r][i], h4 = wh[r][i];
-        const int sh_lo = 2 * sp, sh_hi = 2 * sp + 4;
-        qlo[r] = make_uint4((l4.x & 0x0f0f0f0fu) | (((h4.x >> sh_lo) & 0x03030303u) << 4),
-                            (l4.y & 0x0f0f0f0fu) | (((h4.y >> sh_lo) & 0x03030303u) << 4),
-                            (l4.z & 0x0f0f0f0fu) | (((h4.z >> sh_lo) & 0x03030303u) << 4),
-                            (l4.w & 0x0f0f0f0fu) | (((h4.w >> sh_lo) & 0x03030303u) << 4));
-        qhi[r] = make_uint4(((l4.x >> 4) & 0x0f0f0f0fu) | (((h4.x >> sh_hi) & 0x03030303u) << 4),
-                            ((l4.y >> 4) & 0x0f0f0f0fu) | (((h4.y >> sh_hi) & 0x03030303u) << 4),
-                            ((l4.z >> 4) & 0x0f0f0f0fu) | (((h4.z >> sh_hi) & 0x03030303u) << 4),
-                            ((l4.w >> 4) & 0x0f0f0f0fu) | (((h4.w >> sh_hi) & 0x03030303u) << 4));
-      }
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const uint8_t *a = act + b * act_stride;
-        const int4 xlo = __ldg(reinterpret_cast<const int4 *>(a + sb * 256 + jlo * 16));
-        const int4 xhi = __ldg(reinterpret_cast<const int4 *>(a + sb * 256 + (jlo + 4) * 16));
-        const float xd = __ldg(reinterpret_cast<const float *>(a + sc_off) + sb);
-        const short *bs = reinterpret_cast<const short *>(a + bs_off) + sb * 16;
-        const int blo = __ldg(bs + jlo), bhi = __ldg(bs + jlo + 4);
-#pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-          // codes are stored +32: sum (q-32)*x = dot(q,x) - 32*sum(x)
-          const int s = slo[r] * (dot16(qlo[r], xlo) - 32 * blo) + shi[r] * (dot16(qhi[r], xhi) - 32 * bhi);
-          acc[r][b] = __fadd_rn(acc[r][b], __fmul_rn(__fmul_rn(dw[r], xd), (float)s));
-        }
-      }
-    }
-  }
-}
 
 template <int B>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemv_kernel(const GemvJobs jobs, const uint8_t *__restrict__ act) {
@@ -222,9 +48,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) gemv_kernel(const GemvJob
 #pragma unroll
     for (int b = 0; b < B; ++b) acc[r][b] = 0.0f;
   const int64_t astride = act_row_stride(J.cols);
-  if (J.qt == CMLD_Q4_K) rows_q4_k<B>(row, J.cols, act, astride, lane, acc);
-  else if (J.qt == CMLD_Q6_K) rows_q6_k<B>(row, J.cols, act, astride, lane, acc);
-  else rows_q8_0<B>(row, J.cols, act, astride, lane, acc);
+  if (J.qt == CMLD_Q4_K) rows_q4_k<B, kRows, kUnroll, false>(row, J.cols, act, astride, lane, acc);
+  else if (J.qt == CMLD_Q6_K) rows_q6_k<B, kRows, kUnroll, false>(row, J.cols, act, astride, lane, acc);
+  else rows_q8_0<B, kRows, kUnroll, false>(row, J.cols, act, astride, lane, acc);
 #pragma unroll
   for (int r = 0; r < kRows; ++r)
 #pragma unroll

@@ -1,0 +1,604 @@
+// Staged quantised matvec for sm_100a: the fast path of the decode step.
+//
+// Why this shape.  A decode matvec reads every weight byte once and does ~1 integer MAC per
+// 4 bits: it is HBM-bound and uses no tensor cores.  What limits a simple kernel on B200 is
+// the number of bytes in flight (Little's law at ~6.5 TB/s needs > 40 KB per SM) and the gaps
+// between dependent launches.  So:
+//   * one persistent CTA per SM walks its share of row tiles; a tile of consecutive rows is one
+//     contiguous byte range of the device layout, fetched by ONE bulk asynchronous copy
+//     (cp.async.bulk, the non-tensor TMA path; never multicast) into a shared-memory ring of up
+//     to 8 stages guarded by mbarriers (full: transaction bytes, empty: one arrival per warp);
+//   * a dedicated producer warp issues the copies; it starts BEFORE the kernel waits on its
+//     predecessor (griddepcontrol.wait), because weights never depend on earlier kernels — under
+//     programmatic dependent launch the ring fills while the previous kernel drains;
+//   * the consumer warps first build the quantised activation in shared memory — optionally
+//     fused with RMSNorm or SwiGLU so no separate kernel and no global round trip is needed —
+//     then each lane owns whole superblocks (Q4_K/Q6_K) or 32-value blocks (Q8_0): one f16->f32
+//     and one int->f32 conversion per superblock instead of per 16 bytes, scales decoded once;
+//   * per-superblock integer sums and the two f32 multiply-adds are exactly the CPU's
+//     (q4_k_dot_scalar, src/diffusion_gemma/refmath.rs:504-562; q6_k_wire_row_dot and
+//     q8_0_dot_rows, src/inference.rs:25535 and :26166 in the Camelid tree); lanes are combined
+//     by a fixed shuffle tree, so results are deterministic and differ from the CPU's
+//     block-ordered sum only by f32 reassociation.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit failed polls a thread records
+// CMLD_ERR_TIMEOUT in *status and carries on (results are then invalid, the host reports the
+// error), so a lost copy can never hang the GPU.
+#include "actquant.cuh"
+
+namespace cmld {
+
+constexpr int kPipeConsumerWarps = 8;
+constexpr int kPipeConsumers = kPipeConsumerWarps * 32;
+constexpr int kPipeThreads = kPipeConsumers + 32;  // + the producer warp
+constexpr int kPipeMaxStages = 8;
+constexpr int kActRec = 336;       // one Q8_K activation superblock in shared memory (21 x 16 B: conflict-free lane stride)
+constexpr int kRecBsum16 = 256;    // 16 x i16 sums of 16 codes
+constexpr int kRecBsum32 = 288;    // 8 x i16 sums of 32 codes
+constexpr int kRecD = 304;         // f32 scale
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; returns false (and flags the error) if the phase never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int32_t *status) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (status) atomicExch(status, (int32_t)CMLD_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {  // unsigned bytes x signed bytes
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+struct PipeJob {
+  const uint8_t *w;
+  int32_t qt, rows, tile_rows, first_tile, n_tiles;
+  int64_t stride;
+  float *y;
+  const float *residual;
+  int64_t y_stride;
+};
+
+struct PipeArgs {
+  PipeJob job[3];
+  int32_t n_jobs, total_tiles, cols, batch, stage_bytes, n_stages;
+  int32_t mode;  // 0: quantised activation given (act_in); 1: RMSNorm(x)*norm_w; 2: x as is; 3: SwiGLU(x, x2)
+  const float *x, *x2, *norm_w;
+  int64_t x_stride;
+  float eps;
+  const uint8_t *act_in;  // standard global layout, Q8_K rows (then Q8_0 rows at act_in0)
+  const uint8_t *act_in0;
+  int32_t need_k, need_0;
+  int32_t off_act_k, off_act_0, off_red, off_ring;
+  float *norm_out;        // optional f32 copy of the normalised row (written by CTA 0)
+  int32_t *status;
+};
+
+// ---------------------------------------------------------------- per-superblock dots (shared memory operands)
+
+template <int B>
+__device__ __forceinline__ void sb_dot_q4k(const uint8_t *blk, const uint8_t *rec, int rec_col_stride, float (&acc)[B]) {
+  const uint4 meta = *reinterpret_cast<const uint4 *>(blk);
+  const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
+  // 6-bit scales/mins as bytes (q4_k_scale_min, src/tensor/mod.rs:5997-6006): groups 0..3 and 4..7
+  const uint32_t sc03 = meta.y & 0x3f3f3f3fu, m03 = meta.z & 0x3f3f3f3fu;
+  const uint32_t sc47 = (meta.w & 0x0f0f0f0fu) | ((meta.y >> 2) & 0x30303030u);
+  const uint32_t m47 = ((meta.w >> 4) & 0x0f0f0f0fu) | ((meta.z >> 2) & 0x30303030u);
+  int s[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b) s[b] = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int dl[B], dh[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) dl[b] = dh[b] = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint4 w = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * j + 16 * h);
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const uint8_t *r = rec + b * rec_col_stride;
+        const int4 xlo = *reinterpret_cast<const int4 *>(r + 64 * j + 16 * h);
+        const int4 xhi = *reinterpret_cast<const int4 *>(r + 64 * j + 32 + 16 * h);
+        dl[b] = __dp4a((int)(w.x & 0x0f0f0f0fu), xlo.x, dl[b]);
+        dl[b] = __dp4a((int)(w.y & 0x0f0f0f0fu), xlo.y, dl[b]);
+        dl[b] = __dp4a((int)(w.z & 0x0f0f0f0fu), xlo.z, dl[b]);
+        dl[b] = __dp4a((int)(w.w & 0x0f0f0f0fu), xlo.w, dl[b]);
+        // high nibbles left in place: bytes are 16*nibble (unsigned), the sum is shifted back below
+        dh[b] = dp4a_us(w.x & 0xf0f0f0f0u, xhi.x, dh[b]);
+        dh[b] = dp4a_us(w.y & 0xf0f0f0f0u, xhi.y, dh[b]);
+        dh[b] = dp4a_us(w.z & 0xf0f0f0f0u, xhi.z, dh[b]);
+        dh[b] = dp4a_us(w.w & 0xf0f0f0f0u, xhi.w, dh[b]);
+      }
+    }
+    const uint32_t scw = j < 2 ? sc03 : sc47;
+    const int sl = (scw >> (16 * (j & 1))) & 0xff, sh = (scw >> (16 * (j & 1) + 8)) & 0xff;
+#pragma unroll
+    for (int b = 0; b < B; ++b) s[b] += dl[b] * sl + (dh[b] >> 4) * sh;
+  }
+#pragma unroll
+  for (int b = 0; b < B; ++b) {
+    const uint8_t *r = rec + b * rec_col_stride;
+    const int4 bs = *reinterpret_cast<const int4 *>(r + kRecBsum32);  // 8 x i16 sums of 32 codes
+    int p = __dp2a_lo(bs.x, (int)m03, 0);
+    p = __dp2a_hi(bs.y, (int)m03, p);
+    p = __dp2a_lo(bs.z, (int)m47, p);
+    p = __dp2a_hi(bs.w, (int)m47, p);
+    const float xd = *reinterpret_cast<const float *>(r + kRecD);
+    // sumf = fma(-dmin, prod, sumf); sumf = fma(d, S, sumf)   (refmath.rs:529 and :560)
+    acc[b] = __fmaf_rn(__fmul_rn(xd, d), (float)s[b], __fmaf_rn(-__fmul_rn(xd, dmin), (float)p, acc[b]));
+  }
+}
+
+template <int B>
+__device__ __forceinline__ void sb_dot_q6k(const uint8_t *blk, float dw, const uint8_t *rec, int rec_col_stride, float (&acc)[B]) {
+  const int4 scw = *reinterpret_cast<const int4 *>(blk + 192);  // 16 signed scales
+  int s[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b) s[b] = 0;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const uint4 qh = *reinterpret_cast<const uint4 *>(blk + 128 + 32 * h + 16 * c);
+#pragma unroll
+      for (int sp = 0; sp < 2; ++sp) {
+        const uint4 ql = *reinterpret_cast<const uint4 *>(blk + 64 * h + 32 * sp + 16 * c);
+        const int jlo = 8 * h + 2 * sp + c;  // 16-value group of the low-nibble stream; the high stream is jlo + 4
+        // 6-bit codes: low nibble | two qh bits moved to bits 4..5
+        uint4 lo, hi;
+        if (sp == 0) {
+          lo = make_uint4((ql.x & 0x0f0f0f0fu) | ((qh.x << 4) & 0x30303030u), (ql.y & 0x0f0f0f0fu) | ((qh.y << 4) & 0x30303030u),
+                          (ql.z & 0x0f0f0f0fu) | ((qh.z << 4) & 0x30303030u), (ql.w & 0x0f0f0f0fu) | ((qh.w << 4) & 0x30303030u));
+          hi = make_uint4(((ql.x >> 4) & 0x0f0f0f0fu) | (qh.x & 0x30303030u), ((ql.y >> 4) & 0x0f0f0f0fu) | (qh.y & 0x30303030u),
+                          ((ql.z >> 4) & 0x0f0f0f0fu) | (qh.z & 0x30303030u), ((ql.w >> 4) & 0x0f0f0f0fu) | (qh.w & 0x30303030u));
+        } else {
+          lo = make_uint4((ql.x & 0x0f0f0f0fu) | ((qh.x << 2) & 0x30303030u), (ql.y & 0x0f0f0f0fu) | ((qh.y << 2) & 0x30303030u),
+                          (ql.z & 0x0f0f0f0fu) | ((qh.z << 2) & 0x30303030u), (ql.w & 0x0f0f0f0fu) | ((qh.w << 2) & 0x30303030u));
+          hi = make_uint4(((ql.x >> 4) & 0x0f0f0f0fu) | ((qh.x >> 2) & 0x30303030u), ((ql.y >> 4) & 0x0f0f0f0fu) | ((qh.y >> 2) & 0x30303030u),
+                          ((ql.z >> 4) & 0x0f0f0f0fu) | ((qh.z >> 2) & 0x30303030u), ((ql.w >> 4) & 0x0f0f0f0fu) | ((qh.w >> 2) & 0x30303030u));
+        }
+        const int wsel = jlo >> 2, bsel = jlo & 3;  // scale jlo is byte bsel of word wsel; jlo+4 is the same byte of the next word
+        const int w_lo = wsel == 0 ? scw.x : (wsel == 1 ? scw.y : (wsel == 2 ? scw.z : scw.w));
+        const int w_hi = wsel == 0 ? scw.y : (wsel == 1 ? scw.z : (wsel == 2 ? scw.w : 0));
+        const int slo = (int)(int8_t)(w_lo >> (8 * bsel)), shi = (int)(int8_t)(w_hi >> (8 * bsel));
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const uint8_t *r = rec + b * rec_col_stride;
+          const int4 xlo = *reinterpret_cast<const int4 *>(r + 16 * jlo);
+          const int4 xhi = *reinterpret_cast<const int4 *>(r + 16 * (jlo + 4));
+          int dl = __dp4a((int)lo.x, xlo.x, 0);
+          dl = __dp4a((int)lo.y, xlo.y, dl);
+          dl = __dp4a((int)lo.z, xlo.z, dl);
+          dl = __dp4a((int)lo.w, xlo.w, dl);
+          int dh = __dp4a((int)hi.x, xhi.x, 0);
+          dh = __dp4a((int)hi.y, xhi.y, dh);
+          dh = __dp4a((int)hi.z, xhi.z, dh);
+          dh = __dp4a((int)hi.w, xhi.w, dh);
+          s[b] += slo * dl + shi * dh;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < B; ++b) {
+    const uint8_t *r = rec + b * rec_col_stride;
+    // codes are stored +32: sum_j sc_j * sum (q-32) x = sum_j sc_j*dot_j - 32 * sum_j sc_j * bsum16_j
+    const int4 b0 = *reinterpret_cast<const int4 *>(r + kRecBsum16), b1 = *reinterpret_cast<const int4 *>(r + kRecBsum16 + 16);
+    int corr = __dp2a_lo(b0.x, scw.x, 0);
+    corr = __dp2a_hi(b0.y, scw.x, corr);
+    corr = __dp2a_lo(b0.z, scw.y, corr);
+    corr = __dp2a_hi(b0.w, scw.y, corr);
+    corr = __dp2a_lo(b1.x, scw.z, corr);
+    corr = __dp2a_hi(b1.y, scw.z, corr);
+    corr = __dp2a_lo(b1.z, scw.w, corr);
+    corr = __dp2a_hi(b1.w, scw.w, corr);
+    const float xd = *reinterpret_cast<const float *>(r + kRecD);
+    acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn(dw, xd), (float)(s[b] - 32 * corr)));
+  }
+}
+
+// Sum of v over each group of `len` consecutive lanes (groups start at multiples of len); the
+// result is valid in the first lane of each group.  Fixed order, so deterministic.
+__device__ __forceinline__ float segment_sum(float v, int lane_in_seg, int len) {
+  int cur = len;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    if (off < cur) {
+      const float t = __shfl_down_sync(0xffffffffu, v, off);
+      if (lane_in_seg + off < cur) v += t;
+      cur = off;
+    }
+  }
+  return v;
+}
+
+// ---------------------------------------------------------------- the kernel
+
+template <int B>
+__global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+  uint64_t *empty = full + kPipeMaxStages;
+  uint8_t *act_k = smem + a.off_act_k;
+  uint8_t *act_0 = smem + a.off_act_0;
+  float *red = reinterpret_cast<float *>(smem + a.off_red);
+  uint8_t *ring = smem + a.off_ring;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = a.n_stages;
+  const int n_my = (int)blockIdx.x < a.total_tiles ? (a.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kPipeConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // Let the next kernel of the stream get scheduled as early as the hardware allows; it blocks in
+  // its own griddepcontrol.wait until this grid has completed.
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  if (warp == kPipeConsumerWarps) {
+    // ---------------- producer: weights do not depend on the previous kernel, so no wait here
+    if (lane == 0) {
+      for (int i = 0; i < n_my; ++i) {
+        const int s = i % S;
+        if (i >= S) mbar_wait(&empty[s], (uint32_t)((i / S - 1) & 1), a.status);
+        const int t = (int)blockIdx.x + i * (int)gridDim.x;
+        int j = 0;
+        if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+        if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+        const PipeJob &J = a.job[j];
+        const int row0 = (t - J.first_tile) * J.tile_rows;
+        const int nrows = min(J.tile_rows, J.rows - row0);
+        const uint32_t bytes = (uint32_t)(nrows * J.stride);
+        mbar_expect_tx(&full[s], bytes);
+        bulk_g2s(ring + (int64_t)s * a.stage_bytes, J.w + (int64_t)row0 * J.stride, bytes, &full[s]);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // inputs written by the previous kernel are now visible
+  const int nsb = a.cols >> 8;
+  const int rec_col_stride = nsb * kActRec;
+  const int act0_col_stride = (int)round_up16(a.cols) + (int)round_up16((a.cols >> 5) * 4);
+
+  // Prologue: quantised activation rows into shared memory.
+  for (int b = 0; b < a.batch; ++b) {
+    if (a.mode == 0) {
+      // re-lay the pre-quantised global rows
+      const int64_t astride = act_row_stride(a.cols);
+      if (a.need_k) {
+        const uint8_t *src = a.act_in + b * astride;
+        for (int i = tid; i < nsb * 16; i += kPipeConsumers) {  // 16-byte chunks of codes
+          const int sb = i >> 4, c = i & 15;
+          *reinterpret_cast<uint4 *>(act_k + b * rec_col_stride + sb * kActRec + c * 16) =
+              __ldg(reinterpret_cast<const uint4 *>(src + sb * 256 + c * 16));
+        }
+        for (int i = tid; i < nsb * 8; i += kPipeConsumers) {  // pairs of 16-sums
+          const int sb = i >> 3, g = i & 7;
+          const int pr = __ldg(reinterpret_cast<const int *>(src + act_bsum_off(a.cols)) + i);
+          uint8_t *rec = act_k + b * rec_col_stride + sb * kActRec;
+          reinterpret_cast<int *>(rec + kRecBsum16)[g] = pr;
+          reinterpret_cast<short *>(rec + kRecBsum32)[g] = (short)((int)(short)(pr & 0xffff) + (pr >> 16));
+        }
+        for (int sb = tid; sb < nsb; sb += kPipeConsumers)
+          *reinterpret_cast<float *>(act_k + b * rec_col_stride + sb * kActRec + kRecD) =
+              __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + sb);
+      }
+      if (a.need_0) {
+        const uint8_t *src = a.act_in0 + b * astride;
+        for (int i = tid; i < (a.cols >> 4); i += kPipeConsumers)
+          *reinterpret_cast<uint4 *>(act_0 + b * act0_col_stride + i * 16) = __ldg(reinterpret_cast<const uint4 *>(src) + i);
+        for (int i = tid; i < (a.cols >> 5); i += kPipeConsumers)
+          reinterpret_cast<float *>(act_0 + b * act0_col_stride + round_up16(a.cols))[i] =
+              __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + i);
+      }
+      continue;
+    }
+    const float *x = a.x + (int64_t)b * a.x_stride;
+    const float *x2 = a.mode == 3 ? a.x2 + (int64_t)b * a.x_stride : nullptr;
+    float scale = 1.0f;
+    if (a.mode == 1) {
+      float ss = 0.0f;
+      for (int i = tid; i < a.cols; i += kPipeConsumers) {
+        const float v = __ldcg(x + i);
+        ss = __fmaf_rn(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+      float t = lane < kPipeConsumerWarps ? red[lane] : 0.0f;
+      t = warp_sum(t);
+      scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+    }
+    const int n_chunks = (a.cols + 255) >> 8;
+    for (int ch = warp; ch < n_chunks; ch += kPipeConsumerWarps) {
+      const int e0 = ch * 256 + lane * 8;
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = e0 + i;
+        float t = 0.0f;
+        if (e < a.cols) {
+          if (a.mode == 1) t = __fmul_rn(__fmul_rn(__ldcg(x + e), scale), __ldg(a.norm_w + e));
+          else if (a.mode == 3) t = swiglu(__ldcg(x + e), __ldcg(x2 + e));
+          else t = __ldcg(x + e);
+          if (a.norm_out && blockIdx.x == 0) a.norm_out[(int64_t)b * a.cols + e] = t;
+        }
+        v[i] = t;
+      }
+      if (a.need_k) {
+        int q[8];
+        float d;
+        q8k_quantise_chunk(v, lane, q, d);
+        uint8_t *rec = act_k + b * rec_col_stride + ch * kActRec;
+        *reinterpret_cast<uint2 *>(rec + lane * 8) = pack8(q);
+        int s16 = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
+        s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+        if ((lane & 1) == 0) reinterpret_cast<short *>(rec + kRecBsum16)[lane >> 1] = (short)s16;
+        if ((lane & 3) == 0) reinterpret_cast<short *>(rec + kRecBsum32)[lane >> 2] = (short)s32;
+        if (lane == 0) *reinterpret_cast<float *>(rec + kRecD) = d;
+      }
+      if (a.need_0) {
+        int q[8];
+        float sc;
+        q80_quantise_chunk(v, q, sc);
+        if (e0 < a.cols) {
+          *reinterpret_cast<uint2 *>(act_0 + b * act0_col_stride + e0) = pack8(q);
+          if ((lane & 3) == 0) reinterpret_cast<float *>(act_0 + b * act0_col_stride + round_up16(a.cols))[e0 >> 5] = sc;
+        }
+      }
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+
+  // Main loop over this CTA's tiles.
+  for (int i = 0; i < n_my; ++i) {
+    const int s = i % S;
+    const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+    const int t = (int)blockIdx.x + i * (int)gridDim.x;
+    int j = 0;
+    if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+    if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+    const PipeJob &J = a.job[j];
+    const int row0 = (t - J.first_tile) * J.tile_rows;
+    const int nrows = min(J.tile_rows, J.rows - row0);
+    const uint8_t *tile = ring + (int64_t)s * a.stage_bytes;
+    if (ready) {
+      const int n_it = J.qt == CMLD_Q8_0 ? (a.cols >> 5) : nsb;  // work items per row: blocks or superblocks
+      const int L = n_it < 32 ? n_it : 32;                        // lanes per row
+      const int rpw = 32 / L;                                     // rows per warp
+      const int r_local = warp * rpw + lane / L, lis = lane % L;
+      const bool active = lane < rpw * L && r_local < nrows;
+      float acc[B];
+#pragma unroll
+      for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+      if (active) {
+        const uint8_t *row = tile + (int64_t)r_local * J.stride;
+        if (J.qt == CMLD_Q4_K) {
+          for (int sb = lis; sb < nsb; sb += L) sb_dot_q4k<B>(row + sb * 144, act_k + sb * kActRec, rec_col_stride, acc);
+        } else if (J.qt == CMLD_Q6_K) {
+          for (int sb = lis; sb < nsb; sb += L) {
+            const float dw = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + nsb * 208 + 2 * sb));
+            sb_dot_q6k<B>(row + sb * 208, dw, act_k + sb * kActRec, rec_col_stride, acc);
+          }
+        } else {
+          // Q8_0: a lane owns 32-value blocks; the two 16-byte halves are read in an order that
+          // keeps the eight lanes of a shared-memory phase on distinct banks
+          const int hs = (lane >> 2) & 1;
+          for (int blk = lis; blk < n_it; blk += L) {
+            const uint4 w0 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * hs);
+            const uint4 w1 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * (hs ^ 1));
+            const float ws = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + a.cols + 2 * blk));
+#pragma unroll
+            for (int b = 0; b < B; ++b) {
+              const uint8_t *xa = act_0 + b * act0_col_stride;
+              const int4 x0 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * hs);
+              const int4 x1 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * (hs ^ 1));
+              int isum = __dp4a((int)w0.x, x0.x, 0);
+              isum = __dp4a((int)w0.y, x0.y, isum);
+              isum = __dp4a((int)w0.z, x0.z, isum);
+              isum = __dp4a((int)w0.w, x0.w, isum);
+              isum = __dp4a((int)w1.x, x1.x, isum);
+              isum = __dp4a((int)w1.y, x1.y, isum);
+              isum = __dp4a((int)w1.z, x1.z, isum);
+              isum = __dp4a((int)w1.w, x1.w, isum);
+              const float xs = reinterpret_cast<const float *>(xa + round_up16(a.cols))[blk];
+              acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn((float)isum, ws), xs));  // src/inference.rs:26198
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const float v = segment_sum(acc[b], lis, L);
+        if (active && lis == 0) {
+          const int64_t o = (int64_t)b * J.y_stride + row0 + r_local;
+          J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), v) : v;
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+
+struct PipePlan {
+  PipeArgs args;
+  int smem_bytes;
+};
+
+static int g_sm_count = 0;
+static bool g_attr_set[9] = {false};
+
+template <int B>
+static int32_t launch_pipe_b(const PipePlan &p, int grid, cudaStream_t s, bool pdl) {
+  if (!g_attr_set[B]) {
+    CMLD_CUDA(cudaFuncSetAttribute(gemv_pipe_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    g_attr_set[B] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kPipeThreads);
+  cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CMLD_CUDA(cudaLaunchKernelEx(&cfg, gemv_pipe_kernel<B>, p.args));
+  return CMLD_OK;
+}
+
+// Tile geometry and shared-memory map for these matrices at this batch; false if it does not fit.
+static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &p, bool &need_k, bool &need_0, int &tiles_out) {
+  if (n_jobs < 1 || n_jobs > 3 || batch < 1 || batch > 8) return false;
+  const int64_t cols = jobs[0].cols;
+  if (cols % 32) return false;
+  PipeArgs &a = p.args;
+  need_k = need_0 = false;
+  int stage = 0, tiles = 0;
+  for (int k = 0; k < n_jobs; ++k) {
+    const GemvJob &g = jobs[k];
+    if (g.cols != cols) return false;
+    if (g.qt == CMLD_Q8_0) need_0 = true;
+    else {
+      need_k = true;
+      if (cols % 256) return false;
+    }
+    const int n_it = g.qt == CMLD_Q8_0 ? (int)(cols >> 5) : (int)(cols >> 8);
+    const int L = n_it < 32 ? n_it : 32;
+    PipeJob &J = a.job[k];
+    J.w = g.w;
+    J.qt = g.qt;
+    J.rows = (int32_t)g.rows;
+    J.tile_rows = kPipeConsumerWarps * (32 / L);
+    J.stride = g.stride;
+    J.y = g.y;
+    J.residual = g.residual;
+    J.y_stride = g.y_stride;
+    J.first_tile = tiles;
+    J.n_tiles = (int)((g.rows + J.tile_rows - 1) / J.tile_rows);
+    tiles += J.n_tiles;
+    stage = std::max<int>(stage, (int)(J.tile_rows * g.stride));
+    if (g.stride % 16 || (reinterpret_cast<uintptr_t>(g.w) & 15)) return false;
+  }
+  stage = (stage + 127) & ~127;
+  const int nsb = (int)(cols >> 8);
+  int off = 2 * kPipeMaxStages * 8;
+  a.off_act_k = off;
+  if (need_k) off += batch * nsb * kActRec;
+  off = (off + 15) & ~15;
+  a.off_act_0 = off;
+  if (need_0) off += batch * ((int)round_up16(cols) + (int)round_up16((cols >> 5) * 4));
+  a.off_red = off;
+  off += 64 * 4;
+  off = (off + 127) & ~127;
+  a.off_ring = off;
+  // Prefer a footprint that lets two kernels share an SM (the next one prefetches under PDL).
+  int n_stages = 0;
+  for (int budget : {110 * 1024, 224 * 1024}) {
+    n_stages = std::min<int>(kPipeMaxStages, (budget - off) / stage);
+    if (n_stages >= 3) break;
+  }
+  if (n_stages < 2) return false;
+  p.smem_bytes = off + n_stages * stage;
+  a.stage_bytes = stage;
+  a.n_stages = n_stages;
+  tiles_out = tiles;
+  return true;
+}
+
+int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs) {
+  for (int b = 8; b >= 1; --b) {
+    PipePlan p{};
+    bool nk, n0;
+    int tiles;
+    if (plan_pipe(jobs, n_jobs, b, p, nk, n0, tiles)) return b;
+  }
+  return 0;
+}
+
+// Plans and launches the staged kernel.  Returns CMLD_ERR_UNSUPPORTED (without setting an error
+// message the caller would see) when the shape does not fit; the caller then uses the
+// direct-load kernel.
+int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
+                         cudaStream_t s, bool pdl) {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    CMLD_CUDA(cudaGetDevice(&dev));
+    CMLD_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  PipePlan p{};
+  PipeArgs &a = p.args;
+  bool need_k = false, need_0 = false;
+  int tiles = 0;
+  if (!plan_pipe(jobs, n_jobs, batch, p, need_k, need_0, tiles)) return CMLD_ERR_UNSUPPORTED;
+  const int64_t cols = jobs[0].cols;
+  a.n_jobs = n_jobs;
+  a.total_tiles = tiles;
+  a.cols = (int32_t)cols;
+  a.batch = batch;
+  a.mode = pro.mode;
+  a.x = pro.x;
+  a.x2 = pro.x2;
+  a.norm_w = pro.norm_w;
+  a.x_stride = pro.x_stride;
+  a.eps = pro.eps;
+  a.act_in = pro.act_k;
+  a.act_in0 = pro.act_0;
+  a.need_k = need_k;
+  a.need_0 = need_0;
+  a.norm_out = pro.norm_out;
+  a.status = status;
+  if (a.mode == 0 && ((need_k && !a.act_in) || (need_0 && !a.act_in0))) return fail(CMLD_ERR_INVALID, "gemv: activation buffer missing");
+  const int grid = std::min(tiles, g_sm_count);
+  switch (batch) {
+    case 1: return launch_pipe_b<1>(p, grid, s, pdl);
+    case 2: return launch_pipe_b<2>(p, grid, s, pdl);
+    case 3: return launch_pipe_b<3>(p, grid, s, pdl);
+    case 4: return launch_pipe_b<4>(p, grid, s, pdl);
+    case 5: return launch_pipe_b<5>(p, grid, s, pdl);
+    case 6: return launch_pipe_b<6>(p, grid, s, pdl);
+    case 7: return launch_pipe_b<7>(p, grid, s, pdl);
+    default: return launch_pipe_b<8>(p, grid, s, pdl);
+  }
+}
+
+}  // namespace cmld

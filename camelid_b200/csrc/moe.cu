@@ -147,14 +147,15 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_gemv_kernel(MoeGemvArgs a)
       const int sb = u >> 3, t = u & 7;
       uint4 wq[kMoeRows];
 #pragma unroll
-      for (int r = 0; r < kMoeRows; ++r) wq[r] = ld_stream16(row[r] + (int64_t)u * 16);
+      for (int r = 0; r < kMoeRows; ++r)
+        wq[r] = ld_stream16(row[r] + (QT == CMLD_Q4_K ? (int64_t)sb * 144 + 16 + t * 16 : (int64_t)sb * 208 + t * 16));
       if (QT == CMLD_Q4_K) {
         const int j = t >> 1, h = t & 1;
         const int xo = sb * 256 + 64 * j + 16 * h;
         float dl[kMoeRows], dh[kMoeRows], ml[kMoeRows], mh[kMoeRows];
 #pragma unroll
         for (int r = 0; r < kMoeRows; ++r) {
-          const uint4 meta = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)nsb * 128) + sb);
+          const uint4 meta = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)sb * 144));
           const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
           int s0, m0, s1, m1;
           q4k_scale_min(2 * j, meta.y, meta.z, meta.w, s0, m0);
@@ -210,9 +211,9 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_gemv_kernel(MoeGemvArgs a)
         uint4 qh4[kMoeRows];
 #pragma unroll
         for (int r = 0; r < kMoeRows; ++r) {
-          qh4[r] = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)nsb * 128 + sb * 64 + 32 * h + 16 * cc));
+          qh4[r] = __ldg(reinterpret_cast<const uint4 *>(row[r] + (int64_t)sb * 208 + 128 + 32 * h + 16 * cc));
           const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row[r] + (int64_t)nsb * 208) + sb));
-          const int8_t *sc = reinterpret_cast<const int8_t *>(row[r] + (int64_t)nsb * 192 + sb * 16);
+          const int8_t *sc = reinterpret_cast<const int8_t *>(row[r] + (int64_t)sb * 208 + 192);
           dl[r] = __fmul_rn(d, (float)__ldg(sc + jlo));
           dh[r] = __fmul_rn(d, (float)__ldg(sc + jlo + 4));
         }

@@ -14,7 +14,7 @@ namespace cmld {
 //        its sign, iscale = -127/max, q = min(127, rne(iscale*v)), d = 1/iscale;
 //   Q8_0 (quantize_q8_0_block, src/inference.rs:22510-22528): d = amax/127 kept as its f16
 //        rounding, q = round-half-away(v * (1/d_unrounded)) clamped to [-128,127].
-constexpr int kNormThreads = 512;
+constexpr int kNormThreads = 256;  // same thread count and summation tree as the staged matvec's fused prologue
 
 template <int MODE>  // 0 plain, 1 rmsnorm, 2 swiglu
 __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs a) {

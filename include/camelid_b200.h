@@ -73,7 +73,9 @@ typedef struct {
   int32_t flags;            /* CMLD_FLAG_* */
 } cmld_config;
 
-#define CMLD_FLAG_NO_GRAPH 1u   /* launch kernels directly instead of replaying a CUDA graph */
+#define CMLD_FLAG_NO_GRAPH 1u     /* launch kernels directly instead of replaying a CUDA graph */
+#define CMLD_FLAG_DIRECT_GEMV 2u  /* use the direct-load matvec kernel everywhere (no staged kernel) */
+#define CMLD_FLAG_NO_PDL 4u       /* no programmatic dependent launch between kernels */
 
 typedef struct cmld_engine cmld_engine;
 typedef struct cmld_weight cmld_weight;
@@ -223,6 +225,17 @@ CMLD_API int32_t cmld_act_export(int32_t act_kind, const void *act_dev, int64_t 
  * src/inference.rs:26166, src/diffusion_gemma/refmath.rs:504, src/inference.rs:25535). */
 CMLD_API int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, float *y_dev,
                            const float *residual_dev);
+/* Which matvec kernel cmld_gemv / cmld_gemv_time use: bit 0 clear = the staged (bulk-copy
+ * pipelined) kernel whenever it takes the shape, bit 0 set = the direct-load kernel only; bit 1
+ * set = cmld_gemv_time chains its launches with programmatic dependent launch.  Process-wide;
+ * for A/B runs. */
+CMLD_API int32_t cmld_gemv_select_kernel(int32_t choice);
+/* The staged kernel with its fused prologue: y = W . quantise(f(x)) (+ residual), with
+ * f = RMSNorm(x) * norm_w (mode 1), x (mode 2) or SwiGLU(x, x2) (mode 3); x_dev/x2_dev are f32
+ * [batch][cols], batch <= 8.  One launch replaces norm/activation kernel + quantiser + matvec. */
+CMLD_API int32_t cmld_gemv_fused(const cmld_weight *w, int32_t mode, const float *x_dev, const float *x2_dev,
+                                 const float *norm_w_dev, float eps, int32_t batch, float *y_dev,
+                                 const float *residual_dev);
 /* RMSNorm (rms_norm_into, src/tensor/mod.rs:2707): out_dev and/or act_dev may be NULL. */
 CMLD_API int32_t cmld_rms_norm(const float *x_dev, const float *w_dev, int64_t cols, int32_t batch, float eps,
                                float *out_dev, int32_t act_kind, void *act_dev);
@@ -237,9 +250,10 @@ CMLD_API int32_t cmld_argmax(const float *x_dev, int64_t n, int32_t batch, uint3
 CMLD_API int32_t cmld_attention_decode(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev,
                                        int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int64_t max_pos,
                                        int64_t n_pos, float scale, float *out_dev);
-/* Time `iters` back-to-back launches of cmld_gemv with CUDA events; the weights are
- * `n_copies` distinct matrices visited round-robin so that the stream comes from HBM when
- * their total exceeds the L2.  Returns the mean milliseconds per launch. */
+/* Time `iters` back-to-back launches of cmld_gemv with CUDA events around one CUDA-graph replay of
+ * them (so the host's enqueue rate is not measured); the weights are `n_copies` distinct matrices
+ * visited round-robin so that the stream comes from HBM when their total exceeds the L2.
+ * Returns the mean milliseconds per launch. */
 CMLD_API int32_t cmld_gemv_time(cmld_weight *const *copies, int32_t n_copies, const void *act_dev, int32_t batch,
                                 float *y_dev, int32_t warmup, int32_t iters, float *ms_per_launch_out);
 

@@ -183,6 +183,27 @@ def test_error_paths_do_not_touch_the_device(pair, cm):
     assert ei.value.code == 3  # Q4_0 is outside the path
 
 
+def test_direct_and_staged_matvec_paths_agree(cm, orc):
+    """The engine built with CMLD_FLAG_DIRECT_GEMV (separate quantise kernels + direct-load matvec)
+    and the default engine (staged matvec with fused prologues) see the same quantised codes; their
+    logits agree to f32 reassociation and their greedy tokens are equal."""
+    from camelid_b200 import synth
+
+    for mix in ("q8_0", "q4_k_m"):
+        cfg = synth.engine_config("tiny", max_pos=64)
+        a = ModelPair(cfg, mix, seed=9)
+        b = ModelPair(synth.engine_config("tiny", max_pos=64, flags=2), mix, seed=9)
+        prompt = orc.synth_tokens(8, 1, 8, cfg.vocab)
+        fa, fb = a.engine.prefill_tokens(0, prompt, 0), b.engine.prefill_tokens(0, prompt, 0)
+        _, la, _ = a.engine.step_batch([0], [fa], [8], want_logits=True)
+        _, lb, _ = b.engine.step_batch([0], [fb], [8], want_logits=True)
+        assert fa == fb
+        assert np.abs(la - lb).max() < 1e-4 * np.abs(la).max()
+        _, launches_a = a.engine.last_timing()
+        _, launches_b = b.engine.last_timing()
+        assert launches_a < launches_b  # fused prologues: fewer kernels per step
+
+
 def test_wire_upload_path_equals_device_generated(cm, orc):
     from camelid_b200 import synth
 

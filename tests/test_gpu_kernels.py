@@ -109,9 +109,12 @@ def test_activation_quantisers_bit_exact(cm, orc, cols, batch):
     ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 3072), ("Q4_K", 64, 14336),
     ("Q6_K", 33, 256), ("Q6_K", 512, 4096), ("Q6_K", 130, 3072), ("Q6_K", 64, 14336)])
 @pytest.mark.parametrize("batch", [1, 4, 8])
-def test_gemv_matches_checker(cm, orc, name, rows, cols, batch):
+@pytest.mark.parametrize("kernel", ["staged", "direct"])
+def test_gemv_matches_checker(cm, orc, name, rows, cols, batch, kernel):
     from camelid_b200.engine import quantize_activation, export_activation, DeviceBuffer
+    from camelid_b200._lib import check
 
+    check(cm.lib().cmld_gemv_select_kernel(1 if kernel == "direct" else 0))
     qt = QT[name]
     wire = orc.synth_tensor(qt, 11, rows * 7 + cols, rows, cols, 0.02)
     w = cm.Weight.from_wire(qt, rows, cols, wire)
@@ -136,6 +139,40 @@ def test_gemv_matches_checker(cm, orc, name, rows, cols, batch):
     # batched columns are bitwise the single-column results
     y1 = w.gemv(quantize_activation(kind, x[:1]), 1)
     assert np.array_equal(y1[0], y[0])
+    check(cm.lib().cmld_gemv_select_kernel(0))
+
+
+# The staged kernel's fused prologues: RMSNorm / plain / SwiGLU + quantiser + matvec in one launch
+# equals the three separate steps (same quantised codes, so the same result bit for bit).
+@pytest.mark.parametrize("name,rows,cols", [("Q8_0", 200, 2048), ("Q4_K", 200, 4096), ("Q6_K", 200, 4096), ("Q4_K", 72, 14336),
+                                            ("Q6_K", 100, 3072)])
+@pytest.mark.parametrize("mode", [1, 2, 3])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_fused_prologue_equals_separate_steps(cm, orc, name, rows, cols, mode, batch):
+    from camelid_b200.engine import quantize_activation, DeviceBuffer
+    from camelid_b200._lib import check
+
+    qt = QT[name]
+    w = cm.Weight.from_wire(qt, rows, cols, orc.synth_tensor(qt, 3, cols + rows, rows, cols, 0.02))
+    rng = np.random.default_rng(cols + mode)
+    x = rng.standard_normal((batch, cols)).astype(np.float32) * 1.5
+    x2 = rng.standard_normal((batch, cols)).astype(np.float32)
+    nw = (1.0 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    res = rng.standard_normal((batch, rows)).astype(np.float32)
+    xd, x2d, nwd, resd = (DeviceBuffer.from_numpy(a) for a in (x, x2, nw, res))
+    y = DeviceBuffer(batch * rows * 4)
+    check(cm.lib().cmld_gemv_fused(w._h, mode, xd.ptr, x2d.ptr, nwd.ptr, 1e-5, batch, y.ptr, resd.ptr))
+    got = y.to_numpy(np.float32).reshape(batch, rows)
+    # separate steps on the device: f(x) as f32, then quantise, then matvec + residual
+    fx = DeviceBuffer(x.nbytes)
+    if mode == 1:
+        check(cm.lib().cmld_rms_norm(xd.ptr, nwd.ptr, cols, batch, 1e-5, fx.ptr, 0, None))
+    elif mode == 3:
+        check(cm.lib().cmld_silu_mul(xd.ptr, x2d.ptr, cols, batch, fx.ptr, 0, None))
+    f = fx.to_numpy(np.float32).reshape(batch, cols) if mode != 2 else x
+    act = quantize_activation(cm.ACT_Q8_0 if qt == 8 else cm.ACT_Q8_K, f)
+    want = w.gemv(act, batch, resd)
+    assert np.array_equal(got, want)
 
 
 def test_gemv_end_to_end_against_f32_activation_path(cm, orc):
