@@ -4,6 +4,8 @@
 // same argument meaning, errors as status codes instead of Result<_, String>.
 #include <cmath>
 #include <string>
+#include <map>
+#include <tuple>
 #include <vector>
 
 #include "common.cuh"
@@ -138,6 +140,15 @@ struct cmld_engine {
   float last_ms = 0.0f;
   int64_t last_launches = 0, launches = 0;
   std::vector<void *> allocs;
+  // CUDA graphs of whole steps, keyed by (rows, option bits, score-scale bits).  A key's first
+  // step runs as plain launches (it also sets kernel attributes); its second is captured.
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    int64_t launches = 0;
+    int uses = 0;
+  };
+  std::map<std::tuple<int32_t, uint32_t, uint32_t>, StepGraph> graphs;
+  bool graphs_off = false;
 };
 
 namespace cmld {
@@ -274,6 +285,8 @@ static int32_t engine_init(cmld_engine *e) {
 }
 
 static void engine_free(cmld_engine *e) {
+  for (auto &kv : e->graphs)
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
   for (auto &L : e->layers) {
     for (auto &w : L.proj) weight_free(w);
     for (auto &w : L.exps) weight_free(w);
@@ -529,6 +542,48 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   return CMLD_OK;
 }
 
+// A step through a CUDA graph when possible: one graph launch replaces ~200 kernel launches, and
+// the programmatic-dependent-launch edges between the matvec kernels are kept inside the graph.
+static int32_t run_step(cmld_engine *e, const StepOpts &o) {
+  if ((e->cfg.flags & CMLD_FLAG_NO_GRAPH) || e->graphs_off) return engine_step(e, o);
+  uint32_t bits = (o.from_tokens ? 1u : 0u) | (o.rope_by_position ? 2u : 0u) | (o.logits ? 4u : 0u) | (o.argmax ? 8u : 0u) |
+                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u);
+  uint32_t scale_bits;
+  memcpy(&scale_bits, &o.scale, 4);
+  auto &g = e->graphs[std::make_tuple(o.batch, bits, scale_bits)];
+  if (g.exec) {
+    CMLD_CUDA(cudaGraphLaunch(g.exec, e->stream));
+    e->launches += g.launches;
+    return CMLD_OK;
+  }
+  if (g.uses++ == 0) return engine_step(e, o);
+  const int64_t before = e->launches;
+  if (cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();
+    e->graphs_off = true;
+    return engine_step(e, o);
+  }
+  const int32_t rc = engine_step(e, o);
+  cudaGraph_t graph = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(e->stream, &graph);
+  const int64_t n = e->launches - before;
+  e->launches = before;
+  if (rc == CMLD_OK && ce == cudaSuccess && graph && cudaGraphInstantiate(&g.exec, graph, 0) == cudaSuccess) {
+    cudaGraphDestroy(graph);
+    g.launches = n;
+    CMLD_CUDA(cudaGraphLaunch(g.exec, e->stream));
+    e->launches += n;
+    return CMLD_OK;
+  }
+  // capture or instantiation failed: nothing ran; keep to plain launches from now on
+  if (graph) cudaGraphDestroy(graph);
+  cudaGetLastError();
+  g.exec = nullptr;
+  e->graphs_off = true;
+  if (rc != CMLD_OK) return rc;
+  return engine_step(e, o);
+}
+
 static int32_t require_weights(const cmld_engine *e, bool need_output) {
   for (size_t i = 0; i < e->layers.size(); ++i) {
     const LayerW &L = e->layers[i];
@@ -583,7 +638,7 @@ static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, c
   o.logits = logits;
   o.argmax = argmax;
   o.taps = taps;
-  return engine_step(e, o);
+  return run_step(e, o);
 }
 
 }  // namespace cmld
@@ -981,7 +1036,7 @@ int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *se
   o.batch = n_seqs;
   o.from_tokens = true;
   o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
-  CMLD_TRY(engine_step(e, o));
+  CMLD_TRY(run_step(e, o));
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> toks(n_seqs);
   CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -1016,7 +1071,7 @@ int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *t
     o.from_tokens = true;
     o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
     o.logits = o.argmax = (i + chunk >= n);
-    CMLD_TRY(engine_step(e, o));
+    CMLD_TRY(run_step(e, o));
     last_rows = rows;
   }
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
@@ -1046,7 +1101,7 @@ int32_t cmld_engine_decode_greedy(cmld_engine *e, int32_t n_seqs, const int32_t 
   o.from_tokens = true;
   o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
   o.feed_back = true;
-  for (int s = 0; s < n_steps; ++s) CMLD_TRY(engine_step(e, o));
+  for (int s = 0; s < n_steps; ++s) CMLD_TRY(run_step(e, o));
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> hist((size_t)n_steps * n_seqs);
   CMLD_CUDA(cudaMemcpyAsync(hist.data(), e->d_history, hist.size() * 4, cudaMemcpyDeviceToHost, e->stream));
