@@ -223,3 +223,85 @@ int32_t launch_attention(const AttnArgs &a, cudaStream_t s) {
 }
 
 }  // namespace cmld
+
+// ====================================================================== allocation-free entry point
+//
+// Some hosts must not allocate device memory at the moment they need attention: a serving loop
+// that has handed the whole device to a memory pool, a caller running under a "no allocator
+// calls" rule on its latency path, or an embedder whose CUDA binding exposes launches and copies
+// but no allocator.  cmld_attention_decode() makes a cudaMalloc/cudaFree pair per call for its
+// split-range partials; this variant keeps those partials in a fixed array that is part of the
+// library image, so it makes no allocator call at all.
+//
+// The price: the array exists once per device (every GPU that loads the library carries it until
+// the process exits), problem sizes are capped, and every call uses the same bytes — two calls
+// that overlap on the GPU (different streams or host threads) would corrupt each other.
+
+namespace {
+
+constexpr int kNoAllocMaxHeads = 64;
+constexpr int kNoAllocMaxHeadDim = 128;
+constexpr int kNoAllocSplits = 37;
+constexpr size_t kNoAllocPartBytes = (size_t)kNoAllocMaxHeads * kNoAllocSplits * (kNoAllocMaxHeadDim + 2) * sizeof(float);
+constexpr size_t kNoAllocTicketOff = kNoAllocPartBytes;                      // kNoAllocMaxHeads counters
+constexpr size_t kNoAllocPosOff = kNoAllocTicketOff + kNoAllocMaxHeads * 4;  // position, slot
+constexpr size_t kNoAllocBytes = kNoAllocPosOff + 16;                        // about 1.2 MiB
+
+// Device storage.  In host code this name is only a handle for cudaGetSymbolAddress; it is never
+// passed to a kernel directly.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+unsigned char *g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+
+}  // namespace
+
+extern "C" int32_t cmld_attention_decode_noalloc(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                                 int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int64_t max_pos,
+                                                 int64_t n_pos, float scale, float *out_dev) {
+  using namespace cmld;
+  if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  if (n_heads < 1 || n_kv_heads < 1 || n_heads > kNoAllocMaxHeads || head_dim > kNoAllocMaxHeadDim)
+    return fail(CMLD_ERR_SHAPE, "attention_decode_noalloc takes at most %d query heads of head_dim <= %d (got %d x %d); "
+                "use cmld_attention_decode for larger problems", kNoAllocMaxHeads, kNoAllocMaxHeadDim, n_heads, head_dim);
+  if (n_pos < 1 || n_pos > max_pos) return fail(CMLD_ERR_INVALID, "n_pos %lld out of range", (long long)n_pos);
+  int dev = 0;
+  CMLD_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(CMLD_ERR_INVALID, "device ordinal %d not supported", dev);
+  if (!g_noalloc_ptr[dev]) {
+    // One-time set-up on this device (it is the current one): turn the symbol into a device address.
+    unsigned char *p = nullptr;
+    CMLD_CUDA(cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_noalloc_scratch));
+    if (!p) return fail(CMLD_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_ptr[dev] = p;
+  }
+  unsigned char *scratch = g_noalloc_ptr[dev];
+  // same split count as cmld_attention_decode, so the two give identical bits
+  const int n_splits = (int)std::max<int64_t>(1, std::min<int64_t>(kNoAllocSplits, max_pos / 32));
+  // The array keeps whatever the last call left: the arrival counters must start at zero.
+  CMLD_CUDA(cudaMemsetAsync(scratch + kNoAllocTicketOff, 0, kNoAllocMaxHeads * 4, nullptr));
+  const int32_t ps[2] = {(int32_t)(n_pos - 1), 0};
+  CMLD_CUDA(cudaMemcpyAsync(scratch + kNoAllocPosOff, ps, 8, cudaMemcpyHostToDevice, nullptr));
+  AttnArgs a{};
+  a.q = q_dev;
+  a.k_cache = static_cast<const __half *>(k_cache_dev);
+  a.v_cache = static_cast<const __half *>(v_cache_dev);
+  a.positions = reinterpret_cast<const int32_t *>(scratch + kNoAllocPosOff);
+  a.slots = a.positions + 1;
+  a.n_heads = n_heads;
+  a.n_kv_heads = n_kv_heads;
+  a.head_dim = head_dim;
+  a.batch = 1;
+  a.n_splits = n_splits;
+  a.max_pos = max_pos;
+  a.scale = scale;
+  a.part = reinterpret_cast<float *>(scratch);
+  a.tickets = reinterpret_cast<uint32_t *>(scratch + kNoAllocTicketOff);
+  a.out = out_dev;
+  a.q_stride = (int64_t)n_heads * head_dim;
+  CMLD_TRY(launch_attention(a, nullptr));
+  cudaError_t ce = cudaStreamSynchronize(nullptr);
+  if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "attention_decode_noalloc: %s", cudaGetErrorString(ce));
+  return CMLD_OK;
+}
+

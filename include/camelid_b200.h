@@ -250,6 +250,19 @@ CMLD_API int32_t cmld_argmax(const float *x_dev, int64_t n, int32_t batch, uint3
 CMLD_API int32_t cmld_attention_decode(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev,
                                        int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int64_t max_pos,
                                        int64_t n_pos, float scale, float *out_dev);
+/* cmld_attention_decode without any allocator call (no counterpart in the reference; added for
+ * hosts that cannot call cudaMalloc when they need attention: the device is fully owned by their
+ * own pool, their latency path forbids allocator calls, or their CUDA binding has no allocator).
+ * The split-range partials live in a fixed ~1.2 MiB array inside the library image, present once
+ * on every GPU that loads the library until the process exits.  Limits: n_heads <= 64 and
+ * head_dim <= 128 (anything larger returns CMLD_ERR_SHAPE; use cmld_attention_decode).  The first
+ * call on each device resolves the array's device address; make that call before starting any
+ * stream capture.  All calls share the array: it keeps the previous call's bytes (the counters
+ * that must start at zero are cleared on every call), and two calls that overlap on the GPU
+ * race.  Same arguments and same result bits as cmld_attention_decode. */
+CMLD_API int32_t cmld_attention_decode_noalloc(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                               int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int64_t max_pos,
+                                               int64_t n_pos, float scale, float *out_dev);
 /* Time `iters` back-to-back launches of cmld_gemv with CUDA events around one CUDA-graph replay of
  * them (so the host's enqueue rate is not measured); the weights are `n_copies` distinct matrices
  * visited round-robin so that the stream comes from HBM when their total exceeds the L2.
