@@ -37,15 +37,43 @@ __device__ __forceinline__ void load_halves(const __half *p, float (&out)[PER]) 
   }
 }
 
+constexpr int kMinSplitLen = 64;  // positions per range before another range is opened
+
+// RoPE pair partner and sign: x'[d] = x[d]*c + sgn * x[partner]*s  (src/inference/rope.rs:495-530)
+__device__ __forceinline__ float rope_elem(const float *x, int d, int rope_dim, int split_half, const float *ct, const float *st) {
+  if (d >= rope_dim) return x[d];
+  const int half = rope_dim >> 1;
+  int p, partner;
+  bool first;
+  if (split_half) {
+    first = d < half;
+    p = first ? d : d - half;
+    partner = first ? d + half : d - half;
+  } else {
+    first = (d & 1) == 0;
+    p = d >> 1;
+    partner = first ? d + 1 : d - 1;
+  }
+  const float c = ct[p], sn = st[p];
+  // first of the pair: x0*c - x1*s ; second: x0*s + x1*c
+  return first ? __fsub_rn(__fmul_rn(x[d], c), __fmul_rn(x[partner], sn)) : __fadd_rn(__fmul_rn(x[partner], sn), __fmul_rn(x[d], c));
+}
+
 template <int G, int PER>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   uint32_t *tickets = a.tickets;
   constexpr int HD = PER * 32;
   const int kvh = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int n_pos = a.positions[b] + 1;
+  const int pos = a.positions[b];
+  const int n_pos = pos + 1;
   const int slot = a.slots[b];
-  const int len = (n_pos + a.n_splits - 1) / a.n_splits;
+  // ranges of at least kMinSplitLen positions; CTAs beyond the last range have nothing to do
+  const int len = max((n_pos + a.n_splits - 1) / a.n_splits, kMinSplitLen);
+  const int n_active = (n_pos + len - 1) / len;
+  if (split >= n_active || pos < 0 || pos >= a.max_pos) return;
   const int lo = split * len, hi = min(n_pos, lo + len);
 
   __shared__ float s_q[G][HD];
@@ -54,17 +82,32 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   __shared__ float s_acc[kAttnWarps][G][HD];
   __shared__ bool s_last;
 
+  __half *kbase = const_cast<__half *>(a.k_cache) + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
+  __half *vbase = const_cast<__half *>(a.v_cache) + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
   const float *q = a.q + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
-  for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) s_q[i / HD][i % HD] = q[i];
-  __syncthreads();
+  if (a.fuse_rope) {
+    const int half = a.rope_dim >> 1;
+    const float *ct = a.cos_tab + (int64_t)(a.index_by_position ? pos : b) * half;
+    const float *st = a.sin_tab + (int64_t)(a.index_by_position ? pos : b) * half;
+    for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) s_q[i / HD][i % HD] = rope_elem(q + (i / HD) * HD, i % HD, a.rope_dim, a.split_half, ct, st);
+    if (split == n_active - 1) {
+      // this CTA's range ends at the row's own position: append K (rotated) and V to the cache first
+      const float *kn = a.k_new + (int64_t)b * a.kv_stride + (int64_t)kvh * HD;
+      const float *vn = a.v_new + (int64_t)b * a.kv_stride + (int64_t)kvh * HD;
+      for (int d = threadIdx.x; d < HD; d += kAttnThreads) {
+        kbase[(int64_t)pos * HD + d] = __float2half_rn(rope_elem(kn, d, a.rope_dim, a.split_half, ct, st));
+        vbase[(int64_t)pos * HD + d] = __float2half_rn(vn[d]);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) s_q[i / HD][i % HD] = q[i];
+  }
+  __syncthreads();  // also orders the cache rows written above before this CTA reads them back
   float qr[G][PER];
 #pragma unroll
   for (int g = 0; g < G; ++g)
 #pragma unroll
     for (int e = 0; e < PER; ++e) qr[g][e] = s_q[g][lane * PER + e];
-
-  const __half *kbase = a.k_cache + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
-  const __half *vbase = a.v_cache + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
 
   float m_run[G], l_run[G], acc[G][PER];
 #pragma unroll
@@ -172,40 +215,71 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(&tickets[b * a.n_kv_heads + kvh], 1u) == (unsigned)a.n_splits - 1;
+  if (threadIdx.x == 0) s_last = atomicAdd(&tickets[b * a.n_kv_heads + kvh], 1u) == (unsigned)n_active - 1;
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // merge the ranges: out = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M)
+  // merge the ranges: out = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M).
+  // First the per-(head, range) weights in parallel (s_sc is free now), then one thread per output.
+  float *s_w = &s_sc[0][0];  // [G][n_active] weights, n_active <= 64 <= kAttnChunk
+  for (int i = threadIdx.x; i < G * n_active; i += kAttnThreads) {
+    const int g = i / n_active, s2 = i % n_active;
+    s_w[g * kAttnChunk + s2] = __ldcg(part + ((int64_t)g * a.n_splits + s2) * (HD + 2) + HD);  // m
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int g = threadIdx.x;
+    float M = -INFINITY;
+    for (int s2 = 0; s2 < n_active; ++s2) M = fmaxf(M, s_w[g * kAttnChunk + s2]);
+    s_red[0][g] = M;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * n_active; i += kAttnThreads) {
+    const int g = i / n_active, s2 = i % n_active;
+    const float ms = s_w[g * kAttnChunk + s2];
+    s_w[g * kAttnChunk + s2] = ms == -INFINITY ? 0.0f : expf(ms - s_red[0][g]);
+  }
+  __syncthreads();
   float *out = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
   for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
     const int g = i / HD, d = i % HD;
     const float *pg = part + (int64_t)g * a.n_splits * (HD + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < a.n_splits; ++s) M = fmaxf(M, __ldcg(pg + (int64_t)s * (HD + 2) + HD));
     float L = 0.0f, o = 0.0f;
-    for (int s = 0; s < a.n_splits; ++s) {
-      const float ms = __ldcg(pg + (int64_t)s * (HD + 2) + HD);
-      const float w = ms == -INFINITY ? 0.0f : expf(ms - M);
-      L = __fmaf_rn(__ldcg(pg + (int64_t)s * (HD + 2) + HD + 1), w, L);
-      o = __fmaf_rn(__ldcg(pg + (int64_t)s * (HD + 2) + d), w, o);
+#pragma unroll 4
+    for (int s2 = 0; s2 < n_active; ++s2) {
+      const float w = s_w[g * kAttnChunk + s2];
+      L = __fmaf_rn(__ldcg(pg + (int64_t)s2 * (HD + 2) + HD + 1), w, L);
+      o = __fmaf_rn(__ldcg(pg + (int64_t)s2 * (HD + 2) + d), w, o);
     }
     out[i] = __fdiv_rn(o, L);
   }
   if (threadIdx.x == 0) tickets[b * a.n_kv_heads + kvh] = 0;
 }
 
+template <int G, int PER>
+static int32_t launch_gp(const AttnArgs &a, cudaStream_t s) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)a.n_kv_heads, (unsigned)a.n_splits, (unsigned)a.batch);
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.pdl ? 1 : 0;
+  CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, PER>, a));
+  return CMLD_OK;
+}
+
 template <int G>
 static int32_t launch_g(const AttnArgs &a, cudaStream_t s) {
-  dim3 grid((unsigned)a.n_kv_heads, (unsigned)a.n_splits, (unsigned)a.batch);
+  if (a.n_splits > kAttnChunk) return fail(CMLD_ERR_SHAPE, "attention: more than %d ranges", kAttnChunk);
   switch (a.head_dim) {
-    case 32: attn_decode_kernel<G, 1><<<grid, kAttnThreads, 0, s>>>(a); break;
-    case 64: attn_decode_kernel<G, 2><<<grid, kAttnThreads, 0, s>>>(a); break;
-    case 128: attn_decode_kernel<G, 4><<<grid, kAttnThreads, 0, s>>>(a); break;
+    case 32: return launch_gp<G, 1>(a, s);
+    case 64: return launch_gp<G, 2>(a, s);
+    case 128: return launch_gp<G, 4>(a, s);
     default: return fail(CMLD_ERR_SHAPE, "attention: head_dim %d not in {32,64,128}", a.head_dim);
   }
-  CMLD_CUDA(cudaGetLastError());
-  return CMLD_OK;
 }
 
 // `part` holds [batch][n_heads][n_splits][head_dim+2] floats; `tickets` batch*n_kv_heads

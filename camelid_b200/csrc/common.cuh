@@ -187,6 +187,7 @@ struct NormQuantArgs {
   uint8_t *act;         // quantised result or null
   int32_t act_q8_0, act_q8_k;  // which formats to emit; both allowed: Q8_K at act, Q8_0 at act2
   uint8_t *act2;
+  int32_t pdl;                 // launch with programmatic stream serialisation
 };
 int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s);
 int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx,
@@ -221,6 +222,14 @@ struct AttnArgs {
   uint32_t *tickets;  // [batch][n_kv_heads], zero between launches
   float *out;   // [batch][n_heads*hd]
   int64_t q_stride;
+  // Optional fusion of RoPE and the KV-cache write (fuse_rope != 0): q is rotated on the fly, and
+  // the CTA whose range holds the row's own position rotates k_new, rounds k_new / v_new to f16
+  // and stores them in the cache before using them.
+  int32_t fuse_rope, rope_dim, split_half, index_by_position;
+  const float *k_new, *v_new;      // [batch][n_kv_heads*hd]
+  int64_t kv_stride;
+  const float *cos_tab, *sin_tab;  // [rows][rope_dim/2]
+  int32_t pdl;                     // launch with programmatic stream serialisation
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
 

@@ -358,6 +358,7 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
   a.act_q8_k = need_k;
   a.act = need_k ? e->act_k : e->act_0;
   a.act2 = e->act_0;
+  a.pdl = !(e->cfg.flags & CMLD_FLAG_NO_PDL);
   CMLD_TRY(launch_norm_quant(a, e->stream));
   e->launches += 1;
   return CMLD_OK;
@@ -368,39 +369,47 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
 // of 8 columns).  Shapes it does not take fall back to quantise-kernel + direct-load kernel.
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
                           const float *norm_w, int64_t cols) {
+  bool n0, nk;
+  const Weight *ws[4];
+  for (int i = 0; i < n; ++i) ws[i] = p[i].w;
+  act_kinds(ws, n, n0, nk);
+  const bool fused = (e->cfg.flags & CMLD_FLAG_FUSED_PROLOGUE) != 0;
+  const bool pdl = !(e->cfg.flags & CMLD_FLAG_NO_PDL);
   if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3) {
     GemvJob jobs[3];
     for (int i = 0; i < n; ++i)
       jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
     const int fit = gemv_pipe_fit_batch(jobs, n);  // columns per pass: the same for every batch size, so
-    bool ok = fit > 0;                            // a row's result does not depend on who shares its step
-    for (int b0 = 0; b0 < batch && ok; b0 += fit) {
-      const int nb = std::min(fit, batch - b0);
-      for (int i = 0; i < n; ++i) {
-        jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y + (int64_t)b0 * p[i].y_stride,
-                          p[i].residual ? p[i].residual + (int64_t)b0 * p[i].y_stride : nullptr, p[i].y_stride};
+    if (fit > 0) {                                // a row's result does not depend on who shares its step
+      // Activation preparation.  Default: one small multi-CTA kernel writes the quantised rows once and
+      // every matvec CTA copies them (18 KB at most); with CMLD_FLAG_FUSED_PROLOGUE each matvec CTA
+      // recomputes them itself, which saves a launch but repeats the work 148 times.
+      if (!fused) CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
+      for (int b0 = 0; b0 < batch; b0 += fit) {
+        const int nb = std::min(fit, batch - b0);
+        for (int i = 0; i < n; ++i) {
+          jobs[i].y = p[i].y + (int64_t)b0 * p[i].y_stride;
+          jobs[i].residual = p[i].residual ? p[i].residual + (int64_t)b0 * p[i].y_stride : nullptr;
+        }
+        GemvPrologue pro{};
+        if (fused) {
+          pro.mode = mode;
+          pro.x = x + (int64_t)b0 * cols;
+          pro.x2 = x2 ? x2 + (int64_t)b0 * cols : nullptr;
+          pro.norm_w = norm_w;
+          pro.x_stride = cols;
+          pro.eps = e->cfg.eps;
+        } else {
+          pro.mode = 0;
+          pro.act_k = e->act_k + (int64_t)b0 * act_row_stride(cols);
+          pro.act_0 = e->act_0 + (int64_t)b0 * act_row_stride(cols);
+        }
+        CMLD_TRY(launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, pdl));
+        e->launches += 1;
       }
-      GemvPrologue pro{};
-      pro.mode = mode;
-      pro.x = x + (int64_t)b0 * cols;
-      pro.x2 = x2 ? x2 + (int64_t)b0 * cols : nullptr;
-      pro.norm_w = norm_w;
-      pro.x_stride = cols;
-      pro.eps = e->cfg.eps;
-      const int32_t rc = launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, !(e->cfg.flags & CMLD_FLAG_NO_PDL));
-      if (rc == CMLD_ERR_UNSUPPORTED && b0 == 0) {
-        ok = false;
-        break;
-      }
-      CMLD_TRY(rc);
-      e->launches += 1;
+      return CMLD_OK;
     }
-    if (ok) return CMLD_OK;
   }
-  bool n0, nk;
-  const Weight *ws[4];
-  for (int i = 0; i < n; ++i) ws[i] = p[i].w;
-  act_kinds(ws, n, n0, nk);
   CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
   return run_gemv_group(e, p, n, batch);
 }
@@ -414,6 +423,8 @@ struct StepOpts {
   bool argmax = true;
   bool feed_back = false;  // argmax writes next token / position / history
   bool taps = false;
+  bool shared_slots = false;  // several rows of this step belong to one sequence (prefill, verify): row b
+                              // reads K/V that rows < b write, so the KV append must be a kernel of its own
 };
 
 // moe.cu
@@ -470,31 +481,35 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden));
     }
     {
-      RopeKvArgs r{};
-      r.q = e->q;
-      r.k = e->k;
-      r.v = e->v;
-      r.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
-      r.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
-      r.index_by_position = o.rope_by_position;
-      r.positions = e->d_positions;
-      r.slots = e->d_slots;
-      r.k_cache = e->kcache + (int64_t)li * e->kv_layer_elems;
-      r.v_cache = e->vcache + (int64_t)li * e->kv_layer_elems;
-      r.n_heads = c.n_heads;
-      r.n_kv_heads = c.n_kv_heads;
-      r.head_dim = c.head_dim;
-      r.rope_dim = c.rope_dim;
-      r.split_half = c.split_half_pairing;
-      r.batch = B;
-      r.max_pos = c.max_pos;
-      r.q_stride = e->q_width;
-      r.kv_stride = e->kv_width;
-      CMLD_TRY(launch_rope_kv(r, e->stream));
+      const bool fuse = !o.shared_slots;
+      if (!fuse) {
+        RopeKvArgs r{};
+        r.q = e->q;
+        r.k = e->k;
+        r.v = e->v;
+        r.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
+        r.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
+        r.index_by_position = o.rope_by_position;
+        r.positions = e->d_positions;
+        r.slots = e->d_slots;
+        r.k_cache = e->kcache + (int64_t)li * e->kv_layer_elems;
+        r.v_cache = e->vcache + (int64_t)li * e->kv_layer_elems;
+        r.n_heads = c.n_heads;
+        r.n_kv_heads = c.n_kv_heads;
+        r.head_dim = c.head_dim;
+        r.rope_dim = c.rope_dim;
+        r.split_half = c.split_half_pairing;
+        r.batch = B;
+        r.max_pos = c.max_pos;
+        r.q_stride = e->q_width;
+        r.kv_stride = e->kv_width;
+        CMLD_TRY(launch_rope_kv(r, e->stream));
+        e->launches += 1;
+      }
       AttnArgs a{};
       a.q = e->q;
-      a.k_cache = r.k_cache;
-      a.v_cache = r.v_cache;
+      a.k_cache = e->kcache + (int64_t)li * e->kv_layer_elems;
+      a.v_cache = e->vcache + (int64_t)li * e->kv_layer_elems;
       a.positions = e->d_positions;
       a.slots = e->d_slots;
       a.n_heads = c.n_heads;
@@ -508,8 +523,18 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.tickets = e->attn_tickets;
       a.out = e->attn;
       a.q_stride = e->q_width;
+      a.fuse_rope = fuse ? 1 : 0;  // RoPE(q), RoPE(k) and the f16 KV append inside the attention kernel
+      a.rope_dim = c.rope_dim;
+      a.split_half = c.split_half_pairing;
+      a.index_by_position = o.rope_by_position;
+      a.k_new = e->k;
+      a.v_new = e->v;
+      a.kv_stride = e->kv_width;
+      a.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
+      a.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
+      a.pdl = !(c.flags & CMLD_FLAG_NO_PDL);
       CMLD_TRY(launch_attention(a, e->stream));
-      e->launches += 2;
+      e->launches += 1;
     }
     {
       const Proj p[1] = {{&L.proj[3], e->h, e->h, c.hidden}};
@@ -547,7 +572,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
 static int32_t run_step(cmld_engine *e, const StepOpts &o) {
   if ((e->cfg.flags & CMLD_FLAG_NO_GRAPH) || e->graphs_off) return engine_step(e, o);
   uint32_t bits = (o.from_tokens ? 1u : 0u) | (o.rope_by_position ? 2u : 0u) | (o.logits ? 4u : 0u) | (o.argmax ? 8u : 0u) |
-                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u);
+                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u);
   uint32_t scale_bits;
   memcpy(&scale_bits, &o.scale, 4);
   auto &g = e->graphs[std::make_tuple(o.batch, bits, scale_bits)];
@@ -632,6 +657,7 @@ static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, c
   CMLD_TRY(stage_rows(e, n_rows, nullptr, pos.data(), slots.data()));
   StepOpts o;
   o.batch = n_rows;
+  o.shared_slots = n_rows > 1;
   o.from_tokens = false;
   o.rope_by_position = false;
   o.scale = scale;
@@ -895,6 +921,21 @@ int32_t cmld_engine_set_filled(cmld_engine *e, int64_t filled) {
 int64_t cmld_engine_max_pos(const cmld_engine *e) { return e ? e->cfg.max_pos : 0; }
 int32_t cmld_engine_n_layers(const cmld_engine *e) { return e ? e->cfg.n_layers : 0; }
 
+int32_t cmld_engine_rope_row(const cmld_engine *e, int64_t position, float *cos_out, float *sin_out) {
+  if (!e || !cos_out || !sin_out) return fail(CMLD_ERR_INVALID, "null argument");
+  if (position < 0 || position >= e->cfg.max_pos) return fail(CMLD_ERR_INVALID, "position %lld out of range", (long long)position);
+  const cmld_config &c = e->cfg;
+  const int half = c.rope_dim / 2;
+  const float base = c.rope_theta > 0.0f ? c.rope_theta : 10000.0f;
+  for (int i = 0; i < half; ++i) {
+    const float theta = powf(base, -((float)i * 2.0f) / (float)c.rope_dim);
+    const float ang = (float)position * theta;
+    sin_out[i] = sinf(ang);
+    cos_out[i] = cosf(ang);
+  }
+  return CMLD_OK;
+}
+
 int32_t cmld_engine_forward_token(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
                                   int64_t position, float scale, int32_t compute_logits, uint32_t *token_out) {
   CMLD_ENGINE_ENTER(e);
@@ -1023,6 +1064,13 @@ static int32_t check_rows(cmld_engine *e, int32_t n, const int32_t *seqs, const 
   return CMLD_OK;
 }
 
+static bool has_shared_slots(const int32_t *seqs, int n) {
+  for (int i = 0; i < n; ++i)
+    for (int j = i + 1; j < n; ++j)
+      if (seqs[i] == seqs[j]) return true;
+  return false;
+}
+
 int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *seqs, const int32_t *tokens_in,
                                const int64_t *positions, uint32_t *tokens_out, float *logits_out, float *hidden_out) {
   CMLD_ENGINE_ENTER(e);
@@ -1034,6 +1082,7 @@ int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *se
   CMLD_CUDA(cudaEventRecord(e->ev0, e->stream));
   StepOpts o;
   o.batch = n_seqs;
+  o.shared_slots = has_shared_slots(seqs, n_seqs);
   o.from_tokens = true;
   o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
   CMLD_TRY(run_step(e, o));
@@ -1068,6 +1117,7 @@ int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *t
     CMLD_TRY(stage_rows(e, rows, tokens + i, pos32.data(), seqs.data()));
     StepOpts o;
     o.batch = rows;
+    o.shared_slots = rows > 1;
     o.from_tokens = true;
     o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
     o.logits = o.argmax = (i + chunk >= n);
@@ -1098,6 +1148,7 @@ int32_t cmld_engine_decode_greedy(cmld_engine *e, int32_t n_seqs, const int32_t 
   CMLD_CUDA(cudaEventRecord(e->ev0, e->stream));
   StepOpts o;
   o.batch = n_seqs;
+  o.shared_slots = has_shared_slots(seqs, n_seqs);
   o.from_tokens = true;
   o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
   o.feed_back = true;

@@ -28,8 +28,10 @@
 
 namespace cmld {
 
-constexpr int kPipeConsumerWarps = 8;
-constexpr int kPipeConsumers = kPipeConsumerWarps * 32;
+constexpr int kPipeConsumerWarps = 8;  // warps that share one tile
+constexpr int kPipeGroups = 2;         // consumer groups; group g takes this CTA's tiles g, g+2, ... (more warps to hide latency)
+constexpr int kPipeAllWarps = kPipeConsumerWarps * kPipeGroups;
+constexpr int kPipeConsumers = kPipeAllWarps * 32;
 constexpr int kPipeThreads = kPipeConsumers + 32;  // + the producer warp
 constexpr int kPipeMaxStages = 8;
 constexpr int kActRec = 336;       // one Q8_K activation superblock in shared memory (21 x 16 B: conflict-free lane stride)
@@ -266,7 +268,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   // its own griddepcontrol.wait until this grid has completed.
   asm volatile("griddepcontrol.launch_dependents;");
 
-  if (warp == kPipeConsumerWarps) {
+  if (warp == kPipeAllWarps) {
     // ---------------- producer: weights do not depend on the previous kernel, so no wait here
     if (lane == 0) {
       for (int i = 0; i < n_my; ++i) {
@@ -330,21 +332,24 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const float *x2 = a.mode == 3 ? a.x2 + (int64_t)b * a.x_stride : nullptr;
     float scale = 1.0f;
     if (a.mode == 1) {
+      // the mean square is summed by the first 256 threads in the same order as the stand-alone
+      // norm kernel, so both paths produce the same bits
       float ss = 0.0f;
-      for (int i = tid; i < a.cols; i += kPipeConsumers) {
-        const float v = __ldcg(x + i);
-        ss = __fmaf_rn(v, v, ss);
-      }
+      if (tid < 256)
+        for (int i = tid; i < a.cols; i += 256) {
+          const float v = __ldcg(x + i);
+          ss = __fmaf_rn(v, v, ss);
+        }
       ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
+      if (lane == 0 && warp < 8) red[warp] = ss;
       asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
-      float t = lane < kPipeConsumerWarps ? red[lane] : 0.0f;
+      float t = lane < 8 ? red[lane] : 0.0f;
       t = warp_sum(t);
       scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
       asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
     }
     const int n_chunks = (a.cols + 255) >> 8;
-    for (int ch = warp; ch < n_chunks; ch += kPipeConsumerWarps) {
+    for (int ch = warp; ch < n_chunks; ch += kPipeAllWarps) {
       const int e0 = ch * 256 + lane * 8;
       float v[8];
 #pragma unroll
@@ -385,8 +390,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
 
-  // Main loop over this CTA's tiles.
-  for (int i = 0; i < n_my; ++i) {
+  // Main loop over this CTA's tiles; the two consumer groups alternate.
+  const int group = warp / kPipeConsumerWarps, wg = warp % kPipeConsumerWarps;
+  for (int i = group; i < n_my; i += kPipeGroups) {
     const int s = i % S;
     const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
     const int t = (int)blockIdx.x + i * (int)gridDim.x;
@@ -401,7 +407,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       const int n_it = J.qt == CMLD_Q8_0 ? (a.cols >> 5) : nsb;  // work items per row: blocks or superblocks
       const int L = n_it < 32 ? n_it : 32;                        // lanes per row
       const int rpw = 32 / L;                                     // rows per warp
-      const int r_local = warp * rpw + lane / L, lis = lane % L;
+      const int r_local = wg * rpw + lane / L, lis = lane % L;
       const bool active = lane < rpw * L && r_local < nrows;
       float acc[B];
 #pragma unroll
@@ -532,10 +538,14 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   off = (off + 127) & ~127;
   a.off_ring = off;
   // Prefer a footprint that lets two kernels share an SM (the next one prefetches under PDL).
+  // The stage count must be a multiple of the number of consumer groups: tile i lives in stage i % S and
+  // belongs to group i % kPipeGroups, so with S even every stage is only ever used by one group and a
+  // group meets the phases of its stages in order (an mbarrier parity wait cannot tell phase n from n+2).
   int n_stages = 0;
   for (int budget : {110 * 1024, 224 * 1024}) {
     n_stages = std::min<int>(kPipeMaxStages, (budget - off) / stage);
-    if (n_stages >= 3) break;
+    n_stages -= n_stages % kPipeGroups;
+    if (n_stages >= 4) break;
   }
   if (n_stages < 2) return false;
   p.smem_bytes = off + n_stages * stage;

@@ -18,7 +18,9 @@ constexpr int kNormThreads = 256;  // same thread count and summation tree as th
 
 template <int MODE>  // 0 plain, 1 rmsnorm, 2 swiglu
 __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs a) {
-  const int b = blockIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int b = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const float *x = a.x + (int64_t)b * a.cols;
   const float *x2 = MODE == 2 ? a.x2 + (int64_t)b * a.cols : nullptr;
@@ -44,7 +46,8 @@ __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs 
   }
   const int64_t n_chunks = (a.cols + 255) >> 8;
   const int64_t astride = act_row_stride(a.cols);
-  for (int64_t ch = warp; ch < n_chunks; ch += nwarps) {
+  // every CTA of a row repeats the mean-square (cheap) and quantises its own 256-value chunks
+  for (int64_t ch = (int64_t)blockIdx.x * nwarps + warp; ch < n_chunks; ch += (int64_t)gridDim.x * nwarps) {
     const int64_t e0 = ch * 256 + lane * 8;
     float v[8];
 #pragma unroll
@@ -133,10 +136,19 @@ int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s) {
     return fail(CMLD_ERR_SHAPE, "Q8_K activation width %lld is not a multiple of 256", (long long)a.cols);
   if (a.batch <= 0) return CMLD_OK;
   const int mode = a.x2 ? 2 : (a.weight ? 1 : 0);
-  if (mode == 0) norm_quant_kernel<0><<<a.batch, kNormThreads, 0, s>>>(a);
-  else if (mode == 1) norm_quant_kernel<1><<<a.batch, kNormThreads, 0, s>>>(a);
-  else norm_quant_kernel<2><<<a.batch, kNormThreads, 0, s>>>(a);
-  CMLD_CUDA(cudaGetLastError());
+  const int64_t n_chunks = (a.cols + 255) >> 8;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)((n_chunks + kNormThreads / 32 - 1) / (kNormThreads / 32)), (unsigned)a.batch);
+  cfg.blockDim = dim3(kNormThreads);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.pdl ? 1 : 0;
+  if (mode == 0) CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<0>, a));
+  else if (mode == 1) CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<1>, a));
+  else CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<2>, a));
   return CMLD_OK;
 }
 

@@ -291,6 +291,12 @@ class ResidentDecode:
     def _f(self, a):
         return np.ascontiguousarray(a, np.float32)
 
+    def rope_row(self, position: int):
+        half = (self.cfg.rope_dim or self.cfg.head_dim) // 2
+        c, s = np.empty(half, np.float32), np.empty(half, np.float32)
+        check(lib().cmld_engine_rope_row(self._h, position, _np_ptr(c), _np_ptr(s)))
+        return c, s
+
     def forward_token(self, embedding, cos, sin, position: int, scale: float, compute_logits: bool = True):
         e, c, s = self._f(embedding), self._f(cos), self._f(sin)
         tok = C.c_uint32(0)

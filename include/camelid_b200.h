@@ -76,6 +76,7 @@ typedef struct {
 #define CMLD_FLAG_NO_GRAPH 1u     /* launch kernels directly instead of replaying a CUDA graph */
 #define CMLD_FLAG_DIRECT_GEMV 2u  /* use the direct-load matvec kernel everywhere (no staged kernel) */
 #define CMLD_FLAG_NO_PDL 4u       /* no programmatic dependent launch between kernels */
+#define CMLD_FLAG_FUSED_PROLOGUE 8u /* matvec CTAs recompute norm/SwiGLU/quantise themselves (no prep kernel) */
 
 typedef struct cmld_engine cmld_engine;
 typedef struct cmld_weight cmld_weight;
@@ -132,6 +133,12 @@ CMLD_API int64_t cmld_engine_filled(const cmld_engine *e);
 CMLD_API int32_t cmld_engine_set_filled(cmld_engine *e, int64_t filled);
 CMLD_API int64_t cmld_engine_max_pos(const cmld_engine *e);
 CMLD_API int32_t cmld_engine_n_layers(const cmld_engine *e);
+
+/* The RoPE row of one position, cos_out/sin_out[rope_dim/2], as the engine's own all-position
+ * table holds it: theta_i = powf(rope_theta, -2i/rope_dim), sinf/cosf of position*theta_i with the
+ * host libm — what resident_decode_rope_tables computes per token (src/inference/rope.rs:600-655).
+ * Host-side helper; touches no device memory. */
+CMLD_API int32_t cmld_engine_rope_row(const cmld_engine *e, int64_t position, float *cos_out, float *sin_out);
 
 /* forward_token (src/cuda_resident.rs:19548): embedding[hidden], cos/sin[rope_dim/2], the
  * position to write, the score scale; *token_out receives the argmax id when

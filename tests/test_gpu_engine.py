@@ -193,15 +193,18 @@ def test_direct_and_staged_matvec_paths_agree(cm, orc):
         cfg = synth.engine_config("tiny", max_pos=64)
         a = ModelPair(cfg, mix, seed=9)
         b = ModelPair(synth.engine_config("tiny", max_pos=64, flags=2), mix, seed=9)
+        c = ModelPair(synth.engine_config("tiny", max_pos=64, flags=8 | 1 | 4), mix, seed=9)  # fused prologues, no graph, no PDL
         prompt = orc.synth_tokens(8, 1, 8, cfg.vocab)
-        fa, fb = a.engine.prefill_tokens(0, prompt, 0), b.engine.prefill_tokens(0, prompt, 0)
+        fa, fb, fc = (m.engine.prefill_tokens(0, prompt, 0) for m in (a, b, c))
         _, la, _ = a.engine.step_batch([0], [fa], [8], want_logits=True)
         _, lb, _ = b.engine.step_batch([0], [fb], [8], want_logits=True)
-        assert fa == fb
+        _, lc, _ = c.engine.step_batch([0], [fc], [8], want_logits=True)
+        assert fa == fb == fc
         assert np.abs(la - lb).max() < 1e-4 * np.abs(la).max()
+        assert np.array_equal(la, lc)  # same staged kernel, same quantised codes: identical bits
         _, launches_a = a.engine.last_timing()
-        _, launches_b = b.engine.last_timing()
-        assert launches_a < launches_b  # fused prologues: fewer kernels per step
+        _, launches_c = c.engine.last_timing()
+        assert launches_c < launches_a  # fused prologues: fewer kernels per step
 
 
 def test_wire_upload_path_equals_device_generated(cm, orc):
