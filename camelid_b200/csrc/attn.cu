@@ -201,6 +201,19 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
     for (int e = 0; e < PER; ++e) s_acc[warp][g][lane * PER + e] = acc[g][e];
   __syncthreads();
+  if (n_active == 1) {
+    // a single range: normalise in place, no partials through global memory and no ticket
+    float *out1 = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
+    for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
+      const int g = i / HD, d = i % HD;
+      float sacc = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) sacc += s_acc[w][g][d];
+      // the merge below computes fma(acc, 1, 0) / fma(l, 1, 0): the same bits
+      out1[i] = __fdiv_rn(sacc, l_run[g]);
+    }
+    return;
+  }
   float *part = a.part + (((int64_t)b * a.n_heads + (int64_t)kvh * G) * a.n_splits) * (HD + 2);
   for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
     const int g = i / HD, d = i % HD;
@@ -267,6 +280,11 @@ static int32_t launch_gp(const AttnArgs &a, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    prefer_max_smem_carveout(attn_decode_kernel<G, PER>);
+    carveout_set = true;
+  }
   CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, PER>, a));
   return CMLD_OK;
 }

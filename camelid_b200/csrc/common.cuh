@@ -140,6 +140,13 @@ __device__ __forceinline__ uint4 ld_stream16(const void *p) {
 
 #endif  // __CUDACC__
 
+// Every kernel of the decode step asks for the same (maximum) shared-memory carve-out as the
+// staged matvec: an SM whose L1/shared split has to change between two kernels drains first.
+template <typename K>
+inline void prefer_max_smem_carveout(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 // ------------------------------------------------------------------ kernel launchers (host)
 
 // formats.cu

@@ -373,7 +373,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
   const Weight *ws[4];
   for (int i = 0; i < n; ++i) ws[i] = p[i].w;
   act_kinds(ws, n, n0, nk);
-  const bool fused = (e->cfg.flags & CMLD_FLAG_FUSED_PROLOGUE) != 0;
+  const bool fused = !(e->cfg.flags & CMLD_FLAG_SPLIT_PROLOGUE);
   const bool pdl = !(e->cfg.flags & CMLD_FLAG_NO_PDL);
   if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3) {
     GemvJob jobs[3];
@@ -381,9 +381,10 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
       jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
     const int fit = gemv_pipe_fit_batch(jobs, n);  // columns per pass: the same for every batch size, so
     if (fit > 0) {                                // a row's result does not depend on who shares its step
-      // Activation preparation.  Default: one small multi-CTA kernel writes the quantised rows once and
-      // every matvec CTA copies them (18 KB at most); with CMLD_FLAG_FUSED_PROLOGUE each matvec CTA
-      // recomputes them itself, which saves a launch but repeats the work 148 times.
+      // Activation preparation.  Default: each matvec CTA computes norm / SwiGLU / quantisation itself in
+      // its prologue (repeated on every SM, but no extra launch on the critical path); with
+      // CMLD_FLAG_SPLIT_PROLOGUE one small multi-CTA kernel writes the quantised rows once and the
+      // matvec CTAs copy them.
       if (!fused) CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
       for (int b0 = 0; b0 < batch; b0 += fit) {
         const int nb = std::min(fit, batch - b0);

@@ -158,6 +158,11 @@ __global__ void embed_gather_kernel(const uint8_t *__restrict__ data, int qt, in
 }
 
 int32_t launch_embed_gather(const Weight &w, const int32_t *tokens_dev, int32_t batch, float *out, cudaStream_t s) {
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    prefer_max_smem_carveout(embed_gather_kernel);
+    carveout_set = true;
+  }
   dim3 grid((unsigned)((w.cols + 255) / 256), (unsigned)batch);
   embed_gather_kernel<<<grid, 256, 0, s>>>(w.data, w.qt, w.rows, w.cols, w.stride, tokens_dev, out);
   CMLD_CUDA(cudaGetLastError());

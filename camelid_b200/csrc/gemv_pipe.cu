@@ -336,6 +336,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       // norm kernel, so both paths produce the same bits
       float ss = 0.0f;
       if (tid < 256)
+#pragma unroll 8
         for (int i = tid; i < a.cols; i += 256) {
           const float v = __ldcg(x + i);
           ss = __fmaf_rn(v, v, ss);
@@ -352,17 +353,32 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     for (int ch = warp; ch < n_chunks; ch += kPipeAllWarps) {
       const int e0 = ch * 256 + lane * 8;
       float v[8];
+      if (e0 + 8 <= a.cols) {
+        // 8 consecutive values per lane: two 128-bit loads per operand (cols is a multiple of 32)
+        const float4 xa = __ldcg(reinterpret_cast<const float4 *>(x + e0)), xb = __ldcg(reinterpret_cast<const float4 *>(x + e0) + 1);
+        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        if (a.mode == 1) {
+          const float4 wa = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0)), wb = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0) + 1);
+          const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int e = e0 + i;
-        float t = 0.0f;
-        if (e < a.cols) {
-          if (a.mode == 1) t = __fmul_rn(__fmul_rn(__ldcg(x + e), scale), __ldg(a.norm_w + e));
-          else if (a.mode == 3) t = swiglu(__ldcg(x + e), __ldcg(x2 + e));
-          else t = __ldcg(x + e);
-          if (a.norm_out && blockIdx.x == 0) a.norm_out[(int64_t)b * a.cols + e] = t;
+          for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(xv[i], scale), wv[i]);
+        } else if (a.mode == 3) {
+          const float4 ua = __ldcg(reinterpret_cast<const float4 *>(x2 + e0)), ub = __ldcg(reinterpret_cast<const float4 *>(x2 + e0) + 1);
+          const float uv[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = swiglu(xv[i], uv[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = xv[i];
         }
-        v[i] = t;
+        if (a.norm_out && blockIdx.x == 0) {
+          float4 *o4 = reinterpret_cast<float4 *>(a.norm_out + (int64_t)b * a.cols + e0);
+          o4[0] = make_float4(v[0], v[1], v[2], v[3]);
+          o4[1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.0f;
       }
       if (a.need_k) {
         int q[8];

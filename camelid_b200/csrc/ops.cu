@@ -146,6 +146,13 @@ int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = a.pdl ? 1 : 0;
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    prefer_max_smem_carveout(norm_quant_kernel<0>);
+    prefer_max_smem_carveout(norm_quant_kernel<1>);
+    prefer_max_smem_carveout(norm_quant_kernel<2>);
+    carveout_set = true;
+  }
   if (mode == 0) CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<0>, a));
   else if (mode == 1) CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<1>, a));
   else CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<2>, a));
@@ -292,6 +299,12 @@ __global__ void __launch_bounds__(kArgmaxThreads)
 // history: [max_steps][batch] ids; hist_len lives right after the tickets: ticket[batch..2*batch).
 int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx, uint32_t *ticket,
                       int32_t *out_idx, int32_t *next_tokens, int32_t *positions, int32_t *history, cudaStream_t s) {
+  static bool carveout_set = false;
+  if (!carveout_set) {
+    prefer_max_smem_carveout(argmax_kernel);
+    prefer_max_smem_carveout(rope_kv_kernel);
+    carveout_set = true;
+  }
   dim3 grid(kArgmaxBlocks, (unsigned)batch);
   argmax_kernel<<<grid, kArgmaxThreads, 0, s>>>(x, n, part_val, part_idx, ticket, out_idx, next_tokens, positions, history,
                                                 reinterpret_cast<int32_t *>(ticket) + batch, batch);

@@ -76,7 +76,7 @@ typedef struct {
 #define CMLD_FLAG_NO_GRAPH 1u     /* launch kernels directly instead of replaying a CUDA graph */
 #define CMLD_FLAG_DIRECT_GEMV 2u  /* use the direct-load matvec kernel everywhere (no staged kernel) */
 #define CMLD_FLAG_NO_PDL 4u       /* no programmatic dependent launch between kernels */
-#define CMLD_FLAG_FUSED_PROLOGUE 8u /* matvec CTAs recompute norm/SwiGLU/quantise themselves (no prep kernel) */
+#define CMLD_FLAG_SPLIT_PROLOGUE 8u /* norm/SwiGLU/quantise in a small kernel of its own instead of the matvec prologue */
 
 typedef struct cmld_engine cmld_engine;
 typedef struct cmld_weight cmld_weight;

@@ -193,7 +193,7 @@ def test_direct_and_staged_matvec_paths_agree(cm, orc):
         cfg = synth.engine_config("tiny", max_pos=64)
         a = ModelPair(cfg, mix, seed=9)
         b = ModelPair(synth.engine_config("tiny", max_pos=64, flags=2), mix, seed=9)
-        c = ModelPair(synth.engine_config("tiny", max_pos=64, flags=8 | 1 | 4), mix, seed=9)  # fused prologues, no graph, no PDL
+        c = ModelPair(synth.engine_config("tiny", max_pos=64, flags=8 | 1 | 4), mix, seed=9)  # separate prep kernels, no graph, no PDL
         prompt = orc.synth_tokens(8, 1, 8, cfg.vocab)
         fa, fb, fc = (m.engine.prefill_tokens(0, prompt, 0) for m in (a, b, c))
         _, la, _ = a.engine.step_batch([0], [fa], [8], want_logits=True)
@@ -204,7 +204,7 @@ def test_direct_and_staged_matvec_paths_agree(cm, orc):
         assert np.array_equal(la, lc)  # same staged kernel, same quantised codes: identical bits
         _, launches_a = a.engine.last_timing()
         _, launches_c = c.engine.last_timing()
-        assert launches_c < launches_a  # fused prologues: fewer kernels per step
+        assert launches_a < launches_c  # fused prologues (the default): fewer kernels per step
 
 
 def test_wire_upload_path_equals_device_generated(cm, orc):
