@@ -83,6 +83,7 @@ def lib():
         "cmld_engine_forward_token": (i32, [vp, vp, vp, vp, i64, f32, i32, P(C.c_uint32)]),
         "cmld_engine_forward_token_logits": (i32, [vp, vp, vp, vp, i64, f32, vp]),
         "cmld_engine_forward_token_hidden": (i32, [vp, vp, vp, vp, i64, f32, vp, vp]),
+        "cmld_engine_forward_layer": (i32, [vp, i32, vp, vp, vp, i64, f32, vp]),
         "cmld_engine_prefill_from": (i32, [vp, vp, vp, vp, i64, f32, i64]),
         "cmld_engine_verify_batch": (i32, [vp, vp, vp, vp, i64, i32, f32, vp]),
         "cmld_engine_seed_layer": (i32, [vp, i32, vp, vp, i64]),

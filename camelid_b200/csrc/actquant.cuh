@@ -9,6 +9,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "expf_exact.cuh"
 
 namespace cmld {
 
@@ -69,7 +70,7 @@ __device__ __forceinline__ uint2 pack8(const int (&q)[8]) {
 
 // SwiGLU element (src/inference.rs:13231-13236): g / (1 + exp(-g)) * u.
 __device__ __forceinline__ float swiglu(float g, float u) {
-  return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), u);
+  return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf_exact(-g))), u);
 }
 
 }  // namespace cmld

@@ -8,6 +8,7 @@
 // per head, and the CTA that finishes last merges the ranges.  The result agrees with the
 // CPU's sequential sums up to f32 reassociation.
 #include "common.cuh"
+#include "expf_exact.cuh"
 
 namespace cmld {
 
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     for (int g = 0; g < G; ++g) {
       float s = 0.0f;
       for (int p = threadIdx.x; p < cn; p += kAttnThreads) {
-        const float e = expf(s_sc[g][p] - cm[g]);
+        const float e = expf_exact(s_sc[g][p] - cm[g]);
         s_sc[g][p] = e;
         s += e;
       }
@@ -173,7 +174,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 #pragma unroll
       for (int w = 0; w < kAttnWarps; ++w) s += s_red[w][g];
       ls[g] = s;
-      const float corr = m_run[g] == -INFINITY ? 0.0f : expf(m_run[g] - cm[g]);
+      const float corr = m_run[g] == -INFINITY ? 0.0f : expf_exact(m_run[g] - cm[g]);
       l_run[g] = l_run[g] * corr + ls[g];
 #pragma unroll
       for (int e = 0; e < PER; ++e) acc[g][e] *= corr;
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   for (int i = threadIdx.x; i < G * n_active; i += kAttnThreads) {
     const int g = i / n_active, s2 = i % n_active;
     const float ms = s_w[g * kAttnChunk + s2];
-    s_w[g * kAttnChunk + s2] = ms == -INFINITY ? 0.0f : expf(ms - s_red[0][g]);
+    s_w[g * kAttnChunk + s2] = ms == -INFINITY ? 0.0f : expf_exact(ms - s_red[0][g]);
   }
   __syncthreads();
   float *out = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;

@@ -195,6 +195,7 @@ struct NormQuantArgs {
   int32_t act_q8_0, act_q8_k;  // which formats to emit; both allowed: Q8_K at act, Q8_0 at act2
   uint8_t *act2;
   int32_t pdl;                 // launch with programmatic stream serialisation
+  int32_t exact;               // RMSNorm: add the squares one after another like the CPU (slow)
 };
 int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s);
 int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx,
@@ -239,5 +240,9 @@ struct AttnArgs {
   int32_t pdl;                     // launch with programmatic stream serialisation
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
+
+// exact.cu: reference-order kernels (q already rotated, KV already appended for the attention)
+int32_t launch_gemv_exact(const GemvJob &J, const uint8_t *act, int32_t batch, cudaStream_t s);
+int32_t launch_attention_exact(const AttnArgs &a, cudaStream_t s);
 
 }  // namespace cmld

@@ -359,6 +359,7 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
   a.act = need_k ? e->act_k : e->act_0;
   a.act2 = e->act_0;
   a.pdl = !(e->cfg.flags & CMLD_FLAG_NO_PDL);
+  a.exact = (e->cfg.flags & CMLD_FLAG_EXACT_ORDER) != 0;
   CMLD_TRY(launch_norm_quant(a, e->stream));
   e->launches += 1;
   return CMLD_OK;
@@ -375,6 +376,16 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
   act_kinds(ws, n, n0, nk);
   const bool fused = !(e->cfg.flags & CMLD_FLAG_SPLIT_PROLOGUE);
   const bool pdl = !(e->cfg.flags & CMLD_FLAG_NO_PDL);
+  if (e->cfg.flags & CMLD_FLAG_EXACT_ORDER) {
+    // reference order: quantise once (sequential mean square), then one ordered matvec per matrix
+    CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
+    for (int i = 0; i < n; ++i) {
+      const GemvJob j{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
+      CMLD_TRY(launch_gemv_exact(j, p[i].w->qt == CMLD_Q8_0 ? e->act_0 : e->act_k, batch, e->stream));
+      e->launches += 1;
+    }
+    return CMLD_OK;
+  }
   if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3) {
     GemvJob jobs[3];
     for (int i = 0; i < n; ++i)
@@ -424,6 +435,7 @@ struct StepOpts {
   bool argmax = true;
   bool feed_back = false;  // argmax writes next token / position / history
   bool taps = false;
+  int32_t layer_begin = 0, layer_end = -1;  // layers to run; -1 = through the last
   bool shared_slots = false;  // several rows of this step belong to one sequence (prefill, verify): row b
                               // reads K/V that rows < b write, so the KV append must be a kernel of its own
 };
@@ -473,7 +485,8 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
     CMLD_TRY(launch_embed_gather(e->token_embd, e->d_tokens, B, e->h, e->stream));
     e->launches += 1;
   }
-  for (int32_t li = 0; li < c.n_layers; ++li) {
+  const int32_t l_end = o.layer_end < 0 ? c.n_layers : o.layer_end;
+  for (int32_t li = o.layer_begin; li < l_end; ++li) {
     LayerW &L = e->layers[li];
     {
       const Proj p[3] = {{&L.proj[0], e->q, nullptr, e->q_width},
@@ -482,7 +495,8 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden));
     }
     {
-      const bool fuse = !o.shared_slots;
+      const bool exact = (c.flags & CMLD_FLAG_EXACT_ORDER) != 0;
+      const bool fuse = !o.shared_slots && !exact;
       if (!fuse) {
         RopeKvArgs r{};
         r.q = e->q;
@@ -534,7 +548,8 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
       a.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
       a.pdl = !(c.flags & CMLD_FLAG_NO_PDL);
-      CMLD_TRY(launch_attention(a, e->stream));
+      if (exact) CMLD_TRY(launch_attention_exact(a, e->stream));
+      else CMLD_TRY(launch_attention(a, e->stream));
       e->launches += 1;
     }
     {
@@ -573,7 +588,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
 static int32_t run_step(cmld_engine *e, const StepOpts &o) {
   if ((e->cfg.flags & CMLD_FLAG_NO_GRAPH) || e->graphs_off) return engine_step(e, o);
   uint32_t bits = (o.from_tokens ? 1u : 0u) | (o.rope_by_position ? 2u : 0u) | (o.logits ? 4u : 0u) | (o.argmax ? 8u : 0u) |
-                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u);
+                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u) | ((uint32_t)(o.layer_begin & 0xfff) << 8) | ((uint32_t)((o.layer_end + 1) & 0xfff) << 20);
   uint32_t scale_bits;
   memcpy(&scale_bits, &o.scale, 4);
   auto &g = e->graphs[std::make_tuple(o.batch, bits, scale_bits)];
@@ -642,7 +657,8 @@ static int32_t finish(cmld_engine *e, const char *what) {
 
 // One sequence-0 row fed by an embedding vector: the forward_token family.
 static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, const float *cosv, const float *sinv,
-                                      int64_t position0, int32_t n_rows, float scale, bool logits, bool argmax, bool taps) {
+                                      int64_t position0, int32_t n_rows, float scale, bool logits, bool argmax, bool taps,
+                                      int32_t layer_begin = 0, int32_t layer_end = -1) {
   const cmld_config &c = e->cfg;
   if (!embeddings || !cosv || !sinv) return fail(CMLD_ERR_INVALID, "embedding / cos / sin pointer is null");
   if (position0 < 0 || position0 + n_rows > c.max_pos)
@@ -665,6 +681,8 @@ static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, c
   o.logits = logits;
   o.argmax = argmax;
   o.taps = taps;
+  o.layer_begin = layer_begin;
+  o.layer_end = layer_end;
   return run_step(e, o);
 }
 
@@ -968,6 +986,16 @@ int32_t cmld_engine_forward_token_hidden(cmld_engine *e, const float *embedding,
     CMLD_CUDA(cudaMemcpy2DAsync(layer_taps, (size_t)e->cfg.hidden * 4, e->taps, (size_t)e->max_rows * e->cfg.hidden * 4,
                                 (size_t)e->cfg.hidden * 4, e->cfg.n_layers, cudaMemcpyDeviceToHost, e->stream));
   return finish(e, "forward_token_hidden");
+}
+
+int32_t cmld_engine_forward_layer(cmld_engine *e, int32_t layer, const float *hidden_in, const float *cosv, const float *sinv,
+                                  int64_t position, float scale, float *hidden_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (!hidden_out) return fail(CMLD_ERR_INVALID, "hidden_out is null");
+  if (layer < 0 || layer >= e->cfg.n_layers) return fail(CMLD_ERR_INVALID, "layer %d out of range", layer);
+  CMLD_TRY(forward_embedding_rows(e, hidden_in, cosv, sinv, position, 1, scale, false, false, false, layer, layer + 1));
+  CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
+  return finish(e, "forward_layer");
 }
 
 int32_t cmld_engine_prefill_from(cmld_engine *e, const float *embeddings, const float *cos_all, const float *sin_all,

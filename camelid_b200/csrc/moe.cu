@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "expf_exact.cuh"
 
 namespace cmld {
 
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
   float sum = 0.0f;
   for (int s = 0; s < k; ++s) {
     const float v = logits[idx[s]];
-    w[s] = isfinite(v) ? expf(v - mx) : 0.0f;
+    w[s] = isfinite(v) ? expf_exact(__fsub_rn(v, mx)) : 0.0f;
     sum += w[s];
   }
   for (int s = 0; s < k; ++s) w[s] = sum > 0.0f ? __fdiv_rn(w[s], sum) : __fdiv_rn(1.0f, (float)k);

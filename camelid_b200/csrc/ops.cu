@@ -1,6 +1,6 @@
 // Per-token work around the matvecs: RMSNorm / SwiGLU fused with activation quantisation,
 // RoPE fused with the f16 KV-cache write, and greedy argmax.
-#include "common.cuh"
+#include "actquant.cuh"
 
 namespace cmld {
 
@@ -28,20 +28,30 @@ __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs 
   if (MODE == 1) {
     __shared__ float red[kNormThreads / 32];
     __shared__ float s_scale;
-    float ss = 0.0f;
-    for (int64_t i = threadIdx.x; i < a.cols; i += blockDim.x) {
-      const float v = x[i];
-      ss = __fmaf_rn(v, v, ss);
+    if (a.exact) {
+      // the CPU's order: one accumulator, squares added in index order (rms_norm_into, src/tensor/mod.rs:2755)
+      if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int64_t i = 0; i < a.cols; ++i) t = __fadd_rn(t, __fmul_rn(x[i], x[i]));
+        s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+      }
+      __syncthreads();
+    } else {
+      float ss = 0.0f;
+      for (int64_t i = threadIdx.x; i < a.cols; i += blockDim.x) {
+        const float v = x[i];
+        ss = __fmaf_rn(v, v, ss);
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      if (warp == 0) {
+        float t = lane < nwarps ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+      }
+      __syncthreads();
     }
-    ss = warp_sum(ss);
-    if (lane == 0) red[warp] = ss;
-    __syncthreads();
-    if (warp == 0) {
-      float t = lane < nwarps ? red[lane] : 0.0f;
-      t = warp_sum(t);
-      if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
-    }
-    __syncthreads();
     scale = s_scale;
   }
   const int64_t n_chunks = (a.cols + 255) >> 8;
@@ -58,7 +68,7 @@ __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs 
         if (MODE == 1) t = __fmul_rn(__fmul_rn(x[e], scale), a.weight[e]);
         else if (MODE == 2) {
           const float g = x[e];
-          t = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), x2[e]);
+          t = swiglu(g, x2[e]);
         } else t = x[e];
         if (a.out) a.out[(int64_t)b * a.cols + e] = t;
       }

@@ -318,6 +318,12 @@ class ResidentDecode:
                                                      _np_ptr(out), _np_ptr(t) if taps else None))
         return (out, t) if taps else out
 
+    def forward_layer(self, layer: int, hidden_in, cos, sin, position: int, scale: float) -> np.ndarray:
+        h, c, s = self._f(hidden_in), self._f(cos), self._f(sin)
+        out = np.empty(self.cfg.hidden, np.float32)
+        check(lib().cmld_engine_forward_layer(self._h, layer, _np_ptr(h), _np_ptr(c), _np_ptr(s), position, scale, _np_ptr(out)))
+        return out
+
     def prefill(self, embeddings, cos_all, sin_all, n: int, scale: float):
         self.prefill_from(embeddings, cos_all, sin_all, n, scale, 0)
 

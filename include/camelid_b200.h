@@ -76,6 +76,7 @@ typedef struct {
 #define CMLD_FLAG_NO_GRAPH 1u     /* launch kernels directly instead of replaying a CUDA graph */
 #define CMLD_FLAG_DIRECT_GEMV 2u  /* use the direct-load matvec kernel everywhere (no staged kernel) */
 #define CMLD_FLAG_NO_PDL 4u       /* no programmatic dependent launch between kernels */
+#define CMLD_FLAG_EXACT_ORDER 16u   /* every f32 sum in the CPU path's order (bit-level parity work; slow) */
 #define CMLD_FLAG_SPLIT_PROLOGUE 8u /* norm/SwiGLU/quantise in a small kernel of its own instead of the matvec prologue */
 
 typedef struct cmld_engine cmld_engine;
@@ -156,6 +157,11 @@ CMLD_API int32_t cmld_engine_forward_token_logits(cmld_engine *e, const float *e
 CMLD_API int32_t cmld_engine_forward_token_hidden(cmld_engine *e, const float *embedding, const float *cosv,
                                                   const float *sinv, int64_t position, float scale,
                                                   float *hidden_out, float *layer_taps);
+/* One layer only (no counterpart in the reference; for per-layer parity checks): runs layer
+ * `layer` on hidden_in[hidden] — the residual stream entering that layer — at `position`, writes
+ * that layer's KV row, and returns the residual stream leaving it in hidden_out[hidden]. */
+CMLD_API int32_t cmld_engine_forward_layer(cmld_engine *e, int32_t layer, const float *hidden_in, const float *cosv,
+                                           const float *sinv, int64_t position, float scale, float *hidden_out);
 /* prefill / prefill_from (src/cuda_resident.rs:20266-20316): n positions of one sequence,
  * embeddings[n][hidden], cos_all/sin_all[n][rope_dim/2]; positions [0,start) are kept. */
 CMLD_API int32_t cmld_engine_prefill_from(cmld_engine *e, const float *embeddings, const float *cos_all,

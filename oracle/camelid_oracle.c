@@ -764,6 +764,50 @@ ORACLE_API int orc_attention_head(const float *q, const float *k, const float *v
   return 0;
 }
 
+/* The expf algorithm the CUDA library restates (camelid_b200/csrc/expf_exact.cuh), written the same
+ * way in C so that a CPU test can compare it with this machine's libm expf over many inputs. */
+ORACLE_API float orc_expf_twin(float x) {
+  static const uint64_t T[32] = {
+      0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+      0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+      0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+      0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+      0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+      0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+      0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+      0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull};
+  if (x != x) return x;
+  if (x > 0x1.62e42ep6f) return INFINITY;
+  if (x < -0x1.9fe368p6f) return 0.0f;
+  double xd = (double)x;
+  double z = (0x1.71547652b82fep+0 * 32.0) * xd;
+  double kd = z + 0x1.8p+52;
+  uint64_t ki;
+  memcpy(&ki, &kd, 8);
+  kd = kd - 0x1.8p+52;
+  double r = z - kd;
+  uint64_t t = T[ki & 31] + (ki << 47);
+  double s;
+  memcpy(&s, &t, 8);
+  double zz = (0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0) * r + 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
+  double r2 = r * r;
+  double y = (0x1.62e42ff0c52d6p-1 / 32.0) * r + 1.0;
+  y = zz * r2 + y;
+  y = y * s;
+  return (float)y;
+}
+
+/* Count of inputs in [lo, hi] (n evenly spaced floats) where the twin and libm expf differ. */
+ORACLE_API int64_t orc_expf_twin_mismatches(float lo, float hi, int64_t n) {
+  int64_t bad = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    float x = lo + (hi - lo) * (float)((double)i / (double)(n - 1));
+    float a = orc_expf_twin(x), b = expf(x);
+    if (f32_bits(a) != f32_bits(b)) ++bad;
+  }
+  return bad;
+}
+
 /* src/inference.rs:13231-13236 (SwiGLU line). */
 ORACLE_API void orc_silu_mul(const float *g, const float *u, int64_t n, float *out) {
   for (int64_t i = 0; i < n; ++i) out[i] = (g[i] / (1.0f + expf(-g[i]))) * u[i];

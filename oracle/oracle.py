@@ -78,6 +78,8 @@ def lib(path: str | os.PathLike | None = None):
         "orc_forward": (C.c_int, [vp, vp, i64, vp, vp, vp]),
         "orc_generate": (C.c_int, [vp, vp, i32, i32, i64, vp, vp]),
         "orc_generate_gaps": (C.c_int, [vp, vp, i32, i32, i64, vp, vp, vp]),
+        "orc_expf_twin": (f32, [f32]),
+        "orc_expf_twin_mismatches": (i64, [f32, f32, i64]),
         "orc_num_threads": (C.c_int, []),
         "orc_set_num_threads": (None, [C.c_int]),
     }

@@ -1,0 +1,142 @@
+"""Parity at BASELINE's model shapes (B200, through the C ABI).
+
+Config 1 runs in full: Llama-3.2-1B-shaped, all Q8_0, 32-token prompt, 128 greedy tokens, against
+the CPU checker holding byte-identical weights.  The larger configs are run at their true widths
+(hidden, heads, ffn, vocab) but with fewer layers so the CPU checker finishes in seconds; the
+arithmetic of a layer does not depend on how many follow it.
+Gates: per-layer hidden and logits within max-abs 2e-2 / relative 1e-2; >= 32 equal greedy tokens.
+"""
+import numpy as np
+import pytest
+
+from helpers import ModelPair, greedy_match, hidden_gate
+
+pytestmark = pytest.mark.gpu
+
+
+def _per_layer(pair, orc, prompt, n_positions):
+    """Per-layer agreement with identical inputs: layer l of the engine is fed the checker's own
+    residual stream entering layer l (at every position, so its KV rows are built from the same
+    inputs too) and must return the checker's residual stream leaving it.
+
+    Why layer by layer: the reference quantises every matvec operand to int8.  A value that is
+    1e-6 away (f32 reassociation) from a rounding boundary gets the neighbouring code; in a block
+    that holds an outlier activation one code step is a large absolute step, and the checker
+    itself, fed inputs perturbed by 1e-6, jumps by >1e-2 in the same way.  Feeding each layer the
+    checker's input measures each layer's own error and keeps one such event from being counted
+    again in every later layer.  Gate per (position, layer): max-abs 2e-2 and relative 1e-2."""
+    eng, ref, cfg = pair.engine, pair.oracle, pair.cfg
+    devs = []
+    for pos in range(n_positions):
+        emb = ref.embedding(int(prompt[pos]))
+        c, s = pair.rope(pos)
+        ref_logits, ref_hidden, ref_taps = ref.forward(emb, pos, want_taps=True)
+        for layer in range(cfg.n_layers):
+            h_in = emb if layer == 0 else ref_taps[layer - 1]
+            h_out = eng.forward_layer(layer, h_in, c, s, pos, pair.scale)
+            devs.append(hidden_gate(h_out, ref_taps[layer]) + (pos, layer))
+    ok = np.array([d[0] for d in devs])
+    max_abs = np.array([d[1] for d in devs])
+    worst = max(devs, key=lambda d: d[1])
+    return float(ok.mean()), float(np.median(max_abs)), worst
+
+
+def _greedy(pair, orc, prompt, n_gen, seq=0):
+    eng, ref = pair.engine, pair.oracle
+    ref_tokens, _, gaps = ref.generate(prompt, n_gen, want_gaps=True)
+    first = eng.prefill_tokens(seq, prompt, 0)
+    rest = eng.decode_greedy([seq], [first], [len(prompt)], n_gen - 1)[:, 0]
+    got = np.concatenate([[first], rest])
+    return greedy_match(got, ref_tokens, gaps)
+
+
+def _run(pair, orc, n_prompt, n_gen, seq=0, layer_positions=6):
+    prompt = orc.synth_tokens(20261125, 5, n_prompt, pair.cfg.vocab)
+    frac_ok, median_dev, worst = _per_layer(pair, orc, prompt, min(layer_positions, n_prompt))
+    print(f"per-layer: {frac_ok:.3f} of (position, layer) pairs inside the gate, median max-abs {median_dev:.2e}, worst {worst}")
+    # Every pair is expected inside the gate; a pair outside it is an int8 rounding-boundary event
+    # (see _per_layer) and must stay rare.
+    assert frac_ok >= 0.97 and median_dev < 1e-4, (frac_ok, median_dev, worst)
+    return _greedy(pair, orc, prompt, n_gen, seq)
+
+
+EXACT = 16  # CMLD_FLAG_EXACT_ORDER
+
+
+def _bit_identity(pair, orc, prompt, n_positions):
+    """Whole forward passes (no teacher forcing): residual stream after every layer, and logits."""
+    eng, ref, cfg = pair.engine, pair.oracle, pair.cfg
+    equal_taps = equal_logits = total = 0
+    worst = 0.0
+    for pos in range(n_positions):
+        emb = ref.embedding(int(prompt[pos]))
+        c, s = pair.rope(pos)
+        ref_logits, _, ref_taps = ref.forward(emb, pos, want_taps=True)
+        _, taps = eng.forward_token_hidden(emb, c, s, pos, pair.scale, taps=True)
+        logits = eng.forward_token_logits(emb, c, s, pos, pair.scale)
+        equal_taps += int(np.array_equal(taps, ref_taps))
+        equal_logits += int(np.array_equal(logits, ref_logits))
+        worst = max(worst, float(np.abs(taps - ref_taps).max()), float(np.abs(logits - ref_logits).max()))
+        total += 1
+    return equal_taps, equal_logits, total, worst
+
+
+def test_config1_llama_1b_q8_0_reference_order_is_bit_identical(cm, orc):
+    """Config 1 in full with every f32 sum in the CPU path's order: the residual stream after each
+    of the 16 layers, the logits and all 128 greedy tokens equal the CPU checker's bit for bit."""
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("llama-1b", max_pos=512, flags=EXACT)
+    pair = ModelPair(cfg, "q8_0", seed=20261125)
+    prompt = orc.synth_tokens(20261125, 5, 32, cfg.vocab)
+    eq_t, eq_l, total, worst = _bit_identity(pair, orc, prompt, 6)
+    print(f"reference order: taps bit-identical at {eq_t}/{total} positions, logits at {eq_l}/{total}, worst abs diff {worst:.2e}")
+    assert eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
+    n_match, gap = _greedy(pair, orc, prompt, 128)
+    print(f"config 1, reference order: {n_match}/128 greedy tokens equal")
+    assert n_match == 128, (n_match, gap)
+
+
+@pytest.mark.parametrize("shape,layers", [("llama-3b", 4), ("llama-8b", 3)])
+def test_k_quant_mix_reference_order_is_bit_identical(cm, orc, shape, layers):
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config(shape, max_pos=256, n_layers=layers, flags=EXACT)
+    pair = ModelPair(cfg, "q4_k_m", seed=20261125)
+    prompt = orc.synth_tokens(20261125, 5, 24, cfg.vocab)
+    eq_t, eq_l, total, worst = _bit_identity(pair, orc, prompt, 5)
+    print(f"{shape} reference order: taps bit-identical at {eq_t}/{total} positions, logits {eq_l}/{total}, worst {worst:.2e}")
+    assert eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
+    n_match, gap = _greedy(pair, orc, prompt, 40)
+    assert n_match == 40, (n_match, gap)
+
+
+def test_config1_llama_1b_q8_0_full(cm, orc):
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("llama-1b", max_pos=512)
+    pair = ModelPair(cfg, "q8_0", seed=20261125)
+    n_match, gap = _run(pair, orc, n_prompt=32, n_gen=128)
+    print(f"config 1: {n_match}/128 greedy tokens equal (checker top-2 gap at first difference: {gap})")
+    assert n_match >= 32, (n_match, gap)
+
+
+@pytest.mark.parametrize("shape,layers", [("llama-3b", 4), ("llama-8b", 3)])
+def test_k_quant_mix_at_true_widths(cm, orc, shape, layers):
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config(shape, max_pos=256, n_layers=layers)
+    pair = ModelPair(cfg, "q4_k_m", seed=20261125)
+    n_match, gap = _run(pair, orc, n_prompt=24, n_gen=40)
+    print(f"{shape} x{layers} layers: {n_match}/40 greedy tokens equal (gap {gap})")
+    assert n_match >= 32, (n_match, gap)
+
+
+def test_mixtral_shape_two_layers(cm, orc):
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("mixtral-8x7b", max_pos=128, n_layers=2, max_seqs=2)
+    pair = ModelPair(cfg, "q4_k_m", seed=20261125)
+    n_match, gap = _run(pair, orc, n_prompt=6, n_gen=34, seq=1, layer_positions=3)
+    print(f"mixtral x2 layers: {n_match}/34 greedy tokens equal (gap {gap})")
+    assert n_match >= 32, (n_match, gap)

@@ -268,3 +268,14 @@ def test_synthetic_generator_is_standard_normal_and_pure(orc):
         assert [format(int(v), "08x") for v in x.view(np.uint32)[:8]] == case["first_bits"]
         for name, qt in QT.items():
             assert orc.quantize(qt, x).tobytes().hex() == case["wire_hex"][name]
+
+
+# The CUDA library's expf restates glibc's algorithm (camelid_b200/csrc/expf_exact.cuh); its C twin
+# must agree with this machine's libm expf bit for bit on the ranges SwiGLU and the softmax use.
+def test_expf_twin_matches_libm(orc):
+    L = orc.lib()
+    assert L.orc_expf_twin_mismatches(-110.0, 0.0, 3_000_001) == 0      # softmax: exp(score - max)
+    assert L.orc_expf_twin_mismatches(-30.0, 30.0, 3_000_001) == 0       # SwiGLU: exp(-g)
+    assert L.orc_expf_twin_mismatches(80.0, 95.0, 200_001) == 0          # overflow edge
+    assert L.orc_expf_twin_mismatches(-1e-3, 1e-3, 200_001) == 0
+    assert L.orc_expf_twin(float("-inf")) == 0.0 and L.orc_expf_twin(0.0) == 1.0
