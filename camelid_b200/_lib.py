@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 import re
 from pathlib import Path
 
@@ -50,6 +51,20 @@ def lib():
     if not p.exists():
         raise ImportError(f"{p} is missing: build it with `python -m camelid_b200.build` (needs nvcc); "
                           "this package has no CPU implementation")
+    if "CMLD_NCCL_PATH" not in os.environ:
+        # a sharded engine binds NCCL at run time; point it at the copy PyTorch would load, so that a
+        # process using both ends up with one libnccl.so.2 whichever is imported first
+        try:
+            import importlib.util
+
+            spec = importlib.util.find_spec("nvidia.nccl")
+            for root in (spec.submodule_search_locations if spec else []):
+                cand = Path(root) / "lib" / "libnccl.so.2"
+                if cand.exists():
+                    os.environ["CMLD_NCCL_PATH"] = str(cand)
+                    break
+        except Exception:
+            pass
     L = C.CDLL(str(p))
     vp, i32, i64, u64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float
     P = C.POINTER
@@ -57,6 +72,7 @@ def lib():
         "cmld_last_error": (C.c_char_p, []),
         "cmld_version": (C.c_char_p, []),
         "cmld_device_count": (i32, []),
+        "cmld_set_device": (i32, [i32]),
         "cmld_malloc": (i32, [P(vp), u64]),
         "cmld_free": (i32, [vp]),
         "cmld_memcpy_h2d": (i32, [vp, vp, u64]),
@@ -66,6 +82,8 @@ def lib():
         "cmld_mem_info": (i32, [P(u64), P(u64)]),
         "cmld_engine_create": (i32, [P(Config), P(vp)]),
         "cmld_engine_destroy": (i32, [vp]),
+        "cmld_comm_unique_id": (i32, [vp]),
+        "cmld_engine_comm_init": (i32, [vp, vp, i32, i32]),
         "cmld_engine_set_layer": (i32, [vp, i32, P(Tensor), vp, vp]),
         "cmld_engine_set_layer_moe": (i32, [vp, i32, vp, P(Tensor), P(Tensor), P(Tensor)]),
         "cmld_engine_set_output": (i32, [vp, vp, P(Tensor)]),
@@ -94,6 +112,7 @@ def lib():
         "cmld_engine_last_timing": (i32, [vp, P(f32), P(i64)]),
         "cmld_weight_create": (i32, [i32, i64, i64, vp, u64, P(vp)]),
         "cmld_weight_synth": (i32, [i32, u64, u64, i64, i64, i64, f32, P(vp)]),
+        "cmld_weight_shard": (i32, [vp, i64, i64, i64, i64, i64, i64, P(vp)]),
         "cmld_weight_destroy": (i32, [vp]),
         "cmld_weight_wire_bytes": (i64, [vp]),
         "cmld_weight_export_wire": (i32, [vp, vp]),

@@ -69,7 +69,81 @@ static int32_t gemv_launch(const cmld_weight *w, const uint8_t *act, int32_t bat
   return CMLD_OK;
 }
 
+// One CTA per destination row: up to two byte ranges of the source row (the block bytes, and the
+// per-row scale array that the Q8_0 and Q6_K layouts keep behind them).
+struct ShardSeg {
+  int64_t src_off, dst_off, len;
+};
+__global__ void weight_shard_kernel(const uint8_t *__restrict__ src, int64_t src_stride, uint8_t *__restrict__ dst,
+                                    int64_t dst_stride, int64_t block_rows, int64_t first_block, int64_t block_step,
+                                    ShardSeg s0, ShardSeg s1) {
+  const int64_t r = blockIdx.x;
+  const int64_t src_row = (first_block + (r / block_rows) * block_step) * block_rows + r % block_rows;
+  const uint8_t *sp = src + src_row * src_stride;
+  uint8_t *dp = dst + r * dst_stride;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const ShardSeg g = k ? s1 : s0;
+    if (((g.src_off | g.dst_off | g.len | src_stride | dst_stride) & 15) == 0) {
+      const uint4 *a = reinterpret_cast<const uint4 *>(sp + g.src_off);
+      uint4 *b = reinterpret_cast<uint4 *>(dp + g.dst_off);
+      for (int64_t i = threadIdx.x; i < g.len / 16; i += blockDim.x) b[i] = a[i];
+    } else {
+      for (int64_t i = threadIdx.x; i < g.len; i += blockDim.x) dp[g.dst_off + i] = sp[g.src_off + i];
+    }
+  }
+}
+
 extern "C" {
+
+int32_t cmld_weight_shard(const cmld_weight *src, int64_t block_rows, int64_t first_block, int64_t block_step,
+                          int64_t n_blocks, int64_t col0, int64_t n_cols, cmld_weight **out) {
+  if (!src || !out) return fail(CMLD_ERR_INVALID, "null weight or out pointer");
+  *out = nullptr;
+  if (block_rows <= 0 || n_blocks <= 0 || first_block < 0 || block_step < 1 ||
+      (first_block + (n_blocks - 1) * block_step + 1) * block_rows > src->rows)
+    return fail(CMLD_ERR_SHAPE, "row blocks %lld + %lld*k (k < %lld) of %lld rows leave the %lld-row tensor",
+                (long long)first_block, (long long)block_step, (long long)n_blocks, (long long)block_rows, (long long)src->rows);
+  const int64_t blk = src->qt == CMLD_F32 ? 1 : (src->qt == CMLD_Q8_0 ? 32 : 256);
+  if (col0 < 0 || n_cols <= 0 || col0 + n_cols > src->cols || col0 % blk || n_cols % blk)
+    return fail(CMLD_ERR_SHAPE, "columns %lld..%lld are not whole %lld-value blocks of the %lld-column tensor", (long long)col0,
+                (long long)(col0 + n_cols), (long long)blk, (long long)src->cols);
+  cmld_weight *w = new cmld_weight();
+  int32_t rc = weight_alloc(*w, src->qt, block_rows * n_blocks, n_cols);
+  if (rc != CMLD_OK) {
+    delete w;
+    return rc;
+  }
+  ShardSeg s0{0, 0, 0}, s1{0, 0, 0};
+  switch (src->qt) {
+    case CMLD_F32: s0 = {col0 * 4, 0, n_cols * 4}; break;
+    case CMLD_Q4_K: s0 = {col0 / 256 * 144, 0, n_cols / 256 * 144}; break;
+    case CMLD_Q6_K:
+      s0 = {col0 / 256 * 208, 0, n_cols / 256 * 208};
+      s1 = {src->cols / 256 * 208 + col0 / 256 * 2, n_cols / 256 * 208, n_cols / 256 * 2};
+      break;
+    default:  // Q8_0
+      s0 = {col0, 0, n_cols};
+      s1 = {src->cols + col0 / 32 * 2, n_cols, n_cols / 32 * 2};
+      break;
+  }
+  // the padding behind a row is never read as data, but keep it defined
+  cudaError_t ce = cudaMemset(w->data, 0, (size_t)(w->rows * w->stride));
+  if (ce == cudaSuccess) {
+    weight_shard_kernel<<<(unsigned)w->rows, 256>>>(src->data, src->stride, w->data, w->stride, block_rows, first_block,
+                                                    block_step, s0, s1);
+    ce = cudaGetLastError();
+  }
+  if (ce == cudaSuccess) rc = sync_ok("weight_shard");
+  else rc = fail(CMLD_ERR_CUDA, "weight_shard: %s", cudaGetErrorString(ce));
+  if (rc != CMLD_OK) {
+    weight_free(*w);
+    delete w;
+    return rc;
+  }
+  *out = w;
+  return CMLD_OK;
+}
 
 int32_t cmld_weight_create(int32_t qtype, int64_t rows, int64_t cols, const void *wire, uint64_t nbytes, cmld_weight **out) {
   if (!out) return fail(CMLD_ERR_INVALID, "null out pointer");

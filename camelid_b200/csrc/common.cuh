@@ -198,9 +198,11 @@ struct NormQuantArgs {
   int32_t exact;               // RMSNorm: add the squares one after another like the CPU (slow)
 };
 int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s);
+// key_out != null: a vocabulary shard — the final stage writes the packed (value, idx_offset + index)
+// key per row instead of the token, and leaves the feedback to launch_argmax_finish.
 int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx,
                       uint32_t *ticket, int32_t *out_idx, int32_t *next_tokens, int32_t *positions,
-                      int32_t *history, cudaStream_t s);
+                      int32_t *history, cudaStream_t s, unsigned long long *key_out = nullptr, int32_t idx_offset = 0);
 int argmax_blocks();
 
 struct RopeKvArgs {
@@ -240,6 +242,21 @@ struct AttnArgs {
   int32_t pdl;                     // launch with programmatic stream serialisation
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
+
+// comm.cu: NCCL collectives of the sharded engine
+int32_t comm_unique_id(uint8_t *out128);
+int32_t comm_init(void **comm_out, const uint8_t *id128, int rank, int world);
+void comm_destroy(void *comm);
+int32_t comm_wait_stream(void **comm, cudaStream_t s, int64_t limit_ms, void (*before_abort)(void *), void *ctx);
+int32_t comm_allreduce_sum_f32(void *comm, float *buf, int64_t count, cudaStream_t s);
+int32_t comm_allreduce_max_u64(void *comm, unsigned long long *buf, int64_t count, cudaStream_t s);
+int32_t comm_allgather_f32(void *comm, const float *send, float *recv, int64_t count_per_rank, cudaStream_t s);
+
+// ops.cu: helpers of the sharded step
+int32_t launch_residual_add(float *h, const float *delta, int64_t n, bool pdl, cudaStream_t s);
+int32_t launch_argmax_finish(const unsigned long long *keys, int32_t batch, int32_t *out_idx, int32_t *next_tokens,
+                             int32_t *positions, int32_t *history, uint32_t *ticket_base, cudaStream_t s);
+int32_t launch_gather_permute(const float *gathered, float *out, int32_t ranks, int32_t batch, int64_t per_rank, cudaStream_t s);
 
 // exact.cu: reference-order kernels (q already rotated, KV already appended for the attention)
 int32_t launch_gemv_exact(const GemvJob &J, const uint8_t *act, int32_t batch, cudaStream_t s);

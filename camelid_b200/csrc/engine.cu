@@ -109,7 +109,13 @@ struct LayerW {
 using namespace cmld;
 
 struct cmld_engine {
-  cmld_config cfg{};
+  cmld_config cfg{};   // dimensions of THIS rank: n_heads, n_kv_heads and ffn_dim are the tensor-parallel shares
+  cmld_config full{};  // the model's dimensions as given to cmld_engine_create
+  int32_t tp = 1, ep = 1, shard_rank = 0;
+  int32_t vocab_local = 0;  // rows of the output matrix held here
+  void *comm = nullptr;     // NCCL communicator of a sharded engine
+  unsigned long long *am_keys = nullptr;  // packed (value, index) per row for the sharded argmax
+  float *logits_gather = nullptr, *logits_full = nullptr;
   int device = 0;
   cudaStream_t stream = nullptr;
   int32_t max_rows = 0;  // scratch rows (sequences per step)
@@ -247,7 +253,12 @@ static int32_t engine_init(cmld_engine *e) {
   CMLD_TRY(dev_alloc(e, &e->attn, R * e->q_width));
   CMLD_TRY(dev_alloc(e, &e->gate, R * c.ffn_dim));
   CMLD_TRY(dev_alloc(e, &e->up, R * c.ffn_dim));
-  CMLD_TRY(dev_alloc(e, &e->logits, R * c.vocab));
+  CMLD_TRY(dev_alloc(e, &e->logits, R * (int64_t)e->vocab_local));
+  CMLD_TRY(dev_alloc(e, &e->am_keys, R));
+  if (e->tp > 1) {
+    CMLD_TRY(dev_alloc(e, &e->logits_gather, R * (int64_t)c.vocab));
+    CMLD_TRY(dev_alloc(e, &e->logits_full, R * (int64_t)c.vocab));
+  }
   CMLD_TRY(dev_alloc(e, &e->taps, (int64_t)c.n_layers * R * c.hidden));
   const int64_t widest = std::max<int64_t>(std::max(c.hidden, c.ffn_dim), e->q_width);
   CMLD_TRY(dev_alloc(e, &e->act_k, R * act_row_stride(widest)));
@@ -285,8 +296,13 @@ static int32_t engine_init(cmld_engine *e) {
 }
 
 static void engine_free(cmld_engine *e) {
+  // Graphs first, communicator second: NCCL counts the graphs that captured its collectives and its
+  // teardown waits until the last of them is gone.
   for (auto &kv : e->graphs)
     if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+  e->graphs.clear();
+  comm_destroy(e->comm);
+  e->comm = nullptr;
   for (auto &L : e->layers) {
     for (auto &w : L.proj) weight_free(w);
     for (auto &w : L.exps) weight_free(w);
@@ -449,6 +465,14 @@ int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local
 int32_t moe_combine(float *h, const float *down, const float *sel_w, const int32_t *sel_idx, int hidden, int k, int batch,
                     int first_expert, int expert_step, bool add_residual, cudaStream_t s);
 
+// Sum of the ranks' partial sublayer outputs, in place.  Rank 0's partial carries the residual.
+static int32_t reduce_hidden(cmld_engine *e, int32_t B) {
+  if (!e->comm) return CMLD_OK;
+  CMLD_TRY(comm_allreduce_sum_f32(e->comm, e->h, (int64_t)B * e->cfg.hidden, e->stream));
+  e->launches += 1;
+  return CMLD_OK;
+}
+
 static int ep_size(const cmld_engine *e) { return std::max(1, e->cfg.ep_size); }
 
 // Mixtral FFN on e->normed (f32): route, expert gate/up, SwiGLU, expert down, weighted sum.
@@ -471,14 +495,27 @@ static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
   CMLD_TRY(launch_norm_quant(a, e->stream));
   CMLD_TRY(moe_expert_gemv(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts,
                            e->moe_lists, na, e->stream));
-  CMLD_TRY(moe_combine(e->h, e->moe_down, e->moe_sel_w, e->moe_sel_idx, c.hidden, k, B, first, step, true, e->stream));
+  CMLD_TRY(moe_combine(e->h, e->moe_down, e->moe_sel_w, e->moe_sel_idx, c.hidden, k, B, first, step,
+                       e->ep == 1 || e->shard_rank == 0, e->stream));
   e->launches += 7;
+  if (e->ep > 1) CMLD_TRY(reduce_hidden(e, B));
+  return CMLD_OK;
+}
+
+// [rows][vocab] logits of a vocabulary-sharded engine, assembled on every rank in e->logits_full.
+static int32_t gather_logits(cmld_engine *e, int32_t B) {
+  CMLD_TRY(comm_allgather_f32(e->comm, e->logits, e->logits_gather, (int64_t)B * e->vocab_local, e->stream));
+  CMLD_TRY(launch_gather_permute(e->logits_gather, e->logits_full, e->tp, B, e->vocab_local, e->stream));
   return CMLD_OK;
 }
 
 static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   const cmld_config &c = e->cfg;
   const int32_t B = o.batch;
+  const bool sharded = e->tp > 1 || e->ep > 1;
+  if (sharded && !e->comm)
+    return fail(CMLD_ERR_STATE, "this sharded engine has no communicator (cmld_engine_comm_init not called, or aborted after a peer stopped answering)");
+  const bool lead = e->shard_rank == 0;  // the rank whose partial sums carry the residual
   if (B < 1 || B > e->max_rows) return fail(CMLD_ERR_INVALID, "step of %d rows exceeds the engine's %d", B, e->max_rows);
   if (o.from_tokens) {
     if (!e->has_embd) return fail(CMLD_ERR_STATE, "token embedding table not set");
@@ -553,8 +590,9 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       e->launches += 1;
     }
     {
-      const Proj p[1] = {{&L.proj[3], e->h, e->h, c.hidden}};
+      const Proj p[1] = {{&L.proj[3], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
       CMLD_TRY(gemv_fused(e, p, 1, B, 2, e->attn, nullptr, nullptr, e->q_width));
+      if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
     }
     if (L.moe_set) {
       CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.ffn_norm, c.hidden, B, e->normed, false, false));
@@ -562,8 +600,9 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
     } else {
       const Proj p[2] = {{&L.proj[4], e->gate, nullptr, c.ffn_dim}, {&L.proj[5], e->up, nullptr, c.ffn_dim}};
       CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden));
-      const Proj pd[1] = {{&L.proj[6], e->h, e->h, c.hidden}};
+      const Proj pd[1] = {{&L.proj[6], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
       CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim));
+      if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
     }
     if (o.taps) {
       CMLD_CUDA(cudaMemcpyAsync(e->taps + (int64_t)li * e->max_rows * c.hidden, e->h, (size_t)B * c.hidden * 4,
@@ -572,12 +611,20 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   }
   if (o.logits) {
     if (!e->has_output) return fail(CMLD_ERR_STATE, "output weights not set");
-    const Proj p[1] = {{&e->output, e->logits, nullptr, c.vocab}};
+    const Proj p[1] = {{&e->output, e->logits, nullptr, e->vocab_local}};
     CMLD_TRY(gemv_fused(e, p, 1, B, 1, e->h, nullptr, e->final_norm, c.hidden));
-    if (o.argmax) {
+    if (o.argmax && e->tp == 1) {
       CMLD_TRY(launch_argmax(e->logits, c.vocab, B, e->am_val, e->am_idx, e->am_ticket, e->out_idx,
                              o.feed_back ? e->d_tokens : nullptr, e->d_positions, e->d_history, e->stream));
       e->launches += 1;
+    } else if (o.argmax) {
+      // vocabulary shard: local best as a packed key, max over the ranks, then the feedback
+      CMLD_TRY(launch_argmax(e->logits, e->vocab_local, B, e->am_val, e->am_idx, e->am_ticket, e->out_idx, nullptr,
+                             e->d_positions, e->d_history, e->stream, e->am_keys, e->shard_rank * e->vocab_local));
+      CMLD_TRY(comm_allreduce_max_u64(e->comm, e->am_keys, B, e->stream));
+      CMLD_TRY(launch_argmax_finish(e->am_keys, B, e->out_idx, o.feed_back ? e->d_tokens : nullptr, e->d_positions,
+                                    e->d_history, e->am_ticket, e->stream));
+      e->launches += 3;
     }
   }
   return CMLD_OK;
@@ -646,6 +693,23 @@ static int32_t stage_rows(cmld_engine *e, int32_t n, const int32_t *tokens, cons
 static int32_t finish(cmld_engine *e, const char *what) {
   int32_t st = 0;
   cudaError_t ce = cudaMemcpyAsync(&st, e->d_status, 4, cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess && e->comm) {
+    // sharded: a bounded wait, so a rank whose peer went away returns an error instead of hanging
+    static const int64_t limit_ms = [] {
+      const char *v = getenv("CMLD_COMM_TIMEOUT_MS");
+      const long long n = v ? atoll(v) : 0;
+      return (int64_t)(n > 0 ? n : 120000);
+    }();
+    const int32_t wrc = comm_wait_stream(&e->comm, e->stream, limit_ms, [](void *ctx) {
+      // before the abort: release the graphs that captured the communicator's collectives (an exec that
+      // is still running is freed when it completes), or NCCL's teardown would wait for them for ever
+      cmld_engine *eng = static_cast<cmld_engine *>(ctx);
+      for (auto &kv : eng->graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+      eng->graphs.clear();
+    }, e);
+    if (wrc != CMLD_OK) return wrc;
+  }
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
   if (st != 0) {
@@ -704,6 +768,11 @@ int32_t cmld_device_count(void) {
   return n;
 }
 
+int32_t cmld_set_device(int32_t device) {
+  CMLD_CUDA(cudaSetDevice(device));
+  return CMLD_OK;
+}
+
 int32_t cmld_malloc(void **dev_ptr, uint64_t nbytes) {
   if (!dev_ptr) return fail(CMLD_ERR_INVALID, "null out pointer");
   CMLD_CUDA(cudaMalloc(dev_ptr, (size_t)std::max<uint64_t>(nbytes, 1)));
@@ -737,10 +806,44 @@ int32_t cmld_mem_info(uint64_t *free_bytes, uint64_t *total_bytes) {
   return CMLD_OK;
 }
 
-int32_t cmld_engine_create(const cmld_config *cfg, cmld_engine **out) {
-  if (!cfg || !out) return fail(CMLD_ERR_INVALID, "config or out pointer is null");
+// The dimensions one rank of a tensor-parallel group holds.  Heads split by kv group, so that a query
+// head and its kv head stay on one rank; o and down split by columns on 256-value boundaries (a whole
+// K-quant superblock); the vocabulary splits by rows.
+static int32_t shard_config(const cmld_config &full, cmld_config &local, int32_t &tp, int32_t &ep, int32_t &rank) {
+  local = full;
+  tp = std::max(1, full.tp_size);
+  ep = std::max(1, full.ep_size);
+  rank = 0;
+  if (tp > 1 && ep > 1) return fail(CMLD_ERR_UNSUPPORTED, "tensor and expert parallelism cannot be combined");
+  if (tp > 1) {
+    if (full.n_experts > 0) return fail(CMLD_ERR_UNSUPPORTED, "a Mixtral-shaped model shards by experts (ep_size), not tp_size");
+    if (full.tp_rank < 0 || full.tp_rank >= tp) return fail(CMLD_ERR_INVALID, "tp_rank %d outside 0..%d", full.tp_rank, tp - 1);
+    if (full.n_kv_heads % tp || full.vocab % tp || full.ffn_dim % (tp * 256) ||
+        ((full.n_heads / tp) * full.head_dim) % 256)
+      return fail(CMLD_ERR_SHAPE, "tp_size %d does not divide kv heads %d / vocab %d, or leaves ffn %d / attention width %d "
+                  "shares that are not multiples of 256", tp, full.n_kv_heads, full.vocab, full.ffn_dim, full.n_heads * full.head_dim);
+    local.n_heads = full.n_heads / tp;
+    local.n_kv_heads = full.n_kv_heads / tp;
+    local.ffn_dim = full.ffn_dim / tp;
+    rank = full.tp_rank;
+  }
+  if (ep > 1) {
+    if (full.n_experts <= 0 || full.n_experts % ep) return fail(CMLD_ERR_SHAPE, "ep_size %d does not divide %d experts", ep, full.n_experts);
+    if (full.ep_rank < 0 || full.ep_rank >= ep) return fail(CMLD_ERR_INVALID, "ep_rank %d outside 0..%d", full.ep_rank, ep - 1);
+    rank = full.ep_rank;
+  }
+  return CMLD_OK;
+}
+
+int32_t cmld_engine_create(const cmld_config *cfg_in, cmld_engine **out) {
+  if (!cfg_in || !out) return fail(CMLD_ERR_INVALID, "config or out pointer is null");
   *out = nullptr;
-  CMLD_TRY(validate_config(*cfg));
+  CMLD_TRY(validate_config(*cfg_in));
+  cmld_config local{};
+  int32_t tp = 1, ep = 1, shard_rank = 0;
+  CMLD_TRY(shard_config(*cfg_in, local, tp, ep, shard_rank));
+  CMLD_TRY(validate_config(local));
+  const cmld_config *cfg = &local;
   int ndev = 0;
   if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) {
     cudaGetLastError();
@@ -762,7 +865,12 @@ int32_t cmld_engine_create(const cmld_config *cfg, cmld_engine **out) {
   if (kv_bytes > 0.95 * (double)free_b)
     return fail(CMLD_ERR_OOM, "KV cache of %.1f GiB does not fit in %.1f GiB free", kv_bytes / (1 << 30), (double)free_b / (1 << 30));
   cmld_engine *e = new cmld_engine();
-  e->cfg = *cfg;
+  e->cfg = local;
+  e->full = *cfg_in;
+  e->tp = tp;
+  e->ep = ep;
+  e->shard_rank = shard_rank;
+  e->vocab_local = local.vocab / tp;
   e->device = dev;
   int32_t rc = engine_init(e);
   if (rc != CMLD_OK) {
@@ -780,6 +888,28 @@ int32_t cmld_engine_destroy(cmld_engine *e) {
   cudaStreamSynchronize(e->stream);
   engine_free(e);
   delete e;
+  return CMLD_OK;
+}
+
+int32_t cmld_comm_unique_id(uint8_t out[128]) {
+  if (!out) return fail(CMLD_ERR_INVALID, "null out pointer");
+  return comm_unique_id(out);
+}
+
+int32_t cmld_engine_comm_init(cmld_engine *e, const uint8_t id[128], int32_t rank, int32_t world) {
+  CMLD_ENGINE_ENTER(e);
+  if (!id) return fail(CMLD_ERR_INVALID, "null communicator id");
+  const int32_t want = e->tp > 1 ? e->tp : e->ep;
+  if (want <= 1) return fail(CMLD_ERR_STATE, "this engine is not sharded (tp_size and ep_size are 1)");
+  if (world != want || rank != e->shard_rank)
+    return fail(CMLD_ERR_INVALID, "communicator rank %d of %d does not match the engine's shard %d of %d", rank, world, e->shard_rank, want);
+  if (e->comm) return fail(CMLD_ERR_STATE, "communicator already set");
+  CMLD_TRY(comm_init(&e->comm, id, rank, world));
+  // one small all-reduce now, so that the connections to the peers are made inside this collective
+  // call and not inside the first step
+  CMLD_CUDA(cudaMemsetAsync(e->am_keys, 0, 8, e->stream));
+  CMLD_TRY(comm_allreduce_max_u64(e->comm, e->am_keys, 1, e->stream));
+  CMLD_CUDA(cudaStreamSynchronize(e->stream));
   return CMLD_OK;
 }
 
@@ -834,7 +964,7 @@ int32_t cmld_engine_set_layer_moe(cmld_engine *e, int32_t layer, const float *ro
 int32_t cmld_engine_set_output(cmld_engine *e, const float *final_norm, const cmld_tensor *output) {
   CMLD_ENGINE_ENTER(e);
   if (!output) return fail(CMLD_ERR_INVALID, "set_output: tensor is null");
-  CMLD_TRY(weight_upload(e->output, output->qtype, e->cfg.vocab, e->cfg.hidden, output->data, output->nbytes, e->stream));
+  CMLD_TRY(weight_upload(e->output, output->qtype, e->vocab_local, e->cfg.hidden, output->data, output->nbytes, e->stream));
   if (e->output.qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "set_output: f32 output weights are not supported");
   CMLD_TRY(upload_f32(&e->final_norm, final_norm, e->cfg.hidden, e->stream));
   e->has_output = true;
@@ -854,6 +984,19 @@ static int32_t adopt(Weight &dst, cmld_weight *src, int64_t rows, int64_t cols, 
     return fail(CMLD_ERR_SHAPE, "%s: weight is %lld x %lld, expected %lld x %lld", what, (long long)src->rows, (long long)src->cols,
                 (long long)rows, (long long)cols);
   if (src->qt == CMLD_F32 && !allow_f32) return fail(CMLD_ERR_UNSUPPORTED, "%s: f32 weights are not supported here", what);
+  {
+    // the matrix must live on the engine's GPU: a kernel reading another GPU's memory without peer
+    // access would fault
+    cudaPointerAttributes pa{};
+    int cur = -1;
+    if (cudaPointerGetAttributes(&pa, src->data) != cudaSuccess || cudaGetDevice(&cur) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(CMLD_ERR_CUDA, "%s: cannot query where the weight lives", what);
+    }
+    if (pa.type != cudaMemoryTypeDevice || pa.device != cur)
+      return fail(CMLD_ERR_INVALID, "%s: weight lives on device %d, the engine on device %d (cmld_set_device before making weights)",
+                  what, pa.device, cur);
+  }
   weight_free(dst);
   dst = *src;
   src->data = nullptr;
@@ -910,7 +1053,7 @@ int32_t cmld_engine_adopt_layer_moe(cmld_engine *e, int32_t layer, cmld_weight *
 int32_t cmld_engine_adopt_output(cmld_engine *e, const float *final_norm, cmld_weight *output) {
   CMLD_ENGINE_ENTER(e);
   if (!output) return fail(CMLD_ERR_INVALID, "adopt_output: weight is null");
-  CMLD_TRY(adopt(e->output, output, e->cfg.vocab, e->cfg.hidden, "adopt_output"));
+  CMLD_TRY(adopt(e->output, output, e->vocab_local, e->cfg.hidden, "adopt_output"));
   CMLD_TRY(upload_f32(&e->final_norm, final_norm, e->cfg.hidden, e->stream));
   e->has_output = true;
   return CMLD_OK;
@@ -972,7 +1115,8 @@ int32_t cmld_engine_forward_token_logits(cmld_engine *e, const float *embedding,
   CMLD_ENGINE_ENTER(e);
   if (!logits_out) return fail(CMLD_ERR_INVALID, "logits_out is null");
   CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, true, false, false));
-  CMLD_CUDA(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (e->tp > 1) CMLD_TRY(gather_logits(e, 1));
+  CMLD_CUDA(cudaMemcpyAsync(logits_out, e->tp > 1 ? e->logits_full : e->logits, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
   return finish(e, "forward_token_logits");
 }
 
@@ -1118,7 +1262,8 @@ int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *se
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> toks(n_seqs);
   CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, e->stream));
-  if (logits_out) CMLD_CUDA(cudaMemcpyAsync(logits_out, e->logits, (size_t)n_seqs * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+  if (logits_out && e->tp > 1) CMLD_TRY(gather_logits(e, n_seqs));
+  if (logits_out) CMLD_CUDA(cudaMemcpyAsync(logits_out, e->tp > 1 ? e->logits_full : e->logits, (size_t)n_seqs * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
   if (hidden_out) CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)n_seqs * e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
   CMLD_TRY(finish(e, "step_batch"));
   cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);

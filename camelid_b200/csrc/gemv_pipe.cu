@@ -6,7 +6,7 @@
 // between dependent launches.  So:
 //   * one persistent CTA per SM walks its share of row tiles; a tile of consecutive rows is one
 //     contiguous byte range of the device layout, fetched by ONE bulk asynchronous copy
-//     (cp.async.bulk, the non-tensor TMA path; never multicast) into a shared-memory ring of up
+//     (cp.async.bulk, the non-tensor TMA path) into a shared-memory ring of up
 //     to 8 stages guarded by mbarriers (full: transaction bytes, empty: one arrival per warp);
 //   * a dedicated producer warp issues the copies; it starts BEFORE the kernel waits on its
 //     predecessor (griddepcontrol.wait), because weights never depend on earlier kernels — under

@@ -249,7 +249,7 @@ __device__ __forceinline__ void argmax_combine(float &v, int &i, float ov, int o
 __global__ void __launch_bounds__(kArgmaxThreads)
     argmax_kernel(const float *__restrict__ x, int64_t n, float *part_val, int32_t *part_idx, uint32_t *ticket,
                   int32_t *out_idx, int32_t *next_tokens, int32_t *positions, int32_t *history, int32_t *hist_len,
-                  int32_t batch) {
+                  int32_t batch, unsigned long long *key_out, int32_t idx_offset) {
   const int b = blockIdx.y;
   const float *row = x + (int64_t)b * n;
   const int64_t per = (n + gridDim.x - 1) / gridDim.x;
@@ -293,8 +293,16 @@ __global__ void __launch_bounds__(kArgmaxThreads)
     for (int o = 16; o > 0; o >>= 1) argmax_combine(v, i, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, i, o));
     if (lane == 0) {
       if (i == 0x7fffffff) i = 0;  // all-NaN or -inf row
-      out_idx[b] = i;
       ticket[b] = 0;
+      if (key_out) {
+        // order-preserving bits of the value above, inverted global index below: an unsigned max over
+        // the shards picks the largest value and, among equals, the lowest index
+        uint32_t u = __float_as_uint(v);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        key_out[b] = ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (uint32_t)(i + idx_offset));
+        return;
+      }
+      out_idx[b] = i;
       if (next_tokens) {
         next_tokens[b] = i;
         positions[b] += 1;
@@ -308,7 +316,8 @@ __global__ void __launch_bounds__(kArgmaxThreads)
 
 // history: [max_steps][batch] ids; hist_len lives right after the tickets: ticket[batch..2*batch).
 int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx, uint32_t *ticket,
-                      int32_t *out_idx, int32_t *next_tokens, int32_t *positions, int32_t *history, cudaStream_t s) {
+                      int32_t *out_idx, int32_t *next_tokens, int32_t *positions, int32_t *history, cudaStream_t s,
+                      unsigned long long *key_out, int32_t idx_offset) {
   static bool carveout_set = false;
   if (!carveout_set) {
     prefer_max_smem_carveout(argmax_kernel);
@@ -317,7 +326,64 @@ int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val,
   }
   dim3 grid(kArgmaxBlocks, (unsigned)batch);
   argmax_kernel<<<grid, kArgmaxThreads, 0, s>>>(x, n, part_val, part_idx, ticket, out_idx, next_tokens, positions, history,
-                                                reinterpret_cast<int32_t *>(ticket) + batch, batch);
+                                                reinterpret_cast<int32_t *>(ticket) + batch, batch, key_out, idx_offset);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+// ------------------------------------------------------------------ helpers of the sharded step
+
+__global__ void residual_add_kernel(float *__restrict__ h, const float *__restrict__ delta, int64_t n) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    h[i] = __fadd_rn(h[i], delta[i]);
+}
+
+int32_t launch_residual_add(float *h, const float *delta, int64_t n, bool pdl, cudaStream_t s) {
+  (void)pdl;  // follows a collective: ordinary stream order
+  residual_add_kernel<<<(unsigned)std::min<int64_t>((n + 255) / 256, 1024), 256, 0, s>>>(h, delta, n);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+// After the all-reduce(max) of the packed keys: token = inverted low word; feed it back.
+__global__ void argmax_finish_kernel(const unsigned long long *__restrict__ keys, int32_t batch, int32_t *out_idx,
+                                     int32_t *next_tokens, int32_t *positions, int32_t *history, int32_t *hist_len) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int i = (int)(0xffffffffu - (uint32_t)(keys[b] & 0xffffffffull));
+  out_idx[b] = i;
+  if (next_tokens) {
+    next_tokens[b] = i;
+    positions[b] += 1;
+    const int step = hist_len[b];
+    history[(int64_t)step * batch + b] = i;
+    hist_len[b] = step + 1;
+  }
+}
+
+int32_t launch_argmax_finish(const unsigned long long *keys, int32_t batch, int32_t *out_idx, int32_t *next_tokens,
+                             int32_t *positions, int32_t *history, uint32_t *ticket_base, cudaStream_t s) {
+  argmax_finish_kernel<<<(batch + 63) / 64, 64, 0, s>>>(keys, batch, out_idx, next_tokens, positions, history,
+                                                        reinterpret_cast<int32_t *>(ticket_base) + batch);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+// all-gather output [rank][batch][per_rank] -> [batch][rank * per_rank]
+__global__ void gather_permute_kernel(const float *__restrict__ g, float *__restrict__ out, int ranks, int batch, int64_t per_rank) {
+  const int64_t total = (int64_t)ranks * batch * per_rank;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / (batch * per_rank), rem = i % (batch * per_rank);
+    const int64_t b = rem / per_rank, v = rem % per_rank;
+    out[(b * ranks + r) * per_rank + v] = g[i];
+  }
+}
+
+int32_t launch_gather_permute(const float *gathered, float *out, int32_t ranks, int32_t batch, int64_t per_rank, cudaStream_t s) {
+  const int64_t total = (int64_t)ranks * batch * per_rank;
+  gather_permute_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 2048), 256, 0, s>>>(gathered, out, ranks, batch, per_rank);
   CMLD_CUDA(cudaGetLastError());
   return CMLD_OK;
 }

@@ -103,6 +103,13 @@ class Weight:
         check(lib().cmld_weight_synth(qt, seed, stream, row0, rows, cols, sigma, C.byref(h)))
         return cls(h.value, qt, rows, cols)
 
+    def shard(self, sl) -> "Weight":
+        """The part of this matrix that ``sl`` (a ``shard.Slice``) names, as a new device matrix."""
+        h = C.c_void_p()
+        check(lib().cmld_weight_shard(self._h, sl.block_rows, sl.first_block, sl.block_step, sl.n_blocks, sl.col0, sl.n_cols,
+                                      C.byref(h)))
+        return Weight(h.value, self.qt, sl.rows, sl.n_cols)
+
     @property
     def wire_bytes(self) -> int:
         return int(lib().cmld_weight_wire_bytes(self._h))
@@ -203,6 +210,19 @@ class ResidentDecode:
         if getattr(self, "_h", None):
             lib().cmld_engine_destroy(self._h)
             self._h = None
+
+    # -- sharded engines ---------------------------------------------------------
+    @staticmethod
+    def comm_unique_id() -> bytes:
+        """Made on rank 0 and sent to the other ranks by the caller."""
+        buf = (C.c_uint8 * 128)()
+        check(lib().cmld_comm_unique_id(buf))
+        return bytes(buf)
+
+    def comm_init(self, unique_id: bytes, rank: int, world: int):
+        """Collective over the ranks of the tensor- or expert-parallel group."""
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        check(lib().cmld_engine_comm_init(self._h, buf, rank, world))
 
     def __del__(self):
         try:
@@ -345,7 +365,7 @@ class ResidentDecode:
         check(lib().cmld_engine_seed_layer(self._h, layer, _np_ptr(ck), _np_ptr(cv), n_positions))
 
     def read_kv_layer(self, layer: int, n_positions: int):
-        shape = (self.cfg.n_kv_heads, n_positions, self.cfg.head_dim)
+        shape = (self.cfg.n_kv_heads // max(1, self.cfg.tp_size), n_positions, self.cfg.head_dim)
         ck, cv = np.empty(shape, np.float32), np.empty(shape, np.float32)
         check(lib().cmld_engine_read_kv_layer(self._h, layer, n_positions, _np_ptr(ck), _np_ptr(cv)))
         return ck, cv

