@@ -14,7 +14,7 @@ namespace cmld {
 
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
-constexpr int kAttnChunk = 256;  // positions per softmax chunk
+constexpr int kAttnMaxSplits = 64;  // ranges per (sequence, kv head)
 constexpr int kMaxGroup = 8;     // query heads per kv head
 constexpr int kMaxPer = 8;       // head_dim / 32
 
@@ -35,6 +35,17 @@ __device__ __forceinline__ void load_halves(const __half *p, float (&out)[PER]) 
   } else {
 #pragma unroll
     for (int e = 0; e < PER; ++e) out[e] = __half2float(p[e]);
+  }
+}
+
+// Eight consecutive f16 values (one 16-byte load) widened to f32.
+__device__ __forceinline__ void unpack_halves8(const uint4 &raw, float (&out)[8]) {
+  const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
   }
 }
 
@@ -77,10 +88,17 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   if (split >= n_active || pos < 0 || pos >= a.max_pos) return;
   const int lo = split * len, hi = min(n_pos, lo + len);
 
+  // A cache row is HD f16 = LPP 16-byte pieces: LPP lanes share one position, a warp covers PPW positions
+  // at a time, and the CTA's NGRP lane groups stride through the range.  Each group keeps its own
+  // running (max, sum, accumulator) per query head, so the main loop has no CTA-wide barrier at all;
+  // the groups are merged once at the end.
+  constexpr int LPP = HD / 8, PPW = 32 / LPP, NGRP = kAttnWarps * PPW;
+  constexpr int U = 4;  // positions a group has in flight
   __shared__ float s_q[G][HD];
-  __shared__ float s_sc[G][kAttnChunk];
-  __shared__ float s_red[kAttnWarps][G];
   __shared__ float s_acc[kAttnWarps][G][HD];
+  __shared__ float s_m[kAttnWarps][G], s_l[kAttnWarps][G], s_wgt[kAttnWarps][G];
+  __shared__ float s_w[G][kAttnMaxSplits];
+  __shared__ float s_M[G];
   __shared__ bool s_last;
 
   __half *kbase = const_cast<__half *>(a.k_cache) + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
@@ -104,103 +122,120 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) s_q[i / HD][i % HD] = q[i];
   }
   __syncthreads();  // also orders the cache rows written above before this CTA reads them back
-  float qr[G][PER];
+  const int lig = lane % LPP;
+  float qr[G][8];
 #pragma unroll
   for (int g = 0; g < G; ++g)
 #pragma unroll
-    for (int e = 0; e < PER; ++e) qr[g][e] = s_q[g][lane * PER + e];
+    for (int e = 0; e < 8; ++e) qr[g][e] = s_q[g][lig * 8 + e];
 
-  float m_run[G], l_run[G], acc[G][PER];
+  float m_run[G], l_run[G], acc[G][8];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     m_run[g] = -INFINITY;
     l_run[g] = 0.0f;
 #pragma unroll
-    for (int e = 0; e < PER; ++e) acc[g][e] = 0.0f;
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.0f;
   }
 
-  for (int c0 = lo; c0 < hi; c0 += kAttnChunk) {
-    const int cn = min(kAttnChunk, hi - c0);
-    // scores of this chunk
-    for (int p = warp; p < cn; p += kAttnWarps) {
-      const __half *kr = kbase + (int64_t)(c0 + p) * HD + lane * PER;
-      float kv[PER];
-      load_halves<PER>(kr, kv);
+  // The trip count is the same for every lane of a warp (the shuffles below need the whole warp): a
+  // warp walks bases lo + warp*PPW, + NGRP*U, ...; its groups take consecutive positions from the base
+  // and a position beyond the range simply scores -inf.
+  for (int base = lo + warp * PPW; base < hi; base += NGRP * U) {
+    const int p0 = base + lane / LPP;
+    uint4 kraw[U], vraw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int p = p0 + u * NGRP;
+      if (p < hi) {
+        kraw[u] = *reinterpret_cast<const uint4 *>(kbase + (int64_t)p * HD + lig * 8);
+        vraw[u] = *reinterpret_cast<const uint4 *>(vbase + (int64_t)p * HD + lig * 8);
+      } else {
+        kraw[u] = vraw[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    float sc[U][G];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float kf[8];
+      unpack_halves8(kraw[u], kf);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         float d = 0.0f;
 #pragma unroll
-        for (int e = 0; e < PER; ++e) d = __fmaf_rn(qr[g][e], kv[e], d);
-        d = warp_sum(d);
-        if (lane == 0) s_sc[g][p] = __fmul_rn(d, a.scale);
+        for (int e = 0; e < 8; ++e) d = __fmaf_rn(qr[g][e], kf[e], d);
+#pragma unroll
+        for (int o = LPP / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        sc[u][g] = p0 + u * NGRP < hi ? d * a.scale : -INFINITY;
       }
     }
-    __syncthreads();
-    // chunk maximum per head
-    float cm[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float v = -INFINITY;
-      for (int p = threadIdx.x; p < cn; p += kAttnThreads) v = fmaxf(v, s_sc[g][p]);
-      v = warp_max(v);
-      if (lane == 0) s_red[warp][g] = v;
+      float bm = m_run[g];
+#pragma unroll
+      for (int u = 0; u < U; ++u) bm = fmaxf(bm, sc[u][g]);
+      const float corr = bm == -INFINITY ? 1.0f : __expf(m_run[g] - bm);  // first batch: exp(-inf) = 0 on zeros
+      l_run[g] *= corr;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
+      m_run[g] = bm;
     }
-    __syncthreads();
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float v = s_red[0][g];
-#pragma unroll
-      for (int w = 1; w < kAttnWarps; ++w) v = fmaxf(v, s_red[w][g]);
-      cm[g] = fmaxf(m_run[g], v);
-    }
-    __syncthreads();
-    // probabilities in place, running sums
-    float ls[G];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.0f;
-      for (int p = threadIdx.x; p < cn; p += kAttnThreads) {
-        const float e = expf_exact(s_sc[g][p] - cm[g]);
-        s_sc[g][p] = e;
-        s += e;
-      }
-      s = warp_sum(s);
-      if (lane == 0) s_red[warp][g] = s;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.0f;
-#pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) s += s_red[w][g];
-      ls[g] = s;
-      const float corr = m_run[g] == -INFINITY ? 0.0f : expf_exact(m_run[g] - cm[g]);
-      l_run[g] = l_run[g] * corr + ls[g];
-#pragma unroll
-      for (int e = 0; e < PER; ++e) acc[g][e] *= corr;
-      m_run[g] = cm[g];
-    }
-    // weighted values: warp w takes positions w, w+8, ...
-    for (int p = warp; p < cn; p += kAttnWarps) {
-      const __half *vr = vbase + (int64_t)(c0 + p) * HD + lane * PER;
-      float vv[PER];
-      load_halves<PER>(vr, vv);
+    for (int u = 0; u < U; ++u) {
+      float vf[8];
+      unpack_halves8(vraw[u], vf);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        const float pr = s_sc[g][p];
+        const float pr = sc[u][g] == -INFINITY ? 0.0f : __expf(sc[u][g] - m_run[g]);
+        l_run[g] += pr;
 #pragma unroll
-        for (int e = 0; e < PER; ++e) acc[g][e] = __fmaf_rn(pr, vv[e], acc[g][e]);
+        for (int e = 0; e < 8; ++e) acc[g][e] = __fmaf_rn(pr, vf[e], acc[g][e]);
       }
     }
-    __syncthreads();
   }
 
-  // Each warp accumulated a subset of the positions against the shared (m_run, l_run);
-  // add the warps' accumulators.
+  // Merge the PPW groups of each warp by shuffles (same dims, different positions) ...
 #pragma unroll
-  for (int g = 0; g < G; ++g)
+  for (int off = 16; off >= LPP; off >>= 1) {
 #pragma unroll
-    for (int e = 0; e < PER; ++e) s_acc[warp][g][lane * PER + e] = acc[g][e];
+    for (int g = 0; g < G; ++g) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m_run[g], off), lo2 = __shfl_xor_sync(0xffffffffu, l_run[g], off);
+      const float M = fmaxf(m_run[g], mo);
+      const float wa = m_run[g] == -INFINITY ? 0.0f : __expf(m_run[g] - M), wb = mo == -INFINITY ? 0.0f : __expf(mo - M);
+      l_run[g] = l_run[g] * wa + lo2 * wb;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] = acc[g][e] * wa + __shfl_xor_sync(0xffffffffu, acc[g][e], off) * wb;
+      m_run[g] = M;
+    }
+  }
+  // ... then the warps through shared memory.
+  if (lane < LPP) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_acc[warp][g][lane * 8 + e] = acc[g][e];
+      if (lane == 0) {
+        s_m[warp][g] = m_run[g];
+        s_l[warp][g] = l_run[g];
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int g = threadIdx.x;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) M = fmaxf(M, s_m[w][g]);
+    float L = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float wt = s_m[w][g] == -INFINITY ? 0.0f : __expf(s_m[w][g] - M);
+      s_wgt[w][g] = wt;
+      L = __fmaf_rn(s_l[w][g], wt, L);
+    }
+    s_M[g] = M;
+    s_l[0][g] = L;  // the range's sum, read below as s_l[0][g] (warp 0's own value is folded in already)
+  }
   __syncthreads();
   if (n_active == 1) {
     // a single range: normalise in place, no partials through global memory and no ticket
@@ -209,23 +244,22 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
       const int g = i / HD, d = i % HD;
       float sacc = 0.0f;
 #pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) sacc += s_acc[w][g][d];
-      // the merge below computes fma(acc, 1, 0) / fma(l, 1, 0): the same bits
-      out1[i] = __fdiv_rn(sacc, l_run[g]);
+      for (int w = 0; w < kAttnWarps; ++w) sacc = __fmaf_rn(s_acc[w][g][d], s_wgt[w][g], sacc);
+      out1[i] = __fdiv_rn(sacc, s_l[0][g]);
     }
     return;
   }
   float *part = a.part + (((int64_t)b * a.n_heads + (int64_t)kvh * G) * a.n_splits) * (HD + 2);
   for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
     const int g = i / HD, d = i % HD;
-    float s = 0.0f;
+    float sacc = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) s += s_acc[w][g][d];
-    part[((int64_t)g * a.n_splits + split) * (HD + 2) + d] = s;
+    for (int w = 0; w < kAttnWarps; ++w) sacc = __fmaf_rn(s_acc[w][g][d], s_wgt[w][g], sacc);
+    part[((int64_t)g * a.n_splits + split) * (HD + 2) + d] = sacc;
   }
   if (threadIdx.x < G) {
-    part[((int64_t)threadIdx.x * a.n_splits + split) * (HD + 2) + HD] = m_run[threadIdx.x];
-    part[((int64_t)threadIdx.x * a.n_splits + split) * (HD + 2) + HD + 1] = l_run[threadIdx.x];
+    part[((int64_t)threadIdx.x * a.n_splits + split) * (HD + 2) + HD] = s_M[threadIdx.x];
+    part[((int64_t)threadIdx.x * a.n_splits + split) * (HD + 2) + HD + 1] = s_l[0][threadIdx.x];
   }
   __threadfence();
   __syncthreads();
@@ -234,24 +268,23 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   if (!s_last) return;
   __threadfence();
   // merge the ranges: out = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M).
-  // First the per-(head, range) weights in parallel (s_sc is free now), then one thread per output.
-  float *s_w = &s_sc[0][0];  // [G][n_active] weights, n_active <= 64 <= kAttnChunk
+  // First the per-(head, range) weights in parallel, then one thread per output.
   for (int i = threadIdx.x; i < G * n_active; i += kAttnThreads) {
     const int g = i / n_active, s2 = i % n_active;
-    s_w[g * kAttnChunk + s2] = __ldcg(part + ((int64_t)g * a.n_splits + s2) * (HD + 2) + HD);  // m
+    s_w[g][s2] = __ldcg(part + ((int64_t)g * a.n_splits + s2) * (HD + 2) + HD);  // m
   }
   __syncthreads();
   if (threadIdx.x < G) {
     const int g = threadIdx.x;
     float M = -INFINITY;
-    for (int s2 = 0; s2 < n_active; ++s2) M = fmaxf(M, s_w[g * kAttnChunk + s2]);
-    s_red[0][g] = M;
+    for (int s2 = 0; s2 < n_active; ++s2) M = fmaxf(M, s_w[g][s2]);
+    s_M[g] = M;
   }
   __syncthreads();
   for (int i = threadIdx.x; i < G * n_active; i += kAttnThreads) {
     const int g = i / n_active, s2 = i % n_active;
-    const float ms = s_w[g * kAttnChunk + s2];
-    s_w[g * kAttnChunk + s2] = ms == -INFINITY ? 0.0f : expf_exact(ms - s_red[0][g]);
+    const float ms = s_w[g][s2];
+    s_w[g][s2] = ms == -INFINITY ? 0.0f : __expf(ms - s_M[g]);
   }
   __syncthreads();
   float *out = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
@@ -261,7 +294,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     float L = 0.0f, o = 0.0f;
 #pragma unroll 4
     for (int s2 = 0; s2 < n_active; ++s2) {
-      const float w = s_w[g * kAttnChunk + s2];
+      const float w = s_w[g][s2];
       L = __fmaf_rn(__ldcg(pg + (int64_t)s2 * (HD + 2) + HD + 1), w, L);
       o = __fmaf_rn(__ldcg(pg + (int64_t)s2 * (HD + 2) + d), w, o);
     }
@@ -292,7 +325,7 @@ static int32_t launch_gp(const AttnArgs &a, cudaStream_t s) {
 
 template <int G>
 static int32_t launch_g(const AttnArgs &a, cudaStream_t s) {
-  if (a.n_splits > kAttnChunk) return fail(CMLD_ERR_SHAPE, "attention: more than %d ranges", kAttnChunk);
+  if (a.n_splits > kAttnMaxSplits) return fail(CMLD_ERR_SHAPE, "attention: more than %d ranges", kAttnMaxSplits);
   switch (a.head_dim) {
     case 32: return launch_gp<G, 1>(a, s);
     case 64: return launch_gp<G, 2>(a, s);

@@ -120,6 +120,8 @@ int32_t comm_wait_stream(void **comm, cudaStream_t s, int64_t limit_ms, void (*b
       if (ms > 50) std::this_thread::sleep_for(std::chrono::microseconds(200));  // long wait: stop burning a core
     }
     if (give_up) {
+      const bool dbg = getenv("CMLD_DEBUG_COMM") != nullptr;
+      if (dbg) fprintf(stderr, "[cmld comm] giving up on the stream; aborting the communicator\n");
       // The abort runs on a helper thread: it raises the communicator's abort flag at once (the
       // collective's kernel sees it and returns) but then waits until every CUDA graph that captured
       // the communicator is gone, and those can only be freed once the stream has drained — which is
@@ -134,11 +136,13 @@ int32_t comm_wait_stream(void **comm, cudaStream_t s, int64_t limit_ms, void (*b
       const auto t1 = std::chrono::steady_clock::now();
       auto waited_ms = [&] { return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t1).count(); };
       while (cudaStreamQuery(s) == cudaErrorNotReady && waited_ms() < 20000) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+      if (dbg) fprintf(stderr, "[cmld comm] stream drained=%d after %lld ms\n", (int)(cudaStreamQuery(s) != cudaErrorNotReady), (long long)waited_ms());
       if (before_abort) before_abort(ctx);  // idle graphs are freed at once, which ends the helper's wait for them
       while (!done->load() && waited_ms() < 40000) {
         cudaStreamQuery(s);
         std::this_thread::sleep_for(std::chrono::milliseconds(1));
       }
+      if (dbg) fprintf(stderr, "[cmld comm] abort returned=%d after %lld ms\n", (int)done->load(), (long long)waited_ms());
       if (done->load()) helper.join();
       else helper.detach();
       return fail(CMLD_ERR_TIMEOUT, "a collective did not finish within %lld ms (a peer rank stopped answering): communicator aborted",

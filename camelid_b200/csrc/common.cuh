@@ -114,6 +114,37 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- arrival words written by other GPUs
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits until *flag has reached `want` (counts wrap).  Bounded twice over: by time and by polls.  When
+// the bound passes, or an earlier wait of this step already gave up, records CMLD_ERR_TIMEOUT in
+// *status and returns false; the caller carries on with whatever the slot holds and the host reports
+// the error.
+__device__ __forceinline__ bool peer_wait(const uint32_t *flag, uint32_t want, unsigned long long timeout_ns, int32_t *status) {
+  if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+  if (*reinterpret_cast<volatile int32_t *>(status) == 0) {
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 1; i < (1u << 26); ++i) {
+      if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+      if ((i & 255u) == 0 && global_ns() - t0 > timeout_ns) break;
+    }
+  }
+  atomicExch(status, (int32_t)CMLD_ERR_TIMEOUT);
+  return false;
+}
+
 // Q4_K 6-bit (scale, min) of group g from the 12 packed bytes held as three words
 // (q4_k_scale_min, src/tensor/mod.rs:5997-6006 in the Camelid tree).
 __device__ __forceinline__ void q4k_scale_min(int g, uint32_t s0, uint32_t s1, uint32_t s2, int &sc, int &m) {
@@ -176,11 +207,38 @@ struct GemvPrologue {
   const uint8_t *act_k, *act_0;  // mode 0: Q8_K rows / Q8_0 rows in the global activation layout
   float *norm_out;         // optional: f32 copy of the prologue's result [batch][cols]
 };
+// All-reduce of a tensor-parallel sublayer folded into the matvec kernels that produce and consume it,
+// over peer memory (NVLink): the producing launch (one matrix: o or down) stores its partial result
+// rows into a slot on EVERY rank and, when its last CTA is done, raises this rank's arrival word on
+// every rank; the consuming launch's prologue waits (bounded) for all arrival words and takes the sum
+// of the ranks' partials, in rank order, as its input row.  No collective kernel runs in between.
+constexpr int kMaxPeers = 8;
+constexpr int kPeerRows = 8;  // rows a slot holds (the staged kernel's largest batch)
+struct GemvPeer {
+  int32_t tx_n = 0;                    // ranks; 0 = this launch sends nothing
+  float *tx_part[kMaxPeers] = {};      // on rank p: where this rank's partial rows go, [kPeerRows][hidden]
+  uint32_t *tx_flag[kMaxPeers] = {};   // on rank p: this rank's arrival word for the slot
+  uint32_t *tx_epoch = nullptr;        // local: arrivals sent for the slot so far
+  uint32_t *tx_ticket = nullptr;       // local: CTAs of this launch that are done
+  int32_t rx_n = 0;                    // ranks; 0 = the input row is read as usual
+  const float *rx_part = nullptr;      // local slot: [rank][kPeerRows][hidden]
+  const uint32_t *rx_flag = nullptr;   // local: arrival words [rank]
+  const uint32_t *rx_epoch = nullptr;  // local: the arrival count to wait for
+  float *rx_out = nullptr;             // the summed rows [batch][hidden], written by CTA 0
+  unsigned long long timeout_ns = 0;   // bound of the wait
+  // Optional timeline (engine option CMLD_TRACE): [0] = records taken so far, then 8 words per launch
+  // written by CTA 0: start, inputs visible, peers arrived, prologue done, rows done, ticket taken, n_jobs/tx/rx tag.
+  unsigned long long *trace = nullptr;
+};
+constexpr int kTraceRecords = 4096;
+// Stand-alone form of the receiving side: h[batch][hidden] = sum of the ranks' partials (ops.cu).
+int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, int32_t *status, bool pdl, cudaStream_t s);
+
 // Returns CMLD_ERR_UNSUPPORTED, leaving the error message untouched, when the shape does not fit.
 // Largest batch (<= 8) the staged kernel takes for these matrices in one launch; 0 = none.
 int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs);
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
-                         cudaStream_t s, bool pdl);
+                         cudaStream_t s, bool pdl, const GemvPeer *peer = nullptr);
 
 // ops.cu
 struct NormQuantArgs {

@@ -116,6 +116,17 @@ struct cmld_engine {
   void *comm = nullptr;     // NCCL communicator of a sharded engine
   unsigned long long *am_keys = nullptr;  // packed (value, index) per row for the sharded argmax
   float *logits_gather = nullptr, *logits_full = nullptr;
+  // Peer-memory link of a tensor-parallel group: one region per rank, mapped into every rank.
+  //   parts: [2 slots][rank][kPeerRows][hidden] f32, then arrival words [2 slots][rank] u32
+  struct PeerLink {
+    bool ready = false;
+    uint8_t *region[kMaxPeers] = {};  // [shard_rank] is this rank's own allocation
+    uint32_t *local = nullptr;        // epochs[2], tickets[2]
+    unsigned long long timeout_ns = 0;
+  } peer;
+  unsigned long long *trace = nullptr;  // matvec timeline (environment CMLD_TRACE=<file>), dumped at destroy
+  std::string trace_path;
+  std::map<int32_t, bool> peer_fit;   // rows -> every matvec of a step fits the staged kernel in one pass
   int device = 0;
   cudaStream_t stream = nullptr;
   int32_t max_rows = 0;  // scratch rows (sequences per step)
@@ -288,6 +299,10 @@ static int32_t engine_init(cmld_engine *e) {
     CMLD_TRY(dev_alloc(e, &e->moe_act, na * c.ffn_dim));
     CMLD_TRY(dev_alloc(e, &e->moe_down, na * c.hidden));
   }
+  if (const char *tp = getenv("CMLD_TRACE")) {
+    e->trace_path = std::string(tp) + "." + std::to_string(e->shard_rank);
+    CMLD_TRY(dev_alloc(e, &e->trace, 1 + 8 * (int64_t)kTraceRecords));
+  }
   e->history_cap = 4096;
   CMLD_TRY(dev_alloc(e, &e->d_history, e->history_cap * R));
   CMLD_TRY(dev_alloc(e, &e->d_status, 1));
@@ -295,7 +310,46 @@ static int32_t engine_init(cmld_engine *e) {
   return CMLD_OK;
 }
 
+static void peer_link_close(cmld_engine *e) {
+  cmld_engine::PeerLink &L = e->peer;
+  L.ready = false;
+  for (int p = 0; p < kMaxPeers; ++p) {
+    if (!L.region[p]) continue;
+    if (p == e->shard_rank) cudaFree(L.region[p]);
+    else cudaIpcCloseMemHandle(L.region[p]);
+    L.region[p] = nullptr;
+  }
+  cudaGetLastError();
+}
+
+// Weights changed: graphs captured so far hold the old matrices' addresses.
+static void drop_graphs(cmld_engine *e) {
+  cudaStreamSynchronize(e->stream);
+  for (auto &kv : e->graphs)
+    if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+  e->graphs.clear();
+  e->peer_fit.clear();
+}
+
+static void dump_trace(cmld_engine *e) {
+  if (!e->trace || e->trace_path.empty()) return;
+  std::vector<unsigned long long> host(1 + 8 * (size_t)kTraceRecords);
+  if (cudaMemcpy(host.data(), e->trace, host.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
+  FILE *f = fopen(e->trace_path.c_str(), "w");
+  if (!f) return;
+  const size_t n = std::min<size_t>(host[0], kTraceRecords);
+  fprintf(f, "start_ns,visible,arrived,prologue,rows,ticket,jobs,tx,rx,cols\n");
+  for (size_t i = 0; i < n; ++i) {
+    const unsigned long long *r = host.data() + 1 + i * 8;
+    fprintf(f, "%llu,%lld,%lld,%lld,%lld,%lld,%llu,%llu,%llu,%llu\n", r[0], (long long)(r[1] - r[0]), (long long)(r[2] - r[0]),
+            (long long)(r[3] - r[0]), (long long)(r[4] - r[0]), r[5] ? (long long)(r[5] - r[0]) : -1, r[6] & 0xff, (r[6] >> 8) & 0xff,
+            (r[6] >> 16) & 0xff, r[6] >> 32);
+  }
+  fclose(f);
+}
+
 static void engine_free(cmld_engine *e) {
+  dump_trace(e);
   // Graphs first, communicator second: NCCL counts the graphs that captured its collectives and its
   // teardown waits until the last of them is gone.
   for (auto &kv : e->graphs)
@@ -303,6 +357,7 @@ static void engine_free(cmld_engine *e) {
   e->graphs.clear();
   comm_destroy(e->comm);
   e->comm = nullptr;
+  peer_link_close(e);
   for (auto &L : e->layers) {
     for (auto &w : L.proj) weight_free(w);
     for (auto &w : L.exps) weight_free(w);
@@ -385,7 +440,7 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
 // Fast path: the staged kernel with f and the quantiser fused into its prologue (batch in passes
 // of 8 columns).  Shapes it does not take fall back to quantise-kernel + direct-load kernel.
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
-                          const float *norm_w, int64_t cols) {
+                          const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr) {
   bool n0, nk;
   const Weight *ws[4];
   for (int i = 0; i < n; ++i) ws[i] = p[i].w;
@@ -432,12 +487,19 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
           pro.act_k = e->act_k + (int64_t)b0 * act_row_stride(cols);
           pro.act_0 = e->act_0 + (int64_t)b0 * act_row_stride(cols);
         }
-        CMLD_TRY(launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, pdl));
+        if (peer && (b0 != 0 || nb != batch)) return fail(CMLD_ERR_STATE, "peer-memory matvec split into passes");
+        GemvPeer traced;
+        if (e->trace) {
+          if (peer) traced = *peer;
+          traced.trace = e->trace;
+        }
+        CMLD_TRY(launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, pdl, e->trace ? &traced : peer));
         e->launches += 1;
       }
       return CMLD_OK;
     }
   }
+  if (peer) return fail(CMLD_ERR_STATE, "peer-memory matvec does not fit the staged kernel");
   CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
   return run_gemv_group(e, p, n, batch);
 }
@@ -509,10 +571,70 @@ static int32_t gather_logits(cmld_engine *e, int32_t B) {
   return CMLD_OK;
 }
 
+// ---- peer-memory link (tensor-parallel sublayer sums inside the matvec kernels)
+
+static size_t peer_parts_bytes(const cmld_engine *e) { return (size_t)2 * e->tp * kPeerRows * e->cfg.hidden * 4; }
+static float *peer_part(const cmld_engine *e, int on_rank, int slot, int src_rank) {
+  return reinterpret_cast<float *>(e->peer.region[on_rank]) + ((int64_t)slot * e->tp + src_rank) * kPeerRows * e->cfg.hidden;
+}
+static uint32_t *peer_flag(const cmld_engine *e, int on_rank, int slot, int src_rank) {
+  return reinterpret_cast<uint32_t *>(e->peer.region[on_rank] + peer_parts_bytes(e)) + slot * kMaxPeers + src_rank;
+}
+static void peer_tx(const cmld_engine *e, int slot, GemvPeer &g) {
+  g.tx_n = e->tp;
+  for (int p = 0; p < e->tp; ++p) {
+    g.tx_part[p] = peer_part(e, p, slot, e->shard_rank);
+    g.tx_flag[p] = peer_flag(e, p, slot, e->shard_rank);
+  }
+  g.tx_epoch = e->peer.local + slot;
+  g.tx_ticket = e->peer.local + 2 + slot;
+}
+static void peer_rx(const cmld_engine *e, int slot, GemvPeer &g) {
+  g.rx_n = e->tp;
+  g.rx_part = peer_part(e, e->shard_rank, slot, 0);
+  g.rx_flag = peer_flag(e, e->shard_rank, slot, 0);
+  g.rx_epoch = e->peer.local + slot;
+  g.rx_out = e->h;
+  g.timeout_ns = e->peer.timeout_ns;
+}
+
+// Whether a step of B rows can fold its sublayer sums into the matvec kernels: every matvec of the
+// step must go through the staged kernel in a single pass.
+static bool peer_step_ok(cmld_engine *e, int32_t B, bool taps) {
+  if (!e->peer.ready || e->tp <= 1 || taps || B > kPeerRows) return false;
+  if (e->cfg.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_SPLIT_PROLOGUE | CMLD_FLAG_DIRECT_GEMV | CMLD_FLAG_NCCL_ONLY)) return false;
+  auto it = e->peer_fit.find(B);
+  if (it != e->peer_fit.end()) return it->second;
+  bool ok = e->cfg.hidden % 256 == 0 && e->cfg.hidden <= 8192;
+  auto fits = [&](std::initializer_list<const Weight *> ws) {
+    GemvJob jobs[3];
+    int n = 0;
+    for (const Weight *w : ws) {
+      if (!w->data) return false;
+      jobs[n++] = GemvJob{w->data, w->qt, w->rows, w->cols, w->stride, nullptr, nullptr, w->rows};
+    }
+    return gemv_pipe_fit_batch(jobs, n) >= B;
+  };
+  for (const LayerW &L : e->layers) {
+    if (!ok) break;
+    ok = L.dense_set && !L.moe_set && fits({&L.proj[0], &L.proj[1], &L.proj[2]}) && fits({&L.proj[3]}) &&
+         fits({&L.proj[4], &L.proj[5]}) && fits({&L.proj[6]});
+  }
+  if (ok && e->has_output) ok = fits({&e->output});
+  e->peer_fit[B] = ok;
+  return ok;
+}
+
 static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   const cmld_config &c = e->cfg;
   const int32_t B = o.batch;
   const bool sharded = e->tp > 1 || e->ep > 1;
+  const bool use_peer = peer_step_ok(e, B, o.taps);
+  int pending = -1;  // slot whose partial rows are the not-yet-summed residual stream
+  auto take_pending = [&](GemvPeer &g) {
+    if (pending >= 0) peer_rx(e, pending, g);
+    pending = -1;
+  };
   if (sharded && !e->comm)
     return fail(CMLD_ERR_STATE, "this sharded engine has no communicator (cmld_engine_comm_init not called, or aborted after a peer stopped answering)");
   const bool lead = e->shard_rank == 0;  // the rank whose partial sums carry the residual
@@ -529,7 +651,9 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       const Proj p[3] = {{&L.proj[0], e->q, nullptr, e->q_width},
                          {&L.proj[1], e->k, nullptr, e->kv_width},
                          {&L.proj[2], e->v, nullptr, e->kv_width}};
-      CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden));
+      GemvPeer g{};
+      take_pending(g);
+      CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden, use_peer ? &g : nullptr));
     }
     {
       const bool exact = (c.flags & CMLD_FLAG_EXACT_ORDER) != 0;
@@ -591,18 +715,34 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
     }
     {
       const Proj p[1] = {{&L.proj[3], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
-      CMLD_TRY(gemv_fused(e, p, 1, B, 2, e->attn, nullptr, nullptr, e->q_width));
-      if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
+      if (use_peer) {
+        GemvPeer g{};
+        peer_tx(e, 0, g);
+        CMLD_TRY(gemv_fused(e, p, 1, B, 2, e->attn, nullptr, nullptr, e->q_width, &g));
+        pending = 0;
+      } else {
+        CMLD_TRY(gemv_fused(e, p, 1, B, 2, e->attn, nullptr, nullptr, e->q_width));
+        if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
+      }
     }
     if (L.moe_set) {
       CMLD_TRY(run_norm_quant(e, e->h, nullptr, L.ffn_norm, c.hidden, B, e->normed, false, false));
       CMLD_TRY(moe_ffn_step(e, L, B));
     } else {
       const Proj p[2] = {{&L.proj[4], e->gate, nullptr, c.ffn_dim}, {&L.proj[5], e->up, nullptr, c.ffn_dim}};
-      CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden));
+      GemvPeer g{};
+      take_pending(g);
+      CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden, use_peer ? &g : nullptr));
       const Proj pd[1] = {{&L.proj[6], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
-      CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim));
-      if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
+      if (use_peer) {
+        GemvPeer gd{};
+        peer_tx(e, 1, gd);
+        CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim, &gd));
+        pending = 1;
+      } else {
+        CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim));
+        if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
+      }
     }
     if (o.taps) {
       CMLD_CUDA(cudaMemcpyAsync(e->taps + (int64_t)li * e->max_rows * c.hidden, e->h, (size_t)B * c.hidden * 4,
@@ -612,7 +752,9 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   if (o.logits) {
     if (!e->has_output) return fail(CMLD_ERR_STATE, "output weights not set");
     const Proj p[1] = {{&e->output, e->logits, nullptr, e->vocab_local}};
-    CMLD_TRY(gemv_fused(e, p, 1, B, 1, e->h, nullptr, e->final_norm, c.hidden));
+    GemvPeer g{};
+    take_pending(g);
+    CMLD_TRY(gemv_fused(e, p, 1, B, 1, e->h, nullptr, e->final_norm, c.hidden, use_peer ? &g : nullptr));
     if (o.argmax && e->tp == 1) {
       CMLD_TRY(launch_argmax(e->logits, c.vocab, B, e->am_val, e->am_idx, e->am_ticket, e->out_idx,
                              o.feed_back ? e->d_tokens : nullptr, e->d_positions, e->d_history, e->stream));
@@ -626,6 +768,12 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
                                     e->d_history, e->am_ticket, e->stream));
       e->launches += 3;
     }
+  }
+  if (pending >= 0) {  // the step ends on a sublayer: sum its partial rows into h
+    GemvPeer g{};
+    take_pending(g);
+    CMLD_TRY(launch_peer_reduce(g, B, c.hidden, e->d_status, !(c.flags & CMLD_FLAG_NO_PDL), e->stream));
+    e->launches += 1;
   }
   return CMLD_OK;
 }
@@ -690,26 +838,30 @@ static int32_t stage_rows(cmld_engine *e, int32_t n, const int32_t *tokens, cons
   return CMLD_OK;
 }
 
+// Sharded engines wait for their device work here, with a bound, BEFORE any device-to-host copy: a
+// copy into pageable host memory blocks the calling thread until the stream has drained, and a
+// collective whose peer went away never drains by itself.  No-op for an unsharded engine.
+static int32_t settle(cmld_engine *e) {
+  if (!e->comm) return CMLD_OK;
+  static const int64_t limit_ms = [] {
+    const char *v = getenv("CMLD_COMM_TIMEOUT_MS");
+    const long long n = v ? atoll(v) : 0;
+    return (int64_t)(n > 0 ? n : 120000);
+  }();
+  return comm_wait_stream(&e->comm, e->stream, limit_ms, [](void *ctx) {
+    // once the aborted collective has let the stream drain: release the graphs that captured the
+    // communicator's collectives, or NCCL's teardown would wait for them for ever
+    cmld_engine *eng = static_cast<cmld_engine *>(ctx);
+    for (auto &kv : eng->graphs)
+      if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    eng->graphs.clear();
+  }, e);
+}
+
 static int32_t finish(cmld_engine *e, const char *what) {
+  CMLD_TRY(settle(e));
   int32_t st = 0;
   cudaError_t ce = cudaMemcpyAsync(&st, e->d_status, 4, cudaMemcpyDeviceToHost, e->stream);
-  if (ce == cudaSuccess && e->comm) {
-    // sharded: a bounded wait, so a rank whose peer went away returns an error instead of hanging
-    static const int64_t limit_ms = [] {
-      const char *v = getenv("CMLD_COMM_TIMEOUT_MS");
-      const long long n = v ? atoll(v) : 0;
-      return (int64_t)(n > 0 ? n : 120000);
-    }();
-    const int32_t wrc = comm_wait_stream(&e->comm, e->stream, limit_ms, [](void *ctx) {
-      // before the abort: release the graphs that captured the communicator's collectives (an exec that
-      // is still running is freed when it completes), or NCCL's teardown would wait for them for ever
-      cmld_engine *eng = static_cast<cmld_engine *>(ctx);
-      for (auto &kv : eng->graphs)
-        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
-      eng->graphs.clear();
-    }, e);
-    if (wrc != CMLD_OK) return wrc;
-  }
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "%s: %s", what, cudaGetErrorString(ce));
   if (st != 0) {
@@ -891,6 +1043,60 @@ int32_t cmld_engine_destroy(cmld_engine *e) {
   return CMLD_OK;
 }
 
+// Maps every rank's slot region into this process (CUDA IPC over NVLink peer access).  Collective.
+// When any rank cannot map any other (no peer access, ranks sharing a process, IPC unavailable) all
+// ranks agree to keep the NCCL path; that is not an error.
+static int32_t peer_link_open(cmld_engine *e) {
+  cmld_engine::PeerLink &L = e->peer;
+  const int me = e->shard_rank, n = e->tp;
+  if (n > kMaxPeers) return CMLD_OK;
+  const size_t bytes = peer_parts_bytes(e) + 2 * kMaxPeers * sizeof(uint32_t);
+  void *own = nullptr;
+  CMLD_CUDA(cudaMalloc(&own, bytes));
+  L.region[me] = static_cast<uint8_t *>(own);
+  CMLD_CUDA(cudaMemsetAsync(own, 0, bytes, e->stream));
+  CMLD_TRY(dev_alloc(e, &L.local, 4));
+  // exchange the IPC handles through the communicator (64 bytes per rank)
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t mine{};
+  bool ok = cudaIpcGetMemHandle(&mine, own) == cudaSuccess;
+  if (!ok) cudaGetLastError();
+  float *send = nullptr, *recv = nullptr;
+  CMLD_TRY(dev_alloc(e, &send, 16));
+  CMLD_TRY(dev_alloc(e, &recv, 16 * n));
+  CMLD_CUDA(cudaMemcpyAsync(send, &mine, 64, cudaMemcpyHostToDevice, e->stream));
+  CMLD_TRY(comm_allgather_f32(e->comm, send, recv, 16, e->stream));
+  std::vector<cudaIpcMemHandle_t> all(n);
+  CMLD_CUDA(cudaMemcpyAsync(all.data(), recv, (size_t)64 * n, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  for (int p = 0; p < n && ok; ++p) {
+    if (p == me) continue;
+    void *ptr = nullptr;
+    if (cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      cudaGetLastError();
+      ok = false;
+    } else {
+      L.region[p] = static_cast<uint8_t *>(ptr);
+    }
+  }
+  // agree: one rank that failed sends everybody to the NCCL path
+  const unsigned long long bad = ok ? 0ull : 1ull;
+  CMLD_CUDA(cudaMemcpyAsync(e->am_keys, &bad, 8, cudaMemcpyHostToDevice, e->stream));
+  CMLD_TRY(comm_allreduce_max_u64(e->comm, e->am_keys, 1, e->stream));
+  unsigned long long any_bad = 1;
+  CMLD_CUDA(cudaMemcpyAsync(&any_bad, e->am_keys, 8, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  if (any_bad) {
+    peer_link_close(e);
+    return CMLD_OK;
+  }
+  const char *v = getenv("CMLD_COMM_TIMEOUT_MS");
+  const long long ms = v ? atoll(v) : 0;
+  L.timeout_ns = (unsigned long long)(ms > 0 ? ms : 20000) * 1000000ull;
+  L.ready = true;
+  return CMLD_OK;
+}
+
 int32_t cmld_comm_unique_id(uint8_t out[128]) {
   if (!out) return fail(CMLD_ERR_INVALID, "null out pointer");
   return comm_unique_id(out);
@@ -910,12 +1116,14 @@ int32_t cmld_engine_comm_init(cmld_engine *e, const uint8_t id[128], int32_t ran
   CMLD_CUDA(cudaMemsetAsync(e->am_keys, 0, 8, e->stream));
   CMLD_TRY(comm_allreduce_max_u64(e->comm, e->am_keys, 1, e->stream));
   CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  if (e->tp > 1 && !(e->cfg.flags & CMLD_FLAG_NCCL_ONLY)) CMLD_TRY(peer_link_open(e));
   return CMLD_OK;
 }
 
 int32_t cmld_engine_set_layer(cmld_engine *e, int32_t layer, const cmld_tensor projs[7], const float *attn_norm,
                               const float *ffn_norm) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   const cmld_config &c = e->cfg;
   if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "set_layer: layer %d out of range", layer);
   if (!projs) return fail(CMLD_ERR_INVALID, "set_layer: projections are null");
@@ -941,6 +1149,7 @@ int32_t cmld_engine_set_layer(cmld_engine *e, int32_t layer, const cmld_tensor p
 int32_t cmld_engine_set_layer_moe(cmld_engine *e, int32_t layer, const float *router, const cmld_tensor *gate_exps,
                                   const cmld_tensor *up_exps, const cmld_tensor *down_exps) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   const cmld_config &c = e->cfg;
   if (c.n_experts <= 0) return fail(CMLD_ERR_STATE, "set_layer_moe: engine was created without experts");
   if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "set_layer_moe: layer %d out of range", layer);
@@ -963,6 +1172,7 @@ int32_t cmld_engine_set_layer_moe(cmld_engine *e, int32_t layer, const float *ro
 
 int32_t cmld_engine_set_output(cmld_engine *e, const float *final_norm, const cmld_tensor *output) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   if (!output) return fail(CMLD_ERR_INVALID, "set_output: tensor is null");
   CMLD_TRY(weight_upload(e->output, output->qtype, e->vocab_local, e->cfg.hidden, output->data, output->nbytes, e->stream));
   if (e->output.qt == CMLD_F32) return fail(CMLD_ERR_UNSUPPORTED, "set_output: f32 output weights are not supported");
@@ -973,6 +1183,7 @@ int32_t cmld_engine_set_output(cmld_engine *e, const float *final_norm, const cm
 
 int32_t cmld_engine_set_token_embd(cmld_engine *e, const cmld_tensor *t) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   if (!t) return fail(CMLD_ERR_INVALID, "set_token_embd: tensor is null");
   CMLD_TRY(weight_upload(e->token_embd, t->qtype, e->cfg.vocab, e->cfg.hidden, t->data, t->nbytes, e->stream));
   e->has_embd = true;
@@ -1007,6 +1218,7 @@ static int32_t adopt(Weight &dst, cmld_weight *src, int64_t rows, int64_t cols, 
 int32_t cmld_engine_adopt_layer(cmld_engine *e, int32_t layer, cmld_weight *const projs[7], const float *attn_norm,
                                 const float *ffn_norm) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   const cmld_config &c = e->cfg;
   if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "adopt_layer: layer %d out of range", layer);
   if (!projs) return fail(CMLD_ERR_INVALID, "adopt_layer: projections are null");
@@ -1027,6 +1239,7 @@ int32_t cmld_engine_adopt_layer(cmld_engine *e, int32_t layer, cmld_weight *cons
 int32_t cmld_engine_adopt_layer_moe(cmld_engine *e, int32_t layer, cmld_weight *router_f32, cmld_weight *gate_exps,
                                     cmld_weight *up_exps, cmld_weight *down_exps) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   const cmld_config &c = e->cfg;
   if (c.n_experts <= 0) return fail(CMLD_ERR_STATE, "adopt_layer_moe: engine was created without experts");
   if (layer < 0 || layer >= c.n_layers) return fail(CMLD_ERR_INVALID, "adopt_layer_moe: layer %d out of range", layer);
@@ -1052,6 +1265,7 @@ int32_t cmld_engine_adopt_layer_moe(cmld_engine *e, int32_t layer, cmld_weight *
 
 int32_t cmld_engine_adopt_output(cmld_engine *e, const float *final_norm, cmld_weight *output) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   if (!output) return fail(CMLD_ERR_INVALID, "adopt_output: weight is null");
   CMLD_TRY(adopt(e->output, output, e->vocab_local, e->cfg.hidden, "adopt_output"));
   CMLD_TRY(upload_f32(&e->final_norm, final_norm, e->cfg.hidden, e->stream));
@@ -1061,6 +1275,7 @@ int32_t cmld_engine_adopt_output(cmld_engine *e, const float *final_norm, cmld_w
 
 int32_t cmld_engine_adopt_token_embd(cmld_engine *e, cmld_weight *token_embd) {
   CMLD_ENGINE_ENTER(e);
+  drop_graphs(e);
   if (!token_embd) return fail(CMLD_ERR_INVALID, "adopt_token_embd: weight is null");
   CMLD_TRY(adopt(e->token_embd, token_embd, e->cfg.vocab, e->cfg.hidden, "adopt_token_embd", true));
   e->has_embd = true;
@@ -1104,6 +1319,7 @@ int32_t cmld_engine_forward_token(cmld_engine *e, const float *embedding, const 
   if (compute_logits && !token_out) return fail(CMLD_ERR_INVALID, "token_out is null");
   CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, compute_logits != 0, compute_logits != 0, false));
   int32_t tok = 0;
+  CMLD_TRY(settle(e));
   if (compute_logits) CMLD_CUDA(cudaMemcpyAsync(&tok, e->out_idx, 4, cudaMemcpyDeviceToHost, e->stream));
   CMLD_TRY(finish(e, "forward_token"));
   if (compute_logits) *token_out = (uint32_t)tok;
@@ -1116,6 +1332,7 @@ int32_t cmld_engine_forward_token_logits(cmld_engine *e, const float *embedding,
   if (!logits_out) return fail(CMLD_ERR_INVALID, "logits_out is null");
   CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, true, false, false));
   if (e->tp > 1) CMLD_TRY(gather_logits(e, 1));
+  CMLD_TRY(settle(e));
   CMLD_CUDA(cudaMemcpyAsync(logits_out, e->tp > 1 ? e->logits_full : e->logits, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
   return finish(e, "forward_token_logits");
 }
@@ -1125,6 +1342,7 @@ int32_t cmld_engine_forward_token_hidden(cmld_engine *e, const float *embedding,
   CMLD_ENGINE_ENTER(e);
   if (!hidden_out) return fail(CMLD_ERR_INVALID, "hidden_out is null");
   CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, false, false, layer_taps != nullptr));
+  CMLD_TRY(settle(e));
   CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
   if (layer_taps)
     CMLD_CUDA(cudaMemcpy2DAsync(layer_taps, (size_t)e->cfg.hidden * 4, e->taps, (size_t)e->max_rows * e->cfg.hidden * 4,
@@ -1138,6 +1356,7 @@ int32_t cmld_engine_forward_layer(cmld_engine *e, int32_t layer, const float *hi
   if (!hidden_out) return fail(CMLD_ERR_INVALID, "hidden_out is null");
   if (layer < 0 || layer >= e->cfg.n_layers) return fail(CMLD_ERR_INVALID, "layer %d out of range", layer);
   CMLD_TRY(forward_embedding_rows(e, hidden_in, cosv, sinv, position, 1, scale, false, false, false, layer, layer + 1));
+  CMLD_TRY(settle(e));
   CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
   return finish(e, "forward_layer");
 }
@@ -1163,6 +1382,7 @@ int32_t cmld_engine_verify_batch(cmld_engine *e, const float *embeddings, const 
   if (!tokens_out) return fail(CMLD_ERR_INVALID, "tokens_out is null");
   CMLD_TRY(forward_embedding_rows(e, embeddings, cos_all, sin_all, base_position, k, scale, true, true, false));
   std::vector<int32_t> toks(k);
+  CMLD_TRY(settle(e));
   CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)k * 4, cudaMemcpyDeviceToHost, e->stream));
   CMLD_TRY(finish(e, "verify_batch"));
   for (int i = 0; i < k; ++i) tokens_out[i] = (uint32_t)toks[i];
@@ -1261,8 +1481,9 @@ int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *se
   CMLD_TRY(run_step(e, o));
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> toks(n_seqs);
-  CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, e->stream));
   if (logits_out && e->tp > 1) CMLD_TRY(gather_logits(e, n_seqs));
+  CMLD_TRY(settle(e));
+  CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, e->stream));
   if (logits_out) CMLD_CUDA(cudaMemcpyAsync(logits_out, e->tp > 1 ? e->logits_full : e->logits, (size_t)n_seqs * e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
   if (hidden_out) CMLD_CUDA(cudaMemcpyAsync(hidden_out, e->h, (size_t)n_seqs * e->cfg.hidden * 4, cudaMemcpyDeviceToHost, e->stream));
   CMLD_TRY(finish(e, "step_batch"));
@@ -1300,6 +1521,7 @@ int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *t
   }
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   int32_t tok = 0;
+  CMLD_TRY(settle(e));
   CMLD_CUDA(cudaMemcpyAsync(&tok, e->out_idx + (last_rows - 1), 4, cudaMemcpyDeviceToHost, e->stream));
   CMLD_TRY(finish(e, "prefill_tokens"));
   cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
@@ -1329,6 +1551,7 @@ int32_t cmld_engine_decode_greedy(cmld_engine *e, int32_t n_seqs, const int32_t 
   for (int s = 0; s < n_steps; ++s) CMLD_TRY(run_step(e, o));
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> hist((size_t)n_steps * n_seqs);
+  CMLD_TRY(settle(e));
   CMLD_CUDA(cudaMemcpyAsync(hist.data(), e->d_history, hist.size() * 4, cudaMemcpyDeviceToHost, e->stream));
   CMLD_TRY(finish(e, "decode_greedy"));
   cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);

@@ -13,9 +13,9 @@
 
 namespace cmld {
 
-__device__ __forceinline__ float expf_exact(float x) {
-  // T[i] = bits(2^(i/32)) - (i << 47)
-  constexpr uint64_t T[32] = {
+// T[i] = bits(2^(i/32)) - (i << 47).  In global memory and read through the read-only cache: as a
+// function-local array it would be rebuilt on the stack by every call (256 bytes of local stores).
+static __device__ const uint64_t kExpfTable[32] = {
       0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
       0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
       0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
@@ -24,6 +24,8 @@ __device__ __forceinline__ float expf_exact(float x) {
       0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
       0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
       0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull};
+
+__device__ __forceinline__ float expf_exact(float x) {
   if (x != x) return x;
   if (x > 0x1.62e42ep6f) return __int_as_float(0x7f800000);  // overflow
   if (x < -0x1.9fe368p6f) return 0.0f;                       // underflow
@@ -33,7 +35,7 @@ __device__ __forceinline__ float expf_exact(float x) {
   const uint64_t ki = (uint64_t)__double_as_longlong(kd);
   kd = __dadd_rn(kd, -0x1.8p+52);
   const double r = __dadd_rn(z, -kd);
-  const uint64_t t = T[ki & 31] + (ki << 47);
+  const uint64_t t = __ldg(&kExpfTable[ki & 31]) + (ki << 47);
   const double s = __longlong_as_double((long long)t);
   const double zz = __dadd_rn(__dmul_rn(0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0, r), 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0);
   const double r2 = __dmul_rn(r, r);

@@ -100,7 +100,39 @@ struct PipeArgs {
   int32_t off_act_k, off_act_0, off_red, off_ring;
   float *norm_out;        // optional f32 copy of the normalised row (written by CTA 0)
   int32_t *status;
+  GemvPeer peer;          // tensor-parallel sum folded into this launch (tx_n / rx_n = 0: none)
+  int64_t peer_rank_stride;  // floats between the ranks' partials in the receive slot
 };
+
+// Quantises one 256-value chunk (8 values per lane) of batch row b into the shared-memory operands.
+__device__ __forceinline__ void emit_chunk(const float (&v)[8], const PipeArgs &a, int b, int ch, int lane, uint8_t *act_k,
+                                           uint8_t *act_0, int rec_col_stride, int act0_col_stride) {
+  const int e0 = ch * 256 + lane * 8;
+  if (a.need_k) {
+    int q[8];
+    float d;
+    q8k_quantise_chunk(v, lane, q, d);
+    uint8_t *rec = act_k + b * rec_col_stride + ch * kActRec;
+    *reinterpret_cast<uint2 *>(rec + lane * 8) = pack8(q);
+    int s16 = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
+    s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+    if ((lane & 1) == 0) reinterpret_cast<short *>(rec + kRecBsum16)[lane >> 1] = (short)s16;
+    if ((lane & 3) == 0) reinterpret_cast<short *>(rec + kRecBsum32)[lane >> 2] = (short)s32;
+    if (lane == 0) *reinterpret_cast<float *>(rec + kRecD) = d;
+  }
+  if (a.need_0) {
+    int q[8];
+    float sc;
+    q80_quantise_chunk(v, q, sc);
+    if (e0 < a.cols) {
+      *reinterpret_cast<uint2 *>(act_0 + b * act0_col_stride + e0) = pack8(q);
+      if ((lane & 3) == 0) reinterpret_cast<float *>(act_0 + b * act0_col_stride + round_up16(a.cols))[e0 >> 5] = sc;
+    }
+  }
+}
+
+constexpr int kRxChunks = 2;  // chunks a warp holds in registers in the receiving prologue: hidden <= 16 * 2 * 256
 
 // ---------------------------------------------------------------- per-superblock dots (shared memory operands)
 
@@ -267,6 +299,16 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   // Let the next kernel of the stream get scheduled as early as the hardware allows; it blocks in
   // its own griddepcontrol.wait until this grid has completed.
   asm volatile("griddepcontrol.launch_dependents;");
+  unsigned long long *tr = nullptr;  // timeline record of this launch (CTA 0, thread 0 of the consumers)
+  if (a.peer.trace && blockIdx.x == 0 && tid == 0) {
+    const unsigned long long idx = atomicAdd(a.peer.trace, 1ull);
+    if (idx < (unsigned long long)kTraceRecords) {
+      tr = a.peer.trace + 1 + idx * 8;
+      tr[0] = global_ns();
+      tr[6] = (unsigned long long)a.n_jobs | ((unsigned long long)a.peer.tx_n << 8) | ((unsigned long long)a.peer.rx_n << 16) |
+              ((unsigned long long)a.cols << 32);
+    }
+  }
 
   if (warp == kPipeAllWarps) {
     // ---------------- producer: weights do not depend on the previous kernel, so no wait here
@@ -291,12 +333,72 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 
   // ---------------- consumers
   asm volatile("griddepcontrol.wait;" ::: "memory");  // inputs written by the previous kernel are now visible
+  if (tr) tr[1] = global_ns();
   const int nsb = a.cols >> 8;
   const int rec_col_stride = nsb * kActRec;
   const int act0_col_stride = (int)round_up16(a.cols) + (int)round_up16((a.cols >> 5) * 4);
 
+  if (a.peer.rx_n > 0) {
+    // the input rows are still spread over the ranks: wait for every rank's partial to have arrived
+    if (tid < a.peer.rx_n) peer_wait(a.peer.rx_flag + tid, __ldcg(a.peer.rx_epoch), a.peer.timeout_ns, a.status);
+    asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+  }
+  if (tr) tr[2] = global_ns();
+
   // Prologue: quantised activation rows into shared memory.
   for (int b = 0; b < a.batch; ++b) {
+    if (a.peer.rx_n > 0) {
+      // RMSNorm of the sum of the ranks' partial rows (added in rank order, so every rank gets the same
+      // bits); each warp keeps its chunks of the sum in registers between the two passes
+      float hv[kRxChunks][8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int k = 0; k < kRxChunks; ++k) {
+        const int ch = warp + k * kPipeAllWarps;
+        if (ch * 256 < a.cols) {
+          const float *src = a.peer.rx_part + (int64_t)b * a.cols + ch * 256 + lane * 8;
+          float4 s0 = __ldcg(reinterpret_cast<const float4 *>(src)), s1 = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+          for (int r = 1; r < a.peer.rx_n; ++r) {
+            const float4 t0 = __ldcg(reinterpret_cast<const float4 *>(src + r * a.peer_rank_stride));
+            const float4 t1 = __ldcg(reinterpret_cast<const float4 *>(src + r * a.peer_rank_stride) + 1);
+            s0.x = __fadd_rn(s0.x, t0.x), s0.y = __fadd_rn(s0.y, t0.y), s0.z = __fadd_rn(s0.z, t0.z), s0.w = __fadd_rn(s0.w, t0.w);
+            s1.x = __fadd_rn(s1.x, t1.x), s1.y = __fadd_rn(s1.y, t1.y), s1.z = __fadd_rn(s1.z, t1.z), s1.w = __fadd_rn(s1.w, t1.w);
+          }
+          const float t[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            hv[k][i] = t[i];
+            ss = __fmaf_rn(t[i], t[i], ss);
+          }
+          if (blockIdx.x == 0 && a.peer.rx_out) {
+            float4 *o4 = reinterpret_cast<float4 *>(a.peer.rx_out + (int64_t)b * a.cols + ch * 256 + lane * 8);
+            o4[0] = s0;
+            o4[1] = s1;
+          }
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+      float t = lane < kPipeAllWarps ? red[lane] : 0.0f;
+      t = warp_sum(t);
+      const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+#pragma unroll
+      for (int k = 0; k < kRxChunks; ++k) {
+        const int ch = warp + k * kPipeAllWarps;
+        if (ch * 256 < a.cols) {
+          const int e0 = ch * 256 + lane * 8;
+          const float4 wa = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0)), wb = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0) + 1);
+          const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(hv[k][i], scale), wv[i]);
+          emit_chunk(v, a, b, ch, lane, act_k, act_0, rec_col_stride, act0_col_stride);
+        }
+      }
+      continue;
+    }
     if (a.mode == 0) {
       // re-lay the pre-quantised global rows
       const int64_t astride = act_row_stride(a.cols);
@@ -380,31 +482,11 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
       }
-      if (a.need_k) {
-        int q[8];
-        float d;
-        q8k_quantise_chunk(v, lane, q, d);
-        uint8_t *rec = act_k + b * rec_col_stride + ch * kActRec;
-        *reinterpret_cast<uint2 *>(rec + lane * 8) = pack8(q);
-        int s16 = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
-        s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
-        const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-        if ((lane & 1) == 0) reinterpret_cast<short *>(rec + kRecBsum16)[lane >> 1] = (short)s16;
-        if ((lane & 3) == 0) reinterpret_cast<short *>(rec + kRecBsum32)[lane >> 2] = (short)s32;
-        if (lane == 0) *reinterpret_cast<float *>(rec + kRecD) = d;
-      }
-      if (a.need_0) {
-        int q[8];
-        float sc;
-        q80_quantise_chunk(v, q, sc);
-        if (e0 < a.cols) {
-          *reinterpret_cast<uint2 *>(act_0 + b * act0_col_stride + e0) = pack8(q);
-          if ((lane & 3) == 0) reinterpret_cast<float *>(act_0 + b * act0_col_stride + round_up16(a.cols))[e0 >> 5] = sc;
-        }
-      }
+      emit_chunk(v, a, b, ch, lane, act_k, act_0, rec_col_stride, act0_col_stride);
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+  if (tr) tr[3] = global_ns();
 
   // Main loop over this CTA's tiles; the two consumer groups alternate.
   const int group = warp / kPipeConsumerWarps, wg = warp % kPipeConsumerWarps;
@@ -469,12 +551,36 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
         const float v = segment_sum(acc[b], lis, L);
         if (active && lis == 0) {
           const int64_t o = (int64_t)b * J.y_stride + row0 + r_local;
-          J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), v) : v;
+          const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), v) : v;
+          if (a.peer.tx_n > 0) {
+            for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
+          } else {
+            J.y[o] = out;
+          }
         }
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[s]);
+  }
+  if (tr) tr[4] = global_ns();
+  if (a.peer.tx_n > 0) {
+    // The CTA barrier orders every consumer's stores before thread 0's system-scope fence (fences are
+    // cumulative), and the fence before this CTA's ticket; the CTA that takes the last ticket has
+    // therefore seen the whole launch's rows leave, and raises this rank's arrival word everywhere.
+    // (One fence per CTA: a system-scope fence in every thread costs tens of microseconds.)
+    asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+    if (tid == 0) {
+      __threadfence_system();
+      if (atomicAdd(a.peer.tx_ticket, 1u) == gridDim.x - 1) {
+        __threadfence_system();
+        *a.peer.tx_ticket = 0;
+        const uint32_t epoch = *a.peer.tx_epoch + 1;
+        *a.peer.tx_epoch = epoch;
+        for (int p = 0; p < a.peer.tx_n; ++p) st_release_sys(a.peer.tx_flag[p], epoch);
+      }
+      if (tr) tr[5] = global_ns();
+    }
   }
 }
 
@@ -585,7 +691,7 @@ int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs) {
 // message the caller would see) when the shape does not fit; the caller then uses the
 // direct-load kernel.
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
-                         cudaStream_t s, bool pdl) {
+                         cudaStream_t s, bool pdl, const GemvPeer *peer) {
   if (g_sm_count == 0) {
     int dev = 0;
     CMLD_CUDA(cudaGetDevice(&dev));
@@ -613,6 +719,13 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   a.need_0 = need_0;
   a.norm_out = pro.norm_out;
   a.status = status;
+  if (peer) {
+    a.peer = *peer;
+    a.peer_rank_stride = (int64_t)kPeerRows * cols;
+    if (peer->tx_n > 0 && (n_jobs != 1 || !status)) return fail(CMLD_ERR_INVALID, "gemv: a sending launch takes one matrix and a status word");
+    if (peer->rx_n > 0 && (pro.mode != 1 || cols % 256 || cols > kRxChunks * kPipeAllWarps * 256 || !status))
+      return fail(CMLD_ERR_INVALID, "gemv: a receiving launch is an RMSNorm prologue over at most %d columns", kRxChunks * kPipeAllWarps * 256);
+  }
   if (a.mode == 0 && ((need_k && !a.act_in) || (need_0 && !a.act_in0))) return fail(CMLD_ERR_INVALID, "gemv: activation buffer missing");
   const int grid = std::min(tiles, g_sm_count);
   switch (batch) {

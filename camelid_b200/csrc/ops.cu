@@ -389,3 +389,43 @@ int32_t launch_gather_permute(const float *gathered, float *out, int32_t ranks, 
 }
 
 }  // namespace cmld
+
+// ------------------------------------------------------------------ stand-alone receive of a peer sum
+namespace cmld {
+
+// h[b][c] = sum over ranks (in rank order) of the partial rows in the local slot, once every rank's
+// arrival word has reached the expected count.  The same arithmetic as the matvec kernel's
+// receiving prologue, for a step that ends on a sublayer instead of feeding another matvec.
+__global__ void peer_reduce_kernel(const GemvPeer rx, int32_t batch, int32_t hidden, int32_t *status) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if ((int)threadIdx.x < rx.rx_n) peer_wait(rx.rx_flag + threadIdx.x, __ldcg(rx.rx_epoch), rx.timeout_ns, status);
+  __syncthreads();
+  const int64_t rank_stride = (int64_t)kPeerRows * hidden;
+  const int64_t n4 = (int64_t)batch * hidden / 4;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 s = __ldcg(reinterpret_cast<const float4 *>(rx.rx_part) + i);
+    for (int r = 1; r < rx.rx_n; ++r) {
+      const float4 t = __ldcg(reinterpret_cast<const float4 *>(rx.rx_part + r * rank_stride) + i);
+      s.x = __fadd_rn(s.x, t.x), s.y = __fadd_rn(s.y, t.y), s.z = __fadd_rn(s.z, t.z), s.w = __fadd_rn(s.w, t.w);
+    }
+    reinterpret_cast<float4 *>(rx.rx_out)[i] = s;
+  }
+}
+
+int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, int32_t *status, bool pdl, cudaStream_t s) {
+  if (rx.rx_n < 1 || !rx.rx_out || !status || hidden % 4) return fail(CMLD_ERR_INVALID, "peer_reduce: bad arguments");
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)std::min<int64_t>(((int64_t)batch * hidden / 4 + 255) / 256, 64));
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CMLD_CUDA(cudaLaunchKernelEx(&cfg, peer_reduce_kernel, rx, batch, hidden, status));
+  return CMLD_OK;
+}
+
+}  // namespace cmld

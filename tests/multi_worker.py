@@ -54,6 +54,9 @@ def main():
     if mode == "run":
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **run_model(eng, cfg))
     else:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(70, exit=True)  # a stuck teardown must show where, and end
         # "leave": every rank but 0 goes away between steps, with nothing of its own in flight; rank 0
         # takes one more step, which must end in a timeout error and not in a hang
         first = eng.prefill_tokens(0, prompt(cfg.vocab, 0), 0)

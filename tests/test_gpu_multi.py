@@ -108,7 +108,7 @@ def test_rank_that_leaves_gives_its_peer_a_timeout_not_a_hang(tmp_path):
     """Failure made on the host: rank 1 goes away between steps with nothing in flight (NVLS off);
     rank 0's next step must come back with CMLD_ERR_TIMEOUT within the limit, and the engine must
     refuse further sharded steps with CMLD_ERR_STATE."""
-    _run_ranks(2, "tiny-tp", "q8_0", tmp_path, mode="leave", extra_env={"CMLD_COMM_TIMEOUT_MS": "3000"}, load=False, limit_s=180)
+    _run_ranks(2, "tiny-tp", "q8_0", tmp_path, mode="leave", extra_env={"CMLD_COMM_TIMEOUT_MS": "3000", "CMLD_DEBUG_COMM": "1"}, load=False, limit_s=90)
     outcome, after, waited = (tmp_path / "leave.txt").read_text().split()
     assert outcome == "code=6", outcome   # CMLD_ERR_TIMEOUT
     assert after == "code=7", after       # CMLD_ERR_STATE
