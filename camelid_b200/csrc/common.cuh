@@ -206,6 +206,7 @@ struct GemvPrologue {
   float eps;
   const uint8_t *act_k, *act_0;  // mode 0: Q8_K rows / Q8_0 rows in the global activation layout
   float *norm_out;         // optional: f32 copy of the prologue's result [batch][cols]
+  int32_t pair_swiglu;     // two matrices (gate, up) of equal shape and type: y of the first receives SwiGLU(gate.x, up.x)
 };
 // All-reduce of a tensor-parallel sublayer folded into the matvec kernels that produce and consume it,
 // over peer memory (NVLink): the producing launch (one matrix: o or down) stores its partial result
@@ -236,7 +237,7 @@ int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, in
 
 // Returns CMLD_ERR_UNSUPPORTED, leaving the error message untouched, when the shape does not fit.
 // Largest batch (<= 8) the staged kernel takes for these matrices in one launch; 0 = none.
-int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs);
+int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired = false);
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
                          cudaStream_t s, bool pdl, const GemvPeer *peer = nullptr);
 

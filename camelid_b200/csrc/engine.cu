@@ -439,13 +439,17 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
 // One sublayer's matvecs: y_i = W_i . quantise(f(x)) (+ residual), f = RMSNorm / identity / SwiGLU.
 // Fast path: the staged kernel with f and the quantiser fused into its prologue (batch in passes
 // of 8 columns).  Shapes it does not take fall back to quantise-kernel + direct-load kernel.
+// Prologue in the matvec CTAs only for the smallest batches: every CTA repeats it, so its cost grows with
+// the rows while a separate kernel does it once.
+constexpr int kFusedPrologueMaxBatch = 2;
+
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
-                          const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr) {
+                          const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr, bool pair_swiglu = false) {
   bool n0, nk;
   const Weight *ws[4];
   for (int i = 0; i < n; ++i) ws[i] = p[i].w;
   act_kinds(ws, n, n0, nk);
-  const bool fused = !(e->cfg.flags & CMLD_FLAG_SPLIT_PROLOGUE);
+  const bool fused = !(e->cfg.flags & CMLD_FLAG_SPLIT_PROLOGUE) && (batch <= kFusedPrologueMaxBatch || peer != nullptr);
   const bool pdl = !(e->cfg.flags & CMLD_FLAG_NO_PDL);
   if (e->cfg.flags & CMLD_FLAG_EXACT_ORDER) {
     // reference order: quantise once (sequential mean square), then one ordered matvec per matrix
@@ -461,7 +465,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
     GemvJob jobs[3];
     for (int i = 0; i < n; ++i)
       jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
-    const int fit = gemv_pipe_fit_batch(jobs, n);  // columns per pass: the same for every batch size, so
+    const int fit = gemv_pipe_fit_batch(jobs, n, pair_swiglu);  // columns per pass: the same for every batch size, so
     if (fit > 0) {                                // a row's result does not depend on who shares its step
       // Activation preparation.  Default: each matvec CTA computes norm / SwiGLU / quantisation itself in
       // its prologue (repeated on every SM, but no extra launch on the critical path); with
@@ -475,6 +479,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
           jobs[i].residual = p[i].residual ? p[i].residual + (int64_t)b0 * p[i].y_stride : nullptr;
         }
         GemvPrologue pro{};
+        pro.pair_swiglu = pair_swiglu ? 1 : 0;
         if (fused) {
           pro.mode = mode;
           pro.x = x + (int64_t)b0 * cols;
@@ -499,7 +504,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
       return CMLD_OK;
     }
   }
-  if (peer) return fail(CMLD_ERR_STATE, "peer-memory matvec does not fit the staged kernel");
+  if (peer || pair_swiglu) return fail(CMLD_ERR_STATE, "matvec with a fused sum or SwiGLU does not fit the staged kernel");
   CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
   return run_gemv_group(e, p, n, batch);
 }
@@ -601,7 +606,7 @@ static void peer_rx(const cmld_engine *e, int slot, GemvPeer &g) {
 // Whether a step of B rows can fold its sublayer sums into the matvec kernels: every matvec of the
 // step must go through the staged kernel in a single pass.
 static bool peer_step_ok(cmld_engine *e, int32_t B, bool taps) {
-  if (!e->peer.ready || e->tp <= 1 || taps || B > kPeerRows) return false;
+  if (!e->peer.ready || e->tp <= 1 || taps || B > kPeerRows || B > kFusedPrologueMaxBatch) return false;
   if (e->cfg.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_SPLIT_PROLOGUE | CMLD_FLAG_DIRECT_GEMV | CMLD_FLAG_NCCL_ONLY)) return false;
   auto it = e->peer_fit.find(B);
   if (it != e->peer_fit.end()) return it->second;
@@ -732,15 +737,24 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       const Proj p[2] = {{&L.proj[4], e->gate, nullptr, c.ffn_dim}, {&L.proj[5], e->up, nullptr, c.ffn_dim}};
       GemvPeer g{};
       take_pending(g);
-      CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden, use_peer ? &g : nullptr));
+      // gate and up of equal type: the staged kernel pairs their tiles and writes SwiGLU(gate, up) itself,
+      // so the down projection's operand is a plain quantisation of one vector
+      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt;
+      if (pair) {
+        const GemvJob pj[2] = {{L.proj[4].data, L.proj[4].qt, L.proj[4].rows, L.proj[4].cols, L.proj[4].stride, nullptr, nullptr, 0},
+                               {L.proj[5].data, L.proj[5].qt, L.proj[5].rows, L.proj[5].cols, L.proj[5].stride, nullptr, nullptr, 0}};
+        pair = gemv_pipe_fit_batch(pj, 2, true) >= 1;
+      }
+      CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden, use_peer ? &g : nullptr, pair));
       const Proj pd[1] = {{&L.proj[6], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
+      const int dmode = pair ? 2 : 3;  // operand: the SwiGLU vector already in e->gate, or SwiGLU(gate, up) to be formed
       if (use_peer) {
         GemvPeer gd{};
         peer_tx(e, 1, gd);
-        CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim, &gd));
+        CMLD_TRY(gemv_fused(e, pd, 1, B, dmode, e->gate, pair ? nullptr : e->up, nullptr, c.ffn_dim, &gd));
         pending = 1;
       } else {
-        CMLD_TRY(gemv_fused(e, pd, 1, B, 3, e->gate, e->up, nullptr, c.ffn_dim));
+        CMLD_TRY(gemv_fused(e, pd, 1, B, dmode, e->gate, pair ? nullptr : e->up, nullptr, c.ffn_dim));
         if (e->tp > 1) CMLD_TRY(reduce_hidden(e, B));
       }
     }

@@ -97,6 +97,7 @@ struct PipeArgs {
   const uint8_t *act_in;  // standard global layout, Q8_K rows (then Q8_0 rows at act_in0)
   const uint8_t *act_in0;
   int32_t need_k, need_0;
+  int32_t paired;  // two matrices of equal shape and type: tiles alternate between them and the result is SwiGLU(first, second)
   int32_t off_act_k, off_act_0, off_red, off_ring;
   float *norm_out;        // optional f32 copy of the normalised row (written by CTA 0)
   int32_t *status;
@@ -273,6 +274,62 @@ __device__ __forceinline__ float segment_sum(float v, int lane_in_seg, int len) 
   return v;
 }
 
+// Dot products of one staged tile: on return v[b] holds row r_local's result for batch column b in the
+// lanes with `writer` set (the first lane of each row's lane segment).
+template <int B>
+__device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, const uint8_t *tile, int nrows, int wg, int lane,
+                                         const uint8_t *act_k, const uint8_t *act_0, int nsb, int rec_col_stride,
+                                         int act0_col_stride, float (&v)[B], bool &writer, int &r_local) {
+  const int n_it = J.qt == CMLD_Q8_0 ? (a.cols >> 5) : nsb;  // work items per row: blocks or superblocks
+  const int L = n_it < 32 ? n_it : 32;                        // lanes per row
+  const int rpw = 32 / L;                                     // rows per warp
+  r_local = wg * rpw + lane / L;
+  const int lis = lane % L;
+  const bool active = lane < rpw * L && r_local < nrows;
+  float acc[B];
+#pragma unroll
+  for (int b = 0; b < B; ++b) acc[b] = 0.0f;
+  if (active) {
+    const uint8_t *row = tile + (int64_t)r_local * J.stride;
+    if (J.qt == CMLD_Q4_K) {
+      for (int sb = lis; sb < nsb; sb += L) sb_dot_q4k<B>(row + sb * 144, act_k + sb * kActRec, rec_col_stride, acc);
+    } else if (J.qt == CMLD_Q6_K) {
+      for (int sb = lis; sb < nsb; sb += L) {
+        const float dw = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + nsb * 208 + 2 * sb));
+        sb_dot_q6k<B>(row + sb * 208, dw, act_k + sb * kActRec, rec_col_stride, acc);
+      }
+    } else {
+      // Q8_0: a lane owns 32-value blocks; the two 16-byte halves are read in an order that
+      // keeps the eight lanes of a shared-memory phase on distinct banks
+      const int hs = (lane >> 2) & 1;
+      for (int blk = lis; blk < n_it; blk += L) {
+        const uint4 w0 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * hs);
+        const uint4 w1 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * (hs ^ 1));
+        const float ws = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + a.cols + 2 * blk));
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const uint8_t *xa = act_0 + b * act0_col_stride;
+          const int4 x0 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * hs);
+          const int4 x1 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * (hs ^ 1));
+          int isum = __dp4a((int)w0.x, x0.x, 0);
+          isum = __dp4a((int)w0.y, x0.y, isum);
+          isum = __dp4a((int)w0.z, x0.z, isum);
+          isum = __dp4a((int)w0.w, x0.w, isum);
+          isum = __dp4a((int)w1.x, x1.x, isum);
+          isum = __dp4a((int)w1.y, x1.y, isum);
+          isum = __dp4a((int)w1.z, x1.z, isum);
+          isum = __dp4a((int)w1.w, x1.w, isum);
+          const float xs = reinterpret_cast<const float *>(xa + round_up16(a.cols))[blk];
+          acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn((float)isum, ws), xs));  // src/inference.rs:26198
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int b = 0; b < B; ++b) v[b] = segment_sum(acc[b], lis, L);
+  writer = active && lis == 0;
+}
+
 // ---------------------------------------------------------------- the kernel
 
 template <int B>
@@ -286,7 +343,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   uint8_t *ring = smem + a.off_ring;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = a.n_stages;
-  const int n_my = (int)blockIdx.x < a.total_tiles ? (a.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  // tiles this CTA takes: t = blockIdx.x + i*gridDim.x; in paired mode the unit is a (gate, up) pair of tiles
+  const int n_units = a.paired ? a.job[0].n_tiles : a.total_tiles;
+  const int n_my = ((int)blockIdx.x < n_units ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0) * (a.paired ? 2 : 1);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -316,12 +375,17 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       for (int i = 0; i < n_my; ++i) {
         const int s = i % S;
         if (i >= S) mbar_wait(&empty[s], (uint32_t)((i / S - 1) & 1), a.status);
-        const int t = (int)blockIdx.x + i * (int)gridDim.x;
-        int j = 0;
-        if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
-        if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+        int j = 0, row0;
+        if (a.paired) {
+          j = i & 1;
+          row0 = ((int)blockIdx.x + (i >> 1) * (int)gridDim.x) * a.job[0].tile_rows;
+        } else {
+          const int t = (int)blockIdx.x + i * (int)gridDim.x;
+          if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+          if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+          row0 = (t - a.job[j].first_tile) * a.job[j].tile_rows;
+        }
         const PipeJob &J = a.job[j];
-        const int row0 = (t - J.first_tile) * J.tile_rows;
         const int nrows = min(J.tile_rows, J.rows - row0);
         const uint32_t bytes = (uint32_t)(nrows * J.stride);
         mbar_expect_tx(&full[s], bytes);
@@ -490,78 +554,68 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 
   // Main loop over this CTA's tiles; the two consumer groups alternate.
   const int group = warp / kPipeConsumerWarps, wg = warp % kPipeConsumerWarps;
-  for (int i = group; i < n_my; i += kPipeGroups) {
-    const int s = i % S;
-    const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-    const int t = (int)blockIdx.x + i * (int)gridDim.x;
-    int j = 0;
-    if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
-    if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
-    const PipeJob &J = a.job[j];
-    const int row0 = (t - J.first_tile) * J.tile_rows;
-    const int nrows = min(J.tile_rows, J.rows - row0);
-    const uint8_t *tile = ring + (int64_t)s * a.stage_bytes;
-    if (ready) {
-      const int n_it = J.qt == CMLD_Q8_0 ? (a.cols >> 5) : nsb;  // work items per row: blocks or superblocks
-      const int L = n_it < 32 ? n_it : 32;                        // lanes per row
-      const int rpw = 32 / L;                                     // rows per warp
-      const int r_local = wg * rpw + lane / L, lis = lane % L;
-      const bool active = lane < rpw * L && r_local < nrows;
-      float acc[B];
+  if (a.paired) {
+    // gate and up tiles of the same rows come as consecutive tiles 2k, 2k+1 of this CTA; a group keeps
+    // the gate rows' results in registers, takes the up tile and writes SwiGLU(gate, up) — the f32
+    // activation of the down projection — so neither product goes through memory on its own.
+    for (int k = group; 2 * k < n_my; k += kPipeGroups) {
+      const int pair = (int)blockIdx.x + k * (int)gridDim.x;
+      const int row0 = pair * a.job[0].tile_rows;
+      const int nrows = min(a.job[0].tile_rows, a.job[0].rows - row0);
+      float gv[B], uv[B];
+      bool writer = false;
+      int r_local = 0;
 #pragma unroll
-      for (int b = 0; b < B; ++b) acc[b] = 0.0f;
-      if (active) {
-        const uint8_t *row = tile + (int64_t)r_local * J.stride;
-        if (J.qt == CMLD_Q4_K) {
-          for (int sb = lis; sb < nsb; sb += L) sb_dot_q4k<B>(row + sb * 144, act_k + sb * kActRec, rec_col_stride, acc);
-        } else if (J.qt == CMLD_Q6_K) {
-          for (int sb = lis; sb < nsb; sb += L) {
-            const float dw = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + nsb * 208 + 2 * sb));
-            sb_dot_q6k<B>(row + sb * 208, dw, act_k + sb * kActRec, rec_col_stride, acc);
-          }
+      for (int which = 0; which < 2; ++which) {
+        const int i = 2 * k + which, s = i % S;
+        const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+        if (ready) {
+          if (which == 0) tile_dot<B>(a, a.job[0], ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride, act0_col_stride, gv, writer, r_local);
+          else tile_dot<B>(a, a.job[1], ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride, act0_col_stride, uv, writer, r_local);
         } else {
-          // Q8_0: a lane owns 32-value blocks; the two 16-byte halves are read in an order that
-          // keeps the eight lanes of a shared-memory phase on distinct banks
-          const int hs = (lane >> 2) & 1;
-          for (int blk = lis; blk < n_it; blk += L) {
-            const uint4 w0 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * hs);
-            const uint4 w1 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * (hs ^ 1));
-            const float ws = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + a.cols + 2 * blk));
 #pragma unroll
-            for (int b = 0; b < B; ++b) {
-              const uint8_t *xa = act_0 + b * act0_col_stride;
-              const int4 x0 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * hs);
-              const int4 x1 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * (hs ^ 1));
-              int isum = __dp4a((int)w0.x, x0.x, 0);
-              isum = __dp4a((int)w0.y, x0.y, isum);
-              isum = __dp4a((int)w0.z, x0.z, isum);
-              isum = __dp4a((int)w0.w, x0.w, isum);
-              isum = __dp4a((int)w1.x, x1.x, isum);
-              isum = __dp4a((int)w1.y, x1.y, isum);
-              isum = __dp4a((int)w1.z, x1.z, isum);
-              isum = __dp4a((int)w1.w, x1.w, isum);
-              const float xs = reinterpret_cast<const float *>(xa + round_up16(a.cols))[blk];
-              acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn((float)isum, ws), xs));  // src/inference.rs:26198
+          for (int b = 0; b < B; ++b) gv[b] = uv[b] = 0.0f;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+      }
+      if (writer) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + r_local] = swiglu(gv[b], uv[b]);
+      }
+    }
+  } else {
+    for (int i = group; i < n_my; i += kPipeGroups) {
+      const int s = i % S;
+      const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+      const int t = (int)blockIdx.x + i * (int)gridDim.x;
+      int j = 0;
+      if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+      if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+      const PipeJob &J = a.job[j];
+      const int row0 = (t - J.first_tile) * J.tile_rows;
+      const int nrows = min(J.tile_rows, J.rows - row0);
+      if (ready) {
+        float v[B];
+        bool writer;
+        int r_local;
+        tile_dot<B>(a, J, ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride, act0_col_stride, v, writer, r_local);
+        if (writer) {
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            const int64_t o = (int64_t)b * J.y_stride + row0 + r_local;
+            const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), v[b]) : v[b];
+            if (a.peer.tx_n > 0) {
+              for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
+            } else {
+              J.y[o] = out;
             }
           }
         }
       }
-#pragma unroll
-      for (int b = 0; b < B; ++b) {
-        const float v = segment_sum(acc[b], lis, L);
-        if (active && lis == 0) {
-          const int64_t o = (int64_t)b * J.y_stride + row0 + r_local;
-          const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), v) : v;
-          if (a.peer.tx_n > 0) {
-            for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
-          } else {
-            J.y[o] = out;
-          }
-        }
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
   }
   if (tr) tr[4] = global_ns();
   if (a.peer.tx_n > 0) {
@@ -615,7 +669,8 @@ static int32_t launch_pipe_b(const PipePlan &p, int grid, cudaStream_t s, bool p
 }
 
 // Tile geometry and shared-memory map for these matrices at this batch; false if it does not fit.
-static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &p, bool &need_k, bool &need_0, int &tiles_out) {
+static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &p, bool &need_k, bool &need_0, int &tiles_out,
+                      bool paired = false) {
   if (n_jobs < 1 || n_jobs > 3 || batch < 1 || batch > 8) return false;
   const int64_t cols = jobs[0].cols;
   if (cols % 32) return false;
@@ -666,10 +721,13 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   int n_stages = 0;
   for (int budget : {110 * 1024, 224 * 1024}) {
     n_stages = std::min<int>(kPipeMaxStages, (budget - off) / stage);
-    n_stages -= n_stages % kPipeGroups;
+    // paired mode: a group owns tiles 2k and 2k+1, so a stage stays with one group only if the stage
+    // count is a multiple of twice the number of groups
+    n_stages -= n_stages % (paired ? 2 * kPipeGroups : kPipeGroups);
     if (n_stages >= 4) break;
   }
-  if (n_stages < 2) return false;
+  if (n_stages < (paired ? 4 : 2)) return false;
+  if (paired && (n_jobs != 2 || jobs[0].rows != jobs[1].rows || jobs[0].qt != jobs[1].qt || jobs[0].stride != jobs[1].stride)) return false;
   p.smem_bytes = off + n_stages * stage;
   a.stage_bytes = stage;
   a.n_stages = n_stages;
@@ -677,12 +735,12 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   return true;
 }
 
-int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs) {
+int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired) {
   for (int b = 8; b >= 1; --b) {
     PipePlan p{};
     bool nk, n0;
     int tiles;
-    if (plan_pipe(jobs, n_jobs, b, p, nk, n0, tiles)) return b;
+    if (plan_pipe(jobs, n_jobs, b, p, nk, n0, tiles, paired)) return b;
   }
   return 0;
 }
@@ -701,7 +759,7 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   PipeArgs &a = p.args;
   bool need_k = false, need_0 = false;
   int tiles = 0;
-  if (!plan_pipe(jobs, n_jobs, batch, p, need_k, need_0, tiles)) return CMLD_ERR_UNSUPPORTED;
+  if (!plan_pipe(jobs, n_jobs, batch, p, need_k, need_0, tiles, pro.pair_swiglu != 0)) return CMLD_ERR_UNSUPPORTED;
   const int64_t cols = jobs[0].cols;
   a.n_jobs = n_jobs;
   a.total_tiles = tiles;
@@ -719,6 +777,8 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   a.need_0 = need_0;
   a.norm_out = pro.norm_out;
   a.status = status;
+  a.paired = pro.pair_swiglu ? 1 : 0;
+  if (a.paired && peer && peer->tx_n > 0) return fail(CMLD_ERR_INVALID, "gemv: a paired launch does not send");
   if (peer) {
     a.peer = *peer;
     a.peer_rank_stride = (int64_t)kPeerRows * cols;
@@ -727,7 +787,7 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
       return fail(CMLD_ERR_INVALID, "gemv: a receiving launch is an RMSNorm prologue over at most %d columns", kRxChunks * kPipeAllWarps * 256);
   }
   if (a.mode == 0 && ((need_k && !a.act_in) || (need_0 && !a.act_in0))) return fail(CMLD_ERR_INVALID, "gemv: activation buffer missing");
-  const int grid = std::min(tiles, g_sm_count);
+  const int grid = std::min(a.paired ? a.job[0].n_tiles : tiles, g_sm_count);
   switch (batch) {
     case 1: return launch_pipe_b<1>(p, grid, s, pdl);
     case 2: return launch_pipe_b<2>(p, grid, s, pdl);

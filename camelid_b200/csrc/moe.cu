@@ -24,7 +24,7 @@ void weight_free(Weight &w);
 
 constexpr int kMaxExperts = 64;
 constexpr int kMoeCols = 4;  // activation columns per pass of the expert matvec
-constexpr int kMoeRows = 2;
+constexpr int kMoeRows = 4;
 constexpr int kMoeWarps = 4;
 
 // total_cmp key of an f32 (Rust f32::total_cmp).
