@@ -50,6 +50,18 @@ static int g_gemv_kernel_choice = 0;  // 0 auto (staged when the shape fits), 1 
 static int32_t gemv_launch(const cmld_weight *w, const uint8_t *act, int32_t batch, float *y, const float *residual,
                            cudaStream_t stream = nullptr, bool pdl = false) {
   GemvJob probe{w->data, w->qt, w->rows, w->cols, w->stride, y, residual, w->rows};
+  if (g_gemv_kernel_choice == 0 && batch > 8 && batch <= 32) {
+    // more than 8 rows: one pass over the weights on the tensor cores
+    const int64_t need = gemv_mma_scratch_floats(&probe, 1, batch);
+    if (need >= 0) {
+      float *scratch = nullptr;
+      if (need > 0) CMLD_CUDA(cudaMalloc(&scratch, (size_t)need * 4));
+      int32_t rc = launch_gemv_mma(&probe, 1, act, batch, scratch, need, op_status(), stream, pdl, nullptr);
+      if (rc == CMLD_OK && cudaStreamSynchronize(stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "gemv: batched launch failed");
+      if (scratch) cudaFree(scratch);
+      if (rc != CMLD_ERR_UNSUPPORTED) return rc;
+    }
+  }
   const int fit = g_gemv_kernel_choice == 0 ? gemv_pipe_fit_batch(&probe, 1) : 0;
   const int pass = fit > 0 ? fit : 8;
   for (int b0 = 0; b0 < batch; b0 += pass) {

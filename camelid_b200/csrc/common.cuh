@@ -241,6 +241,11 @@ int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired = false);
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
                          cudaStream_t s, bool pdl, const GemvPeer *peer = nullptr);
 
+// gemv_mma.cu: 9..32 activation rows in one pass over the weights (int8 tensor-core MMA)
+int64_t gemv_mma_scratch_floats(const GemvJob *jobs, int n_jobs, int32_t batch);
+int32_t launch_gemv_mma(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, float *scratch, int64_t scratch_floats,
+                        int32_t *status, cudaStream_t s, bool pdl, int64_t *launches);
+
 // ops.cu
 struct NormQuantArgs {
   const float *x;       // [batch][cols]

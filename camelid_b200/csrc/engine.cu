@@ -124,6 +124,8 @@ struct cmld_engine {
     uint32_t *local = nullptr;        // epochs[2], tickets[2]
     unsigned long long timeout_ns = 0;
   } peer;
+  float *mma_scratch = nullptr;  // per-chunk partial sums of the batched tensor-core matvec
+  int64_t mma_scratch_floats = 0;
   unsigned long long *trace = nullptr;  // matvec timeline (environment CMLD_TRACE=<file>), dumped at destroy
   std::string trace_path;
   std::map<int32_t, bool> peer_fit;   // rows -> every matvec of a step fits the staged kernel in one pass
@@ -225,7 +227,7 @@ static int32_t engine_init(cmld_engine *e) {
   CMLD_CUDA(cudaEventCreate(&e->ev0));
   CMLD_CUDA(cudaEventCreate(&e->ev1));
   const int seqs = std::max(1, c.max_seqs);
-  e->max_rows = std::max(seqs, 16);
+  e->max_rows = std::max(seqs, 32);  // a prompt is ingested 32 rows at a time (one tensor-core pass over the weights)
   e->q_width = c.n_heads * c.head_dim;
   e->kv_width = c.n_kv_heads * c.head_dim;
   e->layers.resize(c.n_layers);
@@ -298,6 +300,18 @@ static int32_t engine_init(cmld_engine *e) {
     CMLD_TRY(dev_alloc(e, &e->moe_u, na * c.ffn_dim));
     CMLD_TRY(dev_alloc(e, &e->moe_act, na * c.ffn_dim));
     CMLD_TRY(dev_alloc(e, &e->moe_down, na * c.hidden));
+  }
+  {
+    // the batched matvec cuts the columns into 1024-wide chunks and sums the chunks afterwards
+    auto chunks = [](int64_t cols) { return (cols / 256 + 3) / 4; };
+    int64_t need = 0;
+    need = std::max(need, chunks(c.hidden) * (e->q_width + 2 * (int64_t)e->kv_width));
+    need = std::max(need, chunks(e->q_width) * c.hidden);
+    need = std::max(need, chunks(c.hidden) * 2 * (int64_t)c.ffn_dim);
+    need = std::max(need, chunks(c.ffn_dim) * c.hidden);
+    need = std::max(need, chunks(c.hidden) * (int64_t)e->vocab_local);
+    e->mma_scratch_floats = need * 32;
+    CMLD_TRY(dev_alloc(e, &e->mma_scratch, e->mma_scratch_floats, false));
   }
   if (const char *tp = getenv("CMLD_TRACE")) {
     e->trace_path = std::string(tp) + "." + std::to_string(e->shard_rank);
@@ -460,6 +474,26 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
       e->launches += 1;
     }
     return CMLD_OK;
+  }
+  if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3 && batch > 8 && !peer && !pair_swiglu && !(n0 && nk)) {
+    // more rows than the dp4a kernel takes in one pass: one pass over the weights on the tensor cores
+    GemvJob jobs[3];
+    for (int i = 0; i < n; ++i)
+      jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
+    const int64_t need = gemv_mma_scratch_floats(jobs, n, std::min(batch, 32));
+    if (need >= 0 && need <= e->mma_scratch_floats) {
+      CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
+      for (int b0 = 0; b0 < batch; b0 += 32) {
+        const int nb = std::min(32, batch - b0);
+        for (int i = 0; i < n; ++i) {
+          jobs[i].y = p[i].y + (int64_t)b0 * p[i].y_stride;
+          jobs[i].residual = p[i].residual ? p[i].residual + (int64_t)b0 * p[i].y_stride : nullptr;
+        }
+        const uint8_t *act = (n0 ? e->act_0 : e->act_k) + (int64_t)b0 * act_row_stride(cols);
+        CMLD_TRY(launch_gemv_mma(jobs, n, act, nb, e->mma_scratch, e->mma_scratch_floats, e->d_status, e->stream, pdl, &e->launches));
+      }
+      return CMLD_OK;
+    }
   }
   if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3) {
     GemvJob jobs[3];
@@ -739,7 +773,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       take_pending(g);
       // gate and up of equal type: the staged kernel pairs their tiles and writes SwiGLU(gate, up) itself,
       // so the down projection's operand is a plain quantisation of one vector
-      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt;
+      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt && B <= 8;
       if (pair) {
         const GemvJob pj[2] = {{L.proj[4].data, L.proj[4].qt, L.proj[4].rows, L.proj[4].cols, L.proj[4].stride, nullptr, nullptr, 0},
                                {L.proj[5].data, L.proj[5].qt, L.proj[5].rows, L.proj[5].cols, L.proj[5].stride, nullptr, nullptr, 0}};
@@ -1380,7 +1414,8 @@ int32_t cmld_engine_prefill_from(cmld_engine *e, const float *embeddings, const 
   CMLD_ENGINE_ENTER(e);
   if (n < 0 || start < 0 || start > n) return fail(CMLD_ERR_INVALID, "prefill: start=%lld exceeds n=%lld", (long long)start, (long long)n);
   const int half = e->cfg.rope_dim / 2;
-  const int chunk = 8;
+  // up to 8 rows go through the row kernel (bit-identical to serial calls); longer prompts 32 rows at a time
+  const int chunk = (n - start > 8 && !(e->cfg.flags & CMLD_FLAG_EXACT_ORDER)) ? 32 : 8;
   for (int64_t i = start; i < n; i += chunk) {
     const int rows = (int)std::min<int64_t>(chunk, n - i);
     CMLD_TRY(forward_embedding_rows(e, embeddings + i * e->cfg.hidden, cos_all + i * half, sin_all + i * half, i, rows, scale,
@@ -1513,7 +1548,7 @@ int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *t
   CMLD_ENGINE_ENTER(e);
   if (n < 1 || !tokens) return fail(CMLD_ERR_INVALID, "prefill_tokens: no tokens");
   CMLD_TRY(require_weights(e, true));
-  const int chunk = 8;
+  const int chunk = (n > 8 && !(e->cfg.flags & CMLD_FLAG_EXACT_ORDER)) ? 32 : 8;
   e->launches = 0;
   CMLD_CUDA(cudaEventRecord(e->ev0, e->stream));
   int last_rows = 0;

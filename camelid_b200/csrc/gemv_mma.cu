@@ -1,0 +1,548 @@
+// Batched quantised matvec for 9..32 activation rows: the weights are streamed ONCE for all rows and the
+// int8 x int8 block dot products run on the tensor cores (mma.sync m16n8k32 / m16n8k16, s8 x s8 -> s32).
+//
+// Same arithmetic as the row kernels (q4_k_q8_k_dot_rows / q6_k_q8_k_dot_rows / q8_0_dot_rows,
+// src/inference.rs:23154-23520 and :26166 in the Camelid tree): integer dot per scale group, integer
+// scale multiply, one f32 step per superblock (per block for Q8_0).  Only the order in which the
+// superblocks' f32 terms of one row are added differs (here: in column order within a 1024-column
+// chunk, chunks added in order), so results agree with the <= 8-row kernel up to f32 reassociation.
+//
+// Layout of the work: the columns are cut into chunks of 1024 (4 superblocks); a CTA owns ONE chunk for
+// its whole life and keeps the quantised activations of that chunk for all rows in shared memory
+// (32 x 1024 codes + scales), so the operand that every weight tile needs is loaded once per CTA.  The
+// CTA walks tiles of 64 weight rows of its chunk: a producer warp copies each row's chunk bytes with
+// one bulk asynchronous copy per row into a padded (bank-conflict-free) slot of an mbarrier ring; two
+// groups of four consumer warps alternate tiles, every warp owning 16 rows (one MMA row tile) for the
+// whole chunk and all <= 4 column tiles of 8 activation rows — no reduction across warps.  With more
+// than one chunk the per-chunk partial sums go to a scratch array and a small kernel adds them in chunk
+// order (plus the residual).  All waits are bounded.
+#include "common.cuh"
+
+namespace cmld {
+
+constexpr int kMmaWarpsPerGroup = 4;
+constexpr int kMmaGroups = 2;
+constexpr int kMmaConsumerWarps = kMmaWarpsPerGroup * kMmaGroups;
+constexpr int kMmaConsumers = kMmaConsumerWarps * 32;
+constexpr int kMmaThreads = kMmaConsumers + 32;
+constexpr int kMmaTileRows = kMmaWarpsPerGroup * 16;
+constexpr int kMmaChunkSb = 4;  // superblocks (of 256 columns) per chunk
+constexpr int kMmaChunkCols = kMmaChunkSb * 256;
+constexpr int kMmaMaxStages = 4;
+constexpr int kMmaCodeStride = kMmaChunkCols + 16;  // bytes between activation rows in shared memory (conflict-free)
+constexpr uint32_t kMmaSpinLimit = 1u << 22;
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint64_t *bar, uint32_t parity, int32_t *status) {
+  for (uint32_t i = 0; i < kMmaSpinLimit; ++i)
+    if (bar_try_wait(bar, parity)) return true;
+  if (status) atomicExch(status, (int32_t)CMLD_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void bulk_copy(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst_smem)),
+               "l"(src), "r"(bytes), "r"(smem_addr(bar))
+               : "memory");
+}
+
+// D(16x8, s32) = A(16x32, s8, row-major) * B(32x8, s8, column-major).  Lane (g = lane/4, t = lane%4) holds
+// A: a0 = row g, k 4t..4t+3; a1 = row g+8, same k; a2 = row g, k 16+4t..; a3 = row g+8, k 16+4t..
+// B: b0 = k 4t..4t+3 of column g; b1 = k 16+4t.. of column g
+// D: d0,d1 = row g, columns 2t, 2t+1; d2,d3 = row g+8, columns 2t, 2t+1
+__device__ __forceinline__ void mma_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+// D(16x8) = A(16x16) * B(16x8): a0 = row g, k 4t..4t+3; a1 = row g+8; b0 = k 4t..4t+3 of column g.
+__device__ __forceinline__ void mma_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+struct MmaJob {
+  const uint8_t *w;
+  int32_t qt, rows, first_tile, n_tiles, row_off;
+  int64_t stride;
+  float *y;
+  const float *residual;
+  int64_t y_stride;
+};
+
+struct MmaArgs {
+  MmaJob job[3];
+  int32_t n_jobs, total_tiles, cols, batch, n_chunks, ctas_per_chunk, stage_bytes, n_stages, rows_cat, q8_0;
+  const uint8_t *act;  // quantised activation rows, global layout, the format the jobs' types need
+  float *partial;      // [chunk][batch][rows_cat] when n_chunks > 1
+  int32_t *status;
+  int32_t off_codes, off_scale, off_bsum, off_ring;
+};
+
+// bytes of one weight row's chunk in shared memory (padded so that 8 rows x 4 words hit 32 distinct banks)
+__host__ __device__ inline int row_pitch(int qt) { return (qt == CMLD_Q4_K ? 4 * 144 : (qt == CMLD_Q6_K ? 4 * 208 : 4 * 256 + 4 * 16)) + 16; }
+
+template <int NT>
+__device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xd,
+                                         const short *bs16, float (&acc)[NT][4]) {
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int pitch = row_pitch(CMLD_Q4_K);
+  const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
+  for (int sb = 0; sb < ns; ++sb) {
+    const uint8_t *plo = rlo + sb * 144, *phi = rhi + sb * 144;
+    const uint4 mlo = *reinterpret_cast<const uint4 *>(plo), mhi = *reinterpret_cast<const uint4 *>(phi);
+    int isum[NT][4], msum[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) isum[nt][i] = msum[nt][i] = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t wl0 = *reinterpret_cast<const uint32_t *>(plo + 16 + j * 32 + t4 * 4);
+      const uint32_t wl1 = *reinterpret_cast<const uint32_t *>(plo + 16 + j * 32 + 16 + t4 * 4);
+      const uint32_t wh0 = *reinterpret_cast<const uint32_t *>(phi + 16 + j * 32 + t4 * 4);
+      const uint32_t wh1 = *reinterpret_cast<const uint32_t *>(phi + 16 + j * 32 + 16 + t4 * 4);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int g = 2 * j + h;
+        int sc_lo, m_lo, sc_hi, m_hi;
+        q4k_scale_min(g, mlo.y, mlo.z, mlo.w, sc_lo, m_lo);
+        q4k_scale_min(g, mhi.y, mhi.z, mhi.w, sc_hi, m_hi);
+        const uint32_t a0 = (wl0 >> (4 * h)) & 0x0f0f0f0fu, a1 = (wh0 >> (4 * h)) & 0x0f0f0f0fu;
+        const uint32_t a2 = (wl1 >> (4 * h)) & 0x0f0f0f0fu, a3 = (wh1 >> (4 * h)) & 0x0f0f0f0fu;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint8_t *xc = codes + (nt * 8 + g8) * kMmaCodeStride + sb * 256 + g * 32 + t4 * 4;
+          const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xc), b1 = *reinterpret_cast<const uint32_t *>(xc + 16);
+          int c[4];
+          mma_k32(c, a0, a1, a2, a3, b0, b1);
+          isum[nt][0] += sc_lo * c[0];
+          isum[nt][1] += sc_lo * c[1];
+          isum[nt][2] += sc_hi * c[2];
+          isum[nt][3] += sc_hi * c[3];
+          // the mins meet the sums of the activation codes of the group: bsum32 = two 16-sums
+          const short *b0p = bs16 + (nt * 8 + t4 * 2) * 64 + sb * 16 + 2 * g;
+          const int s0 = (int)b0p[0] + (int)b0p[1], s1 = (int)b0p[64] + (int)b0p[65];
+          msum[nt][0] += m_lo * s0;
+          msum[nt][1] += m_lo * s1;
+          msum[nt][2] += m_hi * s0;
+          msum[nt][3] += m_hi * s1;
+        }
+      }
+    }
+    const float d_lo = f16_bits_to_f32((uint16_t)(mlo.x & 0xffff)), dm_lo = f16_bits_to_f32((uint16_t)(mlo.x >> 16));
+    const float d_hi = f16_bits_to_f32((uint16_t)(mhi.x & 0xffff)), dm_hi = f16_bits_to_f32((uint16_t)(mhi.x >> 16));
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x = xd[(nt * 8 + t4 * 2 + (i & 1)) * kMmaChunkSb + sb];
+        const float d = i < 2 ? d_lo : d_hi, dm = i < 2 ? dm_lo : dm_hi;
+        // src/inference.rs:23230-23236: sumf = fma(-dmin*xd, mins, sumf); sumf = fma(d*xd, dots, sumf)
+        acc[nt][i] = __fmaf_rn(-__fmul_rn(dm, x), (float)msum[nt][i], acc[nt][i]);
+        acc[nt][i] = __fmaf_rn(__fmul_rn(d, x), (float)isum[nt][i], acc[nt][i]);
+      }
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xd,
+                                         const short *bs16, float d_lo[kMmaChunkSb], float d_hi[kMmaChunkSb], float (&acc)[NT][4]) {
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int pitch = row_pitch(CMLD_Q6_K);
+  const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
+  for (int sb = 0; sb < ns; ++sb) {
+    const uint8_t *plo = rlo + sb * 208, *phi = rhi + sb * 208;
+    int isum[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) isum[nt][i] = 0;
+#pragma unroll
+    for (int s = 0; s < 16; ++s) {
+      // sub-block s of 16 values: half n, quarter qd (which 2 bits of qh, which nibble of which ql half), part lp
+      const int n = s >> 3, qd = (s & 7) >> 1, lp = s & 1;
+      const int qlo = n * 64 + (qd & 1) * 32 + 16 * lp + t4 * 4, qho = 128 + n * 32 + 16 * lp + t4 * 4;
+      const uint32_t wl = *reinterpret_cast<const uint32_t *>(plo + qlo), wlh = *reinterpret_cast<const uint32_t *>(plo + qho);
+      const uint32_t wh = *reinterpret_cast<const uint32_t *>(phi + qlo), whh = *reinterpret_cast<const uint32_t *>(phi + qho);
+      const uint32_t a0 = ((wl >> (4 * (qd >> 1))) & 0x0f0f0f0fu) | (((wlh >> (2 * qd)) & 0x03030303u) << 4);
+      const uint32_t a1 = ((wh >> (4 * (qd >> 1))) & 0x0f0f0f0fu) | (((whh >> (2 * qd)) & 0x03030303u) << 4);
+      const int sc_lo = (int)reinterpret_cast<const int8_t *>(plo + 192)[s], sc_hi = (int)reinterpret_cast<const int8_t *>(phi + 192)[s];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(codes + (nt * 8 + g8) * kMmaCodeStride + sb * 256 + s * 16 + t4 * 4);
+        int c[4];
+        mma_k16(c, a0, a1, b0);
+        // codes are stored +32: sum (q-32) x = sum q x - 32 * (sum of the 16 activation codes)
+        const short *bp = bs16 + (nt * 8 + t4 * 2) * 64 + sb * 16 + s;
+        const int k0 = 32 * (int)bp[0], k1 = 32 * (int)bp[64];
+        isum[nt][0] += sc_lo * (c[0] - k0);
+        isum[nt][1] += sc_lo * (c[1] - k1);
+        isum[nt][2] += sc_hi * (c[2] - k0);
+        isum[nt][3] += sc_hi * (c[3] - k1);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x = xd[(nt * 8 + t4 * 2 + (i & 1)) * kMmaChunkSb + sb];
+        acc[nt][i] = __fadd_rn(acc[nt][i], __fmul_rn(__fmul_rn(i < 2 ? d_lo[sb] : d_hi[sb], x), (float)isum[nt][i]));
+      }
+  }
+}
+
+template <int NT>
+__device__ __forceinline__ void tile_q80(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xs,
+                                         float (&acc)[NT][4]) {
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int pitch = row_pitch(CMLD_Q8_0);
+  const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
+  for (int blk = 0; blk < ns * 8; ++blk) {
+    const uint32_t a0 = *reinterpret_cast<const uint32_t *>(rlo + blk * 32 + t4 * 4), a2 = *reinterpret_cast<const uint32_t *>(rlo + blk * 32 + 16 + t4 * 4);
+    const uint32_t a1 = *reinterpret_cast<const uint32_t *>(rhi + blk * 32 + t4 * 4), a3 = *reinterpret_cast<const uint32_t *>(rhi + blk * 32 + 16 + t4 * 4);
+    const float ws_lo = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rlo + ns * 256 + blk * 2));
+    const float ws_hi = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rhi + ns * 256 + blk * 2));
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint8_t *xc = codes + (nt * 8 + g8) * kMmaCodeStride + blk * 32 + t4 * 4;
+      const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xc), b1 = *reinterpret_cast<const uint32_t *>(xc + 16);
+      int c[4];
+      mma_k32(c, a0, a1, a2, a3, b0, b1);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x = xs[(nt * 8 + t4 * 2 + (i & 1)) * (kMmaChunkSb * 8) + blk];
+        acc[nt][i] = __fadd_rn(acc[nt][i], __fmul_rn(__fmul_rn((float)c[i], i < 2 ? ws_lo : ws_hi), x));  // src/inference.rs:26198
+      }
+    }
+  }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const MmaArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+  uint64_t *empty = full + kMmaMaxStages;
+  uint8_t *codes = smem + a.off_codes;
+  float *xscale = reinterpret_cast<float *>(smem + a.off_scale);
+  short *bs16 = reinterpret_cast<short *>(smem + a.off_bsum);
+  uint8_t *ring = smem + a.off_ring;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = a.n_stages;
+  const int chunk = (int)blockIdx.x % a.n_chunks, slot = (int)blockIdx.x / a.n_chunks;
+  const int nsb = a.cols >> 8;
+  const int sb0 = chunk * kMmaChunkSb, ns = min(kMmaChunkSb, nsb - sb0);
+  const int n_my = slot < a.total_tiles ? (a.total_tiles - slot + a.ctas_per_chunk - 1) / a.ctas_per_chunk : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      bar_init(&full[s], 1);
+      bar_init(&empty[s], kMmaWarpsPerGroup);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  asm volatile("griddepcontrol.launch_dependents;");
+
+  if (warp == kMmaConsumerWarps) {
+    // ---------------- producer: one bulk copy per weight row (two for Q8_0: codes, scales); lanes share the rows
+    for (int i = 0; i < n_my; ++i) {
+      const int s = i % S;
+      bool ok = true;
+      if (i >= S) ok = bar_wait(&empty[s], (uint32_t)((i / S - 1) & 1), a.status);
+      ok = __all_sync(0xffffffffu, ok);
+      const int t = slot + i * a.ctas_per_chunk;
+      int j = 0;
+      if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+      if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+      const MmaJob &J = a.job[j];
+      const int row0 = (t - J.first_tile) * kMmaTileRows;
+      const int nrows = min(kMmaTileRows, J.rows - row0);
+      const int pitch = row_pitch(J.qt);
+      const uint32_t row_bytes = (uint32_t)(J.qt == CMLD_Q4_K ? ns * 144 : (J.qt == CMLD_Q6_K ? ns * 208 : ns * 256 + ns * 16));
+      if (lane == 0) bar_expect_tx(&full[s], row_bytes * (uint32_t)nrows);
+      __syncwarp();
+      uint8_t *dst = ring + (int64_t)s * a.stage_bytes;
+      for (int r = lane; r < nrows; r += 32) {
+        const uint8_t *src = J.w + (int64_t)(row0 + r) * J.stride;
+        if (J.qt == CMLD_Q4_K) bulk_copy(dst + r * pitch, src + (int64_t)sb0 * 144, (uint32_t)ns * 144, &full[s]);
+        else if (J.qt == CMLD_Q6_K) bulk_copy(dst + r * pitch, src + (int64_t)sb0 * 208, (uint32_t)ns * 208, &full[s]);
+        else {
+          bulk_copy(dst + r * pitch, src + (int64_t)sb0 * 256, (uint32_t)ns * 256, &full[s]);
+          bulk_copy(dst + r * pitch + ns * 256, src + a.cols + (int64_t)sb0 * 16, (uint32_t)ns * 16, &full[s]);
+        }
+      }
+      (void)ok;
+    }
+    return;
+  }
+
+  // ---------------- consumers: this chunk's activations for every row into shared memory, once
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t astride = act_row_stride(a.cols);
+  for (int b = 0; b < NT * 8; ++b) {
+    uint8_t *dstc = codes + b * kMmaCodeStride;
+    if (b < a.batch) {
+      const uint8_t *src = a.act + b * astride;
+      for (int i = tid; i < ns * 16; i += kMmaConsumers)
+        *reinterpret_cast<uint4 *>(dstc + i * 16) = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)sb0 * 256) + i);
+      if (a.q8_0) {
+        for (int i = tid; i < ns * 8; i += kMmaConsumers)
+          xscale[b * (kMmaChunkSb * 8) + i] = __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + sb0 * 8 + i);
+      } else {
+        for (int i = tid; i < ns; i += kMmaConsumers)
+          xscale[b * kMmaChunkSb + i] = __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + sb0 + i);
+        for (int i = tid; i < ns * 16; i += kMmaConsumers)
+          bs16[b * 64 + i] = __ldg(reinterpret_cast<const short *>(src + act_bsum_off(a.cols)) + sb0 * 16 + i);
+      }
+    } else {
+      // padding rows of the last column tile: zero codes and scales, their results are never written
+      for (int i = tid; i < kMmaChunkCols / 16; i += kMmaConsumers) *reinterpret_cast<uint4 *>(dstc + i * 16) = make_uint4(0, 0, 0, 0);
+      for (int i = tid; i < kMmaChunkSb * 8; i += kMmaConsumers)
+        if (a.q8_0 || i < kMmaChunkSb) xscale[b * (a.q8_0 ? kMmaChunkSb * 8 : kMmaChunkSb) + i] = 0.0f;
+      if (!a.q8_0)
+        for (int i = tid; i < 64; i += kMmaConsumers) bs16[b * 64 + i] = 0;
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers));
+
+  const int group = warp / kMmaWarpsPerGroup, wg = warp % kMmaWarpsPerGroup;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  for (int i = group; i < n_my; i += kMmaGroups) {
+    const int s = i % S;
+    const bool ready = __all_sync(0xffffffffu, bar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+    const int t = slot + i * a.ctas_per_chunk;
+    int j = 0;
+    if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+    if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+    const MmaJob &J = a.job[j];
+    const int row0 = (t - J.first_tile) * kMmaTileRows;
+    const int nrows = min(kMmaTileRows, J.rows - row0);
+    const int m0 = wg * 16;
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
+    if (ready && m0 < nrows) {
+      // rows of the tile beyond the matrix were not copied: their slots hold stale bytes; the integer and
+      // f32 work on them is harmless and their results are not written
+      const uint8_t *tile = ring + (int64_t)s * a.stage_bytes;
+      if (J.qt == CMLD_Q4_K) {
+        tile_q4k<NT>(tile, m0, ns, lane, codes, xscale, bs16, acc);
+      } else if (J.qt == CMLD_Q6_K) {
+        float d_lo[kMmaChunkSb], d_hi[kMmaChunkSb];
+        const int r_lo = min(row0 + m0 + g8, J.rows - 1), r_hi = min(row0 + m0 + g8 + 8, J.rows - 1);
+#pragma unroll
+        for (int sb = 0; sb < kMmaChunkSb; ++sb) {
+          const int sbc = min(sb, ns - 1);
+          d_lo[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_lo * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
+          d_hi[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_hi * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
+        }
+        tile_q6k<NT>(tile, m0, ns, lane, codes, xscale, bs16, d_lo, d_hi, acc);
+      } else {
+        tile_q80<NT>(tile, m0, ns, lane, codes, xscale, acc);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) bar_arrive(&empty[s]);
+    if (ready) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int col = nt * 8 + t4 * 2 + (k & 1), r = m0 + g8 + (k >= 2 ? 8 : 0);
+          if (col < a.batch && r < nrows) {
+            if (a.n_chunks == 1) {
+              const int64_t o = (int64_t)col * J.y_stride + row0 + r;
+              J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), acc[nt][k]) : acc[nt][k];
+            } else {
+              a.partial[((int64_t)chunk * a.batch + col) * a.rows_cat + J.row_off + row0 + r] = acc[nt][k];
+            }
+          }
+        }
+    }
+  }
+}
+
+// y = residual + sum over chunks (in chunk order) of the partial sums.
+__global__ void mma_reduce_kernel(const MmaArgs a) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int64_t total = (int64_t)a.batch * a.rows_cat;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int col = (int)(i / a.rows_cat), rc = (int)(i % a.rows_cat);
+    int j = 0;
+    if (a.n_jobs > 1 && rc >= a.job[1].row_off) j = 1;
+    if (a.n_jobs > 2 && rc >= a.job[2].row_off) j = 2;
+    const MmaJob &J = a.job[j];
+    const int64_t o = (int64_t)col * J.y_stride + (rc - J.row_off);
+    float v = __ldcg(a.partial + (int64_t)col * a.rows_cat + rc);
+    for (int c = 1; c < a.n_chunks; ++c) v = __fadd_rn(v, __ldcg(a.partial + ((int64_t)c * a.batch + col) * a.rows_cat + rc));
+    J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), v) : v;
+  }
+}
+
+struct MmaPlan {
+  MmaArgs args;
+  int smem_bytes, grid;
+};
+
+int g_mma_sms = 0;
+bool g_mma_attr[5] = {false, false, false, false, false};
+
+bool plan_mma(const GemvJob *jobs, int n_jobs, int32_t batch, MmaPlan &p) {
+  if (n_jobs < 1 || n_jobs > 3 || batch < 1 || batch > 32) return false;
+  const int64_t cols = jobs[0].cols;
+  if (cols % 256) return false;
+  MmaArgs &a = p.args;
+  const bool q80 = jobs[0].qt == CMLD_Q8_0;
+  int tiles = 0, stage = 0, rows_cat = 0;
+  for (int k = 0; k < n_jobs; ++k) {
+    const GemvJob &g = jobs[k];
+    if (g.cols != cols) return false;
+    if (g.qt != CMLD_Q8_0 && g.qt != CMLD_Q4_K && g.qt != CMLD_Q6_K) return false;
+    if ((g.qt == CMLD_Q8_0) != q80) return false;  // one activation format per launch
+    if (g.stride % 16 || (reinterpret_cast<uintptr_t>(g.w) & 15)) return false;
+    MmaJob &J = a.job[k];
+    J.w = g.w;
+    J.qt = g.qt;
+    J.rows = (int32_t)g.rows;
+    J.stride = g.stride;
+    J.y = g.y;
+    J.residual = g.residual;
+    J.y_stride = g.y_stride;
+    J.first_tile = tiles;
+    J.n_tiles = (int)((g.rows + kMmaTileRows - 1) / kMmaTileRows);
+    J.row_off = rows_cat;
+    tiles += J.n_tiles;
+    rows_cat += (int)g.rows;
+    stage = std::max(stage, kMmaTileRows * row_pitch(g.qt));
+  }
+  stage = (stage + 127) & ~127;
+  const int nt = (batch + 7) / 8;
+  int off = 2 * kMmaMaxStages * 8;
+  a.off_codes = off;
+  off += nt * 8 * kMmaCodeStride;
+  a.off_scale = off;
+  off += nt * 8 * (q80 ? kMmaChunkSb * 8 : kMmaChunkSb) * 4;
+  a.off_bsum = off;
+  if (!q80) off += nt * 8 * 64 * 2;
+  off = (off + 127) & ~127;
+  a.off_ring = off;
+  int n_stages = std::min<int>(kMmaMaxStages, (224 * 1024 - off) / stage);
+  n_stages -= n_stages % kMmaGroups;
+  if (n_stages < 2) return false;
+  a.n_stages = n_stages;
+  a.stage_bytes = stage;
+  a.n_jobs = n_jobs;
+  a.total_tiles = tiles;
+  a.cols = (int32_t)cols;
+  a.batch = batch;
+  a.rows_cat = rows_cat;
+  a.q8_0 = q80 ? 1 : 0;
+  a.n_chunks = (int)((cols / 256 + kMmaChunkSb - 1) / kMmaChunkSb);
+  a.ctas_per_chunk = std::max(1, std::min(tiles, g_mma_sms / a.n_chunks));
+  p.grid = a.n_chunks * a.ctas_per_chunk;
+  p.smem_bytes = off + n_stages * stage;
+  return true;
+}
+
+template <int NT>
+int32_t launch_nt(const MmaPlan &p, cudaStream_t s, bool pdl) {
+  if (!g_mma_attr[NT]) {
+    CMLD_CUDA(cudaFuncSetAttribute(gemv_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    g_mma_attr[NT] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)p.grid);
+  cfg.blockDim = dim3(kMmaThreads);
+  cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CMLD_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_kernel<NT>, p.args));
+  return CMLD_OK;
+}
+
+}  // namespace
+
+// Floats of scratch a launch needs for its per-chunk partial sums (0 when the columns fit one chunk);
+// -1 when the matrices do not fit this kernel.
+int64_t gemv_mma_scratch_floats(const GemvJob *jobs, int n_jobs, int32_t batch) {
+  if (g_mma_sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g_mma_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
+  MmaPlan p{};
+  if (!plan_mma(jobs, n_jobs, batch, p)) return -1;
+  return p.args.n_chunks > 1 ? (int64_t)p.args.n_chunks * batch * p.args.rows_cat : 0;
+}
+
+// `act`: the quantised activation rows in the global layout (Q8_0 rows for Q8_0 matrices, Q8_K rows
+// otherwise).  Returns CMLD_ERR_UNSUPPORTED without a message when the shapes do not fit.
+int32_t launch_gemv_mma(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, float *scratch, int64_t scratch_floats,
+                        int32_t *status, cudaStream_t s, bool pdl, int64_t *launches) {
+  const int64_t need = gemv_mma_scratch_floats(jobs, n_jobs, batch);
+  if (need < 0) return CMLD_ERR_UNSUPPORTED;
+  if (need > scratch_floats || (need > 0 && !scratch)) return CMLD_ERR_UNSUPPORTED;
+  if (!act) return fail(CMLD_ERR_INVALID, "gemv: activation buffer missing");
+  MmaPlan p{};
+  plan_mma(jobs, n_jobs, batch, p);
+  p.args.act = act;
+  p.args.partial = scratch;
+  p.args.status = status;
+  const int nt = (batch + 7) / 8;
+  int32_t rc;
+  switch (nt) {
+    case 1: rc = launch_nt<1>(p, s, pdl); break;
+    case 2: rc = launch_nt<2>(p, s, pdl); break;
+    case 3: rc = launch_nt<3>(p, s, pdl); break;
+    default: rc = launch_nt<4>(p, s, pdl); break;
+  }
+  CMLD_TRY(rc);
+  if (launches) *launches += 1;
+  if (p.args.n_chunks > 1) {
+    cudaLaunchConfig_t cfg{};
+    const int64_t total = (int64_t)batch * p.args.rows_cat;
+    cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, 4 * 148));
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    CMLD_CUDA(cudaLaunchKernelEx(&cfg, mma_reduce_kernel, p.args));
+    if (launches) *launches += 1;
+  }
+  return CMLD_OK;
+}
+
+}  // namespace cmld

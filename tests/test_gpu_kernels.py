@@ -175,6 +175,44 @@ def test_fused_prologue_equals_separate_steps(cm, orc, name, rows, cols, mode, b
     assert np.array_equal(got, want)
 
 
+# More than 8 activation rows: the tensor-core kernel (one pass over the weights).  Integer parts are
+# those of the row kernel; only the order of the superblocks' f32 terms differs, so the bar is the same
+# tolerance against the CPU row dot, and closeness (not bit equality) to the <= 8-row kernel.
+@pytest.mark.parametrize("name,rows,cols", [
+    ("Q8_0", 96, 256), ("Q8_0", 515, 2048), ("Q8_0", 70, 1792),
+    ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 1792), ("Q4_K", 64, 14336),
+    ("Q6_K", 33, 256), ("Q6_K", 512, 4096), ("Q6_K", 130, 1792), ("Q6_K", 64, 14336)])
+@pytest.mark.parametrize("batch", [9, 16, 27, 32])
+def test_gemv_batched_tensor_core_kernel_matches_checker(cm, orc, name, rows, cols, batch):
+    from camelid_b200.engine import quantize_activation, export_activation, DeviceBuffer
+    from camelid_b200._lib import check
+
+    qt = QT[name]
+    wire = orc.synth_tensor(qt, 13, rows * 5 + cols, rows, cols, 0.02)
+    w = cm.Weight.from_wire(qt, rows, cols, wire)
+    rng = np.random.default_rng(rows + cols + batch)
+    x = rng.standard_normal((batch, cols)).astype(np.float32)
+    kind = cm.ACT_Q8_0 if qt == 8 else cm.ACT_Q8_K
+    act = quantize_activation(kind, x)
+    codes, scales = export_activation(kind, act, cols, batch)
+    y = w.gemv(act, batch)
+    res = rng.standard_normal((batch, rows)).astype(np.float32)
+    res_d = DeviceBuffer.from_numpy(res)
+    y_res = w.gemv(act, batch, res_d)
+    for b in range(batch):
+        ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
+        ok, max_abs, n_bad = close_enough(y[b], ref, rel=1e-4, floor=1e-5)
+        assert ok, (name, rows, cols, b, max_abs, n_bad)
+        assert np.array_equal(y_res[b], (res[b] + y[b]).astype(np.float32))
+    # the <= 8-row kernel on the first rows: same integers, f32 terms added in another order
+    y8 = w.gemv(quantize_activation(kind, x[:8]), 8)
+    ok, max_abs, n_bad = close_enough(y[:8], y8, rel=1e-5, floor=1e-6)
+    assert ok, (max_abs, n_bad)
+    # and the very same bits whatever the row's neighbours are
+    y_again = w.gemv(quantize_activation(kind, x[::-1].copy()), batch)
+    assert np.array_equal(y_again[::-1], y)
+
+
 def test_gemv_end_to_end_against_f32_activation_path(cm, orc):
     """orc.matvec quantises the f32 activation itself: checks quantise+gemv as one unit."""
     from camelid_b200.engine import quantize_activation
