@@ -32,6 +32,29 @@ static int32_t *op_status(void) {
   return words[dev];
 }
 
+// Partial-sum scratch of the batched matvec for the operator-level calls: one per device, grown on demand
+// (never inside a stream capture: a capture is preceded by warm-up launches of the same shape).
+static float *op_scratch(int64_t floats) {
+  static float *buf[64] = {nullptr};
+  static int64_t cap[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cap[dev] < floats) {
+    if (buf[dev]) {
+      cudaDeviceSynchronize();
+      cudaFree(buf[dev]);
+    }
+    buf[dev] = nullptr;
+    cap[dev] = 0;
+    if (cudaMalloc(&buf[dev], (size_t)floats * 4) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    cap[dev] = floats;
+  }
+  return buf[dev];
+}
+
 static int32_t check_op_status(const char *what) {
   int32_t *w = op_status(), st = 0;
   if (!w) return CMLD_OK;
@@ -45,20 +68,19 @@ static int32_t check_op_status(const char *what) {
 
 static int g_gemv_pdl = 0;            // cmld_gemv_time: chain its launches with programmatic dependent launch
 static int g_gemv_kernel_choice = 0;  // 0 auto (staged when the shape fits), 1 direct-load only
+static int g_gemv_mma_min_batch = 9;  // rows from which the tensor-core kernel is used (bit 2 of the choice: from 1)
 
 // One matvec launch on the default stream: staged kernel if it takes the shape, else direct-load.
 static int32_t gemv_launch(const cmld_weight *w, const uint8_t *act, int32_t batch, float *y, const float *residual,
                            cudaStream_t stream = nullptr, bool pdl = false) {
   GemvJob probe{w->data, w->qt, w->rows, w->cols, w->stride, y, residual, w->rows};
-  if (g_gemv_kernel_choice == 0 && batch > 8 && batch <= 32) {
+  if (g_gemv_kernel_choice == 0 && batch >= g_gemv_mma_min_batch && batch <= 32) {
     // more than 8 rows: one pass over the weights on the tensor cores
     const int64_t need = gemv_mma_scratch_floats(&probe, 1, batch);
     if (need >= 0) {
-      float *scratch = nullptr;
-      if (need > 0) CMLD_CUDA(cudaMalloc(&scratch, (size_t)need * 4));
-      int32_t rc = launch_gemv_mma(&probe, 1, act, batch, scratch, need, op_status(), stream, pdl, nullptr);
-      if (rc == CMLD_OK && cudaStreamSynchronize(stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "gemv: batched launch failed");
-      if (scratch) cudaFree(scratch);
+      float *scratch = need > 0 ? op_scratch(need) : nullptr;
+      if (need > 0 && !scratch) return fail(CMLD_ERR_OOM, "gemv: no room for %lld floats of partial sums", (long long)need);
+      const int32_t rc = launch_gemv_mma(&probe, 1, act, batch, scratch, need, op_status(), stream, pdl, nullptr);
       if (rc != CMLD_ERR_UNSUPPORTED) return rc;
     }
   }
@@ -260,9 +282,10 @@ int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, floa
 }
 
 int32_t cmld_gemv_select_kernel(int32_t choice) {
-  if (choice < 0 || choice > 3) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
+  if (choice < 0 || choice > 7) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
   g_gemv_kernel_choice = choice & 1;
   g_gemv_pdl = (choice >> 1) & 1;
+  g_gemv_mma_min_batch = (choice & 4) ? 1 : 9;
   return CMLD_OK;
 }
 

@@ -132,7 +132,7 @@ struct cmld_engine {
   int device = 0;
   cudaStream_t stream = nullptr;
   int32_t max_rows = 0;  // scratch rows (sequences per step)
-  int32_t n_splits = 1;
+  int32_t n_splits = 1, sm_count = 148;
   int32_t q_width = 0, kv_width = 0;
   std::vector<LayerW> layers;
   Weight output, token_embd;
@@ -279,6 +279,7 @@ static int32_t engine_init(cmld_engine *e) {
   // flash-decoding splits: enough CTAs to cover the SMs twice at batch 1
   int sms = 148;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
+  e->sm_count = sms;
   e->n_splits = std::max(1, std::min<int>(64, (2 * sms + c.n_kv_heads - 1) / c.n_kv_heads));
   e->n_splits = (int)std::min<int64_t>(e->n_splits, std::max<int64_t>(1, c.max_pos / 32));
   CMLD_TRY(dev_alloc(e, &e->attn_part, R * c.n_heads * e->n_splits * (c.head_dim + 2)));
@@ -731,7 +732,9 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.n_kv_heads = c.n_kv_heads;
       a.head_dim = c.head_dim;
       a.batch = B;
-      a.n_splits = e->n_splits;
+      // enough CTAs to fill the machine about twice, and no more: with many rows each (row, kv head) pair
+      // needs few ranges, and a range that is too short is all fixed cost
+      a.n_splits = std::max(1, std::min(e->n_splits, (2 * e->sm_count + B * c.n_kv_heads - 1) / (B * c.n_kv_heads)));
       a.max_pos = c.max_pos;
       a.scale = o.scale;
       a.part = e->attn_part;

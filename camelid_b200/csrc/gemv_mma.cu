@@ -11,7 +11,7 @@
 // its whole life and keeps the quantised activations of that chunk for all rows in shared memory
 // (32 x 1024 codes + scales), so the operand that every weight tile needs is loaded once per CTA.  The
 // CTA walks tiles of 64 weight rows of its chunk: a producer warp copies each row's chunk bytes with
-// one bulk asynchronous copy per row into a padded (bank-conflict-free) slot of an mbarrier ring; two
+// one bulk asynchronous copy per row into a padded (bank-conflict-free) slot of an mbarrier ring; two or three
 // groups of four consumer warps alternate tiles, every warp owning 16 rows (one MMA row tile) for the
 // whole chunk and all <= 4 column tiles of 8 activation rows — no reduction across warps.  With more
 // than one chunk the per-chunk partial sums go to a scratch array and a small kernel adds them in chunk
@@ -21,14 +21,12 @@
 namespace cmld {
 
 constexpr int kMmaWarpsPerGroup = 4;
-constexpr int kMmaGroups = 2;
-constexpr int kMmaConsumerWarps = kMmaWarpsPerGroup * kMmaGroups;
-constexpr int kMmaConsumers = kMmaConsumerWarps * 32;
-constexpr int kMmaThreads = kMmaConsumers + 32;
+constexpr int kMmaMaxGroups = 3;  // consumer groups (2 or 3, as many as the ring has room for: one stage each at least)
+constexpr int kMmaMaxThreads = kMmaMaxGroups * kMmaWarpsPerGroup * 32 + 32;
 constexpr int kMmaTileRows = kMmaWarpsPerGroup * 16;
 constexpr int kMmaChunkSb = 4;  // superblocks (of 256 columns) per chunk
 constexpr int kMmaChunkCols = kMmaChunkSb * 256;
-constexpr int kMmaMaxStages = 4;
+constexpr int kMmaMaxStages = 6;
 constexpr int kMmaCodeStride = kMmaChunkCols + 16;  // bytes between activation rows in shared memory (conflict-free)
 constexpr uint32_t kMmaSpinLimit = 1u << 22;
 
@@ -92,7 +90,7 @@ struct MmaJob {
 
 struct MmaArgs {
   MmaJob job[3];
-  int32_t n_jobs, total_tiles, cols, batch, n_chunks, ctas_per_chunk, stage_bytes, n_stages, rows_cat, q8_0;
+  int32_t n_jobs, total_tiles, cols, batch, n_chunks, ctas_per_chunk, stage_bytes, n_stages, n_groups, rows_cat, q8_0;
   const uint8_t *act;  // quantised activation rows, global layout, the format the jobs' types need
   float *partial;      // [chunk][batch][rows_cat] when n_chunks > 1
   int32_t *status;
@@ -102,20 +100,42 @@ struct MmaArgs {
 // bytes of one weight row's chunk in shared memory (padded so that 8 rows x 4 words hit 32 distinct banks)
 __host__ __device__ inline int row_pitch(int qt) { return (qt == CMLD_Q4_K ? 4 * 144 : (qt == CMLD_Q6_K ? 4 * 208 : 4 * 256 + 4 * 16)) + 16; }
 
+// Byte k of w as an int (0..255).
+__device__ __forceinline__ int byte_of(uint32_t w, int k) { return (int)((w >> (8 * k)) & 0xffu); }
+
 template <int NT>
 __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xd,
-                                         const short *bs16, float (&acc)[NT][4]) {
+                                         const int8_t *bs_hi, const int8_t *bs_lo, float (&acc)[NT][4]) {
   const int g8 = lane >> 2, t4 = lane & 3;
   const int pitch = row_pitch(CMLD_Q4_K);
   const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
   for (int sb = 0; sb < ns; ++sb) {
     const uint8_t *plo = rlo + sb * 144, *phi = rhi + sb * 144;
     const uint4 mlo = *reinterpret_cast<const uint4 *>(plo), mhi = *reinterpret_cast<const uint4 *>(phi);
+    // the eight 6-bit scales and mins of the superblock, unpacked four at a time into bytes
+    // (q4_k_scale_min, src/tensor/mod.rs:5997-6006): groups 0-3 and groups 4-7
+    const uint32_t sc_lo[2] = {mlo.y & 0x3f3f3f3fu, (mlo.w & 0x0f0f0f0fu) | (((mlo.y >> 6) & 0x03030303u) << 4)};
+    const uint32_t mn_lo[2] = {mlo.z & 0x3f3f3f3fu, ((mlo.w >> 4) & 0x0f0f0f0fu) | (((mlo.z >> 6) & 0x03030303u) << 4)};
+    const uint32_t sc_hi[2] = {mhi.y & 0x3f3f3f3fu, (mhi.w & 0x0f0f0f0fu) | (((mhi.y >> 6) & 0x03030303u) << 4)};
+    const uint32_t mn_hi[2] = {mhi.z & 0x3f3f3f3fu, ((mhi.w >> 4) & 0x0f0f0f0fu) | (((mhi.z >> 6) & 0x03030303u) << 4)};
     int isum[NT][4], msum[NT][4];
+    {
+      // sum_g min_g * bsum32_g as one more small matrix product: A = the mins (k = group, 8 of the 16 used),
+      // B = the group sums of the activation codes, split as 64*hi + lo to fit int8
+      const uint32_t a0 = t4 == 0 ? mn_lo[0] : (t4 == 1 ? mn_lo[1] : 0u), a1 = t4 == 0 ? mn_hi[0] : (t4 == 1 ? mn_hi[1] : 0u);
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+      for (int nt = 0; nt < NT; ++nt) {
+        const int o = ((nt * 8 + g8) * kMmaChunkSb + sb) * 8 + (t4 & 1) * 4;
+        int ch[4], cl[4];
+        mma_k16(ch, a0, a1, *reinterpret_cast<const uint32_t *>(bs_hi + o));
+        mma_k16(cl, a0, a1, *reinterpret_cast<const uint32_t *>(bs_lo + o));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) isum[nt][i] = msum[nt][i] = 0;
+        for (int i = 0; i < 4; ++i) {
+          msum[nt][i] = 64 * ch[i] + cl[i];
+          isum[nt][i] = 0;
+        }
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint32_t wl0 = *reinterpret_cast<const uint32_t *>(plo + 16 + j * 32 + t4 * 4);
@@ -125,9 +145,7 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int g = 2 * j + h;
-        int sc_lo, m_lo, sc_hi, m_hi;
-        q4k_scale_min(g, mlo.y, mlo.z, mlo.w, sc_lo, m_lo);
-        q4k_scale_min(g, mhi.y, mhi.z, mhi.w, sc_hi, m_hi);
+        const int s_lo = byte_of(sc_lo[g >> 2], g & 3), s_hi = byte_of(sc_hi[g >> 2], g & 3);
         const uint32_t a0 = (wl0 >> (4 * h)) & 0x0f0f0f0fu, a1 = (wh0 >> (4 * h)) & 0x0f0f0f0fu;
         const uint32_t a2 = (wl1 >> (4 * h)) & 0x0f0f0f0fu, a3 = (wh1 >> (4 * h)) & 0x0f0f0f0fu;
 #pragma unroll
@@ -136,17 +154,10 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
           const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xc), b1 = *reinterpret_cast<const uint32_t *>(xc + 16);
           int c[4];
           mma_k32(c, a0, a1, a2, a3, b0, b1);
-          isum[nt][0] += sc_lo * c[0];
-          isum[nt][1] += sc_lo * c[1];
-          isum[nt][2] += sc_hi * c[2];
-          isum[nt][3] += sc_hi * c[3];
-          // the mins meet the sums of the activation codes of the group: bsum32 = two 16-sums
-          const short *b0p = bs16 + (nt * 8 + t4 * 2) * 64 + sb * 16 + 2 * g;
-          const int s0 = (int)b0p[0] + (int)b0p[1], s1 = (int)b0p[64] + (int)b0p[65];
-          msum[nt][0] += m_lo * s0;
-          msum[nt][1] += m_lo * s1;
-          msum[nt][2] += m_hi * s0;
-          msum[nt][3] += m_hi * s1;
+          isum[nt][0] += s_lo * c[0];
+          isum[nt][1] += s_lo * c[1];
+          isum[nt][2] += s_hi * c[2];
+          isum[nt][3] += s_hi * c[3];
         }
       }
     }
@@ -167,17 +178,29 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
 
 template <int NT>
 __device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xd,
-                                         const short *bs16, float d_lo[kMmaChunkSb], float d_hi[kMmaChunkSb], float (&acc)[NT][4]) {
+                                         const int8_t *b16_hi, const int8_t *b16_lo, float d_lo[kMmaChunkSb], float d_hi[kMmaChunkSb],
+                                         float (&acc)[NT][4]) {
   const int g8 = lane >> 2, t4 = lane & 3;
   const int pitch = row_pitch(CMLD_Q6_K);
   const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
   for (int sb = 0; sb < ns; ++sb) {
     const uint8_t *plo = rlo + sb * 208, *phi = rhi + sb * 208;
     int isum[NT][4];
+    {
+      // codes are stored +32: sum_s sc_s * sum (q-32) x = sum_s sc_s * dot_s - 32 * sum_s sc_s * bsum16_s, and the
+      // last sum is one more small matrix product: A = the 16 int8 scales, B = the 16-sums of the activation
+      // codes split as 64*hi + lo
+      const uint32_t a0 = *reinterpret_cast<const uint32_t *>(plo + 192 + t4 * 4), a1 = *reinterpret_cast<const uint32_t *>(phi + 192 + t4 * 4);
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+      for (int nt = 0; nt < NT; ++nt) {
+        const int o = ((nt * 8 + g8) * kMmaChunkSb + sb) * 16 + t4 * 4;
+        int ch[4], cl[4];
+        mma_k16(ch, a0, a1, *reinterpret_cast<const uint32_t *>(b16_hi + o));
+        mma_k16(cl, a0, a1, *reinterpret_cast<const uint32_t *>(b16_lo + o));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) isum[nt][i] = 0;
+        for (int i = 0; i < 4; ++i) isum[nt][i] = -32 * (64 * ch[i] + cl[i]);
+      }
+    }
 #pragma unroll
     for (int s = 0; s < 16; ++s) {
       // sub-block s of 16 values: half n, quarter qd (which 2 bits of qh, which nibble of which ql half), part lp
@@ -193,13 +216,10 @@ __device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, in
         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(codes + (nt * 8 + g8) * kMmaCodeStride + sb * 256 + s * 16 + t4 * 4);
         int c[4];
         mma_k16(c, a0, a1, b0);
-        // codes are stored +32: sum (q-32) x = sum q x - 32 * (sum of the 16 activation codes)
-        const short *bp = bs16 + (nt * 8 + t4 * 2) * 64 + sb * 16 + s;
-        const int k0 = 32 * (int)bp[0], k1 = 32 * (int)bp[64];
-        isum[nt][0] += sc_lo * (c[0] - k0);
-        isum[nt][1] += sc_lo * (c[1] - k1);
-        isum[nt][2] += sc_hi * (c[2] - k0);
-        isum[nt][3] += sc_hi * (c[3] - k1);
+        isum[nt][0] += sc_lo * c[0];
+        isum[nt][1] += sc_lo * c[1];
+        isum[nt][2] += sc_hi * c[2];
+        isum[nt][3] += sc_hi * c[3];
       }
     }
 #pragma unroll
@@ -239,16 +259,19 @@ __device__ __forceinline__ void tile_q80(const uint8_t *tile, int m0, int ns, in
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const MmaArgs a) {
+__global__ void __launch_bounds__(kMmaMaxThreads, 1) gemv_mma_kernel(const MmaArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + kMmaMaxStages;
   uint8_t *codes = smem + a.off_codes;
   float *xscale = reinterpret_cast<float *>(smem + a.off_scale);
-  short *bs16 = reinterpret_cast<short *>(smem + a.off_bsum);
+  // sums of the activation codes per 32 (Q4_K mins) and per 16 (Q6_K offset), each split as 64*hi + lo
+  int8_t *bs32_hi = reinterpret_cast<int8_t *>(smem + a.off_bsum), *bs32_lo = bs32_hi + NT * 8 * kMmaChunkSb * 8;
+  int8_t *bs16_hi = bs32_lo + NT * 8 * kMmaChunkSb * 8, *bs16_lo = bs16_hi + NT * 8 * kMmaChunkSb * 16;
   uint8_t *ring = smem + a.off_ring;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = a.n_stages;
+  const int n_consumer_warps = a.n_groups * kMmaWarpsPerGroup, n_consumers = n_consumer_warps * 32;
   const int chunk = (int)blockIdx.x % a.n_chunks, slot = (int)blockIdx.x / a.n_chunks;
   const int nsb = a.cols >> 8;
   const int sb0 = chunk * kMmaChunkSb, ns = min(kMmaChunkSb, nsb - sb0);
@@ -264,7 +287,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const MmaArgs 
   __syncthreads();
   asm volatile("griddepcontrol.launch_dependents;");
 
-  if (warp == kMmaConsumerWarps) {
+  if (warp == n_consumer_warps) {
     // ---------------- producer: one bulk copy per weight row (two for Q8_0: codes, scales); lanes share the rows
     for (int i = 0; i < n_my; ++i) {
       const int s = i % S;
@@ -300,35 +323,52 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const MmaArgs 
   // ---------------- consumers: this chunk's activations for every row into shared memory, once
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t astride = act_row_stride(a.cols);
-  for (int b = 0; b < NT * 8; ++b) {
-    uint8_t *dstc = codes + b * kMmaCodeStride;
-    if (b < a.batch) {
-      const uint8_t *src = a.act + b * astride;
-      for (int i = tid; i < ns * 16; i += kMmaConsumers)
-        *reinterpret_cast<uint4 *>(dstc + i * 16) = __ldg(reinterpret_cast<const uint4 *>(src + (int64_t)sb0 * 256) + i);
-      if (a.q8_0) {
-        for (int i = tid; i < ns * 8; i += kMmaConsumers)
-          xscale[b * (kMmaChunkSb * 8) + i] = __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + sb0 * 8 + i);
-      } else {
-        for (int i = tid; i < ns; i += kMmaConsumers)
-          xscale[b * kMmaChunkSb + i] = __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + sb0 + i);
-        for (int i = tid; i < ns * 16; i += kMmaConsumers)
-          bs16[b * 64 + i] = __ldg(reinterpret_cast<const short *>(src + act_bsum_off(a.cols)) + sb0 * 16 + i);
+  // (flat loops: every thread has several independent loads in flight; a loop over the rows with one row
+  // per trip would serialise 32 round trips to L2)
+  constexpr int NB = NT * 8;
+  for (int idx = tid; idx < NB * (kMmaChunkCols / 16); idx += n_consumers) {
+    const int b = idx / (kMmaChunkCols / 16), i = idx % (kMmaChunkCols / 16);
+    uint4 v = make_uint4(0, 0, 0, 0);  // padding rows of the last column tile and the columns beyond a short chunk
+    if (b < a.batch && i < ns * 16) v = __ldg(reinterpret_cast<const uint4 *>(a.act + b * astride + (int64_t)sb0 * 256) + i);
+    *reinterpret_cast<uint4 *>(codes + b * kMmaCodeStride + i * 16) = v;
+  }
+  if (a.q8_0) {
+    for (int idx = tid; idx < NB * (kMmaChunkSb * 8); idx += n_consumers) {
+      const int b = idx / (kMmaChunkSb * 8), i = idx % (kMmaChunkSb * 8);
+      float v = 0.0f;
+      if (b < a.batch && i < ns * 8) v = __ldg(reinterpret_cast<const float *>(a.act + b * astride + act_scale_off(a.cols)) + sb0 * 8 + i);
+      xscale[idx] = v;
+    }
+  } else {
+    for (int idx = tid; idx < NB * kMmaChunkSb; idx += n_consumers) {
+      const int b = idx / kMmaChunkSb, i = idx % kMmaChunkSb;
+      float v = 0.0f;
+      if (b < a.batch && i < ns) v = __ldg(reinterpret_cast<const float *>(a.act + b * astride + act_scale_off(a.cols)) + sb0 + i);
+      xscale[idx] = v;
+    }
+    for (int idx = tid; idx < NB * (kMmaChunkSb * 8); idx += n_consumers) {
+      const int b = idx / (kMmaChunkSb * 8), i = idx % (kMmaChunkSb * 8);
+      int v0 = 0, v1 = 0;
+      if (b < a.batch && i < ns * 8) {
+        const int pr = __ldg(reinterpret_cast<const int *>(a.act + b * astride + act_bsum_off(a.cols)) + sb0 * 8 + i);  // two 16-sums
+        v0 = (int)(short)(pr & 0xffff);
+        v1 = pr >> 16;
       }
-    } else {
-      // padding rows of the last column tile: zero codes and scales, their results are never written
-      for (int i = tid; i < kMmaChunkCols / 16; i += kMmaConsumers) *reinterpret_cast<uint4 *>(dstc + i * 16) = make_uint4(0, 0, 0, 0);
-      for (int i = tid; i < kMmaChunkSb * 8; i += kMmaConsumers)
-        if (a.q8_0 || i < kMmaChunkSb) xscale[b * (a.q8_0 ? kMmaChunkSb * 8 : kMmaChunkSb) + i] = 0.0f;
-      if (!a.q8_0)
-        for (int i = tid; i < 64; i += kMmaConsumers) bs16[b * 64 + i] = 0;
+      const int l0 = ((v0 + 32) & 63) - 32, l1 = ((v1 + 32) & 63) - 32;
+      bs16_lo[b * (kMmaChunkSb * 16) + 2 * i] = (int8_t)l0;
+      bs16_hi[b * (kMmaChunkSb * 16) + 2 * i] = (int8_t)((v0 - l0) / 64);
+      bs16_lo[b * (kMmaChunkSb * 16) + 2 * i + 1] = (int8_t)l1;
+      bs16_hi[b * (kMmaChunkSb * 16) + 2 * i + 1] = (int8_t)((v1 - l1) / 64);
+      const int v = v0 + v1, lo = ((v + 32) & 63) - 32;
+      bs32_lo[idx] = (int8_t)lo;
+      bs32_hi[idx] = (int8_t)((v - lo) / 64);
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kMmaConsumers));
+  asm volatile("bar.sync 1, %0;" ::"r"(n_consumers));
 
   const int group = warp / kMmaWarpsPerGroup, wg = warp % kMmaWarpsPerGroup;
   const int g8 = lane >> 2, t4 = lane & 3;
-  for (int i = group; i < n_my; i += kMmaGroups) {
+  for (int i = group; i < n_my; i += a.n_groups) {
     const int s = i % S;
     const bool ready = __all_sync(0xffffffffu, bar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
     const int t = slot + i * a.ctas_per_chunk;
@@ -349,7 +389,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const MmaArgs 
       // f32 work on them is harmless and their results are not written
       const uint8_t *tile = ring + (int64_t)s * a.stage_bytes;
       if (J.qt == CMLD_Q4_K) {
-        tile_q4k<NT>(tile, m0, ns, lane, codes, xscale, bs16, acc);
+        tile_q4k<NT>(tile, m0, ns, lane, codes, xscale, bs32_hi, bs32_lo, acc);
       } else if (J.qt == CMLD_Q6_K) {
         float d_lo[kMmaChunkSb], d_hi[kMmaChunkSb];
         const int r_lo = min(row0 + m0 + g8, J.rows - 1), r_hi = min(row0 + m0 + g8 + 8, J.rows - 1);
@@ -359,7 +399,7 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const MmaArgs 
           d_lo[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_lo * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
           d_hi[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_hi * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
         }
-        tile_q6k<NT>(tile, m0, ns, lane, codes, xscale, bs16, d_lo, d_hi, acc);
+        tile_q6k<NT>(tile, m0, ns, lane, codes, xscale, bs16_hi, bs16_lo, d_lo, d_hi, acc);
       } else {
         tile_q80<NT>(tile, m0, ns, lane, codes, xscale, acc);
       }
@@ -447,12 +487,16 @@ bool plan_mma(const GemvJob *jobs, int n_jobs, int32_t batch, MmaPlan &p) {
   a.off_scale = off;
   off += nt * 8 * (q80 ? kMmaChunkSb * 8 : kMmaChunkSb) * 4;
   a.off_bsum = off;
-  if (!q80) off += nt * 8 * 64 * 2;
+  if (!q80) off += nt * 8 * kMmaChunkSb * (8 + 8 + 16 + 16);
   off = (off + 127) & ~127;
   a.off_ring = off;
+  // as many consumer groups as the ring has stages for (a stage belongs to one group: the stage count
+  // is a multiple of the group count)
   int n_stages = std::min<int>(kMmaMaxStages, (224 * 1024 - off) / stage);
-  n_stages -= n_stages % kMmaGroups;
   if (n_stages < 2) return false;
+  const int n_groups = std::min(kMmaMaxGroups, n_stages);
+  n_stages -= n_stages % n_groups;
+  a.n_groups = n_groups;
   a.n_stages = n_stages;
   a.stage_bytes = stage;
   a.n_jobs = n_jobs;
@@ -476,7 +520,7 @@ int32_t launch_nt(const MmaPlan &p, cudaStream_t s, bool pdl) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)p.grid);
-  cfg.blockDim = dim3(kMmaThreads);
+  cfg.blockDim = dim3((unsigned)(p.args.n_groups * kMmaWarpsPerGroup * 32 + 32));
   cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];

@@ -410,6 +410,42 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   if (tr) tr[2] = global_ns();
 
   // Prologue: quantised activation rows into shared memory.
+  if (a.mode == 0) {
+    // re-lay the pre-quantised global rows; flat loops over (row, piece) so that every thread has several
+    // independent loads in flight instead of one L2 round trip per row
+    const int64_t astride = act_row_stride(a.cols);
+    if (a.need_k) {
+      for (int idx = tid; idx < a.batch * nsb * 16; idx += kPipeConsumers) {  // 16-byte chunks of codes
+        const int b = idx / (nsb * 16), i = idx % (nsb * 16), sb = i >> 4, c = i & 15;
+        *reinterpret_cast<uint4 *>(act_k + b * rec_col_stride + sb * kActRec + c * 16) =
+            __ldg(reinterpret_cast<const uint4 *>(a.act_in + b * astride + sb * 256 + c * 16));
+      }
+      for (int idx = tid; idx < a.batch * nsb * 8; idx += kPipeConsumers) {  // pairs of 16-sums
+        const int b = idx / (nsb * 8), i = idx % (nsb * 8), sb = i >> 3, g = i & 7;
+        const int pr = __ldg(reinterpret_cast<const int *>(a.act_in + b * astride + act_bsum_off(a.cols)) + i);
+        uint8_t *rec = act_k + b * rec_col_stride + sb * kActRec;
+        reinterpret_cast<int *>(rec + kRecBsum16)[g] = pr;
+        reinterpret_cast<short *>(rec + kRecBsum32)[g] = (short)((int)(short)(pr & 0xffff) + (pr >> 16));
+      }
+      for (int idx = tid; idx < a.batch * nsb; idx += kPipeConsumers) {
+        const int b = idx / nsb, sb = idx % nsb;
+        *reinterpret_cast<float *>(act_k + b * rec_col_stride + sb * kActRec + kRecD) =
+            __ldg(reinterpret_cast<const float *>(a.act_in + b * astride + act_scale_off(a.cols)) + sb);
+      }
+    }
+    if (a.need_0) {
+      const int n16 = a.cols >> 4, n32 = a.cols >> 5;
+      for (int idx = tid; idx < a.batch * n16; idx += kPipeConsumers) {
+        const int b = idx / n16, i = idx % n16;
+        *reinterpret_cast<uint4 *>(act_0 + b * act0_col_stride + i * 16) = __ldg(reinterpret_cast<const uint4 *>(a.act_in0 + b * astride) + i);
+      }
+      for (int idx = tid; idx < a.batch * n32; idx += kPipeConsumers) {
+        const int b = idx / n32, i = idx % n32;
+        reinterpret_cast<float *>(act_0 + b * act0_col_stride + round_up16(a.cols))[i] =
+            __ldg(reinterpret_cast<const float *>(a.act_in0 + b * astride + act_scale_off(a.cols)) + i);
+      }
+    }
+  }
   for (int b = 0; b < a.batch; ++b) {
     if (a.peer.rx_n > 0) {
       // RMSNorm of the sum of the ranks' partial rows (added in rank order, so every rank gets the same
@@ -463,37 +499,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       }
       continue;
     }
-    if (a.mode == 0) {
-      // re-lay the pre-quantised global rows
-      const int64_t astride = act_row_stride(a.cols);
-      if (a.need_k) {
-        const uint8_t *src = a.act_in + b * astride;
-        for (int i = tid; i < nsb * 16; i += kPipeConsumers) {  // 16-byte chunks of codes
-          const int sb = i >> 4, c = i & 15;
-          *reinterpret_cast<uint4 *>(act_k + b * rec_col_stride + sb * kActRec + c * 16) =
-              __ldg(reinterpret_cast<const uint4 *>(src + sb * 256 + c * 16));
-        }
-        for (int i = tid; i < nsb * 8; i += kPipeConsumers) {  // pairs of 16-sums
-          const int sb = i >> 3, g = i & 7;
-          const int pr = __ldg(reinterpret_cast<const int *>(src + act_bsum_off(a.cols)) + i);
-          uint8_t *rec = act_k + b * rec_col_stride + sb * kActRec;
-          reinterpret_cast<int *>(rec + kRecBsum16)[g] = pr;
-          reinterpret_cast<short *>(rec + kRecBsum32)[g] = (short)((int)(short)(pr & 0xffff) + (pr >> 16));
-        }
-        for (int sb = tid; sb < nsb; sb += kPipeConsumers)
-          *reinterpret_cast<float *>(act_k + b * rec_col_stride + sb * kActRec + kRecD) =
-              __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + sb);
-      }
-      if (a.need_0) {
-        const uint8_t *src = a.act_in0 + b * astride;
-        for (int i = tid; i < (a.cols >> 4); i += kPipeConsumers)
-          *reinterpret_cast<uint4 *>(act_0 + b * act0_col_stride + i * 16) = __ldg(reinterpret_cast<const uint4 *>(src) + i);
-        for (int i = tid; i < (a.cols >> 5); i += kPipeConsumers)
-          reinterpret_cast<float *>(act_0 + b * act0_col_stride + round_up16(a.cols))[i] =
-              __ldg(reinterpret_cast<const float *>(src + act_scale_off(a.cols)) + i);
-      }
-      continue;
-    }
+    if (a.mode == 0) continue;  // copied above
     const float *x = a.x + (int64_t)b * a.x_stride;
     const float *x2 = a.mode == 3 ? a.x2 + (int64_t)b * a.x_stride : nullptr;
     float scale = 1.0f;

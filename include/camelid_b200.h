@@ -266,8 +266,8 @@ CMLD_API int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t ba
                            const float *residual_dev);
 /* Which matvec kernel cmld_gemv / cmld_gemv_time use: bit 0 clear = the staged (bulk-copy
  * pipelined) kernel whenever it takes the shape, bit 0 set = the direct-load kernel only; bit 1
- * set = cmld_gemv_time chains its launches with programmatic dependent launch.  Process-wide;
- * for A/B runs. */
+ * set = cmld_gemv_time chains its launches with programmatic dependent launch; bit 2 set = the
+ * tensor-core kernel (normally used from 9 rows) from 1 row.  Process-wide; for A/B runs. */
 CMLD_API int32_t cmld_gemv_select_kernel(int32_t choice);
 /* The staged kernel with its fused prologue: y = W . quantise(f(x)) (+ residual), with
  * f = RMSNorm(x) * norm_w (mode 1), x (mode 2) or SwiGLU(x, x2) (mode 3); x_dev/x2_dev are f32
