@@ -9,60 +9,27 @@
 //
 // Layout of the work: the columns are cut into chunks of 1024 (4 superblocks); a CTA owns ONE chunk for
 // its whole life and keeps the quantised activations of that chunk for all rows in shared memory
-// (32 x 1024 codes + scales), so the operand that every weight tile needs is loaded once per CTA.  The
-// CTA walks tiles of 64 weight rows of its chunk: a producer warp copies each row's chunk bytes with
-// one bulk asynchronous copy per row into a padded (bank-conflict-free) slot of an mbarrier ring; two or three
-// groups of four consumer warps alternate tiles, every warp owning 16 rows (one MMA row tile) for the
-// whole chunk and all <= 4 column tiles of 8 activation rows — no reduction across warps.  With more
-// than one chunk the per-chunk partial sums go to a scratch array and a small kernel adds them in chunk
-// order (plus the residual).  All waits are bounded.
+// (32 x 1024 codes + scales), so the operand that every weight needs is loaded once per CTA.  Each warp
+// works alone on units of 16 weight rows (one MMA row tile) of the CTA's chunk, for all <= 4 column
+// tiles of 8 activation rows: no reduction across warps, no CTA barrier after the start.  A warp copies
+// the next unit's chunk bytes into its second buffer with 16-byte asynchronous copies (cp.async) while
+// it computes on the first — a row's chunk is only 576..1088 bytes, and one bulk (TMA) request per such
+// piece was measured to cap the kernel at about 50 ns per request per SM; rows are padded in shared
+// memory to a bank-conflict-free pitch.  With more than one chunk the per-chunk partial sums go to a
+// scratch array and a small kernel adds them in chunk order (plus the residual).
 #include "common.cuh"
 
 namespace cmld {
 
-constexpr int kMmaWarpsPerGroup = 4;
-constexpr int kMmaMaxGroups = 3;  // consumer groups (2 or 3, as many as the ring has room for: one stage each at least)
-constexpr int kMmaMaxThreads = kMmaMaxGroups * kMmaWarpsPerGroup * 32 + 32;
-constexpr int kMmaTileRows = kMmaWarpsPerGroup * 16;
+constexpr int kMmaMaxWarps = 12;  // warps per CTA: as many as have room for their two buffers
+constexpr int kMmaMaxThreads = kMmaMaxWarps * 32;
 constexpr int kMmaChunkSb = 4;  // superblocks (of 256 columns) per chunk
 constexpr int kMmaChunkCols = kMmaChunkSb * 256;
-constexpr int kMmaMaxStages = 6;
 constexpr int kMmaCodeStride = kMmaChunkCols + 16;  // bytes between activation rows in shared memory (conflict-free)
-constexpr uint32_t kMmaSpinLimit = 1u << 22;
 
 namespace {
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void bar_init(uint64_t *bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void bar_expect_tx(uint64_t *bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void bar_arrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ bool bar_try_wait(uint64_t *bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool bar_wait(uint64_t *bar, uint32_t parity, int32_t *status) {
-  for (uint32_t i = 0; i < kMmaSpinLimit; ++i)
-    if (bar_try_wait(bar, parity)) return true;
-  if (status) atomicExch(status, (int32_t)CMLD_ERR_TIMEOUT);
-  return false;
-}
-__device__ __forceinline__ void bulk_copy(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_addr(dst_smem)),
-               "l"(src), "r"(bytes), "r"(smem_addr(bar))
-               : "memory");
-}
-
 // D(16x8, s32) = A(16x32, s8, row-major) * B(32x8, s8, column-major).  Lane (g = lane/4, t = lane%4) holds
 // A: a0 = row g, k 4t..4t+3; a1 = row g+8, same k; a2 = row g, k 16+4t..; a3 = row g+8, k 16+4t..
 // B: b0 = k 4t..4t+3 of column g; b1 = k 16+4t.. of column g
@@ -90,7 +57,7 @@ struct MmaJob {
 
 struct MmaArgs {
   MmaJob job[3];
-  int32_t n_jobs, total_tiles, cols, batch, n_chunks, ctas_per_chunk, stage_bytes, n_stages, n_groups, rows_cat, q8_0;
+  int32_t n_jobs, total_tiles, cols, batch, n_chunks, ctas_per_chunk, stage_bytes, n_warps, rows_cat, q8_0;
   const uint8_t *act;  // quantised activation rows, global layout, the format the jobs' types need
   float *partial;      // [chunk][batch][rows_cat] when n_chunks > 1
   int32_t *status;
@@ -258,70 +225,72 @@ __device__ __forceinline__ void tile_q80(const uint8_t *tile, int m0, int ns, in
   }
 }
 
+// 16-byte asynchronous global->shared copy (LDGSTS); the data is only read once, so it bypasses L1.
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Which matrix and which 16 rows unit u of the launch is.
+struct MmaUnit {
+  int j, row0, nrows;
+};
+__device__ __forceinline__ MmaUnit unit_of(const MmaArgs &a, int u) {
+  int j = 0;
+  if (a.n_jobs > 1 && u >= a.job[1].first_tile) j = 1;
+  if (a.n_jobs > 2 && u >= a.job[2].first_tile) j = 2;
+  MmaUnit m;
+  m.j = j;
+  m.row0 = (u - a.job[j].first_tile) * 16;
+  m.nrows = min(16, a.job[j].rows - m.row0);
+  return m;
+}
+
+// This warp's copy of the chunk bytes of 16 weight rows into its own buffer: 16-byte pieces, lanes
+// running along a row, rows padded to the conflict-free pitch.
+__device__ __forceinline__ void fetch_unit(const MmaArgs &a, const MmaUnit &m, int sb0, int ns, int lane, uint8_t *buf) {
+  const MmaJob &J = a.job[m.j];
+  const int pitch = row_pitch(J.qt);
+  const int seg = J.qt == CMLD_Q4_K ? ns * 9 : (J.qt == CMLD_Q6_K ? ns * 13 : ns * 16);  // 16-byte pieces of the block bytes
+  const int64_t off = (int64_t)sb0 * (J.qt == CMLD_Q4_K ? 144 : (J.qt == CMLD_Q6_K ? 208 : 256));
+  const int extra = J.qt == CMLD_Q8_0 ? ns : 0;  // pieces of the per-block f16 scales behind the codes
+  const int per_row = seg + extra;
+  for (int i = lane; i < m.nrows * per_row; i += 32) {
+    const int r = i / per_row, c = i % per_row;
+    const uint8_t *row = J.w + (int64_t)(m.row0 + r) * J.stride;
+    const uint8_t *src = c < seg ? row + off + c * 16 : row + a.cols + (int64_t)sb0 * 16 + (c - seg) * 16;
+    cp_async16(buf + r * pitch + c * 16, src);
+  }
+}
+
 template <int NT>
 __global__ void __launch_bounds__(kMmaMaxThreads, 1) gemv_mma_kernel(const MmaArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint64_t *full = reinterpret_cast<uint64_t *>(smem);
-  uint64_t *empty = full + kMmaMaxStages;
   uint8_t *codes = smem + a.off_codes;
   float *xscale = reinterpret_cast<float *>(smem + a.off_scale);
   // sums of the activation codes per 32 (Q4_K mins) and per 16 (Q6_K offset), each split as 64*hi + lo
   int8_t *bs32_hi = reinterpret_cast<int8_t *>(smem + a.off_bsum), *bs32_lo = bs32_hi + NT * 8 * kMmaChunkSb * 8;
   int8_t *bs16_hi = bs32_lo + NT * 8 * kMmaChunkSb * 8, *bs16_lo = bs16_hi + NT * 8 * kMmaChunkSb * 16;
-  uint8_t *ring = smem + a.off_ring;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int S = a.n_stages;
-  const int n_consumer_warps = a.n_groups * kMmaWarpsPerGroup, n_consumers = n_consumer_warps * 32;
+  const int n_warps = (int)blockDim.x >> 5, n_consumers = (int)blockDim.x;
   const int chunk = (int)blockIdx.x % a.n_chunks, slot = (int)blockIdx.x / a.n_chunks;
   const int nsb = a.cols >> 8;
   const int sb0 = chunk * kMmaChunkSb, ns = min(kMmaChunkSb, nsb - sb0);
-  const int n_my = slot < a.total_tiles ? (a.total_tiles - slot + a.ctas_per_chunk - 1) / a.ctas_per_chunk : 0;
-
-  if (tid == 0) {
-    for (int s = 0; s < S; ++s) {
-      bar_init(&full[s], 1);
-      bar_init(&empty[s], kMmaWarpsPerGroup);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
+  // units of 16 weight rows; this warp takes units first, first + stride, ...
+  const int first = slot * n_warps + warp, stride = a.ctas_per_chunk * n_warps;
+  uint8_t *buf0 = smem + a.off_ring + warp * 2 * a.stage_bytes, *buf1 = buf0 + a.stage_bytes;
   asm volatile("griddepcontrol.launch_dependents;");
 
-  if (warp == n_consumer_warps) {
-    // ---------------- producer: one bulk copy per weight row (two for Q8_0: codes, scales); lanes share the rows
-    for (int i = 0; i < n_my; ++i) {
-      const int s = i % S;
-      bool ok = true;
-      if (i >= S) ok = bar_wait(&empty[s], (uint32_t)((i / S - 1) & 1), a.status);
-      ok = __all_sync(0xffffffffu, ok);
-      const int t = slot + i * a.ctas_per_chunk;
-      int j = 0;
-      if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
-      if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
-      const MmaJob &J = a.job[j];
-      const int row0 = (t - J.first_tile) * kMmaTileRows;
-      const int nrows = min(kMmaTileRows, J.rows - row0);
-      const int pitch = row_pitch(J.qt);
-      const uint32_t row_bytes = (uint32_t)(J.qt == CMLD_Q4_K ? ns * 144 : (J.qt == CMLD_Q6_K ? ns * 208 : ns * 256 + ns * 16));
-      if (lane == 0) bar_expect_tx(&full[s], row_bytes * (uint32_t)nrows);
-      __syncwarp();
-      uint8_t *dst = ring + (int64_t)s * a.stage_bytes;
-      for (int r = lane; r < nrows; r += 32) {
-        const uint8_t *src = J.w + (int64_t)(row0 + r) * J.stride;
-        if (J.qt == CMLD_Q4_K) bulk_copy(dst + r * pitch, src + (int64_t)sb0 * 144, (uint32_t)ns * 144, &full[s]);
-        else if (J.qt == CMLD_Q6_K) bulk_copy(dst + r * pitch, src + (int64_t)sb0 * 208, (uint32_t)ns * 208, &full[s]);
-        else {
-          bulk_copy(dst + r * pitch, src + (int64_t)sb0 * 256, (uint32_t)ns * 256, &full[s]);
-          bulk_copy(dst + r * pitch + ns * 256, src + a.cols + (int64_t)sb0 * 16, (uint32_t)ns * 16, &full[s]);
-        }
-      }
-      (void)ok;
-    }
-    return;
-  }
-
-  // ---------------- consumers: this chunk's activations for every row into shared memory, once
+  // weights do not depend on the previous kernel: the first unit's copy is in flight before the wait
+  if (first < a.total_tiles) fetch_unit(a, unit_of(a, first), sb0, ns, lane, buf0);
+  cp_async_commit();
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---------------- this chunk's activations for every row into shared memory, once
   const int64_t astride = act_row_stride(a.cols);
   // (flat loops: every thread has several independent loads in flight; a loop over the rows with one row
   // per trip would serialise 32 round trips to L2)
@@ -364,65 +333,57 @@ __global__ void __launch_bounds__(kMmaMaxThreads, 1) gemv_mma_kernel(const MmaAr
       bs32_hi[idx] = (int8_t)((v - lo) / 64);
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"r"(n_consumers));
+  __syncthreads();
 
-  const int group = warp / kMmaWarpsPerGroup, wg = warp % kMmaWarpsPerGroup;
   const int g8 = lane >> 2, t4 = lane & 3;
-  for (int i = group; i < n_my; i += a.n_groups) {
-    const int s = i % S;
-    const bool ready = __all_sync(0xffffffffu, bar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-    const int t = slot + i * a.ctas_per_chunk;
-    int j = 0;
-    if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
-    if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
-    const MmaJob &J = a.job[j];
-    const int row0 = (t - J.first_tile) * kMmaTileRows;
-    const int nrows = min(kMmaTileRows, J.rows - row0);
-    const int m0 = wg * 16;
+  int it = 0;
+  for (int u = first; u < a.total_tiles; u += stride, ++it) {
+    uint8_t *cur = (it & 1) ? buf1 : buf0, *nxt = (it & 1) ? buf0 : buf1;
+    if (u + stride < a.total_tiles) fetch_unit(a, unit_of(a, u + stride), sb0, ns, lane, nxt);
+    cp_async_commit();
+    cp_async_wait<1>();  // everything but the copy just issued has landed: unit u is complete
+    __syncwarp();
+    const MmaUnit m = unit_of(a, u);
+    const MmaJob &J = a.job[m.j];
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
-    if (ready && m0 < nrows) {
-      // rows of the tile beyond the matrix were not copied: their slots hold stale bytes; the integer and
-      // f32 work on them is harmless and their results are not written
-      const uint8_t *tile = ring + (int64_t)s * a.stage_bytes;
-      if (J.qt == CMLD_Q4_K) {
-        tile_q4k<NT>(tile, m0, ns, lane, codes, xscale, bs32_hi, bs32_lo, acc);
-      } else if (J.qt == CMLD_Q6_K) {
-        float d_lo[kMmaChunkSb], d_hi[kMmaChunkSb];
-        const int r_lo = min(row0 + m0 + g8, J.rows - 1), r_hi = min(row0 + m0 + g8 + 8, J.rows - 1);
+    // rows beyond the matrix were not copied: their slots hold stale bytes; the integer and f32 work on
+    // them is harmless and their results are not written
+    if (J.qt == CMLD_Q4_K) {
+      tile_q4k<NT>(cur, 0, ns, lane, codes, xscale, bs32_hi, bs32_lo, acc);
+    } else if (J.qt == CMLD_Q6_K) {
+      float d_lo[kMmaChunkSb], d_hi[kMmaChunkSb];
+      const int r_lo = min(m.row0 + g8, J.rows - 1), r_hi = min(m.row0 + g8 + 8, J.rows - 1);
 #pragma unroll
-        for (int sb = 0; sb < kMmaChunkSb; ++sb) {
-          const int sbc = min(sb, ns - 1);
-          d_lo[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_lo * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
-          d_hi[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_hi * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
-        }
-        tile_q6k<NT>(tile, m0, ns, lane, codes, xscale, bs16_hi, bs16_lo, d_lo, d_hi, acc);
-      } else {
-        tile_q80<NT>(tile, m0, ns, lane, codes, xscale, acc);
+      for (int sb = 0; sb < kMmaChunkSb; ++sb) {
+        const int sbc = min(sb, ns - 1);
+        d_lo[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_lo * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
+        d_hi[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_hi * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
       }
+      tile_q6k<NT>(cur, 0, ns, lane, codes, xscale, bs16_hi, bs16_lo, d_lo, d_hi, acc);
+    } else {
+      tile_q80<NT>(cur, 0, ns, lane, codes, xscale, acc);
     }
-    __syncwarp();
-    if (lane == 0) bar_arrive(&empty[s]);
-    if (ready) {
+    __syncwarp();  // every lane is done with `cur` before the next trip's copy overwrites it
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int col = nt * 8 + t4 * 2 + (k & 1), r = m0 + g8 + (k >= 2 ? 8 : 0);
-          if (col < a.batch && r < nrows) {
-            if (a.n_chunks == 1) {
-              const int64_t o = (int64_t)col * J.y_stride + row0 + r;
-              J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), acc[nt][k]) : acc[nt][k];
-            } else {
-              a.partial[((int64_t)chunk * a.batch + col) * a.rows_cat + J.row_off + row0 + r] = acc[nt][k];
-            }
+      for (int k = 0; k < 4; ++k) {
+        const int col = nt * 8 + t4 * 2 + (k & 1), r = g8 + (k >= 2 ? 8 : 0);
+        if (col < a.batch && r < m.nrows) {
+          if (a.n_chunks == 1) {
+            const int64_t o = (int64_t)col * J.y_stride + m.row0 + r;
+            J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), acc[nt][k]) : acc[nt][k];
+          } else {
+            a.partial[((int64_t)chunk * a.batch + col) * a.rows_cat + J.row_off + m.row0 + r] = acc[nt][k];
           }
         }
-    }
+      }
   }
+  cp_async_wait<0>();
 }
 
 // y = residual + sum over chunks (in chunk order) of the partial sums.
@@ -473,15 +434,15 @@ bool plan_mma(const GemvJob *jobs, int n_jobs, int32_t batch, MmaPlan &p) {
     J.residual = g.residual;
     J.y_stride = g.y_stride;
     J.first_tile = tiles;
-    J.n_tiles = (int)((g.rows + kMmaTileRows - 1) / kMmaTileRows);
+    J.n_tiles = (int)((g.rows + 15) / 16);  // units of 16 rows: one MMA row tile, one warp
     J.row_off = rows_cat;
     tiles += J.n_tiles;
     rows_cat += (int)g.rows;
-    stage = std::max(stage, kMmaTileRows * row_pitch(g.qt));
+    stage = std::max(stage, 16 * row_pitch(g.qt));
   }
   stage = (stage + 127) & ~127;
   const int nt = (batch + 7) / 8;
-  int off = 2 * kMmaMaxStages * 8;
+  int off = 0;
   a.off_codes = off;
   off += nt * 8 * kMmaCodeStride;
   a.off_scale = off;
@@ -490,14 +451,11 @@ bool plan_mma(const GemvJob *jobs, int n_jobs, int32_t batch, MmaPlan &p) {
   if (!q80) off += nt * 8 * kMmaChunkSb * (8 + 8 + 16 + 16);
   off = (off + 127) & ~127;
   a.off_ring = off;
-  // as many consumer groups as the ring has stages for (a stage belongs to one group: the stage count
-  // is a multiple of the group count)
-  int n_stages = std::min<int>(kMmaMaxStages, (224 * 1024 - off) / stage);
-  if (n_stages < 2) return false;
-  const int n_groups = std::min(kMmaMaxGroups, n_stages);
-  n_stages -= n_stages % n_groups;
-  a.n_groups = n_groups;
-  a.n_stages = n_stages;
+  // every warp owns two buffers of 16 row chunks (the one it computes on and the one being filled)
+  int n_warps = std::min<int>(kMmaMaxWarps, (224 * 1024 - off) / (2 * stage));
+  if (const char *v = getenv("CMLD_MMA_WARPS")) n_warps = std::max(1, std::min(n_warps, atoi(v)));  // A/B runs
+  if (n_warps < 2) return false;
+  a.n_warps = n_warps;
   a.stage_bytes = stage;
   a.n_jobs = n_jobs;
   a.total_tiles = tiles;
@@ -506,9 +464,9 @@ bool plan_mma(const GemvJob *jobs, int n_jobs, int32_t batch, MmaPlan &p) {
   a.rows_cat = rows_cat;
   a.q8_0 = q80 ? 1 : 0;
   a.n_chunks = (int)((cols / 256 + kMmaChunkSb - 1) / kMmaChunkSb);
-  a.ctas_per_chunk = std::max(1, std::min(tiles, g_mma_sms / a.n_chunks));
+  a.ctas_per_chunk = std::max(1, std::min((tiles + n_warps - 1) / n_warps, g_mma_sms / a.n_chunks));
   p.grid = a.n_chunks * a.ctas_per_chunk;
-  p.smem_bytes = off + n_stages * stage;
+  p.smem_bytes = off + n_warps * 2 * stage;
   return true;
 }
 
@@ -520,7 +478,7 @@ int32_t launch_nt(const MmaPlan &p, cudaStream_t s, bool pdl) {
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)p.grid);
-  cfg.blockDim = dim3((unsigned)(p.args.n_groups * kMmaWarpsPerGroup * 32 + 32));
+  cfg.blockDim = dim3((unsigned)(p.args.n_warps * 32));
   cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
