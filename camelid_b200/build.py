@@ -75,7 +75,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         cmd = [nvcc(), *ARCH, "-shared", "-cudart", "static", "-o", str(LIB), *objs]
         if host_cc:
             cmd[1:1] = ["-ccbin", host_cc]
-        cmd += ["-ldl"]  # NCCL is bound with dlopen when a sharded engine first needs it
+        cmd += ["-ldl", "-lpthread", "-lrt", "-Xlinker", "--no-undefined"]  # NCCL is bound with dlopen when a sharded engine first needs it
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

@@ -246,6 +246,11 @@ int64_t gemv_mma_scratch_floats(const GemvJob *jobs, int n_jobs, int32_t batch);
 int32_t launch_gemv_mma(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, float *scratch, int64_t scratch_floats,
                         int32_t *status, cudaStream_t s, bool pdl, int64_t *launches);
 
+int64_t gemv_mma_expert_scratch_floats(const GemvJob *jobs, int n_jobs, int nt, int n_experts, int n_pass);
+int32_t launch_gemv_mma_experts(const GemvJob *jobs, int n_jobs, const uint8_t *act, int nt, int n_experts, int n_pass,
+                                const int32_t *counts, int first_expert, int expert_step, int cap, int count_mul, float *scratch,
+                                int64_t scratch_floats, int32_t *status, cudaStream_t s, bool pdl, int64_t *launches);
+
 // ops.cu
 struct NormQuantArgs {
   const float *x;       // [batch][cols]

@@ -153,6 +153,12 @@ struct cmld_engine {
   int64_t history_cap = 0;
   int32_t *moe_sel_idx = nullptr, *moe_counts = nullptr, *moe_lists = nullptr;
   float *moe_sel_w = nullptr, *moe_g = nullptr, *moe_u = nullptr, *moe_act = nullptr, *moe_down = nullptr;
+  // tensor-core expert path: three Q8_K rows per assignment, `moe_cap` rows per local expert
+  int32_t *moe_pos = nullptr;
+  int32_t moe_cap = 0, moe_pass_rows = 0;
+  uint8_t *moe_act3_h = nullptr, *moe_act3_f = nullptr;
+  float *moe_g3 = nullptr, *moe_u3 = nullptr, *moe_d3 = nullptr, *moe_scratch = nullptr;
+  int64_t moe_scratch_floats = 0;
   int32_t *d_status = nullptr;  // set by a kernel whose bounded wait gave up
   int64_t filled = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -301,6 +307,22 @@ static int32_t engine_init(cmld_engine *e) {
     CMLD_TRY(dev_alloc(e, &e->moe_u, na * c.ffn_dim));
     CMLD_TRY(dev_alloc(e, &e->moe_act, na * c.ffn_dim));
     CMLD_TRY(dev_alloc(e, &e->moe_down, na * c.hidden));
+    CMLD_TRY(dev_alloc(e, &e->moe_pos, na));
+    if (c.hidden % 256 == 0 && c.ffn_dim % 256 == 0 && !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV))) {
+      const int64_t n_local = c.n_experts / std::max(1, c.ep_size);
+      e->moe_cap = (int32_t)(3 * na);  // every assignment could land on one expert
+      const int64_t rows = n_local * e->moe_cap;
+      CMLD_TRY(dev_alloc(e, &e->moe_act3_h, rows * act_row_stride(c.hidden)));
+      CMLD_TRY(dev_alloc(e, &e->moe_act3_f, rows * act_row_stride(c.ffn_dim)));
+      CMLD_TRY(dev_alloc(e, &e->moe_g3, rows * c.ffn_dim, false));
+      CMLD_TRY(dev_alloc(e, &e->moe_u3, rows * c.ffn_dim, false));
+      CMLD_TRY(dev_alloc(e, &e->moe_d3, rows * c.hidden, false));
+      // per-chunk partial sums of the expert matvecs: (rows in flight + one pass of padding) per local expert
+      auto chunks = [](int64_t cols) { return (cols / 256 + 3) / 4; };
+      const int64_t per_row = std::max(chunks(c.hidden) * 2 * (int64_t)c.ffn_dim, chunks(c.ffn_dim) * (int64_t)c.hidden);
+      e->moe_scratch_floats = n_local * per_row * (e->moe_cap + 32);
+      CMLD_TRY(dev_alloc(e, &e->moe_scratch, e->moe_scratch_floats, false));
+    }
   }
   {
     // the batched matvec cuts the columns into 1024-wide chunks and sums the chunks afterwards
@@ -373,6 +395,7 @@ static void engine_free(cmld_engine *e) {
   comm_destroy(e->comm);
   e->comm = nullptr;
   peer_link_close(e);
+
   for (auto &L : e->layers) {
     for (auto &w : L.proj) weight_free(w);
     for (auto &w : L.exps) weight_free(w);
@@ -560,7 +583,11 @@ struct StepOpts {
 
 // moe.cu
 int32_t moe_route(const float *normed, const float *router, int hidden, int n_exp, int k, int batch, int32_t *sel_idx,
-                  float *sel_w, int32_t *counts, int32_t *lists, cudaStream_t s);
+                  float *sel_w, int32_t *counts, int32_t *lists, cudaStream_t s, int32_t *pos);
+int32_t moe_quant3(const float *x, const float *x2, int mode, int cols, int k, int n_assign, int n_local, int first_expert,
+                   int expert_step, int cap, const int32_t *counts, const int32_t *lists, uint8_t *act, cudaStream_t s);
+int32_t moe_combine3(float *h, const float *y3, const float *sel_w, const int32_t *sel_idx, const int32_t *pos, int hidden, int k,
+                     int batch, int first_expert, int expert_step, int cap, bool add_residual, cudaStream_t s);
 int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
                         const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
                         int n_assign, cudaStream_t s);
@@ -577,13 +604,52 @@ static int32_t reduce_hidden(cmld_engine *e, int32_t B) {
 
 static int ep_size(const cmld_engine *e) { return std::max(1, e->cfg.ep_size); }
 
+// The expert matvecs on the tensor cores (three Q8_K rows per assignment).  Returns CMLD_ERR_UNSUPPORTED, having
+// launched nothing, when the shapes or the scratch do not allow it.
+static int32_t moe_ffn_step_mma(cmld_engine *e, LayerW &L, int32_t B) {
+  const cmld_config &c = e->cfg;
+  if (!e->moe_act3_h || L.exps[0].qt != L.exps[1].qt) return CMLD_ERR_UNSUPPORTED;
+  const int k = c.n_experts_used, na = B * k;
+  const int n_local = c.n_experts / ep_size(e), first = ep_size(e) > 1 ? c.ep_rank : 0, step = ep_size(e);
+  const bool pdl = !(c.flags & CMLD_FLAG_NO_PDL);
+  // rows per pass: enough for the expected load of an expert (3 rows per assignment), at most 32
+  const int expect = 3 * ((na + c.n_experts - 1) / c.n_experts);
+  const int nt = std::max(1, std::min(4, (expect * 3 / 2 + 7) / 8));
+  const int n_pass = (3 * na + nt * 8 - 1) / (nt * 8);
+  GemvJob gu[2] = {{L.exps[0].data, L.exps[0].qt, c.ffn_dim, c.hidden, L.exps[0].stride, e->moe_g3, nullptr, c.ffn_dim},
+                   {L.exps[1].data, L.exps[1].qt, c.ffn_dim, c.hidden, L.exps[1].stride, e->moe_u3, nullptr, c.ffn_dim}};
+  GemvJob dn[1] = {{L.exps[2].data, L.exps[2].qt, c.hidden, c.ffn_dim, L.exps[2].stride, e->moe_d3, nullptr, c.hidden}};
+  const int64_t need_gu = gemv_mma_expert_scratch_floats(gu, 2, nt, n_local, n_pass), need_dn = gemv_mma_expert_scratch_floats(dn, 1, nt, n_local, n_pass);
+  if (need_gu < 0 || need_dn < 0 || std::max(need_gu, need_dn) > e->moe_scratch_floats) return CMLD_ERR_UNSUPPORTED;
+  CMLD_TRY(moe_route(e->normed, L.router, c.hidden, c.n_experts, k, B, e->moe_sel_idx, e->moe_sel_w, e->moe_counts,
+                     e->moe_lists, e->stream, e->moe_pos));
+  CMLD_TRY(moe_quant3(e->normed, nullptr, 0, c.hidden, k, na, n_local, first, step, e->moe_cap, e->moe_counts, e->moe_lists,
+                      e->moe_act3_h, e->stream));
+  e->launches += 3;
+  CMLD_TRY(launch_gemv_mma_experts(gu, 2, e->moe_act3_h, nt, n_local, n_pass, e->moe_counts, first, step, e->moe_cap, 3,
+                                   e->moe_scratch, e->moe_scratch_floats, e->d_status, e->stream, pdl, &e->launches));
+  CMLD_TRY(moe_quant3(e->moe_g3, e->moe_u3, 1, c.ffn_dim, k, na, n_local, first, step, e->moe_cap, e->moe_counts, e->moe_lists,
+                      e->moe_act3_f, e->stream));
+  CMLD_TRY(launch_gemv_mma_experts(dn, 1, e->moe_act3_f, nt, n_local, n_pass, e->moe_counts, first, step, e->moe_cap, 3,
+                                   e->moe_scratch, e->moe_scratch_floats, e->d_status, e->stream, pdl, &e->launches));
+  CMLD_TRY(moe_combine3(e->h, e->moe_d3, e->moe_sel_w, e->moe_sel_idx, e->moe_pos, c.hidden, k, B, first, step, e->moe_cap,
+                        e->ep == 1 || e->shard_rank == 0, e->stream));
+  e->launches += 2;
+  if (e->ep > 1) CMLD_TRY(reduce_hidden(e, B));
+  return CMLD_OK;
+}
+
 // Mixtral FFN on e->normed (f32): route, expert gate/up, SwiGLU, expert down, weighted sum.
 static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
   const cmld_config &c = e->cfg;
+  {
+    const int32_t rc = moe_ffn_step_mma(e, L, B);
+    if (rc != CMLD_ERR_UNSUPPORTED) return rc;
+  }
   const int k = c.n_experts_used, na = B * k;
   const int n_local = c.n_experts / ep_size(e), first = ep_size(e) > 1 ? c.ep_rank : 0, step = ep_size(e);
   CMLD_TRY(moe_route(e->normed, L.router, c.hidden, c.n_experts, k, B, e->moe_sel_idx, e->moe_sel_w, e->moe_counts,
-                     e->moe_lists, e->stream));
+                     e->moe_lists, e->stream, e->moe_pos));
   CMLD_TRY(moe_expert_gemv(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts,
                            e->moe_lists, na, e->stream));
   CMLD_TRY(moe_expert_gemv(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts,

@@ -62,17 +62,26 @@ struct MmaArgs {
   float *partial;      // [chunk][batch][rows_cat] when n_chunks > 1
   int32_t *status;
   int32_t off_codes, off_scale, off_bsum, off_ring;
+  // expert mode (counts != null): blockIdx.y = local expert, blockIdx.z = pass of NT*8 activation rows.  Expert e's
+  // matrices are rows [e*rows, (e+1)*rows) of each slab, its activation rows start at row e*cap of `act`, its
+  // results at row e*cap of y, and only count_mul * counts[first_expert + e*expert_step] of them exist.
+  const int32_t *counts;
+  int32_t first_expert, expert_step, cap, count_mul;
 };
 
 // bytes of one weight row's chunk in shared memory (padded so that 8 rows x 4 words hit 32 distinct banks)
-__host__ __device__ inline int row_pitch(int qt) { return (qt == CMLD_Q4_K ? 4 * 144 : (qt == CMLD_Q6_K ? 4 * 208 : 4 * 256 + 4 * 16)) + 16; }
+constexpr int kMmaPieceSb = 2;  // superblocks a warp buffers at a time (half a chunk)
+__host__ __device__ inline int row_pitch(int qt) {
+  return (qt == CMLD_Q4_K ? kMmaPieceSb * 144 : (qt == CMLD_Q6_K ? kMmaPieceSb * 208 : kMmaPieceSb * 256 + kMmaPieceSb * 16)) + 16;
+}
 
 // Byte k of w as an int (0..255).
 __device__ __forceinline__ int byte_of(uint32_t w, int k) { return (int)((w >> (8 * k)) & 0xffu); }
 
 template <int NT>
-__device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xd,
+__device__ __forceinline__ void tile_q4k(const uint8_t *tile, int sbo, int ns, int lane, const uint8_t *codes, const float *xd,
                                          const int8_t *bs_hi, const int8_t *bs_lo, float (&acc)[NT][4]) {
+  constexpr int m0 = 0;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int pitch = row_pitch(CMLD_Q4_K);
   const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
@@ -92,7 +101,7 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
       const uint32_t a0 = t4 == 0 ? mn_lo[0] : (t4 == 1 ? mn_lo[1] : 0u), a1 = t4 == 0 ? mn_hi[0] : (t4 == 1 ? mn_hi[1] : 0u);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int o = ((nt * 8 + g8) * kMmaChunkSb + sb) * 8 + (t4 & 1) * 4;
+        const int o = ((nt * 8 + g8) * kMmaChunkSb + sbo + sb) * 8 + (t4 & 1) * 4;
         int ch[4], cl[4];
         mma_k16(ch, a0, a1, *reinterpret_cast<const uint32_t *>(bs_hi + o));
         mma_k16(cl, a0, a1, *reinterpret_cast<const uint32_t *>(bs_lo + o));
@@ -117,7 +126,7 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
         const uint32_t a2 = (wl1 >> (4 * h)) & 0x0f0f0f0fu, a3 = (wh1 >> (4 * h)) & 0x0f0f0f0fu;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const uint8_t *xc = codes + (nt * 8 + g8) * kMmaCodeStride + sb * 256 + g * 32 + t4 * 4;
+          const uint8_t *xc = codes + (nt * 8 + g8) * kMmaCodeStride + (sbo + sb) * 256 + g * 32 + t4 * 4;
           const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xc), b1 = *reinterpret_cast<const uint32_t *>(xc + 16);
           int c[4];
           mma_k32(c, a0, a1, a2, a3, b0, b1);
@@ -134,7 +143,7 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float x = xd[(nt * 8 + t4 * 2 + (i & 1)) * kMmaChunkSb + sb];
+        const float x = xd[(nt * 8 + t4 * 2 + (i & 1)) * kMmaChunkSb + sbo + sb];
         const float d = i < 2 ? d_lo : d_hi, dm = i < 2 ? dm_lo : dm_hi;
         // src/inference.rs:23230-23236: sumf = fma(-dmin*xd, mins, sumf); sumf = fma(d*xd, dots, sumf)
         acc[nt][i] = __fmaf_rn(-__fmul_rn(dm, x), (float)msum[nt][i], acc[nt][i]);
@@ -144,9 +153,10 @@ __device__ __forceinline__ void tile_q4k(const uint8_t *tile, int m0, int ns, in
 }
 
 template <int NT>
-__device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xd,
-                                         const int8_t *b16_hi, const int8_t *b16_lo, float d_lo[kMmaChunkSb], float d_hi[kMmaChunkSb],
+__device__ __forceinline__ void tile_q6k(const uint8_t *tile, int sbo, int ns, int lane, const uint8_t *codes, const float *xd,
+                                         const int8_t *b16_hi, const int8_t *b16_lo, float d_lo[kMmaPieceSb], float d_hi[kMmaPieceSb],
                                          float (&acc)[NT][4]) {
+  constexpr int m0 = 0;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int pitch = row_pitch(CMLD_Q6_K);
   const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
@@ -160,7 +170,7 @@ __device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, in
       const uint32_t a0 = *reinterpret_cast<const uint32_t *>(plo + 192 + t4 * 4), a1 = *reinterpret_cast<const uint32_t *>(phi + 192 + t4 * 4);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const int o = ((nt * 8 + g8) * kMmaChunkSb + sb) * 16 + t4 * 4;
+        const int o = ((nt * 8 + g8) * kMmaChunkSb + sbo + sb) * 16 + t4 * 4;
         int ch[4], cl[4];
         mma_k16(ch, a0, a1, *reinterpret_cast<const uint32_t *>(b16_hi + o));
         mma_k16(cl, a0, a1, *reinterpret_cast<const uint32_t *>(b16_lo + o));
@@ -180,7 +190,7 @@ __device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, in
       const int sc_lo = (int)reinterpret_cast<const int8_t *>(plo + 192)[s], sc_hi = (int)reinterpret_cast<const int8_t *>(phi + 192)[s];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(codes + (nt * 8 + g8) * kMmaCodeStride + sb * 256 + s * 16 + t4 * 4);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(codes + (nt * 8 + g8) * kMmaCodeStride + (sbo + sb) * 256 + s * 16 + t4 * 4);
         int c[4];
         mma_k16(c, a0, a1, b0);
         isum[nt][0] += sc_lo * c[0];
@@ -193,15 +203,16 @@ __device__ __forceinline__ void tile_q6k(const uint8_t *tile, int m0, int ns, in
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float x = xd[(nt * 8 + t4 * 2 + (i & 1)) * kMmaChunkSb + sb];
+        const float x = xd[(nt * 8 + t4 * 2 + (i & 1)) * kMmaChunkSb + sbo + sb];
         acc[nt][i] = __fadd_rn(acc[nt][i], __fmul_rn(__fmul_rn(i < 2 ? d_lo[sb] : d_hi[sb], x), (float)isum[nt][i]));
       }
   }
 }
 
 template <int NT>
-__device__ __forceinline__ void tile_q80(const uint8_t *tile, int m0, int ns, int lane, const uint8_t *codes, const float *xs,
+__device__ __forceinline__ void tile_q80(const uint8_t *tile, int sbo, int ns, int lane, const uint8_t *codes, const float *xs,
                                          float (&acc)[NT][4]) {
+  constexpr int m0 = 0;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int pitch = row_pitch(CMLD_Q8_0);
   const uint8_t *rlo = tile + (m0 + g8) * pitch, *rhi = rlo + 8 * pitch;
@@ -212,13 +223,13 @@ __device__ __forceinline__ void tile_q80(const uint8_t *tile, int m0, int ns, in
     const float ws_hi = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(rhi + ns * 256 + blk * 2));
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const uint8_t *xc = codes + (nt * 8 + g8) * kMmaCodeStride + blk * 32 + t4 * 4;
+      const uint8_t *xc = codes + (nt * 8 + g8) * kMmaCodeStride + sbo * 256 + blk * 32 + t4 * 4;
       const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xc), b1 = *reinterpret_cast<const uint32_t *>(xc + 16);
       int c[4];
       mma_k32(c, a0, a1, a2, a3, b0, b1);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float x = xs[(nt * 8 + t4 * 2 + (i & 1)) * (kMmaChunkSb * 8) + blk];
+        const float x = xs[(nt * 8 + t4 * 2 + (i & 1)) * (kMmaChunkSb * 8) + sbo * 8 + blk];
         acc[nt][i] = __fadd_rn(acc[nt][i], __fmul_rn(__fmul_rn((float)c[i], i < 2 ? ws_lo : ws_hi), x));  // src/inference.rs:26198
       }
     }
@@ -250,19 +261,20 @@ __device__ __forceinline__ MmaUnit unit_of(const MmaArgs &a, int u) {
   return m;
 }
 
-// This warp's copy of the chunk bytes of 16 weight rows into its own buffer: 16-byte pieces, lanes
-// running along a row, rows padded to the conflict-free pitch.
-__device__ __forceinline__ void fetch_unit(const MmaArgs &a, const MmaUnit &m, int sb0, int ns, int lane, uint8_t *buf) {
+// This warp's copy of one piece (kMmaPieceSb superblocks of the chunk, `np` of them real) of 16 weight rows
+// into one of its buffers: 16-byte pieces, lanes running along a row, rows padded to the conflict-free pitch.
+__device__ __forceinline__ void fetch_piece(const MmaArgs &a, const MmaUnit &m, int64_t row_base, int sb_first, int np, int lane,
+                                            uint8_t *buf) {
   const MmaJob &J = a.job[m.j];
   const int pitch = row_pitch(J.qt);
-  const int seg = J.qt == CMLD_Q4_K ? ns * 9 : (J.qt == CMLD_Q6_K ? ns * 13 : ns * 16);  // 16-byte pieces of the block bytes
-  const int64_t off = (int64_t)sb0 * (J.qt == CMLD_Q4_K ? 144 : (J.qt == CMLD_Q6_K ? 208 : 256));
-  const int extra = J.qt == CMLD_Q8_0 ? ns : 0;  // pieces of the per-block f16 scales behind the codes
+  const int seg = J.qt == CMLD_Q4_K ? np * 9 : (J.qt == CMLD_Q6_K ? np * 13 : np * 16);  // 16-byte pieces of the block bytes
+  const int64_t off = (int64_t)sb_first * (J.qt == CMLD_Q4_K ? 144 : (J.qt == CMLD_Q6_K ? 208 : 256));
+  const int extra = J.qt == CMLD_Q8_0 ? np : 0;  // pieces of the per-block f16 scales behind the codes
   const int per_row = seg + extra;
   for (int i = lane; i < m.nrows * per_row; i += 32) {
     const int r = i / per_row, c = i % per_row;
-    const uint8_t *row = J.w + (int64_t)(m.row0 + r) * J.stride;
-    const uint8_t *src = c < seg ? row + off + c * 16 : row + a.cols + (int64_t)sb0 * 16 + (c - seg) * 16;
+    const uint8_t *row = J.w + (row_base * J.rows + m.row0 + r) * J.stride;
+    const uint8_t *src = c < seg ? row + off + c * 16 : row + a.cols + (int64_t)sb_first * 16 + (c - seg) * 16;
     cp_async16(buf + r * pitch + c * 16, src);
   }
 }
@@ -284,42 +296,62 @@ __global__ void __launch_bounds__(kMmaMaxThreads, 1) gemv_mma_kernel(const MmaAr
   const int first = slot * n_warps + warp, stride = a.ctas_per_chunk * n_warps;
   uint8_t *buf0 = smem + a.off_ring + warp * 2 * a.stage_bytes, *buf1 = buf0 + a.stage_bytes;
   asm volatile("griddepcontrol.launch_dependents;");
-
-  // weights do not depend on the previous kernel: the first unit's copy is in flight before the wait
-  if (first < a.total_tiles) fetch_unit(a, unit_of(a, first), sb0, ns, lane, buf0);
+  const int64_t astride = act_row_stride(a.cols);
+  constexpr int NB = NT * 8;
+  int batch = a.batch, pb = a.batch;  // rows of this launch; rows per chunk in the partial-sum layout
+  int64_t e_local = 0, y_base = 0;
+  const uint8_t *act = a.act;
+  float *partial = a.partial;
+  if (a.counts) {
+    // how many rows this expert has is written by the kernel before: nothing can start before the wait
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    e_local = blockIdx.y;
+    const int col0 = (int)blockIdx.z * NB;
+    batch = min(NB, a.count_mul * __ldcg(a.counts + a.first_expert + (int)e_local * a.expert_step) - col0);
+    if (batch <= 0) return;
+    pb = NB;
+    act += (e_local * a.cap + col0) * astride;
+    y_base = e_local * a.cap + col0;
+    partial += (e_local * gridDim.z + blockIdx.z) * (int64_t)a.n_chunks * NB * a.rows_cat;
+  }
+  // a unit (16 rows x this chunk) is worked through in pieces of kMmaPieceSb superblocks: trip `it` handles piece
+  // it % n_pieces of unit first + (it / n_pieces) * stride, while the copy of trip it+1 is in flight
+  const int n_pieces = (ns + kMmaPieceSb - 1) / kMmaPieceSb;
+  const int n_units = first < a.total_tiles ? (a.total_tiles - first + stride - 1) / stride : 0;
+  const int n_trips = n_units * n_pieces;
+  // weights do not depend on the previous kernel: the first piece's copy is in flight before the wait
+  if (n_trips > 0) fetch_piece(a, unit_of(a, first), e_local, sb0, min(kMmaPieceSb, ns), lane, buf0);
   cp_async_commit();
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!a.counts) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---------------- this chunk's activations for every row into shared memory, once
-  const int64_t astride = act_row_stride(a.cols);
   // (flat loops: every thread has several independent loads in flight; a loop over the rows with one row
   // per trip would serialise 32 round trips to L2)
-  constexpr int NB = NT * 8;
   for (int idx = tid; idx < NB * (kMmaChunkCols / 16); idx += n_consumers) {
     const int b = idx / (kMmaChunkCols / 16), i = idx % (kMmaChunkCols / 16);
     uint4 v = make_uint4(0, 0, 0, 0);  // padding rows of the last column tile and the columns beyond a short chunk
-    if (b < a.batch && i < ns * 16) v = __ldg(reinterpret_cast<const uint4 *>(a.act + b * astride + (int64_t)sb0 * 256) + i);
+    if (b < batch && i < ns * 16) v = __ldg(reinterpret_cast<const uint4 *>(act + b * astride + (int64_t)sb0 * 256) + i);
     *reinterpret_cast<uint4 *>(codes + b * kMmaCodeStride + i * 16) = v;
   }
   if (a.q8_0) {
     for (int idx = tid; idx < NB * (kMmaChunkSb * 8); idx += n_consumers) {
       const int b = idx / (kMmaChunkSb * 8), i = idx % (kMmaChunkSb * 8);
       float v = 0.0f;
-      if (b < a.batch && i < ns * 8) v = __ldg(reinterpret_cast<const float *>(a.act + b * astride + act_scale_off(a.cols)) + sb0 * 8 + i);
+      if (b < batch && i < ns * 8) v = __ldg(reinterpret_cast<const float *>(act + b * astride + act_scale_off(a.cols)) + sb0 * 8 + i);
       xscale[idx] = v;
     }
   } else {
     for (int idx = tid; idx < NB * kMmaChunkSb; idx += n_consumers) {
       const int b = idx / kMmaChunkSb, i = idx % kMmaChunkSb;
       float v = 0.0f;
-      if (b < a.batch && i < ns) v = __ldg(reinterpret_cast<const float *>(a.act + b * astride + act_scale_off(a.cols)) + sb0 + i);
+      if (b < batch && i < ns) v = __ldg(reinterpret_cast<const float *>(act + b * astride + act_scale_off(a.cols)) + sb0 + i);
       xscale[idx] = v;
     }
     for (int idx = tid; idx < NB * (kMmaChunkSb * 8); idx += n_consumers) {
       const int b = idx / (kMmaChunkSb * 8), i = idx % (kMmaChunkSb * 8);
       int v0 = 0, v1 = 0;
-      if (b < a.batch && i < ns * 8) {
-        const int pr = __ldg(reinterpret_cast<const int *>(a.act + b * astride + act_bsum_off(a.cols)) + sb0 * 8 + i);  // two 16-sums
+      if (b < batch && i < ns * 8) {
+        const int pr = __ldg(reinterpret_cast<const int *>(act + b * astride + act_bsum_off(a.cols)) + sb0 * 8 + i);  // two 16-sums
         v0 = (int)(short)(pr & 0xffff);
         v1 = pr >> 16;
       }
@@ -336,49 +368,56 @@ __global__ void __launch_bounds__(kMmaMaxThreads, 1) gemv_mma_kernel(const MmaAr
   __syncthreads();
 
   const int g8 = lane >> 2, t4 = lane & 3;
-  int it = 0;
-  for (int u = first; u < a.total_tiles; u += stride, ++it) {
+  float acc[NT][4];
+  for (int it = 0; it < n_trips; ++it) {
     uint8_t *cur = (it & 1) ? buf1 : buf0, *nxt = (it & 1) ? buf0 : buf1;
-    if (u + stride < a.total_tiles) fetch_unit(a, unit_of(a, u + stride), sb0, ns, lane, nxt);
+    if (it + 1 < n_trips) {
+      const int pc = (it + 1) % n_pieces;
+      fetch_piece(a, unit_of(a, first + ((it + 1) / n_pieces) * stride), e_local, sb0 + pc * kMmaPieceSb,
+                  min(kMmaPieceSb, ns - pc * kMmaPieceSb), lane, nxt);
+    }
     cp_async_commit();
-    cp_async_wait<1>();  // everything but the copy just issued has landed: unit u is complete
+    cp_async_wait<1>();  // everything but the copy just issued has landed: this trip's piece is complete
     __syncwarp();
-    const MmaUnit m = unit_of(a, u);
+    const int piece = it % n_pieces, sbo = piece * kMmaPieceSb, np = min(kMmaPieceSb, ns - sbo);
+    const MmaUnit m = unit_of(a, first + (it / n_pieces) * stride);
     const MmaJob &J = a.job[m.j];
-    float acc[NT][4];
+    if (piece == 0) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
+        for (int k = 0; k < 4; ++k) acc[nt][k] = 0.0f;
+    }
     // rows beyond the matrix were not copied: their slots hold stale bytes; the integer and f32 work on
     // them is harmless and their results are not written
     if (J.qt == CMLD_Q4_K) {
-      tile_q4k<NT>(cur, 0, ns, lane, codes, xscale, bs32_hi, bs32_lo, acc);
+      tile_q4k<NT>(cur, sbo, np, lane, codes, xscale, bs32_hi, bs32_lo, acc);
     } else if (J.qt == CMLD_Q6_K) {
-      float d_lo[kMmaChunkSb], d_hi[kMmaChunkSb];
+      float d_lo[kMmaPieceSb], d_hi[kMmaPieceSb];
       const int r_lo = min(m.row0 + g8, J.rows - 1), r_hi = min(m.row0 + g8 + 8, J.rows - 1);
 #pragma unroll
-      for (int sb = 0; sb < kMmaChunkSb; ++sb) {
-        const int sbc = min(sb, ns - 1);
-        d_lo[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_lo * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
-        d_hi[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (int64_t)r_hi * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
+      for (int sb = 0; sb < kMmaPieceSb; ++sb) {
+        const int sbc = min(sbo + sb, ns - 1);
+        d_lo[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (e_local * J.rows + r_lo) * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
+        d_hi[sb] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(J.w + (e_local * J.rows + r_hi) * J.stride + (int64_t)nsb * 208) + sb0 + sbc));
       }
-      tile_q6k<NT>(cur, 0, ns, lane, codes, xscale, bs16_hi, bs16_lo, d_lo, d_hi, acc);
+      tile_q6k<NT>(cur, sbo, np, lane, codes, xscale, bs16_hi, bs16_lo, d_lo, d_hi, acc);
     } else {
-      tile_q80<NT>(cur, 0, ns, lane, codes, xscale, acc);
+      tile_q80<NT>(cur, sbo, np, lane, codes, xscale, acc);
     }
     __syncwarp();  // every lane is done with `cur` before the next trip's copy overwrites it
+    if (piece + 1 < n_pieces) continue;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int col = nt * 8 + t4 * 2 + (k & 1), r = g8 + (k >= 2 ? 8 : 0);
-        if (col < a.batch && r < m.nrows) {
+        if (col < batch && r < m.nrows) {
           if (a.n_chunks == 1) {
-            const int64_t o = (int64_t)col * J.y_stride + m.row0 + r;
+            const int64_t o = (y_base + col) * J.y_stride + m.row0 + r;
             J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), acc[nt][k]) : acc[nt][k];
           } else {
-            a.partial[((int64_t)chunk * a.batch + col) * a.rows_cat + J.row_off + m.row0 + r] = acc[nt][k];
+            partial[((int64_t)chunk * pb + col) * a.rows_cat + J.row_off + m.row0 + r] = acc[nt][k];
           }
         }
       }
@@ -387,26 +426,38 @@ __global__ void __launch_bounds__(kMmaMaxThreads, 1) gemv_mma_kernel(const MmaAr
 }
 
 // y = residual + sum over chunks (in chunk order) of the partial sums.
-__global__ void mma_reduce_kernel(const MmaArgs a) {
+__global__ void mma_reduce_kernel(const MmaArgs a, int nb) {
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int64_t total = (int64_t)a.batch * a.rows_cat;
+  int batch = a.batch, pb = a.batch;
+  int64_t y_base = 0;
+  const float *partial = a.partial;
+  if (a.counts) {
+    const int64_t e_local = blockIdx.y;
+    const int col0 = (int)blockIdx.z * nb;
+    batch = min(nb, a.count_mul * __ldcg(a.counts + a.first_expert + (int)e_local * a.expert_step) - col0);
+    if (batch <= 0) return;
+    pb = nb;
+    y_base = e_local * a.cap + col0;
+    partial += (e_local * gridDim.z + blockIdx.z) * (int64_t)a.n_chunks * nb * a.rows_cat;
+  }
+  const int64_t total = (int64_t)batch * a.rows_cat;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int col = (int)(i / a.rows_cat), rc = (int)(i % a.rows_cat);
     int j = 0;
     if (a.n_jobs > 1 && rc >= a.job[1].row_off) j = 1;
     if (a.n_jobs > 2 && rc >= a.job[2].row_off) j = 2;
     const MmaJob &J = a.job[j];
-    const int64_t o = (int64_t)col * J.y_stride + (rc - J.row_off);
-    float v = __ldcg(a.partial + (int64_t)col * a.rows_cat + rc);
-    for (int c = 1; c < a.n_chunks; ++c) v = __fadd_rn(v, __ldcg(a.partial + ((int64_t)c * a.batch + col) * a.rows_cat + rc));
+    const int64_t o = (y_base + col) * J.y_stride + (rc - J.row_off);
+    float v = __ldcg(partial + (int64_t)col * a.rows_cat + rc);
+    for (int c = 1; c < a.n_chunks; ++c) v = __fadd_rn(v, __ldcg(partial + ((int64_t)c * pb + col) * a.rows_cat + rc));
     J.y[o] = J.residual ? __fadd_rn(__ldcg(J.residual + o), v) : v;
   }
 }
 
 struct MmaPlan {
   MmaArgs args;
-  int smem_bytes, grid;
+  int smem_bytes, grid, grid_y = 1, grid_z = 1;
 };
 
 int g_mma_sms = 0;
@@ -477,7 +528,7 @@ int32_t launch_nt(const MmaPlan &p, cudaStream_t s, bool pdl) {
     g_mma_attr[NT] = true;
   }
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)p.grid);
+  cfg.gridDim = dim3((unsigned)p.grid, (unsigned)p.grid_y, (unsigned)p.grid_z);
   cfg.blockDim = dim3((unsigned)(p.args.n_warps * 32));
   cfg.dynamicSmemBytes = (size_t)p.smem_bytes;
   cfg.stream = s;
@@ -487,6 +538,21 @@ int32_t launch_nt(const MmaPlan &p, cudaStream_t s, bool pdl) {
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   CMLD_CUDA(cudaLaunchKernelEx(&cfg, gemv_mma_kernel<NT>, p.args));
+  return CMLD_OK;
+}
+
+int32_t launch_reduce(const MmaPlan &p, int nb, cudaStream_t s, bool pdl) {
+  cudaLaunchConfig_t cfg{};
+  const int64_t total = (int64_t)std::min(nb, p.args.counts ? nb : p.args.batch) * p.args.rows_cat;
+  cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, p.args.counts ? 64 : 4 * 148), (unsigned)p.grid_y, (unsigned)p.grid_z);
+  cfg.blockDim = dim3(256);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CMLD_CUDA(cudaLaunchKernelEx(&cfg, mma_reduce_kernel, p.args, nb));
   return CMLD_OK;
 }
 
@@ -531,17 +597,54 @@ int32_t launch_gemv_mma(const GemvJob *jobs, int n_jobs, const uint8_t *act, int
   CMLD_TRY(rc);
   if (launches) *launches += 1;
   if (p.args.n_chunks > 1) {
-    cudaLaunchConfig_t cfg{};
-    const int64_t total = (int64_t)batch * p.args.rows_cat;
-    cfg.gridDim = dim3((unsigned)std::min<int64_t>((total + 255) / 256, 4 * 148));
-    cfg.blockDim = dim3(256);
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    CMLD_CUDA(cudaLaunchKernelEx(&cfg, mma_reduce_kernel, p.args));
+    CMLD_TRY(launch_reduce(p, nt * 8, s, pdl));
+    if (launches) *launches += 1;
+  }
+  return CMLD_OK;
+}
+
+// Expert form: `jobs` describe ONE expert's matrices (rows per expert; the slabs hold n_experts of them one
+// after the other), `act` holds `cap` activation rows per local expert of which count_mul * counts[e] are
+// real, y receives `cap` result rows per local expert.  nt column tiles (8 rows each) per pass, n_pass passes
+// (those beyond an expert's rows exit at once).  scratch: gemv_mma_expert_scratch_floats.
+int64_t gemv_mma_expert_scratch_floats(const GemvJob *jobs, int n_jobs, int nt, int n_experts, int n_pass) {
+  const int64_t one = gemv_mma_scratch_floats(jobs, n_jobs, nt * 8);
+  return one < 0 ? -1 : one * n_experts * n_pass;
+}
+
+int32_t launch_gemv_mma_experts(const GemvJob *jobs, int n_jobs, const uint8_t *act, int nt, int n_experts, int n_pass,
+                                const int32_t *counts, int first_expert, int expert_step, int cap, int count_mul, float *scratch,
+                                int64_t scratch_floats, int32_t *status, cudaStream_t s, bool pdl, int64_t *launches) {
+  const int64_t need = gemv_mma_expert_scratch_floats(jobs, n_jobs, nt, n_experts, n_pass);
+  if (need < 0 || need > scratch_floats || (need > 0 && !scratch)) return CMLD_ERR_UNSUPPORTED;
+  if (!act || !counts || nt < 1 || nt > 4) return fail(CMLD_ERR_INVALID, "expert matvec: bad arguments");
+  MmaPlan p{};
+  plan_mma(jobs, n_jobs, nt * 8, p);
+  MmaArgs &a = p.args;
+  a.act = act;
+  a.partial = scratch;
+  a.status = status;
+  a.counts = counts;
+  a.first_expert = first_expert;
+  a.expert_step = expert_step;
+  a.cap = cap;
+  a.count_mul = count_mul;
+  // all experts stream at once: share the SMs between them
+  a.ctas_per_chunk = std::max(1, std::min((a.total_tiles + a.n_warps - 1) / a.n_warps, g_mma_sms / (a.n_chunks * std::max(1, n_experts))));
+  p.grid = a.n_chunks * a.ctas_per_chunk;
+  p.grid_y = n_experts;
+  p.grid_z = n_pass;
+  int32_t rc;
+  switch (nt) {
+    case 1: rc = launch_nt<1>(p, s, pdl); break;
+    case 2: rc = launch_nt<2>(p, s, pdl); break;
+    case 3: rc = launch_nt<3>(p, s, pdl); break;
+    default: rc = launch_nt<4>(p, s, pdl); break;
+  }
+  CMLD_TRY(rc);
+  if (launches) *launches += 1;
+  if (a.n_chunks > 1) {
+    CMLD_TRY(launch_reduce(p, nt * 8, s, pdl));
     if (launches) *launches += 1;
   }
   return CMLD_OK;

@@ -522,31 +522,12 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
     }
     const int n_chunks = (a.cols + 255) >> 8;
-    // this warp's chunks: all their loads first (independent, in flight together), then the arithmetic
-    constexpr int kPre = 4;
-    float4 pre_a[kPre], pre_b[kPre];
-#pragma unroll
-    for (int k = 0; k < kPre; ++k) {
-      const int e0 = (warp + k * kPipeAllWarps) * 256 + lane * 8;
-      if (e0 + 8 <= a.cols) {
-        pre_a[k] = __ldcg(reinterpret_cast<const float4 *>(x + e0));
-        pre_b[k] = __ldcg(reinterpret_cast<const float4 *>(x + e0) + 1);
-      }
-    }
-    int kk = 0;
-    for (int ch = warp; ch < n_chunks; ch += kPipeAllWarps, ++kk) {
+    for (int ch = warp; ch < n_chunks; ch += kPipeAllWarps) {
       const int e0 = ch * 256 + lane * 8;
       float v[8];
       if (e0 + 8 <= a.cols) {
         // 8 consecutive values per lane: two 128-bit loads per operand (cols is a multiple of 32)
-        float4 xa, xb;
-        if (kk < kPre) {
-          xa = kk == 0 ? pre_a[0] : (kk == 1 ? pre_a[1] : (kk == 2 ? pre_a[2] : pre_a[3]));
-          xb = kk == 0 ? pre_b[0] : (kk == 1 ? pre_b[1] : (kk == 2 ? pre_b[2] : pre_b[3]));
-        } else {
-          xa = __ldcg(reinterpret_cast<const float4 *>(x + e0));
-          xb = __ldcg(reinterpret_cast<const float4 *>(x + e0) + 1);
-        }
+        const float4 xa = __ldcg(reinterpret_cast<const float4 *>(x + e0)), xb = __ldcg(reinterpret_cast<const float4 *>(x + e0) + 1);
         const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
         if (a.mode == 1) {
           const float4 wa = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0)), wb = __ldg(reinterpret_cast<const float4 *>(a.norm_w + e0) + 1);

@@ -14,8 +14,7 @@
 #include <string>
 #include <vector>
 
-#include "common.cuh"
-#include "expf_exact.cuh"
+#include "actquant.cuh"
 
 namespace cmld {
 
@@ -88,13 +87,109 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
 
 // Bucket the batch*k assignments by expert, in ascending assignment order.
 __global__ void moe_group_kernel(const int32_t *__restrict__ sel_idx, int n_assign, int n_exp, int32_t *__restrict__ counts,
-                                 int32_t *__restrict__ lists) {
+                                 int32_t *__restrict__ lists, int32_t *__restrict__ pos) {
   const int e = threadIdx.x;
   if (e >= n_exp) return;
   int n = 0;
   for (int a = 0; a < n_assign; ++a)
-    if (sel_idx[a] == e) lists[e * n_assign + n++] = a;
+    if (sel_idx[a] == e) {
+      if (pos) pos[a] = n;  // where assignment a sits in its expert's list
+      lists[e * n_assign + n++] = a;
+    }
   counts[e] = n;
+}
+
+// ------------------------------------------------------------------ expert matvecs on the tensor cores
+//
+// The reference multiplies the experts' dequantised weights with the UNQUANTISED f32 activation.  To keep that
+// precision on the int8 tensor-core kernel, an activation vector x is written as the sum of three Q8_K vectors:
+// x1 = Q8_K(x), x2 = Q8_K(x - x1), x3 = Q8_K(x - x1 - x2).  Every stage shrinks the remainder by about 1/254,
+// so what is left after three is below 1e-7 of the block's largest value: the size of an f32 rounding error of the
+// dot product itself.  The matvec runs over the three rows as if they were three tokens (exact integer dots, one
+// f32 scale step per superblock) and the three results are added.  Rows of expert e (local index) live at
+// [e*cap + 3*j + p] for the j-th assignment of its list, in the standard quantised-activation row layout.
+
+struct Quant3Args {
+  const float *x;        // source rows (mode 0: [token][cols]; mode 1: g3 / u3 result rows, 3 per assignment)
+  const float *x2;       // mode 1: the "up" result rows
+  int32_t mode;          // 0: x[token]; 1: SwiGLU(sum of 3 gate rows, sum of 3 up rows)
+  int32_t cols, k, n_assign, first_expert, expert_step, cap;
+  const int32_t *counts, *lists;
+  uint8_t *act;          // [local expert][cap] rows of act_row_stride(cols) bytes
+};
+
+__global__ void __launch_bounds__(256) moe_quant3_kernel(const Quant3Args a) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int j = blockIdx.x, e_local = blockIdx.y, e = a.first_expert + e_local * a.expert_step;
+  if (j >= a.counts[e]) return;
+  const int asg = a.lists[e * a.n_assign + j];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t astride = act_row_stride(a.cols);
+  const int64_t row0 = (int64_t)e_local * a.cap + 3 * j;
+  const int n_chunks = a.cols >> 8;
+  for (int ch = blockIdx.z * 8 + warp; ch < n_chunks; ch += 8 * gridDim.z) {
+    const int e0 = ch * 256 + lane * 8;
+    float v[8];
+    if (a.mode == 0) {
+      const float *src = a.x + (int64_t)(asg / a.k) * a.cols + e0;
+      const float4 p = __ldcg(reinterpret_cast<const float4 *>(src)), q = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
+      v[0] = p.x, v[1] = p.y, v[2] = p.z, v[3] = p.w, v[4] = q.x, v[5] = q.y, v[6] = q.z, v[7] = q.w;
+    } else {
+      float g[8], u[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g[i] = u[i] = 0.0f;
+#pragma unroll
+      for (int p3 = 0; p3 < 3; ++p3) {  // the three partial results, added in order
+        const float *gs = a.x + (row0 + p3) * a.cols + e0, *us = a.x2 + (row0 + p3) * a.cols + e0;
+        const float4 g0 = __ldcg(reinterpret_cast<const float4 *>(gs)), g1 = __ldcg(reinterpret_cast<const float4 *>(gs) + 1);
+        const float4 u0 = __ldcg(reinterpret_cast<const float4 *>(us)), u1 = __ldcg(reinterpret_cast<const float4 *>(us) + 1);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          g[i] = __fadd_rn(g[i], gv[i]);
+          u[i] = __fadd_rn(u[i], uv[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = swiglu(g[i], u[i]);
+    }
+#pragma unroll
+    for (int p3 = 0; p3 < 3; ++p3) {
+      int q[8];
+      float d;
+      q8k_quantise_chunk(v, lane, q, d);
+      uint8_t *row = a.act + (row0 + p3) * astride;
+      *reinterpret_cast<uint2 *>(row + e0) = pack8(q);
+      int s16 = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
+      s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+      if ((lane & 1) == 0) reinterpret_cast<short *>(row + act_bsum_off(a.cols))[ch * 16 + (lane >> 1)] = (short)s16;
+      if (lane == 0) reinterpret_cast<float *>(row + act_scale_off(a.cols))[ch] = d;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __fsub_rn(v[i], __fmul_rn(d, (float)q[i]));  // what this stage did not capture
+    }
+  }
+}
+
+// h[b] (+)= sum_s w[b][s] * (sum of the three result rows of assignment (b, s)), in selection order from zero.
+__global__ void moe_combine3_kernel(float *__restrict__ h, const float *__restrict__ y3, const float *__restrict__ sel_w,
+                                    const int32_t *__restrict__ sel_idx, const int32_t *__restrict__ pos, int hidden, int k,
+                                    int first_expert, int expert_step, int cap, int add_residual) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int b = blockIdx.y;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < hidden; c += gridDim.x * blockDim.x) {
+    float out = 0.0f;
+    for (int s = 0; s < k; ++s) {
+      const int e = sel_idx[b * k + s];
+      if ((e - first_expert) % expert_step != 0 || e < first_expert) continue;  // expert held by another rank
+      const int64_t row = (int64_t)((e - first_expert) / expert_step) * cap + 3 * pos[b * k + s];
+      const float *y = y3 + row * hidden + c;
+      const float v = __fadd_rn(__fadd_rn(__ldcg(y), __ldcg(y + hidden)), __ldcg(y + 2 * hidden));
+      out = __fadd_rn(out, __fmul_rn(v, sel_w[b * k + s]));
+    }
+    h[(int64_t)b * hidden + c] = add_residual ? __fadd_rn(h[(int64_t)b * hidden + c], out) : out;
+  }
 }
 
 // float(code) of byte `sel` of w without an int->float conversion: place the byte in the
@@ -293,11 +388,11 @@ using namespace cmld;
 namespace cmld {
 
 int32_t moe_route(const float *normed, const float *router, int hidden, int n_exp, int k, int batch, int32_t *sel_idx,
-                  float *sel_w, int32_t *counts, int32_t *lists, cudaStream_t s) {
+                  float *sel_w, int32_t *counts, int32_t *lists, cudaStream_t s, int32_t *pos) {
   if (n_exp > kMaxExperts) return fail(CMLD_ERR_SHAPE, "more than %d experts", kMaxExperts);
   moe_route_kernel<<<batch, 256, 0, s>>>(normed, router, hidden, n_exp, k, sel_idx, sel_w);
   CMLD_CUDA(cudaGetLastError());
-  moe_group_kernel<<<1, kMaxExperts, 0, s>>>(sel_idx, batch * k, n_exp, counts, lists);
+  moe_group_kernel<<<1, kMaxExperts, 0, s>>>(sel_idx, batch * k, n_exp, counts, lists, pos);
   CMLD_CUDA(cudaGetLastError());
   return CMLD_OK;
 }
@@ -319,6 +414,27 @@ int32_t moe_combine(float *h, const float *down, const float *sel_w, const int32
                     int first_expert, int expert_step, bool add_residual, cudaStream_t s) {
   dim3 grid((unsigned)((hidden + 255) / 256), (unsigned)batch);
   moe_combine_kernel<<<grid, 256, 0, s>>>(h, down, sel_w, sel_idx, hidden, k, first_expert, expert_step, add_residual ? 1 : 0);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+// Three-stage Q8_K rows of the experts' operands.  mode 0: from the token rows x[token][cols]; mode 1: from the
+// gate/up result rows (SwiGLU of their sums).
+int32_t moe_quant3(const float *x, const float *x2, int mode, int cols, int k, int n_assign, int n_local, int first_expert,
+                   int expert_step, int cap, const int32_t *counts, const int32_t *lists, uint8_t *act, cudaStream_t s) {
+  if (cols % 256) return fail(CMLD_ERR_SHAPE, "expert operand width %d is not a multiple of 256", cols);
+  Quant3Args a{x, x2, mode, cols, k, n_assign, first_expert, expert_step, cap, counts, lists, act};
+  const int z = std::max(1, std::min(8, (cols >> 8) / 8));  // CTAs that share one row's chunks
+  moe_quant3_kernel<<<dim3((unsigned)n_assign, (unsigned)n_local, (unsigned)z), 256, 0, s>>>(a);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+int32_t moe_combine3(float *h, const float *y3, const float *sel_w, const int32_t *sel_idx, const int32_t *pos, int hidden, int k,
+                     int batch, int first_expert, int expert_step, int cap, bool add_residual, cudaStream_t s) {
+  dim3 grid((unsigned)((hidden + 255) / 256), (unsigned)batch);
+  moe_combine3_kernel<<<grid, 256, 0, s>>>(h, y3, sel_w, sel_idx, pos, hidden, k, first_expert, std::max(1, expert_step), cap,
+                                           add_residual ? 1 : 0);
   CMLD_CUDA(cudaGetLastError());
   return CMLD_OK;
 }
