@@ -7,6 +7,8 @@
 // query heads of its kv head so each K/V row is read once, keeps a running (max, sum, acc)
 // per head, and the CTA that finishes last merges the ranges.  The result agrees with the
 // CPU's sequential sums up to f32 reassociation.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "expf_exact.cuh"
 
@@ -15,6 +17,7 @@ namespace cmld {
 constexpr int kAttnThreads = 256;
 constexpr int kAttnWarps = kAttnThreads / 32;
 constexpr int kAttnMaxSplits = 64;  // ranges per (sequence, kv head)
+constexpr int kAttnCluster = 8;     // CTAs of a cluster (one per range) in the cluster form
 constexpr int kMaxGroup = 8;     // query heads per kv head
 constexpr int kMaxPer = 8;       // head_dim / 32
 
@@ -71,7 +74,10 @@ __device__ __forceinline__ float rope_elem(const float *x, int d, int rope_dim, 
   return first ? __fsub_rn(__fmul_rn(x[d], c), __fmul_rn(x[partner], sn)) : __fadd_rn(__fmul_rn(x[partner], sn), __fmul_rn(x[d], c));
 }
 
-template <int G, int PER>
+// CL = false: ranges through global memory, the CTA that finishes last merges them (any context length).
+// CL = true: the kAttnCluster ranges of one (sequence, kv head) are the CTAs of one thread-block cluster and are
+// merged through distributed shared memory: no partials in global memory, no fence, no ticket.
+template <int G, int PER, bool CL>
 __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -82,11 +88,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
   const int pos = a.positions[b];
   const int n_pos = pos + 1;
   const int slot = a.slots[b];
-  // ranges of at least kMinSplitLen positions; CTAs beyond the last range have nothing to do
-  const int len = max((n_pos + a.n_splits - 1) / a.n_splits, kMinSplitLen);
-  const int n_active = (n_pos + len - 1) / len;
-  if (split >= n_active || pos < 0 || pos >= a.max_pos) return;
+  // ranges of at least kMinSplitLen positions; CTAs beyond the last range have nothing to do.  In the cluster
+  // form every CTA stays (an empty range contributes weight zero): all of them meet at the cluster barriers.
+  const int len = CL ? (n_pos + kAttnCluster - 1) / kAttnCluster : max((n_pos + a.n_splits - 1) / a.n_splits, kMinSplitLen);
+  const int n_active = CL ? kAttnCluster : (n_pos + len - 1) / len;
+  if (pos < 0 || pos >= a.max_pos) return;  // the same for every CTA of a cluster
+  if (!CL && split >= n_active) return;
   const int lo = split * len, hi = min(n_pos, lo + len);
+  const bool owns_pos = CL ? (pos / len == split) : (split == n_active - 1);
 
   // A cache row is HD f16 = LPP 16-byte pieces: LPP lanes share one position, a warp covers PPW positions
   // at a time, and the CTA's NGRP lane groups stride through the range.  Each group keeps its own
@@ -109,8 +118,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     const float *ct = a.cos_tab + (int64_t)(a.index_by_position ? pos : b) * half;
     const float *st = a.sin_tab + (int64_t)(a.index_by_position ? pos : b) * half;
     for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) s_q[i / HD][i % HD] = rope_elem(q + (i / HD) * HD, i % HD, a.rope_dim, a.split_half, ct, st);
-    if (split == n_active - 1) {
-      // this CTA's range ends at the row's own position: append K (rotated) and V to the cache first
+    if (owns_pos) {
+      // this CTA's range holds the row's own position: append K (rotated) and V to the cache first
       const float *kn = a.k_new + (int64_t)b * a.kv_stride + (int64_t)kvh * HD;
       const float *vn = a.v_new + (int64_t)b * a.kv_stride + (int64_t)kvh * HD;
       for (int d = threadIdx.x; d < HD; d += kAttnThreads) {
@@ -237,6 +246,46 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     s_l[0][g] = L;  // the range's sum, read below as s_l[0][g] (warp 0's own value is folded in already)
   }
   __syncthreads();
+  if constexpr (CL) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    // this range's accumulator (the query copy is no longer needed: every lane holds its part in registers)
+    for (int i = threadIdx.x; i < G * HD; i += kAttnThreads) {
+      const int g = i / HD, d = i % HD;
+      float sacc = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) sacc = __fmaf_rn(s_acc[w][g][d], s_wgt[w][g], sacc);
+      s_q[g][d] = sacc;
+    }
+    cluster.sync();
+    // every CTA merges its share of the outputs, reading the eight ranges' (max, sum, accumulator) from the
+    // cluster's shared memory
+    constexpr int OPC = G * HD / kAttnCluster;
+    float *out = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
+    for (int o = threadIdx.x; o < OPC; o += kAttnThreads) {
+      const int i = split * OPC + o, g = i / HD;
+      float Mr[kAttnCluster], Lr[kAttnCluster], Ar[kAttnCluster];
+#pragma unroll
+      for (int r = 0; r < kAttnCluster; ++r) {
+        Mr[r] = cluster.map_shared_rank(&s_M[0], r)[g];
+        Lr[r] = cluster.map_shared_rank(&s_l[0][0], r)[g];
+        Ar[r] = cluster.map_shared_rank(&s_q[0][0], r)[i];
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < kAttnCluster; ++r) M = fmaxf(M, Mr[r]);
+      float L = 0.0f, acc_o = 0.0f;
+#pragma unroll
+      for (int r = 0; r < kAttnCluster; ++r) {
+        const float w = Mr[r] == -INFINITY ? 0.0f : __expf(Mr[r] - M);
+        L = __fmaf_rn(Lr[r], w, L);
+        acc_o = __fmaf_rn(Ar[r], w, acc_o);
+      }
+      out[i] = __fdiv_rn(acc_o, L);
+    }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
+    return;
+  }
   if (n_active == 1) {
     // a single range: normalise in place, no partials through global memory and no ticket
     float *out1 = a.out + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
@@ -306,20 +355,33 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
 template <int G, int PER>
 static int32_t launch_gp(const AttnArgs &a, cudaStream_t s) {
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)a.n_kv_heads, (unsigned)a.n_splits, (unsigned)a.batch);
+  cfg.gridDim = dim3((unsigned)a.n_kv_heads, (unsigned)(a.cluster ? kAttnCluster : a.n_splits), (unsigned)a.batch);
   cfg.blockDim = dim3(kAttnThreads);
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (a.pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  if (a.cluster) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = kAttnCluster;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = a.pdl ? 1 : 0;
+  cfg.numAttrs = n_attr;
   static bool carveout_set = false;
   if (!carveout_set) {
-    prefer_max_smem_carveout(attn_decode_kernel<G, PER>);
+    prefer_max_smem_carveout(attn_decode_kernel<G, PER, false>);
+    prefer_max_smem_carveout(attn_decode_kernel<G, PER, true>);
     carveout_set = true;
   }
-  CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, PER>, a));
+  if (a.cluster) CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, PER, true>, a));
+  else CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_decode_kernel<G, PER, false>, a));
   return CMLD_OK;
 }
 

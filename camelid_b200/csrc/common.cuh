@@ -309,6 +309,7 @@ struct AttnArgs {
   int64_t kv_stride;
   const float *cos_tab, *sin_tab;  // [rows][rope_dim/2]
   int32_t pdl;                     // launch with programmatic stream serialisation
+  int32_t cluster;                 // ranges as the CTAs of a thread-block cluster, merged through distributed shared memory
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
 

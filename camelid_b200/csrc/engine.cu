@@ -577,6 +577,7 @@ struct StepOpts {
   bool feed_back = false;  // argmax writes next token / position / history
   bool taps = false;
   int32_t layer_begin = 0, layer_end = -1;  // layers to run; -1 = through the last
+  bool attn_cluster = false;  // short contexts, few rows: attention ranges as a thread-block cluster (host-side choice)
   bool shared_slots = false;  // several rows of this step belong to one sequence (prefill, verify): row b
                               // reads K/V that rows < b write, so the KV append must be a kernel of its own
 };
@@ -817,6 +818,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
       a.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
       a.pdl = !(c.flags & CMLD_FLAG_NO_PDL);
+      a.cluster = o.attn_cluster && !exact ? 1 : 0;
       if (exact) CMLD_TRY(launch_attention_exact(a, e->stream));
       else CMLD_TRY(launch_attention(a, e->stream));
       e->launches += 1;
@@ -900,7 +902,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
 static int32_t run_step(cmld_engine *e, const StepOpts &o) {
   if ((e->cfg.flags & CMLD_FLAG_NO_GRAPH) || e->graphs_off) return engine_step(e, o);
   uint32_t bits = (o.from_tokens ? 1u : 0u) | (o.rope_by_position ? 2u : 0u) | (o.logits ? 4u : 0u) | (o.argmax ? 8u : 0u) |
-                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u) | ((uint32_t)(o.layer_begin & 0xfff) << 8) | ((uint32_t)((o.layer_end + 1) & 0xfff) << 20);
+                  (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u) | (o.attn_cluster ? 128u : 0u) | ((uint32_t)(o.layer_begin & 0xfff) << 8) | ((uint32_t)((o.layer_end + 1) & 0xfff) << 20);
   uint32_t scale_bits;
   memcpy(&scale_bits, &o.scale, 4);
   auto &g = e->graphs[std::make_tuple(o.batch, bits, scale_bits)];
@@ -946,6 +948,12 @@ static int32_t require_weights(const cmld_engine *e, bool need_output) {
   if (need_output && !e->has_output) return fail(CMLD_ERR_STATE, "output weights not set");
   return CMLD_OK;
 }
+
+// Attention ranges as a thread-block cluster: worth it while a range (1/8 of the context) is short and the rows
+// are few; beyond that the 37-way split through global memory, or no split at all for many rows, is better.
+// The rule does not depend on the row count up to 8 rows, so that a step of <= 8 rows keeps giving the bits of
+// the same rows stepped one by one (as long as all of them are on one side of the context threshold).
+static bool use_attn_cluster(int32_t rows, int64_t max_position) { return rows <= 8 && max_position < 2048; }
 
 // Rows of one step: tokens (or none), positions and KV slots to the device.
 static int32_t stage_rows(cmld_engine *e, int32_t n, const int32_t *tokens, const int32_t *positions, const int32_t *slots) {
@@ -1016,6 +1024,7 @@ static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, c
   o.taps = taps;
   o.layer_begin = layer_begin;
   o.layer_end = layer_end;
+  o.attn_cluster = use_attn_cluster(n_rows, position0 + n_rows - 1);
   return run_step(e, o);
 }
 
@@ -1596,6 +1605,11 @@ int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *se
   o.shared_slots = has_shared_slots(seqs, n_seqs);
   o.from_tokens = true;
   o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
+  {
+    int64_t mx = 0;
+    for (int i = 0; i < n_seqs; ++i) mx = std::max<int64_t>(mx, positions[i]);
+    o.attn_cluster = use_attn_cluster(n_seqs, mx);
+  }
   CMLD_TRY(run_step(e, o));
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> toks(n_seqs);
@@ -1666,7 +1680,12 @@ int32_t cmld_engine_decode_greedy(cmld_engine *e, int32_t n_seqs, const int32_t 
   o.from_tokens = true;
   o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
   o.feed_back = true;
-  for (int s = 0; s < n_steps; ++s) CMLD_TRY(run_step(e, o));
+  int64_t max_start = 0;
+  for (int i = 0; i < n_seqs; ++i) max_start = std::max<int64_t>(max_start, positions[i]);
+  for (int s = 0; s < n_steps; ++s) {
+    o.attn_cluster = use_attn_cluster(n_seqs, max_start + s);
+    CMLD_TRY(run_step(e, o));
+  }
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
   std::vector<int32_t> hist((size_t)n_steps * n_seqs);
   CMLD_TRY(settle(e));
