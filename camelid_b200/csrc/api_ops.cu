@@ -437,6 +437,7 @@ int32_t cmld_attention_decode(const float *q_dev, const void *k_cache_dev, const
   a.tickets = reinterpret_cast<uint32_t *>(scratch + part_bytes);
   a.out = out_dev;
   a.q_stride = (int64_t)n_heads * head_dim;
+  a.cluster = n_pos <= 2048 ? 1 : 0;  // the engine's rule: short contexts merge their ranges inside a cluster
   int32_t rc = launch_attention(a, nullptr);
   if (rc == CMLD_OK) rc = sync_ok("attention_decode");
   cudaFree(scratch);

@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_kernel(AttnArgs a) {
     const int g = i / HD, d = i % HD;
     const float *pg = part + (int64_t)g * a.n_splits * (HD + 2);
     float L = 0.0f, o = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
     for (int s2 = 0; s2 < n_active; ++s2) {
       const float w = s_w[g][s2];
       L = __fmaf_rn(__ldcg(pg + (int64_t)s2 * (HD + 2) + HD + 1), w, L);
@@ -487,6 +487,7 @@ extern "C" int32_t cmld_attention_decode_noalloc(const float *q_dev, const void 
   a.tickets = reinterpret_cast<uint32_t *>(scratch + kNoAllocTicketOff);
   a.out = out_dev;
   a.q_stride = (int64_t)n_heads * head_dim;
+  a.cluster = n_pos <= 2048 ? 1 : 0;  // as cmld_attention_decode
   CMLD_TRY(launch_attention(a, nullptr));
   cudaError_t ce = cudaStreamSynchronize(nullptr);
   if (ce != cudaSuccess) return fail(CMLD_ERR_CUDA, "attention_decode_noalloc: %s", cudaGetErrorString(ce));

@@ -273,12 +273,15 @@ def test_argmax_lowest_index_wins(cm, orc):
 
 # attention_decode_matches_cpu (src/cuda_resident/tests.rs:5066) with GQA and split ranges.
 @pytest.mark.parametrize("n_heads,n_kv,hd,n_pos", [(2, 1, 32, 1), (2, 1, 32, 4), (32, 8, 64, 33), (24, 8, 128, 300),
-                                                    (32, 8, 128, 1153), (8, 8, 128, 70), (8, 1, 64, 515)])
+                                                    (32, 8, 128, 1153), (8, 8, 128, 70), (8, 1, 64, 515),
+                                                    (32, 8, 128, 2048), (32, 8, 128, 2049), (16, 4, 64, 3000)])
 def test_attention_matches_checker(cm, orc, n_heads, n_kv, hd, n_pos):
+    """Up to 2048 positions the ranges are merged inside a thread-block cluster; beyond that through global
+    memory by the CTA that finishes last: both forms are covered."""
     from camelid_b200.engine import DeviceBuffer
     from camelid_b200._lib import check
 
-    max_pos = 2048
+    max_pos = 2048 if n_pos <= 2048 else 4096
     rng = np.random.default_rng(n_heads * n_pos)
     q = rng.standard_normal((n_heads, hd)).astype(np.float32)
     k = np.zeros((n_kv, max_pos, hd), np.float16)
