@@ -637,7 +637,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
         *a.peer.tx_ticket = 0;
         const uint32_t epoch = *a.peer.tx_epoch + 1;
         *a.peer.tx_epoch = epoch;
-        for (int p = 0; p < a.peer.tx_n; ++p) st_release_sys(a.peer.tx_flag[p], epoch);
+        // one fence (above) orders every row before every arrival word; the words themselves go out as plain
+        // stores (a release store per rank would wait for the previous rank's round trip each time: ~3 us x ranks)
+        for (int p = 0; p < a.peer.tx_n; ++p) st_relaxed_sys(a.peer.tx_flag[p], epoch);
       }
       if (tr) tr[5] = global_ns();
     }
