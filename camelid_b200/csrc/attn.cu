@@ -5,8 +5,11 @@
 // sum_p prob_p * V_p.  Here the positions of one (sequence, kv head) are cut into n_splits
 // ranges handled by separate CTAs (flash-decoding): every CTA serves all n_heads/n_kv_heads
 // query heads of its kv head so each K/V row is read once, keeps a running (max, sum, acc)
-// per head, and the CTA that finishes last merges the ranges.  The result agrees with the
-// CPU's sequential sums up to f32 reassociation.
+// per head.  The ranges are merged either inside a thread-block cluster through distributed shared
+// memory (short contexts: eight ranges, one cluster per (sequence, kv head)) or through global memory
+// by the CTA that finishes last (any context length).  The result agrees with the CPU's sequential
+// sums up to f32 reassociation; the softmax exponentials are __expf (the reference-order kernel in
+// exact.cu uses the bit-exact expf).
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -20,26 +23,6 @@ constexpr int kAttnMaxSplits = 64;  // ranges per (sequence, kv head)
 constexpr int kAttnCluster = 8;     // CTAs of a cluster (one per range) in the cluster form
 constexpr int kMaxGroup = 8;     // query heads per kv head
 constexpr int kMaxPer = 8;       // head_dim / 32
-
-// PER consecutive f16 values of a cache row, widened to f32 (one 2/4/8-byte load).
-template <int PER>
-__device__ __forceinline__ void load_halves(const __half *p, float (&out)[PER]) {
-  if constexpr (PER == 4) {
-    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-    const __half2 h0 = *reinterpret_cast<const __half2 *>(&raw.x), h1 = *reinterpret_cast<const __half2 *>(&raw.y);
-    out[0] = __low2float(h0);
-    out[1] = __high2float(h0);
-    out[2] = __low2float(h1);
-    out[3] = __high2float(h1);
-  } else if constexpr (PER == 2) {
-    const __half2 h0 = *reinterpret_cast<const __half2 *>(p);
-    out[0] = __low2float(h0);
-    out[1] = __high2float(h0);
-  } else {
-#pragma unroll
-    for (int e = 0; e < PER; ++e) out[e] = __half2float(p[e]);
-  }
-}
 
 // Eight consecutive f16 values (one 16-byte load) widened to f32.
 __device__ __forceinline__ void unpack_halves8(const uint4 &raw, float (&out)[8]) {

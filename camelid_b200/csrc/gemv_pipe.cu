@@ -21,9 +21,17 @@
 //     by a fixed shuffle tree, so results are deterministic and differ from the CPU's
 //     block-ordered sum only by f32 reassociation.
 //
-// Every wait on an mbarrier is bounded: after kSpinLimit failed polls a thread records
+//   * sixteen consumer warps in two groups that alternate tiles (a stage belongs to one group: the stage count
+//     is a multiple of the group count, see plan_pipe);
+//   * paired mode (gate and up of an FFN): tiles 2k and 2k+1 of a CTA are the same rows of the two matrices,
+//     one group keeps the first result in registers and writes SwiGLU(first, second);
+//   * peer mode (tensor parallel): the epilogue stores this rank's partial rows into a slot on every rank and
+//     the last CTA raises arrival words; the next launch's prologue waits for all ranks' words and takes the
+//     sum of the partial rows as its RMSNorm input — the all-reduce of the sublayer without a collective kernel.
+//
+// Every wait (mbarrier, arrival word) is bounded: when the bound passes a thread records
 // CMLD_ERR_TIMEOUT in *status and carries on (results are then invalid, the host reports the
-// error), so a lost copy can never hang the GPU.
+// error), so a lost copy or a peer that went away can never hang the GPU.
 #include "actquant.cuh"
 
 namespace cmld {
