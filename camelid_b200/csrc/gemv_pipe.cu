@@ -24,7 +24,7 @@
 //   * sixteen consumer warps in two groups that alternate tiles (a stage belongs to one group: the stage count
 //     is a multiple of the group count, see plan_pipe);
 //   * paired mode (gate and up of an FFN): tiles 2k and 2k+1 of a CTA are the same rows of the two matrices,
-//     one group keeps the first result in registers and writes SwiGLU(first, second);
+//     the two groups take them at the same time and the first writes SwiGLU(first, second);
 //   * peer mode (tensor parallel): the epilogue stores this rank's partial rows into a slot on every rank and
 //     the last CTA raises arrival words; the next launch's prologue waits for all ranks' words and takes the
 //     sum of the partial rows as its RMSNorm input — the all-reduce of the sublayer without a collective kernel.
@@ -106,7 +106,7 @@ struct PipeArgs {
   const uint8_t *act_in0;
   int32_t need_k, need_0;
   int32_t paired;  // two matrices of equal shape and type: tiles alternate between them and the result is SwiGLU(first, second)
-  int32_t off_act_k, off_act_0, off_red, off_ring;
+  int32_t off_act_k, off_act_0, off_red, off_pair, off_ring;
   float *norm_out;        // optional f32 copy of the normalised row (written by CTA 0)
   int32_t *status;
   GemvPeer peer;          // tensor-parallel sum folded into this launch (tx_n / rx_n = 0: none)
@@ -569,33 +569,39 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   // Main loop over this CTA's tiles; the two consumer groups alternate.
   const int group = warp / kPipeConsumerWarps, wg = warp % kPipeConsumerWarps;
   if (a.paired) {
-    // gate and up tiles of the same rows come as consecutive tiles 2k, 2k+1 of this CTA; a group keeps
-    // the gate rows' results in registers, takes the up tile and writes SwiGLU(gate, up) — the f32
-    // activation of the down projection — so neither product goes through memory on its own.
-    for (int k = group; 2 * k < n_my; k += kPipeGroups) {
+    // gate and up tiles of the same rows are consecutive tiles 2k, 2k+1 of this CTA: group 0 takes the gate tile,
+    // group 1 the up tile, at the same time; group 1 hands its results over through shared memory (two
+    // buffers, one barrier of all consumers per pair) and group 0 writes SwiGLU(gate, up) — the f32 operand
+    // of the down projection — so neither product goes through memory on its own.
+    float *pairbuf = reinterpret_cast<float *>(smem + a.off_pair);  // [2][tile_rows][B]
+    const int tile_rows = a.job[0].tile_rows;
+    for (int k = 0; 2 * k < n_my; ++k) {
       const int pair = (int)blockIdx.x + k * (int)gridDim.x;
-      const int row0 = pair * a.job[0].tile_rows;
-      const int nrows = min(a.job[0].tile_rows, a.job[0].rows - row0);
-      float gv[B], uv[B];
+      const int row0 = pair * tile_rows;
+      const int nrows = min(tile_rows, a.job[0].rows - row0);
+      const int i = 2 * k + group, s = i % S;
+      const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+      float v[B];
       bool writer = false;
       int r_local = 0;
+      if (ready) {
+        tile_dot<B>(a, a.job[group], ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride,
+                    act0_col_stride, v, writer, r_local);
+      } else {
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const int i = 2 * k + which, s = i % S;
-        const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-        if (ready) {
-          if (which == 0) tile_dot<B>(a, a.job[0], ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride, act0_col_stride, gv, writer, r_local);
-          else tile_dot<B>(a, a.job[1], ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride, act0_col_stride, uv, writer, r_local);
-        } else {
-#pragma unroll
-          for (int b = 0; b < B; ++b) gv[b] = uv[b] = 0.0f;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
+        for (int b = 0; b < B; ++b) v[b] = 0.0f;
       }
-      if (writer) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      float *slot = pairbuf + ((k & 1) * tile_rows + r_local) * B;
+      if (group == 1 && writer) {
 #pragma unroll
-        for (int b = 0; b < B; ++b) a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + r_local] = swiglu(gv[b], uv[b]);
+        for (int b = 0; b < B; ++b) slot[b] = v[b];
+      }
+      asm volatile("bar.sync 2, %0;" ::"n"(kPipeConsumers));
+      if (group == 0 && writer) {
+#pragma unroll
+        for (int b = 0; b < B; ++b) a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + r_local] = swiglu(v[b], slot[b]);
       }
     }
   } else {
@@ -728,6 +734,8 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   if (need_0) off += batch * ((int)round_up16(cols) + (int)round_up16((cols >> 5) * 4));
   a.off_red = off;
   off += 64 * 4;
+  a.off_pair = off;
+  if (paired) off += 2 * a.job[0].tile_rows * batch * 4;
   off = (off + 127) & ~127;
   a.off_ring = off;
   // Prefer a footprint that lets two kernels share an SM (the next one prefetches under PDL).
@@ -737,12 +745,10 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   int n_stages = 0;
   for (int budget : {110 * 1024, 224 * 1024}) {
     n_stages = std::min<int>(kPipeMaxStages, (budget - off) / stage);
-    // paired mode: a group owns tiles 2k and 2k+1, so a stage stays with one group only if the stage
-    // count is a multiple of twice the number of groups
-    n_stages -= n_stages % (paired ? 2 * kPipeGroups : kPipeGroups);
+    n_stages -= n_stages % kPipeGroups;
     if (n_stages >= 4) break;
   }
-  if (n_stages < (paired ? 4 : 2)) return false;
+  if (n_stages < 2) return false;
   if (paired && (n_jobs != 2 || jobs[0].rows != jobs[1].rows || jobs[0].qt != jobs[1].qt || jobs[0].stride != jobs[1].stride)) return false;
   p.smem_bytes = off + n_stages * stage;
   a.stage_bytes = stage;
