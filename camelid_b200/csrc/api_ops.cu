@@ -281,6 +281,37 @@ int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, floa
   return check_op_status("gemv");
 }
 
+// Runs the receiving side of a peer-memory sum against an arrival word that nobody raises: the wait must run
+// out after timeout_ms, record the status word and let the kernel finish.  Returns what the status word said
+// (CMLD_ERR_TIMEOUT when the bound works); the context stays usable.
+int32_t cmld_peer_wait_selftest(int32_t timeout_ms) {
+  if (timeout_ms < 1 || timeout_ms > 5000) return fail(CMLD_ERR_INVALID, "timeout_ms %d out of 1..=5000", timeout_ms);
+  const int hidden = 256;
+  uint8_t *buf = nullptr;
+  CMLD_CUDA(cudaMalloc(&buf, (size_t)(2 * kPeerRows * hidden + hidden) * 4 + 64));
+  cudaMemset(buf, 0, (size_t)(2 * kPeerRows * hidden + hidden) * 4 + 64);
+  float *parts = reinterpret_cast<float *>(buf), *out = parts + 2 * kPeerRows * hidden;
+  uint32_t *flag = reinterpret_cast<uint32_t *>(out + hidden), *epoch = flag + 2;
+  const uint32_t one = 1;
+  cudaMemcpy(epoch, &one, 4, cudaMemcpyHostToDevice);  // one arrival expected, none will come
+  GemvPeer rx{};
+  rx.rx_n = 2;
+  rx.rx_part = parts;
+  rx.rx_flag = flag;
+  rx.rx_epoch = epoch;
+  rx.rx_out = out;
+  rx.timeout_ns = (unsigned long long)timeout_ms * 1000000ull;
+  int32_t rc = launch_peer_reduce(rx, 1, hidden, op_status(), false, nullptr);
+  if (rc == CMLD_OK) rc = sync_ok("peer_wait_selftest");
+  int32_t st = 0;
+  if (rc == CMLD_OK && cudaMemcpy(&st, op_status(), 4, cudaMemcpyDeviceToHost) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "status read failed");
+  cudaMemset(op_status(), 0, 4);
+  cudaFree(buf);
+  if (rc != CMLD_OK) return rc;
+  if (st == CMLD_ERR_TIMEOUT) return fail(CMLD_ERR_TIMEOUT, "the wait ran out after %d ms as it should", timeout_ms);
+  return fail(CMLD_ERR_STATE, "the wait did not report a timeout (status %d)", st);
+}
+
 int32_t cmld_gemv_select_kernel(int32_t choice) {
   if (choice < 0 || choice > 7) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
   g_gemv_kernel_choice = choice & 1;

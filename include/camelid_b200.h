@@ -269,6 +269,10 @@ CMLD_API int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t ba
  * set = cmld_gemv_time chains its launches with programmatic dependent launch; bit 2 set = the
  * tensor-core kernel (normally used from 9 rows) from 1 row.  Process-wide; for A/B runs. */
 CMLD_API int32_t cmld_gemv_select_kernel(int32_t choice);
+/* Self-test of the bounded device-side wait of the peer-memory path (no reference counterpart): waits for an
+ * arrival word that nobody raises; returns CMLD_ERR_TIMEOUT after timeout_ms (1..5000) when the bound works,
+ * CMLD_ERR_STATE otherwise.  One GPU; nothing faults or hangs. */
+CMLD_API int32_t cmld_peer_wait_selftest(int32_t timeout_ms);
 /* The staged kernel with its fused prologue: y = W . quantise(f(x)) (+ residual), with
  * f = RMSNorm(x) * norm_w (mode 1), x (mode 2) or SwiGLU(x, x2) (mode 3); x_dev/x2_dev are f32
  * [batch][cols], batch <= 8.  One launch replaces norm/activation kernel + quantiser + matvec. */

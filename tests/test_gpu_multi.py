@@ -153,3 +153,16 @@ def test_sharded_engine_refuses_to_step_without_a_communicator(cm):
         e1 = cm.ResidentDecode(synth.engine_config("tiny", max_pos=32, device=1))
         w = cm.Weight.synth(cm.Q8_0, 1, 1, 512, 256, 0.02)  # current device is 0
         e1.adopt_output(np.ones(256, np.float32), w)
+
+
+@pytest.mark.skipif(not has_gpu(), reason="needs a GPU")
+def test_device_side_wait_runs_out_and_the_context_stays_usable(cm):
+    """The bounded wait of the peer-memory path, on one GPU: an arrival word that nothing raises.  The kernel gives
+    up after the limit, records the status, returns; the library reports CMLD_ERR_TIMEOUT and keeps working."""
+    t0 = time.time()
+    rc = cm.lib().cmld_peer_wait_selftest(300)
+    assert rc == 6, (rc, cm.lib().cmld_last_error())
+    assert 0.25 < time.time() - t0 < 10.0
+    w = cm.Weight.synth(cm.Q8_0, 1, 1, 64, 256, 0.02)  # the context is alive
+    assert w.dequant().shape == (64, 256)
+    assert cm.lib().cmld_peer_wait_selftest(0) == 1    # argument check
