@@ -1648,6 +1648,7 @@ int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *t
     o.from_tokens = true;
     o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
     o.logits = o.argmax = (i + chunk >= n);
+    o.attn_cluster = use_attn_cluster(rows, start_pos + i + rows - 1);
     CMLD_TRY(run_step(e, o));
     last_rows = rows;
   }

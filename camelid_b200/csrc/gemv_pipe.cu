@@ -454,17 +454,21 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       }
     }
   }
+  const bool chunked_norm = a.mode == 1 && (a.cols & 255) == 0 && a.cols <= kRxChunks * kPipeAllWarps * 256;
   for (int b = 0; b < a.batch; ++b) {
-    if (a.peer.rx_n > 0) {
-      // RMSNorm of the sum of the ranks' partial rows (added in rank order, so every rank gets the same
-      // bits); each warp keeps its chunks of the sum in registers between the two passes
+    if (a.peer.rx_n > 0 || chunked_norm) {
+      // RMSNorm with ONE load of the row: each warp keeps its chunks in registers between the mean-square
+      // pass and the scaling pass.  The squares are added per lane over the warp's chunks, by the shuffle
+      // tree within the warp, then the sixteen warp sums by one more shuffle tree — the order the
+      // stand-alone norm kernel reproduces, so both give the same bits.  With a peer sum the row is the sum
+      // of the ranks' partial rows (added in rank order, so every rank gets the same bits).
       float hv[kRxChunks][8];
       float ss = 0.0f;
 #pragma unroll
       for (int k = 0; k < kRxChunks; ++k) {
         const int ch = warp + k * kPipeAllWarps;
         if (ch * 256 < a.cols) {
-          const float *src = a.peer.rx_part + (int64_t)b * a.cols + ch * 256 + lane * 8;
+          const float *src = (a.peer.rx_n > 0 ? a.peer.rx_part + (int64_t)b * a.cols : a.x + (int64_t)b * a.x_stride) + ch * 256 + lane * 8;
           float4 s0 = __ldcg(reinterpret_cast<const float4 *>(src)), s1 = __ldcg(reinterpret_cast<const float4 *>(src) + 1);
           for (int r = 1; r < a.peer.rx_n; ++r) {
             const float4 t0 = __ldcg(reinterpret_cast<const float4 *>(src + r * a.peer_rank_stride));
@@ -502,6 +506,11 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
           float v[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(hv[k][i], scale), wv[i]);
+          if (a.norm_out && blockIdx.x == 0) {
+            float4 *o4 = reinterpret_cast<float4 *>(a.norm_out + (int64_t)b * a.cols + e0);
+            o4[0] = make_float4(v[0], v[1], v[2], v[3]);
+            o4[1] = make_float4(v[4], v[5], v[6], v[7]);
+          }
           emit_chunk(v, a, b, ch, lane, act_k, act_0, rec_col_stride, act0_col_stride);
         }
       }

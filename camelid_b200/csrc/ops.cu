@@ -37,20 +37,48 @@ __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs 
       }
       __syncthreads();
     } else {
-      float ss = 0.0f;
-      for (int64_t i = threadIdx.x; i < a.cols; i += blockDim.x) {
-        const float v = x[i];
-        ss = __fmaf_rn(v, v, ss);
+      if ((a.cols & 255) == 0 && a.cols <= 8192 && blockDim.x == 256) {
+        // the order of the matvec kernel's fused prologue (sixteen warps there, each holding chunks w and w+16):
+        // per lane over those chunks' values, shuffle tree within the warp, shuffle tree over the sixteen sums
+        __shared__ float red16[16];
+        for (int vw = warp; vw < 16; vw += 8) {
+          float ss = 0.0f;
+          for (int k = 0; k < 2; ++k) {
+            const int64_t e0 = (int64_t)(vw + 16 * k) * 256 + lane * 8;
+            if (e0 < a.cols) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const float v = x[e0 + i];
+                ss = __fmaf_rn(v, v, ss);
+              }
+            }
+          }
+          ss = warp_sum(ss);
+          if (lane == 0) red16[vw] = ss;
+        }
+        __syncthreads();
+        if (warp == 0) {
+          float t = lane < 16 ? red16[lane] : 0.0f;
+          t = warp_sum(t);
+          if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+        }
+        __syncthreads();
+      } else {
+        float ss = 0.0f;
+        for (int64_t i = threadIdx.x; i < a.cols; i += blockDim.x) {
+          const float v = x[i];
+          ss = __fmaf_rn(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (warp == 0) {
+          float t = lane < nwarps ? red[lane] : 0.0f;
+          t = warp_sum(t);
+          if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+        }
+        __syncthreads();
       }
-      ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
-      __syncthreads();
-      if (warp == 0) {
-        float t = lane < nwarps ? red[lane] : 0.0f;
-        t = warp_sum(t);
-        if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
-      }
-      __syncthreads();
     }
     scale = s_scale;
   }
