@@ -1,4 +1,4 @@
-"""Quantised-matvec microbenchmark (BASELINE config 2): weights M x K in
+"""Quantised-matvec microbenchmark (benchmark configuration 2): weights M x K in
 {4096x4096, 14336x4096, 4096x14336, 128256x4096} x {Q8_0, Q4_K, Q6_K}, seeded N(0, 0.02);
 activations f32 N(0,1) at batch 1, 4, 8; outputs f32.  Prints one JSON line per case with the
 achieved HBM GB/s (algorithmic bytes = weight wire bytes + int8 activation codes + f32 outputs,

@@ -38,7 +38,7 @@ def engine_config(shape: str, max_pos: int, max_seqs: int = 1, n_layers: int | N
 
 def quant_plan(mix: str) -> dict:
     """Tensor role -> GGUF type.  "q8_0": everything Q8_0.  "q4_k_m": Q4_K except attn_v,
-    ffn_down and output in Q6_K (the mix BASELINE's configs name)."""
+    ffn_down and output in Q6_K (the mix the benchmark configurations name)."""
     if mix == "q8_0":
         return {r: Q8_0 for r in SLOTS + ("token_embd", "output")}
     if mix == "q4_k_m":

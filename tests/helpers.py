@@ -25,7 +25,7 @@ def close_enough(got, ref, rel=1e-4, floor=1e-5):
 
 
 def hidden_gate(got, ref):
-    """BASELINE's per-layer gate: max-abs 2e-2 and relative 1e-2 (relative to the row's RMS)."""
+    """The acceptance gate per layer: max-abs 2e-2 and relative 1e-2 (relative to the row's RMS)."""
     got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
     max_abs = float(np.abs(got - ref).max())
     rel = float(np.abs(got - ref).max() / (np.sqrt((ref ** 2).mean()) + 1e-30))

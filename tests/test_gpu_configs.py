@@ -1,4 +1,4 @@
-"""Parity at BASELINE's model shapes (B200, through the C ABI).
+"""Parity at the benchmark's model shapes (B200, through the C ABI).
 
 Config 1 runs in full: Llama-3.2-1B-shaped, all Q8_0, 32-token prompt, 128 greedy tokens, against
 the CPU checker holding byte-identical weights.  The larger configs are run at their true widths
@@ -13,10 +13,10 @@ output.  The CPU checker fed inputs perturbed by 1e-6 jumps in the same way.
 
 * reference order (CMLD_FLAG_EXACT_ORDER): every f32 sum in the CPU path's order.  Bar: the residual
   stream after every layer, the logits and every greedy token are BIT-IDENTICAL to the checker.
-  BASELINE's gates (max-abs 2e-2 / relative 1e-2 per layer and logits, >= 32 equal greedy tokens)
+  The acceptance gates (max-abs 2e-2 / relative 1e-2 per layer and logits, >= 32 equal greedy tokens)
   hold with zero difference.
 * fast order (default; shuffle-tree sums): each layer, fed the checker's own input, is inside
-  BASELINE's gate for most (position, layer) pairs with a median deviation of 1e-6..1e-3; pairs
+  the acceptance gate for most (position, layer) pairs with a median deviation of 1e-6..1e-3; pairs
   outside it are rounding-boundary events.  Greedy streams leave the checker's where its top-2 logit
   gap is of the size of those events; the lengths are printed, not gated.
 """

@@ -1,7 +1,7 @@
 """Engine-level parity on a B200 through the C ABI: whole decode steps against the CPU
 checker holding byte-identical weights.
 
-Gates (BASELINE's): per-layer hidden states and logits within max-abs 2e-2 and relative
+Acceptance gates: per-layer hidden states and logits within max-abs 2e-2 and relative
 1e-2; greedy token ids equal for at least the first 32 generated tokens; KV rows equal to
 what serial single-token calls write.
 """
