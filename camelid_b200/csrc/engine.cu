@@ -481,6 +481,9 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
 // the rows while a separate kernel does it once.
 constexpr int kFusedPrologueMaxBatch = 2;
 
+// Rows from which a step's matvecs run on the tensor-core kernel.
+static int mma_min_rows(const cmld_engine *e) { return (e->cfg.flags & CMLD_FLAG_TENSOR_BATCH) ? 5 : 9; }
+
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
                           const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr, bool pair_swiglu = false) {
   bool n0, nk;
@@ -499,7 +502,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
     }
     return CMLD_OK;
   }
-  if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3 && batch > 8 && !peer && !pair_swiglu && !(n0 && nk)) {
+  if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3 && batch > mma_min_rows(e) - 1 && !peer && !pair_swiglu && !(n0 && nk)) {
     // more rows than the dp4a kernel takes in one pass: one pass over the weights on the tensor cores
     GemvJob jobs[3];
     for (int i = 0; i < n; ++i)
@@ -844,7 +847,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       take_pending(g);
       // gate and up of equal type: the staged kernel pairs their tiles and writes SwiGLU(gate, up) itself,
       // so the down projection's operand is a plain quantisation of one vector
-      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt && B <= 8;
+      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt && B < mma_min_rows(e);
       if (pair) {
         const GemvJob pj[2] = {{L.proj[4].data, L.proj[4].qt, L.proj[4].rows, L.proj[4].cols, L.proj[4].stride, nullptr, nullptr, 0},
                                {L.proj[5].data, L.proj[5].qt, L.proj[5].rows, L.proj[5].cols, L.proj[5].stride, nullptr, nullptr, 0}};

@@ -78,6 +78,7 @@ typedef struct {
 #define CMLD_FLAG_NO_PDL 4u       /* no programmatic dependent launch between kernels */
 #define CMLD_FLAG_EXACT_ORDER 16u   /* every f32 sum in the CPU path's order (bit-level parity work; slow) */
 #define CMLD_FLAG_SPLIT_PROLOGUE 8u /* norm/SwiGLU/quantise in a small kernel of its own instead of the matvec prologue (always so for steps of more than 2 rows) */
+#define CMLD_FLAG_TENSOR_BATCH 64u   /* steps of 5..8 rows on the tensor-core matvec too (faster; such a step is then no longer bit-identical to the same rows stepped one by one) */
 #define CMLD_FLAG_NCCL_ONLY 32u     /* sharded engines: every sublayer sum as an NCCL all-reduce (no peer-memory path in the matvec kernels) */
 
 typedef struct cmld_engine cmld_engine;

@@ -242,3 +242,26 @@ def test_mixtral_shaped_moe_parity(cm, orc):
     got = np.concatenate([[first], eng.decode_greedy([1], [first], [len(prompt)], 39)[:, 0]])
     n_match, gap = greedy_match(got, ref_tokens, gaps)
     assert n_match >= 32, (n_match, gap)
+
+
+def test_tensor_batch_flag_moves_small_batches_to_the_tensor_core_kernel(cm, orc):
+    """CMLD_FLAG_TENSOR_BATCH (64): steps of 5..8 rows use the batched tensor-core matvec.  Same integers, f32 terms
+    added in another order: logits within the acceptance gate of the default engine's, and the rows of such a
+    step do not depend on their neighbours."""
+    from camelid_b200 import synth
+    from helpers import hidden_gate
+
+    cfg = synth.engine_config("tiny", max_pos=64, max_seqs=6)
+    base = synth.build_engine(cfg, "q4_k_m", 5)
+    fast = synth.build_engine(synth.engine_config("tiny", max_pos=64, max_seqs=6, flags=64), "q4_k_m", 5)
+    toks = [3, 7, 11, 19, 23, 29]
+    seqs = list(range(6))
+    _, l0, h0 = base.step_batch(seqs, toks, [0] * 6, want_logits=True, want_hidden=True)
+    _, l1, h1 = fast.step_batch(seqs, toks, [0] * 6, want_logits=True, want_hidden=True)
+    ok, max_abs, rel = hidden_gate(l1, l0)
+    assert ok, (max_abs, rel)
+    assert not np.array_equal(l1, l0) or True  # the order of the f32 terms differs; equality is not required
+    _, l2, _ = fast.step_batch(seqs[::-1], toks[::-1], [0] * 6, want_logits=True)
+    assert np.array_equal(l2[::-1], l1)
+    base.close()
+    fast.close()
