@@ -129,6 +129,7 @@ def lib():
         "cmld_argmax": (i32, [vp, i64, i32, vp]),
         "cmld_attention_decode": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, f32, vp]),
         "cmld_attention_decode_noalloc": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, f32, vp]),
+        "cmld_attention_decode_ordered": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, f32, vp]),
         "cmld_gemv_time": (i32, [P(vp), i32, vp, i32, vp, i32, i32, P(f32)]),
     }
     for name, (res, args) in sig.items():

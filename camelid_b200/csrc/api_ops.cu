@@ -67,10 +67,10 @@ static int32_t check_op_status(const char *what) {
 }
 
 static int g_gemv_pdl = 0;            // cmld_gemv_time: chain its launches with programmatic dependent launch
-static int g_gemv_kernel_choice = 0;  // 0 auto (staged when the shape fits), 1 direct-load only
-static int g_gemv_mma_min_batch = 9;  // rows from which the tensor-core kernel is used (bit 2 of the choice: from 1)
+static int g_gemv_kernel_choice = 0;  // 0 auto (staged when the shape fits), 1 generic kernel only
+static int g_gemv_mma_min_batch = 1 << 30;  // rows from which the int8 mma.sync kernel is used (opt-in: bit 3 of the choice from 9 rows, bit 2 from 1)
 
-// One matvec launch on the default stream: staged kernel if it takes the shape, else direct-load.
+// One matvec launch on the default stream: staged kernel if it takes the shape, else the generic one.
 static int32_t gemv_launch(const cmld_weight *w, const uint8_t *act, int32_t batch, float *y, const float *residual,
                            cudaStream_t stream = nullptr, bool pdl = false) {
   GemvJob probe{w->data, w->qt, w->rows, w->cols, w->stride, y, residual, w->rows};
@@ -313,10 +313,10 @@ int32_t cmld_peer_wait_selftest(int32_t timeout_ms) {
 }
 
 int32_t cmld_gemv_select_kernel(int32_t choice) {
-  if (choice < 0 || choice > 7) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
+  if (choice < 0 || choice > 15) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
   g_gemv_kernel_choice = choice & 1;
   g_gemv_pdl = (choice >> 1) & 1;
-  g_gemv_mma_min_batch = (choice & 4) ? 1 : 9;
+  g_gemv_mma_min_batch = (choice & 4) ? 1 : ((choice & 8) ? 9 : (1 << 30));
   return CMLD_OK;
 }
 
@@ -472,6 +472,44 @@ int32_t cmld_attention_decode(const float *q_dev, const void *k_cache_dev, const
   int32_t rc = launch_attention(a, nullptr);
   if (rc == CMLD_OK) rc = sync_ok("attention_decode");
   cudaFree(scratch);
+  return rc;
+}
+
+// The reference-order attention of the decode step (attn_ordered.cu; contexts it does not take use the
+// plain reference-order kernel): the output has the CPU path's bits.
+int32_t cmld_attention_decode_ordered(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev, int32_t n_heads,
+                                      int32_t n_kv_heads, int32_t head_dim, int64_t max_pos, int64_t n_pos, float scale,
+                                      float *out_dev) {
+  if (!q_dev || !k_cache_dev || !v_cache_dev || !out_dev) return fail(CMLD_ERR_INVALID, "null buffer");
+  if (n_pos < 1 || n_pos > max_pos) return fail(CMLD_ERR_INVALID, "n_pos %lld out of range", (long long)n_pos);
+  if (n_kv_heads < 1 || n_heads % n_kv_heads) return fail(CMLD_ERR_SHAPE, "n_heads must be a multiple of n_kv_heads");
+  int32_t *pos_slot = nullptr;
+  CMLD_CUDA(cudaMalloc(&pos_slot, 8));
+  const int32_t ps[2] = {(int32_t)(n_pos - 1), 0};
+  cudaMemcpy(pos_slot, ps, 8, cudaMemcpyHostToDevice);
+  AttnArgs a{};
+  a.q = q_dev;
+  a.k_cache = static_cast<const __half *>(k_cache_dev);
+  a.v_cache = static_cast<const __half *>(v_cache_dev);
+  a.positions = pos_slot;
+  a.slots = pos_slot + 1;
+  a.n_heads = n_heads;
+  a.n_kv_heads = n_kv_heads;
+  a.head_dim = head_dim;
+  a.batch = 1;
+  a.n_splits = 1;
+  a.max_pos = max_pos;
+  a.scale = scale;
+  a.out = out_dev;
+  a.q_stride = (int64_t)n_heads * head_dim;
+  int64_t cap = 0;
+  for (int64_t c : {1024, 2048, 4096, 8192})
+    if (cap == 0 && n_pos <= c) cap = c;
+  int32_t rc;
+  if (cap > 0 && attention_ordered_fits(n_heads, n_kv_heads, head_dim, cap)) rc = launch_attention_ordered(a, cap, nullptr);
+  else rc = launch_attention_exact(a, nullptr);
+  if (rc == CMLD_OK) rc = sync_ok("attention_decode_ordered");
+  cudaFree(pos_slot);
   return rc;
 }
 

@@ -240,7 +240,7 @@ int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, in
 
 // Returns CMLD_ERR_UNSUPPORTED, leaving the error message untouched, when the shape does not fit.
 // Largest batch (<= 8) the staged kernel takes for these matrices in one launch; 0 = none.
-int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired = false);
+int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired = false, bool norm = false);
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
                          cudaStream_t s, bool pdl, const GemvPeer *peer = nullptr);
 
@@ -315,6 +315,9 @@ struct AttnArgs {
   int32_t cluster;                 // ranges as the CTAs of a thread-block cluster, merged through distributed shared memory
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
+// attn_ordered.cu: the reference-order cluster kernel (contexts of at most `cap` positions)
+bool attention_ordered_fits(int n_heads, int n_kv_heads, int head_dim, int64_t cap);
+int32_t launch_attention_ordered(const AttnArgs &a, int64_t cap, cudaStream_t s);
 
 // comm.cu: NCCL collectives of the sharded engine
 int32_t comm_unique_id(uint8_t *out128);

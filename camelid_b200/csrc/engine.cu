@@ -308,7 +308,7 @@ static int32_t engine_init(cmld_engine *e) {
     CMLD_TRY(dev_alloc(e, &e->moe_act, na * c.ffn_dim));
     CMLD_TRY(dev_alloc(e, &e->moe_down, na * c.hidden));
     CMLD_TRY(dev_alloc(e, &e->moe_pos, na));
-    if (c.hidden % 256 == 0 && c.ffn_dim % 256 == 0 && !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV))) {
+    if (c.hidden % 256 == 0 && c.ffn_dim % 256 == 0 && (c.flags & CMLD_FLAG_TENSOR_BATCH) && !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV))) {
       const int64_t n_local = c.n_experts / std::max(1, c.ep_size);
       e->moe_cap = (int32_t)(3 * na);  // every assignment could land on one expert
       const int64_t rows = n_local * e->moe_cap;
@@ -481,8 +481,10 @@ static int32_t run_norm_quant(cmld_engine *e, const float *x, const float *x2, c
 // the rows while a separate kernel does it once.
 constexpr int kFusedPrologueMaxBatch = 2;
 
-// Rows from which a step's matvecs run on the tensor-core kernel.
-static int mma_min_rows(const cmld_engine *e) { return (e->cfg.flags & CMLD_FLAG_TENSOR_BATCH) ? 5 : 9; }
+// Rows from which a step's matvecs run on the int8 mma.sync kernel.  That kernel adds a row's terms in a
+// different order from the CPU path, so it is opt-in (CMLD_FLAG_TENSOR_BATCH); by default every step
+// goes through the staged kernel, in passes of up to 8 rows.
+static int mma_min_rows(const cmld_engine *e) { return (e->cfg.flags & CMLD_FLAG_TENSOR_BATCH) ? 5 : (1 << 30); }
 
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
                           const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr, bool pair_swiglu = false) {
@@ -526,7 +528,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
     GemvJob jobs[3];
     for (int i = 0; i < n; ++i)
       jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
-    const int fit = gemv_pipe_fit_batch(jobs, n, pair_swiglu);  // columns per pass: the same for every batch size, so
+    const int fit = gemv_pipe_fit_batch(jobs, n, pair_swiglu, fused && mode == 1);  // columns per pass: the same for every batch size, so
     if (fit > 0) {                                // a row's result does not depend on who shares its step
       // Activation preparation.  Default: each matvec CTA computes norm / SwiGLU / quantisation itself in
       // its prologue (repeated on every SM, but no extra launch on the critical path); with
@@ -581,6 +583,7 @@ struct StepOpts {
   bool taps = false;
   int32_t layer_begin = 0, layer_end = -1;  // layers to run; -1 = through the last
   bool attn_cluster = false;  // short contexts, few rows: attention ranges as a thread-block cluster (host-side choice)
+  int32_t attn_cap = 0;       // bound on the context length of every row of this step (a bucket: 1024, 2048, 4096, 8192), 0 = unknown
   bool shared_slots = false;  // several rows of this step belong to one sequence (prefill, verify): row b
                               // reads K/V that rows < b write, so the KV append must be a kernel of its own
 };
@@ -595,6 +598,9 @@ int32_t moe_combine3(float *h, const float *y3, const float *sel_w, const int32_
 int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
                         const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
                         int n_assign, cudaStream_t s);
+int32_t moe_expert_gemv_ordered(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
+                                const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
+                                int n_assign, cudaStream_t s);
 int32_t moe_combine(float *h, const float *down, const float *sel_w, const int32_t *sel_idx, int hidden, int k, int batch,
                     int first_expert, int expert_step, bool add_residual, cudaStream_t s);
 
@@ -646,18 +652,23 @@ static int32_t moe_ffn_step_mma(cmld_engine *e, LayerW &L, int32_t B) {
 // Mixtral FFN on e->normed (f32): route, expert gate/up, SwiGLU, expert down, weighted sum.
 static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
   const cmld_config &c = e->cfg;
-  {
+  // Default: the expert matvecs in the CPU path's order (f32 activation x dequantised weight, one accumulator).
+  // CMLD_FLAG_TENSOR_BATCH opts into the int8 tensor-core form (three residual Q8_K rows per activation), which
+  // reads the weights once for all rows but adds in another order.
+  const bool fast = (c.flags & CMLD_FLAG_TENSOR_BATCH) != 0;
+  if (fast) {
     const int32_t rc = moe_ffn_step_mma(e, L, B);
     if (rc != CMLD_ERR_UNSUPPORTED) return rc;
   }
   const int k = c.n_experts_used, na = B * k;
   const int n_local = c.n_experts / ep_size(e), first = ep_size(e) > 1 ? c.ep_rank : 0, step = ep_size(e);
+  auto expert_gemv = fast ? moe_expert_gemv : moe_expert_gemv_ordered;
   CMLD_TRY(moe_route(e->normed, L.router, c.hidden, c.n_experts, k, B, e->moe_sel_idx, e->moe_sel_w, e->moe_counts,
                      e->moe_lists, e->stream, e->moe_pos));
-  CMLD_TRY(moe_expert_gemv(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts,
-                           e->moe_lists, na, e->stream));
-  CMLD_TRY(moe_expert_gemv(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts,
-                           e->moe_lists, na, e->stream));
+  CMLD_TRY(expert_gemv(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts,
+                       e->moe_lists, na, e->stream));
+  CMLD_TRY(expert_gemv(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts,
+                       e->moe_lists, na, e->stream));
   NormQuantArgs a{};
   a.x = e->moe_g;
   a.x2 = e->moe_u;
@@ -665,8 +676,8 @@ static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
   a.batch = na;
   a.out = e->moe_act;
   CMLD_TRY(launch_norm_quant(a, e->stream));
-  CMLD_TRY(moe_expert_gemv(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts,
-                           e->moe_lists, na, e->stream));
+  CMLD_TRY(expert_gemv(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts,
+                       e->moe_lists, na, e->stream));
   CMLD_TRY(moe_combine(e->h, e->moe_down, e->moe_sel_w, e->moe_sel_idx, c.hidden, k, B, first, step,
                        e->ep == 1 || e->shard_rank == 0, e->stream));
   e->launches += 7;
@@ -716,21 +727,21 @@ static bool peer_step_ok(cmld_engine *e, int32_t B, bool taps) {
   auto it = e->peer_fit.find(B);
   if (it != e->peer_fit.end()) return it->second;
   bool ok = e->cfg.hidden % 256 == 0 && e->cfg.hidden <= 8192;
-  auto fits = [&](std::initializer_list<const Weight *> ws) {
+  auto fits = [&](std::initializer_list<const Weight *> ws, bool norm = false) {
     GemvJob jobs[3];
     int n = 0;
     for (const Weight *w : ws) {
       if (!w->data) return false;
       jobs[n++] = GemvJob{w->data, w->qt, w->rows, w->cols, w->stride, nullptr, nullptr, w->rows};
     }
-    return gemv_pipe_fit_batch(jobs, n) >= B;
+    return gemv_pipe_fit_batch(jobs, n, false, norm) >= B;
   };
   for (const LayerW &L : e->layers) {
     if (!ok) break;
-    ok = L.dense_set && !L.moe_set && fits({&L.proj[0], &L.proj[1], &L.proj[2]}) && fits({&L.proj[3]}) &&
-         fits({&L.proj[4], &L.proj[5]}) && fits({&L.proj[6]});
+    ok = L.dense_set && !L.moe_set && fits({&L.proj[0], &L.proj[1], &L.proj[2]}, true) && fits({&L.proj[3]}) &&
+         fits({&L.proj[4], &L.proj[5]}, true) && fits({&L.proj[6]});
   }
-  if (ok && e->has_output) ok = fits({&e->output});
+  if (ok && e->has_output) ok = fits({&e->output}, true);
   e->peer_fit[B] = ok;
   return ok;
 }
@@ -766,8 +777,13 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden, use_peer ? &g : nullptr));
     }
     {
-      const bool exact = (c.flags & CMLD_FLAG_EXACT_ORDER) != 0;
-      const bool fuse = !o.shared_slots && !exact;
+      // Attention.  Default: the reference-order cluster kernel (the CPU path's bits); contexts or shapes it
+      // does not take, and CMLD_FLAG_EXACT_ORDER, use the plain reference-order kernel; CMLD_FLAG_FAST_ORDER
+      // opts into the split-range (flash-decoding) kernel, whose sums are trees.
+      const bool fast = (c.flags & CMLD_FLAG_FAST_ORDER) && !(c.flags & CMLD_FLAG_EXACT_ORDER);
+      const bool ordered = !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && o.attn_cap > 0 &&
+                           attention_ordered_fits(c.n_heads, c.n_kv_heads, c.head_dim, o.attn_cap);
+      const bool fuse = !o.shared_slots && (fast || ordered);
       if (!fuse) {
         RopeKvArgs r{};
         r.q = e->q;
@@ -821,9 +837,10 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
       a.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
       a.pdl = !(c.flags & CMLD_FLAG_NO_PDL);
-      a.cluster = o.attn_cluster && !exact ? 1 : 0;
-      if (exact) CMLD_TRY(launch_attention_exact(a, e->stream));
-      else CMLD_TRY(launch_attention(a, e->stream));
+      a.cluster = o.attn_cluster && fast ? 1 : 0;
+      if (ordered) CMLD_TRY(launch_attention_ordered(a, o.attn_cap, e->stream));
+      else if (fast) CMLD_TRY(launch_attention(a, e->stream));
+      else CMLD_TRY(launch_attention_exact(a, e->stream));
       e->launches += 1;
     }
     {
@@ -851,7 +868,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       if (pair) {
         const GemvJob pj[2] = {{L.proj[4].data, L.proj[4].qt, L.proj[4].rows, L.proj[4].cols, L.proj[4].stride, nullptr, nullptr, 0},
                                {L.proj[5].data, L.proj[5].qt, L.proj[5].rows, L.proj[5].cols, L.proj[5].stride, nullptr, nullptr, 0}};
-        pair = gemv_pipe_fit_batch(pj, 2, true) >= 1;
+        pair = gemv_pipe_fit_batch(pj, 2, true, true) >= 1;
       }
       CMLD_TRY(gemv_fused(e, p, 2, B, 1, e->h, nullptr, L.ffn_norm, c.hidden, use_peer ? &g : nullptr, pair));
       const Proj pd[1] = {{&L.proj[6], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
@@ -908,7 +925,7 @@ static int32_t run_step(cmld_engine *e, const StepOpts &o) {
                   (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u) | (o.attn_cluster ? 128u : 0u) | ((uint32_t)(o.layer_begin & 0xfff) << 8) | ((uint32_t)((o.layer_end + 1) & 0xfff) << 20);
   uint32_t scale_bits;
   memcpy(&scale_bits, &o.scale, 4);
-  auto &g = e->graphs[std::make_tuple(o.batch, bits, scale_bits)];
+  auto &g = e->graphs[std::make_tuple(o.batch | (o.attn_cap << 8), bits, scale_bits)];
   if (g.exec) {
     CMLD_CUDA(cudaGraphLaunch(g.exec, e->stream));
     e->launches += g.launches;
@@ -957,6 +974,14 @@ static int32_t require_weights(const cmld_engine *e, bool need_output) {
 // The rule does not depend on the row count up to 8 rows, so that a step of <= 8 rows keeps giving the bits of
 // the same rows stepped one by one (as long as all of them are on one side of the context threshold).
 static bool use_attn_cluster(int32_t rows, int64_t max_position) { return rows <= 8 && max_position < 2048; }
+
+// Bound on the context length handed to the reference-order attention kernel: the smallest of a few buckets
+// that holds every row's context (a step graph is kept per bucket), 0 beyond the largest.
+static int32_t attn_cap_for(int64_t max_position) {
+  for (int32_t cap : {1024, 2048, 4096, 8192})
+    if (max_position < cap) return cap;
+  return 0;
+}
 
 // Rows of one step: tokens (or none), positions and KV slots to the device.
 static int32_t stage_rows(cmld_engine *e, int32_t n, const int32_t *tokens, const int32_t *positions, const int32_t *slots) {
@@ -1028,6 +1053,7 @@ static int32_t forward_embedding_rows(cmld_engine *e, const float *embeddings, c
   o.layer_begin = layer_begin;
   o.layer_end = layer_end;
   o.attn_cluster = use_attn_cluster(n_rows, position0 + n_rows - 1);
+  o.attn_cap = attn_cap_for(position0 + n_rows - 1);
   return run_step(e, o);
 }
 
@@ -1612,6 +1638,7 @@ int32_t cmld_engine_step_batch(cmld_engine *e, int32_t n_seqs, const int32_t *se
     int64_t mx = 0;
     for (int i = 0; i < n_seqs; ++i) mx = std::max<int64_t>(mx, positions[i]);
     o.attn_cluster = use_attn_cluster(n_seqs, mx);
+    o.attn_cap = attn_cap_for(mx);
   }
   CMLD_TRY(run_step(e, o));
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));
@@ -1652,6 +1679,7 @@ int32_t cmld_engine_prefill_tokens(cmld_engine *e, int32_t seq, const int32_t *t
     o.scale = 1.0f / sqrtf((float)e->cfg.head_dim);
     o.logits = o.argmax = (i + chunk >= n);
     o.attn_cluster = use_attn_cluster(rows, start_pos + i + rows - 1);
+    o.attn_cap = attn_cap_for(start_pos + i + rows - 1);
     CMLD_TRY(run_step(e, o));
     last_rows = rows;
   }
@@ -1688,6 +1716,7 @@ int32_t cmld_engine_decode_greedy(cmld_engine *e, int32_t n_seqs, const int32_t 
   for (int i = 0; i < n_seqs; ++i) max_start = std::max<int64_t>(max_start, positions[i]);
   for (int s = 0; s < n_steps; ++s) {
     o.attn_cluster = use_attn_cluster(n_seqs, max_start + s);
+    o.attn_cap = attn_cap_for(max_start + s);
     CMLD_TRY(run_step(e, o));
   }
   CMLD_CUDA(cudaEventRecord(e->ev1, e->stream));

@@ -1,30 +1,33 @@
-// Staged quantised matvec for sm_100a: the fast path of the decode step.
+// Staged quantised matvec for sm_100a: the fast path of the decode step, with every f32 operation
+// in the order of Camelid's CPU path, so its results are the CPU path's bits.
 //
 // Why this shape.  A decode matvec reads every weight byte once and does ~1 integer MAC per
 // 4 bits: it is HBM-bound and uses no tensor cores.  What limits a simple kernel on B200 is
 // the number of bytes in flight (Little's law at ~6.5 TB/s needs > 40 KB per SM) and the gaps
 // between dependent launches.  So:
-//   * one persistent CTA per SM walks its share of row tiles; a tile of consecutive rows is one
-//     contiguous byte range of the device layout, fetched by ONE bulk asynchronous copy
-//     (cp.async.bulk, the non-tensor TMA path) into a shared-memory ring of up
-//     to 8 stages guarded by mbarriers (full: transaction bytes, empty: one arrival per warp);
+//   * one persistent CTA per SM walks its share of row tiles; a tile is a few consecutive rows, or for
+//     long rows a run of up to 32 superblocks of each of them (a "piece"), fetched by bulk
+//     asynchronous copies (cp.async.bulk, the non-tensor TMA path: one copy when the piece is whole
+//     rows, else one per row) into a shared-memory ring of 4 or 8 stages guarded by mbarriers
+//     (full: transaction bytes, empty: one arrival per warp);
 //   * a dedicated producer warp issues the copies; it starts BEFORE the kernel waits on its
 //     predecessor (griddepcontrol.wait), because weights never depend on earlier kernels — under
 //     programmatic dependent launch the ring fills while the previous kernel drains;
 //   * the consumer warps first build the quantised activation in shared memory — optionally
 //     fused with RMSNorm or SwiGLU so no separate kernel and no global round trip is needed —
-//     then each lane owns whole superblocks (Q4_K/Q6_K) or 32-value blocks (Q8_0): one f16->f32
-//     and one int->f32 conversion per superblock instead of per 16 bytes, scales decoded once;
-//   * per-superblock integer sums and the two f32 multiply-adds are exactly the CPU's
-//     (q4_k_dot_scalar, src/diffusion_gemma/refmath.rs:504-562; q6_k_wire_row_dot and
-//     q8_0_dot_rows, src/inference.rs:25535 and :26166 in the Camelid tree); lanes are combined
-//     by a fixed shuffle tree, so results are deterministic and differ from the CPU's
-//     block-ordered sum only by f32 reassociation.
-//
-//   * sixteen consumer warps in two groups that alternate tiles (a stage belongs to one group: the stage count
-//     is a multiple of the group count, see plan_pipe);
-//   * paired mode (gate and up of an FFN): tiles 2k and 2k+1 of a CTA are the same rows of the two matrices,
-//     the two groups take them at the same time and the first writes SwiGLU(first, second);
+//     then each lane owns whole superblocks (Q4_K/Q6_K) or 32-value blocks (Q8_0) and computes their
+//     integer dot products with dp4a;
+//   * the f32 part of a row is a dependent chain in block order on the CPU (q4_k_dot_scalar,
+//     src/diffusion_gemma/refmath.rs:504-562: two fused multiply-adds per superblock;
+//     q6_k_wire_row_dot, src/inference.rs:25535-25581: eight accumulators by index mod 8, then their
+//     left-to-right sum; q8_0_dot_rows, src/inference.rs:26191-26199: ((isum*ws)*xs) added block by
+//     block, in the Camelid tree).  The lanes hand their per-block terms over through a small
+//     per-warp buffer and a few "chain lanes" walk them in that order, so the result has the CPU's
+//     bits; the chains cost latency only, which the other warps cover;
+//   * sixteen consumer warps in four groups; group g takes units g, g+4, ... of the CTA's sequence (a
+//     ring stage belongs to one group: the stage count is a multiple of the group count);
+//   * paired mode (gate and up of an FFN): two neighbouring groups take the same rows of the two
+//     matrices at the same time and the first writes SwiGLU(first, second);
 //   * peer mode (tensor parallel): the epilogue stores this rank's partial rows into a slot on every rank and
 //     the last CTA raises arrival words; the next launch's prologue waits for all ranks' words and takes the
 //     sum of the partial rows as its RMSNorm input — the all-reduce of the sublayer without a collective kernel.
@@ -33,19 +36,30 @@
 // CMLD_ERR_TIMEOUT in *status and carries on (results are then invalid, the host reports the
 // error), so a lost copy or a peer that went away can never hang the GPU.
 #include "actquant.cuh"
+#include "exact_sum.cuh"
 
 namespace cmld {
 
-constexpr int kPipeConsumerWarps = 8;  // warps that share one tile
-constexpr int kPipeGroups = 2;         // consumer groups; group g takes this CTA's tiles g, g+2, ... (more warps to hide latency)
-constexpr int kPipeAllWarps = kPipeConsumerWarps * kPipeGroups;
+constexpr int kPipeGroups = 4;      // consumer groups; group g takes this CTA's units g, g+4, ...
+constexpr int kPipeGroupWarps = 4;  // warps that share one tile
+constexpr int kPipeAllWarps = kPipeGroupWarps * kPipeGroups;
 constexpr int kPipeConsumers = kPipeAllWarps * 32;
 constexpr int kPipeThreads = kPipeConsumers + 32;  // + the producer warp
 constexpr int kPipeMaxStages = 8;
-constexpr int kActRec = 336;       // one Q8_K activation superblock in shared memory (21 x 16 B: conflict-free lane stride)
+constexpr int kActRec = 336;       // one Q8_K activation superblock for Q4_K rows (21 x 16 B: conflict-free lane stride)
 constexpr int kRecBsum16 = 256;    // 16 x i16 sums of 16 codes
 constexpr int kRecBsum32 = 288;    // 8 x i16 sums of 32 codes
 constexpr int kRecD = 304;         // f32 scale
+// The same superblock for Q6_K rows: q6_k_wire_row_dot keeps eight accumulators by (index mod 8), so
+// the integer dot of a 16-value scale group is needed as eight pair sums x[l]*w[l] + x[l+8]*w[l+8].
+// Group j holds eight words: Ylo_k = [x(2k), x(2k+8), 0, 0] for k = 0..3, then Yhi_k =
+// [0, 0, x(2k+1), x(2k+9)]: a dp4a of the pair-interleaved weight word [w(2k), w(2k+8), w(2k+1),
+// w(2k+9)] with Ylo_k / Yhi_k is the pair sum for l = 2k / 2k+1.
+constexpr int kActRec6 = 528;      // 16 groups x 32 B + scale (33 x 16 B: conflict-free lane stride)
+constexpr int kRec6D = 512;
+constexpr int kTermBytes = 2048;   // per consumer warp: the terms of one pass over 32 blocks
+constexpr int kPieceBlocks = 32;   // superblocks (K-quants) per row in a piece
+constexpr int kPieceBlocks0 = 64;  // 32-value blocks (Q8_0) per row in a piece
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -89,6 +103,9 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {  // unsigned 
 struct PipeJob {
   const uint8_t *w;
   int32_t qt, rows, tile_rows, first_tile, n_tiles;
+  int32_t n_it;          // blocks (Q8_0) or superblocks (K-quants) per row
+  int32_t n_pieces;      // pieces a row is cut into
+  int32_t piece_blocks;  // blocks per piece (the last piece may be shorter)
   int64_t stride;
   float *y;
   const float *residual;
@@ -104,31 +121,57 @@ struct PipeArgs {
   float eps;
   const uint8_t *act_in;  // standard global layout, Q8_K rows (then Q8_0 rows at act_in0)
   const uint8_t *act_in0;
-  int32_t need_k, need_0;
-  int32_t paired;  // two matrices of equal shape and type: tiles alternate between them and the result is SwiGLU(first, second)
-  int32_t off_act_k, off_act_0, off_red, off_pair, off_ring;
+  int32_t need_k4, need_k6, need_0;
+  int32_t paired;  // two matrices of equal shape and type: the result is SwiGLU(first, second)
+  int32_t off_act_k, off_act_6, off_act_0, off_red, off_pair, off_term, off_ring;
   float *norm_out;        // optional f32 copy of the normalised row (written by CTA 0)
   int32_t *status;
   GemvPeer peer;          // tensor-parallel sum folded into this launch (tx_n / rx_n = 0: none)
   int64_t peer_rank_stride;  // floats between the ranks' partials in the receive slot
 };
 
+// One Q8_K chunk (the codes of 256 values, 8 per lane, scale d) into the shared-memory operand records.
+__device__ __forceinline__ void emit_q8k(uint2 pk, float d, int lane, bool k4, bool k6, uint8_t *rec4, uint8_t *rec6) {
+  if (k4) {
+    *reinterpret_cast<uint2 *>(rec4 + lane * 8) = pk;
+    int s16 = __dp4a((int)pk.y, 0x01010101, __dp4a((int)pk.x, 0x01010101, 0));
+    s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
+    if ((lane & 1) == 0) reinterpret_cast<short *>(rec4 + kRecBsum16)[lane >> 1] = (short)s16;
+    if ((lane & 3) == 0) reinterpret_cast<short *>(rec4 + kRecBsum32)[lane >> 2] = (short)s32;
+    if (lane == 0) *reinterpret_cast<float *>(rec4 + kRecD) = d;
+  }
+  if (k6) {
+    // a 16-value group lives in two neighbouring lanes: the even one holds values 0..7, the odd one 8..15
+    const uint32_t ox = __shfl_xor_sync(0xffffffffu, pk.x, 1), oy = __shfl_xor_sync(0xffffffffu, pk.y, 1);
+    const bool odd = lane & 1;
+    const uint32_t a0 = odd ? ox : pk.x, a1 = odd ? oy : pk.y, b0 = odd ? pk.x : ox, b1 = odd ? pk.y : oy;
+    uint4 o;
+    if (!odd) {  // Ylo_k = [x(2k), x(2k+8), 0, 0]
+      o.x = __byte_perm(a0, b0, 0x0040) & 0x0000ffffu;
+      o.y = __byte_perm(a0, b0, 0x0062) & 0x0000ffffu;
+      o.z = __byte_perm(a1, b1, 0x0040) & 0x0000ffffu;
+      o.w = __byte_perm(a1, b1, 0x0062) & 0x0000ffffu;
+    } else {     // Yhi_k = [0, 0, x(2k+1), x(2k+9)]
+      o.x = __byte_perm(a0, b0, 0x5100) & 0xffff0000u;
+      o.y = __byte_perm(a0, b0, 0x7300) & 0xffff0000u;
+      o.z = __byte_perm(a1, b1, 0x5100) & 0xffff0000u;
+      o.w = __byte_perm(a1, b1, 0x7300) & 0xffff0000u;
+    }
+    *reinterpret_cast<uint4 *>(rec6 + 32 * (lane >> 1) + 16 * (int)odd) = o;
+    if (lane == 0) *reinterpret_cast<float *>(rec6 + kRec6D) = d;
+  }
+}
+
 // Quantises one 256-value chunk (8 values per lane) of batch row b into the shared-memory operands.
 __device__ __forceinline__ void emit_chunk(const float (&v)[8], const PipeArgs &a, int b, int ch, int lane, uint8_t *act_k,
-                                           uint8_t *act_0, int rec_col_stride, int act0_col_stride) {
+                                           uint8_t *act_6, uint8_t *act_0, int nsb, int act0_col_stride) {
   const int e0 = ch * 256 + lane * 8;
-  if (a.need_k) {
+  if (a.need_k4 | a.need_k6) {
     int q[8];
     float d;
     q8k_quantise_chunk(v, lane, q, d);
-    uint8_t *rec = act_k + b * rec_col_stride + ch * kActRec;
-    *reinterpret_cast<uint2 *>(rec + lane * 8) = pack8(q);
-    int s16 = q[0] + q[1] + q[2] + q[3] + q[4] + q[5] + q[6] + q[7];
-    s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
-    const int s32 = s16 + __shfl_xor_sync(0xffffffffu, s16, 2);
-    if ((lane & 1) == 0) reinterpret_cast<short *>(rec + kRecBsum16)[lane >> 1] = (short)s16;
-    if ((lane & 3) == 0) reinterpret_cast<short *>(rec + kRecBsum32)[lane >> 2] = (short)s32;
-    if (lane == 0) *reinterpret_cast<float *>(rec + kRecD) = d;
+    emit_q8k(pack8(q), d, lane, a.need_k4 != 0, a.need_k6 != 0, act_k + (b * nsb + ch) * kActRec, act_6 + (b * nsb + ch) * kActRec6);
   }
   if (a.need_0) {
     int q[8];
@@ -141,21 +184,23 @@ __device__ __forceinline__ void emit_chunk(const float (&v)[8], const PipeArgs &
   }
 }
 
-constexpr int kRxChunks = 2;  // chunks a warp holds in registers in the receiving prologue: hidden <= 16 * 2 * 256
+constexpr int kRxChunks = 2;  // chunks a warp holds in registers in the norm prologue: hidden <= 16 * 2 * 256
 
-// ---------------------------------------------------------------- per-superblock dots (shared memory operands)
+// ---------------------------------------------------------------- per-superblock integer dots (shared memory operands)
 
+// Q4_K: S[b] = sum_g sc_g * dot32_g and P[b] = sum_g min_g * bsum32_g, the two integers of refmath.rs:504-562.
 template <int B>
-__device__ __forceinline__ void sb_dot_q4k(const uint8_t *blk, const uint8_t *rec, int rec_col_stride, float (&acc)[B]) {
+__device__ __forceinline__ void sb_ints_q4k(const uint8_t *blk, const uint8_t *rec, int rec_col_stride, int (&S)[B], int (&P)[B],
+                                            float &dw, float &dmw) {
   const uint4 meta = *reinterpret_cast<const uint4 *>(blk);
-  const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
+  dw = f16_bits_to_f32((uint16_t)(meta.x & 0xffff));
+  dmw = f16_bits_to_f32((uint16_t)(meta.x >> 16));
   // 6-bit scales/mins as bytes (q4_k_scale_min, src/tensor/mod.rs:5997-6006): groups 0..3 and 4..7
   const uint32_t sc03 = meta.y & 0x3f3f3f3fu, m03 = meta.z & 0x3f3f3f3fu;
   const uint32_t sc47 = (meta.w & 0x0f0f0f0fu) | ((meta.y >> 2) & 0x30303030u);
   const uint32_t m47 = ((meta.w >> 4) & 0x0f0f0f0fu) | ((meta.z >> 2) & 0x30303030u);
-  int s[B];
 #pragma unroll
-  for (int b = 0; b < B; ++b) s[b] = 0;
+  for (int b = 0; b < B; ++b) S[b] = 0;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     int dl[B], dh[B];
@@ -183,142 +228,233 @@ __device__ __forceinline__ void sb_dot_q4k(const uint8_t *blk, const uint8_t *re
     const uint32_t scw = j < 2 ? sc03 : sc47;
     const int sl = (scw >> (16 * (j & 1))) & 0xff, sh = (scw >> (16 * (j & 1) + 8)) & 0xff;
 #pragma unroll
-    for (int b = 0; b < B; ++b) s[b] += dl[b] * sl + (dh[b] >> 4) * sh;
+    for (int b = 0; b < B; ++b) S[b] += dl[b] * sl + (dh[b] >> 4) * sh;
   }
 #pragma unroll
   for (int b = 0; b < B; ++b) {
-    const uint8_t *r = rec + b * rec_col_stride;
-    const int4 bs = *reinterpret_cast<const int4 *>(r + kRecBsum32);  // 8 x i16 sums of 32 codes
+    const int4 bs = *reinterpret_cast<const int4 *>(rec + b * rec_col_stride + kRecBsum32);  // 8 x i16 sums of 32 codes
     int p = __dp2a_lo(bs.x, (int)m03, 0);
     p = __dp2a_hi(bs.y, (int)m03, p);
     p = __dp2a_lo(bs.z, (int)m47, p);
-    p = __dp2a_hi(bs.w, (int)m47, p);
-    const float xd = *reinterpret_cast<const float *>(r + kRecD);
-    // sumf = fma(-dmin, prod, sumf); sumf = fma(d, S, sumf)   (refmath.rs:529 and :560)
-    acc[b] = __fmaf_rn(__fmul_rn(xd, d), (float)s[b], __fmaf_rn(-__fmul_rn(xd, dmin), (float)p, acc[b]));
+    P[b] = __dp2a_hi(bs.w, (int)m47, p);
   }
 }
 
+// One 16-value scale group of a Q6_K superblock: n = its four code words as 4*(q-32) in natural
+// order.  aux[b][l] += sc * (pair sum l) * 4.
 template <int B>
-__device__ __forceinline__ void sb_dot_q6k(const uint8_t *blk, float dw, const uint8_t *rec, int rec_col_stride, float (&acc)[B]) {
-  const int4 scw = *reinterpret_cast<const int4 *>(blk + 192);  // 16 signed scales
-  int s[B];
+__device__ __forceinline__ void q6k_group(const uint4 &n, int sc, const uint8_t *y, int rec6_col_stride, int (&aux)[B][8]) {
+  const int v0 = (int)__byte_perm(n.x, n.z, 0x5140), v1 = (int)__byte_perm(n.x, n.z, 0x7362);
+  const int v2 = (int)__byte_perm(n.y, n.w, 0x5140), v3 = (int)__byte_perm(n.y, n.w, 0x7362);
 #pragma unroll
-  for (int b = 0; b < B; ++b) s[b] = 0;
+  for (int b = 0; b < B; ++b) {
+    const int4 ylo = *reinterpret_cast<const int4 *>(y + b * rec6_col_stride);
+    const int4 yhi = *reinterpret_cast<const int4 *>(y + b * rec6_col_stride + 16);
+    aux[b][0] += sc * __dp4a(v0, ylo.x, 0);
+    aux[b][1] += sc * __dp4a(v0, yhi.x, 0);
+    aux[b][2] += sc * __dp4a(v1, ylo.y, 0);
+    aux[b][3] += sc * __dp4a(v1, yhi.y, 0);
+    aux[b][4] += sc * __dp4a(v2, ylo.z, 0);
+    aux[b][5] += sc * __dp4a(v2, yhi.z, 0);
+    aux[b][6] += sc * __dp4a(v3, ylo.w, 0);
+    aux[b][7] += sc * __dp4a(v3, yhi.w, 0);
+  }
+}
+
+// Q6_K: aux[b][l] = 4 * sum_j sc_j * (x[16j+l]*a[16j+l] + x[16j+8+l]*a[16j+8+l]), the eight integers of
+// src/inference.rs:25560-25575 (times four: the signed codes are built as (q ^ 32) << 2, which is
+// 4*(q-32) as a signed byte, so no offset correction is needed).
+template <int B>
+__device__ __forceinline__ void sb_ints_q6k(const uint8_t *blk, const uint8_t *rec6, int rec6_col_stride, int (&aux)[B][8]) {
+  const int4 scw = *reinterpret_cast<const int4 *>(blk + 192);  // 16 signed scales
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+#pragma unroll
+    for (int l = 0; l < 8; ++l) aux[b][l] = 0;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
-      const uint4 qh = *reinterpret_cast<const uint4 *>(blk + 128 + 32 * h + 16 * c);
+      uint4 qh = *reinterpret_cast<const uint4 *>(blk + 128 + 32 * h + 16 * c);
+      // flip the top bit of every 2-bit field: q ^ 32
+      qh.x ^= 0xaaaaaaaau, qh.y ^= 0xaaaaaaaau, qh.z ^= 0xaaaaaaaau, qh.w ^= 0xaaaaaaaau;
 #pragma unroll
       for (int sp = 0; sp < 2; ++sp) {
         const uint4 ql = *reinterpret_cast<const uint4 *>(blk + 64 * h + 32 * sp + 16 * c);
         const int jlo = 8 * h + 2 * sp + c;  // 16-value group of the low-nibble stream; the high stream is jlo + 4
-        // 6-bit codes: low nibble | two qh bits moved to bits 4..5
+        const int sl = 6 - 2 * sp, sh = 2 - 2 * sp;  // field sp / field 2+sp of qh moved to bits 6..7
         uint4 lo, hi;
-        if (sp == 0) {
-          lo = make_uint4((ql.x & 0x0f0f0f0fu) | ((qh.x << 4) & 0x30303030u), (ql.y & 0x0f0f0f0fu) | ((qh.y << 4) & 0x30303030u),
-                          (ql.z & 0x0f0f0f0fu) | ((qh.z << 4) & 0x30303030u), (ql.w & 0x0f0f0f0fu) | ((qh.w << 4) & 0x30303030u));
-          hi = make_uint4(((ql.x >> 4) & 0x0f0f0f0fu) | (qh.x & 0x30303030u), ((ql.y >> 4) & 0x0f0f0f0fu) | (qh.y & 0x30303030u),
-                          ((ql.z >> 4) & 0x0f0f0f0fu) | (qh.z & 0x30303030u), ((ql.w >> 4) & 0x0f0f0f0fu) | (qh.w & 0x30303030u));
-        } else {
-          lo = make_uint4((ql.x & 0x0f0f0f0fu) | ((qh.x << 2) & 0x30303030u), (ql.y & 0x0f0f0f0fu) | ((qh.y << 2) & 0x30303030u),
-                          (ql.z & 0x0f0f0f0fu) | ((qh.z << 2) & 0x30303030u), (ql.w & 0x0f0f0f0fu) | ((qh.w << 2) & 0x30303030u));
-          hi = make_uint4(((ql.x >> 4) & 0x0f0f0f0fu) | ((qh.x >> 2) & 0x30303030u), ((ql.y >> 4) & 0x0f0f0f0fu) | ((qh.y >> 2) & 0x30303030u),
-                          ((ql.z >> 4) & 0x0f0f0f0fu) | ((qh.z >> 2) & 0x30303030u), ((ql.w >> 4) & 0x0f0f0f0fu) | ((qh.w >> 2) & 0x30303030u));
-        }
+        lo.x = ((ql.x << 2) & 0x3c3c3c3cu) | ((qh.x << sl) & 0xc0c0c0c0u);
+        lo.y = ((ql.y << 2) & 0x3c3c3c3cu) | ((qh.y << sl) & 0xc0c0c0c0u);
+        lo.z = ((ql.z << 2) & 0x3c3c3c3cu) | ((qh.z << sl) & 0xc0c0c0c0u);
+        lo.w = ((ql.w << 2) & 0x3c3c3c3cu) | ((qh.w << sl) & 0xc0c0c0c0u);
+        hi.x = ((ql.x >> 2) & 0x3c3c3c3cu) | ((qh.x << sh) & 0xc0c0c0c0u);
+        hi.y = ((ql.y >> 2) & 0x3c3c3c3cu) | ((qh.y << sh) & 0xc0c0c0c0u);
+        hi.z = ((ql.z >> 2) & 0x3c3c3c3cu) | ((qh.z << sh) & 0xc0c0c0c0u);
+        hi.w = ((ql.w >> 2) & 0x3c3c3c3cu) | ((qh.w << sh) & 0xc0c0c0c0u);
         const int wsel = jlo >> 2, bsel = jlo & 3;  // scale jlo is byte bsel of word wsel; jlo+4 is the same byte of the next word
         const int w_lo = wsel == 0 ? scw.x : (wsel == 1 ? scw.y : (wsel == 2 ? scw.z : scw.w));
         const int w_hi = wsel == 0 ? scw.y : (wsel == 1 ? scw.z : (wsel == 2 ? scw.w : 0));
         const int slo = (int)(int8_t)(w_lo >> (8 * bsel)), shi = (int)(int8_t)(w_hi >> (8 * bsel));
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-          const uint8_t *r = rec + b * rec_col_stride;
-          const int4 xlo = *reinterpret_cast<const int4 *>(r + 16 * jlo);
-          const int4 xhi = *reinterpret_cast<const int4 *>(r + 16 * (jlo + 4));
-          int dl = __dp4a((int)lo.x, xlo.x, 0);
-          dl = __dp4a((int)lo.y, xlo.y, dl);
-          dl = __dp4a((int)lo.z, xlo.z, dl);
-          dl = __dp4a((int)lo.w, xlo.w, dl);
-          int dh = __dp4a((int)hi.x, xhi.x, 0);
-          dh = __dp4a((int)hi.y, xhi.y, dh);
-          dh = __dp4a((int)hi.z, xhi.z, dh);
-          dh = __dp4a((int)hi.w, xhi.w, dh);
-          s[b] += slo * dl + shi * dh;
-        }
+        q6k_group<B>(lo, slo, rec6 + 32 * jlo, rec6_col_stride, aux);
+        q6k_group<B>(hi, shi, rec6 + 32 * (jlo + 4), rec6_col_stride, aux);
       }
     }
   }
-#pragma unroll
-  for (int b = 0; b < B; ++b) {
-    const uint8_t *r = rec + b * rec_col_stride;
-    // codes are stored +32: sum_j sc_j * sum (q-32) x = sum_j sc_j*dot_j - 32 * sum_j sc_j * bsum16_j
-    const int4 b0 = *reinterpret_cast<const int4 *>(r + kRecBsum16), b1 = *reinterpret_cast<const int4 *>(r + kRecBsum16 + 16);
-    int corr = __dp2a_lo(b0.x, scw.x, 0);
-    corr = __dp2a_hi(b0.y, scw.x, corr);
-    corr = __dp2a_lo(b0.z, scw.y, corr);
-    corr = __dp2a_hi(b0.w, scw.y, corr);
-    corr = __dp2a_lo(b1.x, scw.z, corr);
-    corr = __dp2a_hi(b1.y, scw.z, corr);
-    corr = __dp2a_lo(b1.z, scw.w, corr);
-    corr = __dp2a_hi(b1.w, scw.w, corr);
-    const float xd = *reinterpret_cast<const float *>(r + kRecD);
-    acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn(dw, xd), (float)(s[b] - 32 * corr)));
-  }
 }
 
-// Sum of v over each group of `len` consecutive lanes (groups start at multiples of len); the
-// result is valid in the first lane of each group.  Fixed order, so deterministic.
-__device__ __forceinline__ float segment_sum(float v, int lane_in_seg, int len) {
-  int cur = len;
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    if (off < cur) {
-      const float t = __shfl_down_sync(0xffffffffu, v, off);
-      if (lane_in_seg + off < cur) v += t;
-      cur = off;
-    }
+// Shape of a job's lane assignment: L lanes per row, rpw rows per warp.
+__device__ __forceinline__ int lanes_per_row(int n_it) { return n_it < 32 ? n_it : 32; }
+
+// The chain lanes.  After tile_dot, res[k] of a chain lane is a finished or running row sum; this says which
+// (row of the tile, batch column) it belongs to.  Q4_K: rounds of up to 4 columns; Q8_0: one round of all
+// columns; Q6_K: rounds of 2 columns (at most two rows per warp), eight lanes per (row, column), result in the first of them.
+template <int B>
+__device__ __forceinline__ bool chain_slot(int qt, int n_it, int k, int lane, int &r, int &b) {
+  const int rpw = 32 / lanes_per_row(n_it);
+  if (qt == CMLD_Q4_K) {
+    const int nb = min(4, B - 4 * k);
+    if (nb <= 0 || lane >= rpw * nb) return false;
+    r = lane / nb;
+    b = 4 * k + lane % nb;
+    return true;
   }
-  return v;
+  if (qt == CMLD_Q6_K) {
+    const int nb = min(2, B - 2 * k);
+    if (nb <= 0 || lane >= rpw * nb * 8 || (lane & 7)) return false;
+    r = (lane >> 3) / nb;
+    b = 2 * k + (lane >> 3) % nb;
+    return true;
+  }
+  if (k != 0 || lane >= rpw * B) return false;
+  r = lane / B;
+  b = lane % B;
+  return true;
 }
 
-// Dot products of one staged tile: on return v[b] holds row r_local's result for batch column b in the
-// lanes with `writer` set (the first lane of each row's lane segment).
+// One staged piece: rows wg*rpw .. of the tile, blocks [it0, it0+cnt_it) of each.  res[] carries the chain
+// lanes' running sums from piece to piece; `last` finishes them (Q6_K: the left-to-right sum of the eight).
+// Piece layout in the stage: whole rows (stride J.stride) when the job has one piece; else per row
+// [blocks | scales]: Q4_K cnt*144; Q6_K cnt*208 then cnt f16 d; Q8_0 cnt*32 codes then cnt f16 scales.
 template <int B>
 __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, const uint8_t *tile, int nrows, int wg, int lane,
-                                         const uint8_t *act_k, const uint8_t *act_0, int nsb, int rec_col_stride,
-                                         int act0_col_stride, float (&v)[B], bool &writer, int &r_local) {
-  const int n_it = J.qt == CMLD_Q8_0 ? (a.cols >> 5) : nsb;  // work items per row: blocks or superblocks
-  const int L = n_it < 32 ? n_it : 32;                        // lanes per row
-  const int rpw = 32 / L;                                     // rows per warp
-  r_local = wg * rpw + lane / L;
-  const int lis = lane % L;
-  const bool active = lane < rpw * L && r_local < nrows;
-  float acc[B];
+                                         int it0, int cnt_it, bool last, const uint8_t *act_k, const uint8_t *act_6,
+                                         const uint8_t *act_0, int nsb, int act0_col_stride, float *tb, float (&res)[B]) {
+  const int L = lanes_per_row(J.n_it), rpw = 32 / L;
+  const int lis = lane % L, r_local = wg * rpw + lane / L;
+  const bool row_ok = lane < rpw * L && r_local < nrows;
+  const int rec_col_stride = nsb * kActRec, rec6_col_stride = nsb * kActRec6;
+  const bool whole = J.n_pieces == 1;
+  if (J.qt == CMLD_Q4_K) {
+    const int row_bytes = whole ? (int)J.stride : cnt_it * 144;
+    const uint8_t *row = tile + (int64_t)r_local * row_bytes;
+    float4 *t4 = reinterpret_cast<float4 *>(tb);
+    constexpr int R = (B + 3) / 4;
+    for (int p0 = 0; p0 < cnt_it; p0 += 32) {
+      const int i = p0 + lis, cnt = min(L, cnt_it - p0);
+      const bool act = row_ok && i < cnt_it;
+      int S[B], P[B];
+      float dw = 0.0f, dmw = 0.0f;
+      if (act) sb_ints_q4k<B>(row + i * 144, act_k + (it0 + i) * kActRec, rec_col_stride, S, P, dw, dmw);
 #pragma unroll
-  for (int b = 0; b < B; ++b) acc[b] = 0.0f;
-  if (active) {
-    const uint8_t *row = tile + (int64_t)r_local * J.stride;
-    if (J.qt == CMLD_Q4_K) {
-      for (int sb = lis; sb < nsb; sb += L) sb_dot_q4k<B>(row + sb * 144, act_k + sb * kActRec, rec_col_stride, acc);
-    } else if (J.qt == CMLD_Q6_K) {
-      for (int sb = lis; sb < nsb; sb += L) {
-        const float dw = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + nsb * 208 + 2 * sb));
-        sb_dot_q6k<B>(row + sb * 208, dw, act_k + sb * kActRec, rec_col_stride, acc);
+      for (int k = 0; k < R; ++k) {
+        const int nb = (B - 4 * k) < 4 ? (B - 4 * k) : 4;
+        if (act) {
+#pragma unroll
+          for (int bb = 0; bb < nb; ++bb) {
+            const int b = 4 * k + bb;
+            const float xd = *reinterpret_cast<const float *>(act_k + b * rec_col_stride + (it0 + i) * kActRec + kRecD);
+            // sumf = fma(-dmin, prod, sumf); sumf = fma(d, S, sumf) with d = xd*dw, dmin = xd*dminw (refmath.rs:529, :560)
+            t4[lane * nb + bb] = make_float4(__fmul_rn(xd, dw), (float)S[b], -__fmul_rn(xd, dmw), (float)P[b]);
+          }
+        }
+        __syncwarp();
+        if (lane < rpw * nb) {
+          const int r = lane / nb, bb = lane % nb;
+          if (wg * rpw + r < nrows) {
+            float s = res[k];
+            for (int j = 0; j < cnt; ++j) {
+              const float4 t = t4[(r * L + j) * nb + bb];
+              s = __fmaf_rn(t.z, t.w, s);
+              s = __fmaf_rn(t.x, t.y, s);
+            }
+            res[k] = s;
+          }
+        }
+        __syncwarp();
       }
-    } else {
-      // Q8_0: a lane owns 32-value blocks; the two 16-byte halves are read in an order that
-      // keeps the eight lanes of a shared-memory phase on distinct banks
-      const int hs = (lane >> 2) & 1;
-      for (int blk = lis; blk < n_it; blk += L) {
-        const uint4 w0 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * hs);
-        const uint4 w1 = *reinterpret_cast<const uint4 *>(row + blk * 32 + 16 * (hs ^ 1));
-        const float ws = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(row + a.cols + 2 * blk));
+    }
+  } else if (J.qt == CMLD_Q6_K) {
+    const int row_bytes = whole ? (int)J.stride : (int)round_up16(cnt_it * 208 + cnt_it * 2);
+    const uint8_t *row = tile + (int64_t)r_local * row_bytes;
+    const uint16_t *dws = reinterpret_cast<const uint16_t *>(row + (whole ? J.n_it : cnt_it) * 208);
+    constexpr int R = (B + 1) / 2;
+    for (int p0 = 0; p0 < cnt_it; p0 += 32) {
+      const int i = p0 + lis, cnt = min(L, cnt_it - p0);
+      const bool act = row_ok && i < cnt_it;
+      int aux[B][8];
+      float dw = 0.0f;
+      if (act) {
+        sb_ints_q6k<B>(row + i * 208, act_6 + (it0 + i) * kActRec6, rec6_col_stride, aux);
+        dw = f16_bits_to_f32(dws[i]);
+      }
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        const int nb = (B - 2 * k) < 2 ? (B - 2 * k) : 2;
+        if (act) {
+#pragma unroll
+          for (int bb = 0; bb < nb; ++bb) {
+            const int b = 2 * k + bb;
+            const float xd = *reinterpret_cast<const float *>(act_6 + b * rec6_col_stride + (it0 + i) * kActRec6 + kRec6D);
+            const float dd = __fmul_rn(dw, xd);  // src/inference.rs:25545
+            // sums[l] += dd * (float)aux[l]: the product here, the addition in block order by the chain lanes
+            float4 *dst = reinterpret_cast<float4 *>(tb + (lane * nb + bb) * 8);
+            dst[0] = make_float4(__fmul_rn(dd, (float)(aux[b][0] >> 2)), __fmul_rn(dd, (float)(aux[b][1] >> 2)),
+                                 __fmul_rn(dd, (float)(aux[b][2] >> 2)), __fmul_rn(dd, (float)(aux[b][3] >> 2)));
+            dst[1] = make_float4(__fmul_rn(dd, (float)(aux[b][4] >> 2)), __fmul_rn(dd, (float)(aux[b][5] >> 2)),
+                                 __fmul_rn(dd, (float)(aux[b][6] >> 2)), __fmul_rn(dd, (float)(aux[b][7] >> 2)));
+          }
+        }
+        __syncwarp();
+        if (lane < rpw * nb * 8) {
+          const int l = lane & 7, r = (lane >> 3) / nb, bb = (lane >> 3) % nb;
+          if (wg * rpw + r < nrows) {
+            float s = res[k];
+            for (int j = 0; j < cnt; ++j) s = __fadd_rn(s, tb[((r * L + j) * nb + bb) * 8 + l]);
+            res[k] = s;
+          }
+        }
+        __syncwarp();
+      }
+    }
+    if (last) {
+#pragma unroll
+      for (int k = 0; k < R; ++k) {
+        float tot = 0.0f;  // 0 + sums[0] + sums[1] + ... (src/inference.rs:25578-25580)
+#pragma unroll
+        for (int l = 0; l < 8; ++l) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, res[k], (lane & ~7) + l));
+        res[k] = tot;
+      }
+    }
+  } else {
+    // Q8_0: a lane owns 32-value blocks
+    const int row_bytes = whole ? (int)J.stride : (int)round_up16(cnt_it * 32 + cnt_it * 2);
+    const uint8_t *row = tile + (int64_t)r_local * row_bytes;
+    const uint16_t *wss = reinterpret_cast<const uint16_t *>(row + (whole ? a.cols : cnt_it * 32));
+    for (int p0 = 0; p0 < cnt_it; p0 += 32) {
+      const int i = p0 + lis, cnt = min(L, cnt_it - p0);
+      const bool act = row_ok && i < cnt_it;
+      if (act) {
+        // the two 16-byte halves are read in an order that keeps the eight lanes of a shared-memory phase on distinct banks
+        const int hs = (lane >> 2) & 1;
+        const uint4 w0 = *reinterpret_cast<const uint4 *>(row + i * 32 + 16 * hs);
+        const uint4 w1 = *reinterpret_cast<const uint4 *>(row + i * 32 + 16 * (hs ^ 1));
+        const float ws = f16_bits_to_f32(wss[i]);
 #pragma unroll
         for (int b = 0; b < B; ++b) {
           const uint8_t *xa = act_0 + b * act0_col_stride;
-          const int4 x0 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * hs);
-          const int4 x1 = *reinterpret_cast<const int4 *>(xa + blk * 32 + 16 * (hs ^ 1));
+          const int4 x0 = *reinterpret_cast<const int4 *>(xa + (it0 + i) * 32 + 16 * hs);
+          const int4 x1 = *reinterpret_cast<const int4 *>(xa + (it0 + i) * 32 + 16 * (hs ^ 1));
           int isum = __dp4a((int)w0.x, x0.x, 0);
           isum = __dp4a((int)w0.y, x0.y, isum);
           isum = __dp4a((int)w0.z, x0.z, isum);
@@ -327,15 +463,39 @@ __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, co
           isum = __dp4a((int)w1.y, x1.y, isum);
           isum = __dp4a((int)w1.z, x1.z, isum);
           isum = __dp4a((int)w1.w, x1.w, isum);
-          const float xs = reinterpret_cast<const float *>(xa + round_up16(a.cols))[blk];
-          acc[b] = __fadd_rn(acc[b], __fmul_rn(__fmul_rn((float)isum, ws), xs));  // src/inference.rs:26198
+          const float xs = reinterpret_cast<const float *>(xa + round_up16(a.cols))[it0 + i];
+          tb[b * 32 + lane] = __fmul_rn(__fmul_rn((float)isum, ws), xs);  // src/inference.rs:26198
         }
       }
+      __syncwarp();
+      if (lane < rpw * B) {
+        const int r = lane / B, bb = lane % B;
+        if (wg * rpw + r < nrows) {
+          float s = res[0];
+          for (int j = 0; j < cnt; ++j) s = __fadd_rn(s, tb[bb * 32 + r * L + j]);
+          res[0] = s;
+        }
+      }
+      __syncwarp();
     }
   }
-#pragma unroll
-  for (int b = 0; b < B; ++b) v[b] = segment_sum(acc[b], lis, L);
-  writer = active && lis == 0;
+}
+
+// Where unit i of a CTA's sequence lies: units come in rounds of kPipeGroups tiles (one per group), the
+// pieces of a group's tile one after another, so that unit i always belongs to group i % kPipeGroups and a
+// group meets the pieces of its tile in order.  Returns the index of the tile in this CTA's list.
+__device__ __forceinline__ int unit_tile(int i, int n_pieces, int &piece) {
+  const int per_round = kPipeGroups * n_pieces;
+  piece = (i % per_round) / kPipeGroups;
+  return (i / per_round) * kPipeGroups + i % kPipeGroups;
+}
+
+// Job and first row of tile t of the launch (the jobs' tiles are numbered one after another).
+__device__ __forceinline__ int tile_job(const PipeArgs &a, int t) {
+  int j = 0;
+  if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
+  if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+  return j;
 }
 
 // ---------------------------------------------------------------- the kernel
@@ -346,19 +506,24 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + kPipeMaxStages;
   uint8_t *act_k = smem + a.off_act_k;
+  uint8_t *act_6 = smem + a.off_act_6;
   uint8_t *act_0 = smem + a.off_act_0;
   float *red = reinterpret_cast<float *>(smem + a.off_red);
   uint8_t *ring = smem + a.off_ring;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = a.n_stages;
-  // tiles this CTA takes: t = blockIdx.x + i*gridDim.x; in paired mode the unit is a (gate, up) pair of tiles
-  const int n_units = a.paired ? a.job[0].n_tiles : a.total_tiles;
-  const int n_my = ((int)blockIdx.x < n_units ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0) * (a.paired ? 2 : 1);
+  // Tiles this CTA takes: t = blockIdx.x + k*gridDim.x.  In paired mode the unit of distribution is a pair of
+  // tiles (the same rows of the two matrices), which occupies two neighbouring groups.
+  const int n_dist = a.paired ? a.job[0].n_tiles : a.total_tiles;
+  const int n_mine = (int)blockIdx.x < n_dist ? (n_dist - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int n_my_tiles = a.paired ? 2 * n_mine : n_mine;  // entries of this CTA's tile list
+  const int n_pieces = a.job[0].n_pieces;                 // the same for every job of a launch
+  const int n_units = ((n_my_tiles + kPipeGroups - 1) / kPipeGroups) * kPipeGroups * n_pieces;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kPipeConsumerWarps);
+      mbar_init(&empty[s], kPipeGroupWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -380,24 +545,42 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   if (warp == kPipeAllWarps) {
     // ---------------- producer: weights do not depend on the previous kernel, so no wait here
     if (lane == 0) {
-      for (int i = 0; i < n_my; ++i) {
+      for (int i = 0; i < n_units; ++i) {
+        int piece;
+        const int tl = unit_tile(i, n_pieces, piece);
+        if (tl >= n_my_tiles) continue;  // the last round may be short (only at the end of the sequence)
         const int s = i % S;
         if (i >= S) mbar_wait(&empty[s], (uint32_t)((i / S - 1) & 1), a.status);
-        int j = 0, row0;
+        int j, row0;
         if (a.paired) {
-          j = i & 1;
-          row0 = ((int)blockIdx.x + (i >> 1) * (int)gridDim.x) * a.job[0].tile_rows;
+          j = tl & 1;
+          row0 = ((int)blockIdx.x + (tl >> 1) * (int)gridDim.x) * a.job[0].tile_rows;
         } else {
-          const int t = (int)blockIdx.x + i * (int)gridDim.x;
-          if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
-          if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
+          const int t = (int)blockIdx.x + tl * (int)gridDim.x;
+          j = tile_job(a, t);
           row0 = (t - a.job[j].first_tile) * a.job[j].tile_rows;
         }
         const PipeJob &J = a.job[j];
         const int nrows = min(J.tile_rows, J.rows - row0);
-        const uint32_t bytes = (uint32_t)(nrows * J.stride);
-        mbar_expect_tx(&full[s], bytes);
-        bulk_g2s(ring + (int64_t)s * a.stage_bytes, J.w + (int64_t)row0 * J.stride, bytes, &full[s]);
+        uint8_t *dst = ring + (int64_t)s * a.stage_bytes;
+        if (J.n_pieces == 1) {
+          const uint32_t bytes = (uint32_t)(nrows * J.stride);
+          mbar_expect_tx(&full[s], bytes);
+          bulk_g2s(dst, J.w + (int64_t)row0 * J.stride, bytes, &full[s]);
+        } else {
+          const int it0 = piece * J.piece_blocks, cnt = min(J.piece_blocks, J.n_it - it0);
+          // per row: the piece's blocks, then its per-block scales (Q6_K, Q8_0), at a 16-byte aligned row pitch
+          const int blk = J.qt == CMLD_Q4_K ? 144 : (J.qt == CMLD_Q6_K ? 208 : 32);
+          const int main_bytes = cnt * blk, sc_bytes = J.qt == CMLD_Q4_K ? 0 : cnt * 2;
+          const int pitch = (int)round_up16(main_bytes + sc_bytes);
+          const int64_t sc_off = J.qt == CMLD_Q6_K ? (int64_t)J.n_it * 208 : a.cols;
+          mbar_expect_tx(&full[s], (uint32_t)(nrows * (main_bytes + sc_bytes)));
+          for (int r = 0; r < nrows; ++r) {
+            const uint8_t *src = J.w + (int64_t)(row0 + r) * J.stride;
+            bulk_g2s(dst + r * pitch, src + (int64_t)it0 * blk, (uint32_t)main_bytes, &full[s]);
+            if (sc_bytes) bulk_g2s(dst + r * pitch + main_bytes, src + sc_off + it0 * 2, (uint32_t)sc_bytes, &full[s]);
+          }
+        }
       }
     }
     return;
@@ -407,7 +590,6 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   asm volatile("griddepcontrol.wait;" ::: "memory");  // inputs written by the previous kernel are now visible
   if (tr) tr[1] = global_ns();
   const int nsb = a.cols >> 8;
-  const int rec_col_stride = nsb * kActRec;
   const int act0_col_stride = (int)round_up16(a.cols) + (int)round_up16((a.cols >> 5) * 4);
 
   if (a.peer.rx_n > 0) {
@@ -419,26 +601,14 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 
   // Prologue: quantised activation rows into shared memory.
   if (a.mode == 0) {
-    // re-lay the pre-quantised global rows; flat loops over (row, piece) so that every thread has several
-    // independent loads in flight instead of one L2 round trip per row
+    // re-lay the pre-quantised global rows
     const int64_t astride = act_row_stride(a.cols);
-    if (a.need_k) {
-      for (int idx = tid; idx < a.batch * nsb * 16; idx += kPipeConsumers) {  // 16-byte chunks of codes
-        const int b = idx / (nsb * 16), i = idx % (nsb * 16), sb = i >> 4, c = i & 15;
-        *reinterpret_cast<uint4 *>(act_k + b * rec_col_stride + sb * kActRec + c * 16) =
-            __ldg(reinterpret_cast<const uint4 *>(a.act_in + b * astride + sb * 256 + c * 16));
-      }
-      for (int idx = tid; idx < a.batch * nsb * 8; idx += kPipeConsumers) {  // pairs of 16-sums
-        const int b = idx / (nsb * 8), i = idx % (nsb * 8), sb = i >> 3, g = i & 7;
-        const int pr = __ldg(reinterpret_cast<const int *>(a.act_in + b * astride + act_bsum_off(a.cols)) + i);
-        uint8_t *rec = act_k + b * rec_col_stride + sb * kActRec;
-        reinterpret_cast<int *>(rec + kRecBsum16)[g] = pr;
-        reinterpret_cast<short *>(rec + kRecBsum32)[g] = (short)((int)(short)(pr & 0xffff) + (pr >> 16));
-      }
-      for (int idx = tid; idx < a.batch * nsb; idx += kPipeConsumers) {
-        const int b = idx / nsb, sb = idx % nsb;
-        *reinterpret_cast<float *>(act_k + b * rec_col_stride + sb * kActRec + kRecD) =
-            __ldg(reinterpret_cast<const float *>(a.act_in + b * astride + act_scale_off(a.cols)) + sb);
+    if (a.need_k4 | a.need_k6) {
+      for (int idx = warp; idx < a.batch * nsb; idx += kPipeAllWarps) {
+        const int b = idx / nsb, ch = idx % nsb;
+        const uint2 pk = __ldg(reinterpret_cast<const uint2 *>(a.act_in + b * astride + ch * 256) + lane);
+        const float d = __ldg(reinterpret_cast<const float *>(a.act_in + b * astride + act_scale_off(a.cols)) + ch);
+        emit_q8k(pk, d, lane, a.need_k4 != 0, a.need_k6 != 0, act_k + idx * kActRec, act_6 + idx * kActRec6);
       }
     }
     if (a.need_0) {
@@ -456,14 +626,14 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   }
   const bool chunked_norm = a.mode == 1 && (a.cols & 255) == 0 && a.cols <= kRxChunks * kPipeAllWarps * 256;
   for (int b = 0; b < a.batch; ++b) {
-    if (a.peer.rx_n > 0 || chunked_norm) {
+    if (chunked_norm) {
       // RMSNorm with ONE load of the row: each warp keeps its chunks in registers between the mean-square
-      // pass and the scaling pass.  The squares are added per lane over the warp's chunks, by the shuffle
-      // tree within the warp, then the sixteen warp sums by one more shuffle tree — the order the
-      // stand-alone norm kernel reproduces, so both give the same bits.  With a peer sum the row is the sum
+      // pass and the scaling pass.  The squares are summed with the bits of the CPU's one-accumulator loop
+      // (rms_norm_into, src/tensor/mod.rs:2740-2764; see exact_sum.cuh).  With a peer sum the row is the sum
       // of the ranks' partial rows (added in rank order, so every rank gets the same bits).
+      float *sq = reinterpret_cast<float *>(smem + a.off_term);  // the term buffers are idle during the prologue
+      uint8_t *ws = smem + a.off_term + a.cols * 4;
       float hv[kRxChunks][8];
-      float ss = 0.0f;
 #pragma unroll
       for (int k = 0; k < kRxChunks; ++k) {
         const int ch = warp + k * kPipeAllWarps;
@@ -477,11 +647,13 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
             s1.x = __fadd_rn(s1.x, t1.x), s1.y = __fadd_rn(s1.y, t1.y), s1.z = __fadd_rn(s1.z, t1.z), s1.w = __fadd_rn(s1.w, t1.w);
           }
           const float t[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+          float4 q0, q1;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            hv[k][i] = t[i];
-            ss = __fmaf_rn(t[i], t[i], ss);
-          }
+          for (int i = 0; i < 8; ++i) hv[k][i] = t[i];
+          q0 = make_float4(__fmul_rn(t[0], t[0]), __fmul_rn(t[1], t[1]), __fmul_rn(t[2], t[2]), __fmul_rn(t[3], t[3]));
+          q1 = make_float4(__fmul_rn(t[4], t[4]), __fmul_rn(t[5], t[5]), __fmul_rn(t[6], t[6]), __fmul_rn(t[7], t[7]));
+          reinterpret_cast<float4 *>(sq + ch * 256 + lane * 8)[0] = q0;
+          reinterpret_cast<float4 *>(sq + ch * 256 + lane * 8)[1] = q1;
           if (blockIdx.x == 0 && a.peer.rx_out) {
             float4 *o4 = reinterpret_cast<float4 *>(a.peer.rx_out + (int64_t)b * a.cols + ch * 256 + lane * 8);
             o4[0] = s0;
@@ -489,13 +661,11 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
           }
         }
       }
-      ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
-      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
-      float t = lane < kPipeAllWarps ? red[lane] : 0.0f;
-      t = warp_sum(t);
-      const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
-      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
+      const int nch = a.cols >> 8;
+      const float ss = xsum::cta_sum<kPipeAllWarps>(sq, a.cols, warp, lane, 1, reinterpret_cast<double *>(ws),
+                                                    reinterpret_cast<uint32_t *>(ws + nch * 8),
+                                                    reinterpret_cast<xsum::Item *>(ws + nch * 16), red);
+      const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.cols), a.eps)));
 #pragma unroll
       for (int k = 0; k < kRxChunks; ++k) {
         const int ch = warp + k * kPipeAllWarps;
@@ -511,9 +681,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
             o4[0] = make_float4(v[0], v[1], v[2], v[3]);
             o4[1] = make_float4(v[4], v[5], v[6], v[7]);
           }
-          emit_chunk(v, a, b, ch, lane, act_k, act_0, rec_col_stride, act0_col_stride);
+          emit_chunk(v, a, b, ch, lane, act_k, act_6, act_0, nsb, act0_col_stride);
         }
       }
+      asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));  // sq is reused by the next row
       continue;
     }
     if (a.mode == 0) continue;  // copied above
@@ -521,21 +692,17 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const float *x2 = a.mode == 3 ? a.x2 + (int64_t)b * a.x_stride : nullptr;
     float scale = 1.0f;
     if (a.mode == 1) {
-      // the mean square is summed by the first 256 threads in the same order as the stand-alone
-      // norm kernel, so both paths produce the same bits
-      float ss = 0.0f;
-      if (tid < 256)
-#pragma unroll 8
-        for (int i = tid; i < a.cols; i += 256) {
+      // a width the chunked form does not take: the CPU's loop itself, by one thread
+      if (tid == 0) {
+        float t = 0.0f;
+        for (int i = 0; i < a.cols; ++i) {
           const float v = __ldcg(x + i);
-          ss = __fmaf_rn(v, v, ss);
+          t = __fadd_rn(t, __fmul_rn(v, v));
         }
-      ss = warp_sum(ss);
-      if (lane == 0 && warp < 8) red[warp] = ss;
+        red[0] = t;
+      }
       asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
-      float t = lane < 8 ? red[lane] : 0.0f;
-      t = warp_sum(t);
-      scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+      scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(red[0], (float)a.cols), a.eps)));
       asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
     }
     const int n_chunks = (a.cols + 255) >> 8;
@@ -569,81 +736,86 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.0f;
       }
-      emit_chunk(v, a, b, ch, lane, act_k, act_0, rec_col_stride, act0_col_stride);
+      emit_chunk(v, a, b, ch, lane, act_k, act_6, act_0, nsb, act0_col_stride);
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
   if (tr) tr[3] = global_ns();
 
-  // Main loop over this CTA's tiles; the two consumer groups alternate.
-  const int group = warp / kPipeConsumerWarps, wg = warp % kPipeConsumerWarps;
-  if (a.paired) {
-    // gate and up tiles of the same rows are consecutive tiles 2k, 2k+1 of this CTA: group 0 takes the gate tile,
-    // group 1 the up tile, at the same time; group 1 hands its results over through shared memory (two
-    // buffers, one barrier of all consumers per pair) and group 0 writes SwiGLU(gate, up) — the f32 operand
-    // of the down projection — so neither product goes through memory on its own.
-    float *pairbuf = reinterpret_cast<float *>(smem + a.off_pair);  // [2][tile_rows][B]
-    const int tile_rows = a.job[0].tile_rows;
-    for (int k = 0; 2 * k < n_my; ++k) {
-      const int pair = (int)blockIdx.x + k * (int)gridDim.x;
-      const int row0 = pair * tile_rows;
-      const int nrows = min(tile_rows, a.job[0].rows - row0);
-      const int i = 2 * k + group, s = i % S;
-      const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-      float v[B];
-      bool writer = false;
-      int r_local = 0;
-      if (ready) {
-        tile_dot<B>(a, a.job[group], ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride,
-                    act0_col_stride, v, writer, r_local);
-      } else {
-#pragma unroll
-        for (int b = 0; b < B; ++b) v[b] = 0.0f;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
-      float *slot = pairbuf + ((k & 1) * tile_rows + r_local) * B;
-      if (group == 1 && writer) {
-#pragma unroll
-        for (int b = 0; b < B; ++b) slot[b] = v[b];
-      }
-      asm volatile("bar.sync 2, %0;" ::"n"(kPipeConsumers));
-      if (group == 0 && writer) {
-#pragma unroll
-        for (int b = 0; b < B; ++b) a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + r_local] = swiglu(v[b], slot[b]);
-      }
+  // Main loop over this CTA's units; group g takes units g, g + kPipeGroups, ...
+  const int group = warp / kPipeGroupWarps, wg = warp % kPipeGroupWarps;
+  float *tb = reinterpret_cast<float *>(smem + a.off_term + warp * kTermBytes);
+  float *pairbuf = reinterpret_cast<float *>(smem + a.off_pair);  // paired mode: [pair slot][tile_rows][B]
+  float res[B];
+  int done_pairs = 0;
+  for (int i = group; i < n_units; i += kPipeGroups) {
+    int piece;
+    const int tl = unit_tile(i, n_pieces, piece);
+    if (tl >= n_my_tiles) break;
+    const int s = i % S;
+    int j, row0;
+    if (a.paired) {
+      j = tl & 1;
+      row0 = ((int)blockIdx.x + (tl >> 1) * (int)gridDim.x) * a.job[0].tile_rows;
+    } else {
+      const int t = (int)blockIdx.x + tl * (int)gridDim.x;
+      j = tile_job(a, t);
+      row0 = (t - a.job[j].first_tile) * a.job[j].tile_rows;
     }
-  } else {
-    for (int i = group; i < n_my; i += kPipeGroups) {
-      const int s = i % S;
-      const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-      const int t = (int)blockIdx.x + i * (int)gridDim.x;
-      int j = 0;
-      if (a.n_jobs > 1 && t >= a.job[1].first_tile) j = 1;
-      if (a.n_jobs > 2 && t >= a.job[2].first_tile) j = 2;
-      const PipeJob &J = a.job[j];
-      const int row0 = (t - J.first_tile) * J.tile_rows;
-      const int nrows = min(J.tile_rows, J.rows - row0);
-      if (ready) {
-        float v[B];
-        bool writer;
-        int r_local;
-        tile_dot<B>(a, J, ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, act_k, act_0, nsb, rec_col_stride, act0_col_stride, v, writer, r_local);
-        if (writer) {
+    const PipeJob &J = a.job[j];
+    const int nrows = min(J.tile_rows, J.rows - row0);
+    const int it0 = piece * J.piece_blocks, cnt_it = min(J.piece_blocks, J.n_it - it0);
+    const bool last = piece == J.n_pieces - 1;
+    if (piece == 0) {
 #pragma unroll
-          for (int b = 0; b < B; ++b) {
-            const int64_t o = (int64_t)b * J.y_stride + row0 + r_local;
-            const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), v[b]) : v[b];
-            if (a.peer.tx_n > 0) {
-              for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
-            } else {
-              J.y[o] = out;
-            }
+      for (int k = 0; k < B; ++k) res[k] = 0.0f;
+    }
+    const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+    if (ready)
+      tile_dot<B>(a, J, ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, it0, cnt_it, last, act_k, act_6, act_0, nsb,
+                  act0_col_stride, tb, res);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+    if (!last) continue;
+    const int rpw = 32 / lanes_per_row(J.n_it);
+    if (a.paired) {
+      // groups 2p (first matrix) and 2p+1 (second) hold the same rows: the second hands its results over through
+      // shared memory (double-buffered, one barrier of the two groups per pair) and the first writes
+      // SwiGLU(first, second) — the f32 operand of the down projection — so neither product goes through memory.
+      const int slot = group >> 1;
+      float *buf = pairbuf + ((slot * 2 + (done_pairs & 1)) * J.tile_rows) * B;
+      if (group & 1) {
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          int r, b;
+          if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wg * rpw + r < nrows) buf[(wg * rpw + r) * B + b] = res[k];
+        }
+      }
+      if (slot == 0) asm volatile("bar.sync 2, %0;" ::"n"(2 * kPipeGroupWarps * 32));
+      else asm volatile("bar.sync 3, %0;" ::"n"(2 * kPipeGroupWarps * 32));
+      if (!(group & 1)) {
+#pragma unroll
+        for (int k = 0; k < B; ++k) {
+          int r, b;
+          if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wg * rpw + r < nrows)
+            a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + wg * rpw + r] = swiglu(res[k], buf[(wg * rpw + r) * B + b]);
+        }
+      }
+      ++done_pairs;
+    } else if (ready) {
+#pragma unroll
+      for (int k = 0; k < B; ++k) {
+        int r, b;
+        if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wg * rpw + r < nrows) {
+          const int64_t o = (int64_t)b * J.y_stride + row0 + wg * rpw + r;
+          const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), res[k]) : res[k];
+          if (a.peer.tx_n > 0) {
+            for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
+          } else {
+            J.y[o] = out;
           }
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);
     }
   }
   if (tr) tr[4] = global_ns();
@@ -700,29 +872,42 @@ static int32_t launch_pipe_b(const PipePlan &p, int grid, cudaStream_t s, bool p
 }
 
 // Tile geometry and shared-memory map for these matrices at this batch; false if it does not fit.
-static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &p, bool &need_k, bool &need_0, int &tiles_out,
-                      bool paired = false) {
+static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &p, bool &need_k4, bool &need_k6, bool &need_0,
+                      int &tiles_out, bool paired, bool norm) {
   if (n_jobs < 1 || n_jobs > 3 || batch < 1 || batch > 8) return false;
   const int64_t cols = jobs[0].cols;
   if (cols % 32) return false;
   PipeArgs &a = p.args;
-  need_k = need_0 = false;
-  int stage = 0, tiles = 0;
+  need_k4 = need_k6 = need_0 = false;
+  int stage = 0, tiles = 0, n_pieces = -1;
   for (int k = 0; k < n_jobs; ++k) {
     const GemvJob &g = jobs[k];
     if (g.cols != cols) return false;
-    if (g.qt == CMLD_Q8_0) need_0 = true;
-    else {
-      need_k = true;
-      if (cols % 256) return false;
-    }
     const int n_it = g.qt == CMLD_Q8_0 ? (int)(cols >> 5) : (int)(cols >> 8);
-    const int L = n_it < 32 ? n_it : 32;
+    const int L = n_it < 32 ? n_it : 32, rpw = 32 / L;
+    // the chain lanes of a warp must fit in it (see chain_slot)
+    if (g.qt == CMLD_Q8_0) {
+      need_0 = true;
+      if (rpw * batch > 32) return false;
+    } else {
+      if (cols % 256) return false;
+      if (g.qt == CMLD_Q4_K) {
+        need_k4 = true;
+        if (rpw > 8) return false;
+      } else if (g.qt == CMLD_Q6_K) {
+        need_k6 = true;
+        if (rpw > 2) return false;
+      } else {
+        return false;
+      }
+    }
+    const int per_piece = g.qt == CMLD_Q8_0 ? kPieceBlocks0 : kPieceBlocks;
     PipeJob &J = a.job[k];
     J.w = g.w;
     J.qt = g.qt;
     J.rows = (int32_t)g.rows;
-    J.tile_rows = kPipeConsumerWarps * (32 / L);
+    J.tile_rows = kPipeGroupWarps * rpw;
+    J.n_it = n_it;
     J.stride = g.stride;
     J.y = g.y;
     J.residual = g.residual;
@@ -730,34 +915,55 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
     J.first_tile = tiles;
     J.n_tiles = (int)((g.rows + J.tile_rows - 1) / J.tile_rows);
     tiles += J.n_tiles;
-    stage = std::max<int>(stage, (int)(J.tile_rows * g.stride));
     if (g.stride % 16 || (reinterpret_cast<uintptr_t>(g.w) & 15)) return false;
+    // whole rows when a tile of them is a moderate stage; else pieces of per_piece blocks
+    const int blk = g.qt == CMLD_Q4_K ? 144 : (g.qt == CMLD_Q6_K ? 208 : 32);
+    int np = 1, st = (int)(J.tile_rows * g.stride);
+    J.piece_blocks = n_it;
+    if (n_it > per_piece) {
+      np = (n_it + per_piece - 1) / per_piece;
+      J.piece_blocks = per_piece;
+      // every piece's scale run must start on a 16-byte boundary and be a multiple of 16 bytes long
+      if (g.qt != CMLD_Q4_K && (n_it % 8)) return false;
+      st = J.tile_rows * (int)round_up16(per_piece * blk + (g.qt == CMLD_Q4_K ? 0 : per_piece * 2));
+    }
+    J.n_pieces = np;
+    if (n_pieces < 0) n_pieces = np;
+    if (np != n_pieces) return false;  // jobs of one launch are cut alike (they share cols; types may differ)
+    stage = std::max(stage, st);
   }
   stage = (stage + 127) & ~127;
   const int nsb = (int)(cols >> 8);
   int off = 2 * kPipeMaxStages * 8;
   a.off_act_k = off;
-  if (need_k) off += batch * nsb * kActRec;
+  if (need_k4) off += batch * nsb * kActRec;
+  off = (off + 15) & ~15;
+  a.off_act_6 = off;
+  if (need_k6) off += batch * nsb * kActRec6;
   off = (off + 15) & ~15;
   a.off_act_0 = off;
   if (need_0) off += batch * ((int)round_up16(cols) + (int)round_up16((cols >> 5) * 4));
   a.off_red = off;
   off += 64 * 4;
   a.off_pair = off;
-  if (paired) off += 2 * a.job[0].tile_rows * batch * 4;
+  if (paired) off += 4 * a.job[0].tile_rows * batch * 4;
+  off = (off + 15) & ~15;
+  a.off_term = off;
+  {
+    int term = kPipeAllWarps * kTermBytes;
+    // the norm prologue borrows this region for the squares and the exact sum's workspace
+    if (norm && cols % 256 == 0 && cols <= kRxChunks * kPipeAllWarps * 256)
+      term = std::max(term, (int)cols * 4 + (int)(cols >> 8) * 16 + (int)(cols >> 3) * 8 + 16);
+    off += term;
+  }
   off = (off + 127) & ~127;
   a.off_ring = off;
-  // Prefer a footprint that lets two kernels share an SM (the next one prefetches under PDL).
-  // The stage count must be a multiple of the number of consumer groups: tile i lives in stage i % S and
-  // belongs to group i % kPipeGroups, so with S even every stage is only ever used by one group and a
-  // group meets the phases of its stages in order (an mbarrier parity wait cannot tell phase n from n+2).
-  int n_stages = 0;
-  for (int budget : {110 * 1024, 224 * 1024}) {
-    n_stages = std::min<int>(kPipeMaxStages, (budget - off) / stage);
-    n_stages -= n_stages % kPipeGroups;
-    if (n_stages >= 4) break;
-  }
-  if (n_stages < 2) return false;
+  // The stage count must be a multiple of the number of consumer groups: unit i lives in stage i % S and
+  // belongs to group i % kPipeGroups, so every stage is only ever used by one group and a group meets the
+  // phases of its stages in order (an mbarrier parity wait cannot tell phase n from n+2).
+  int n_stages = std::min<int>(kPipeMaxStages, (226 * 1024 - off) / stage);
+  n_stages -= n_stages % kPipeGroups;
+  if (n_stages < kPipeGroups) return false;
   if (paired && (n_jobs != 2 || jobs[0].rows != jobs[1].rows || jobs[0].qt != jobs[1].qt || jobs[0].stride != jobs[1].stride)) return false;
   p.smem_bytes = off + n_stages * stage;
   a.stage_bytes = stage;
@@ -766,19 +972,19 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   return true;
 }
 
-int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired) {
+int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired, bool norm) {
   for (int b = 8; b >= 1; --b) {
     PipePlan p{};
-    bool nk, n0;
+    bool k4, k6, n0;
     int tiles;
-    if (plan_pipe(jobs, n_jobs, b, p, nk, n0, tiles, paired)) return b;
+    if (plan_pipe(jobs, n_jobs, b, p, k4, k6, n0, tiles, paired, norm)) return b;
   }
   return 0;
 }
 
 // Plans and launches the staged kernel.  Returns CMLD_ERR_UNSUPPORTED (without setting an error
 // message the caller would see) when the shape does not fit; the caller then uses the
-// direct-load kernel.
+// generic kernel.
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
                          cudaStream_t s, bool pdl, const GemvPeer *peer) {
   if (g_sm_count == 0) {
@@ -788,9 +994,9 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   }
   PipePlan p{};
   PipeArgs &a = p.args;
-  bool need_k = false, need_0 = false;
+  bool need_k4 = false, need_k6 = false, need_0 = false;
   int tiles = 0;
-  if (!plan_pipe(jobs, n_jobs, batch, p, need_k, need_0, tiles, pro.pair_swiglu != 0)) return CMLD_ERR_UNSUPPORTED;
+  if (!plan_pipe(jobs, n_jobs, batch, p, need_k4, need_k6, need_0, tiles, pro.pair_swiglu != 0, pro.mode == 1)) return CMLD_ERR_UNSUPPORTED;
   const int64_t cols = jobs[0].cols;
   a.n_jobs = n_jobs;
   a.total_tiles = tiles;
@@ -804,7 +1010,8 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   a.eps = pro.eps;
   a.act_in = pro.act_k;
   a.act_in0 = pro.act_0;
-  a.need_k = need_k;
+  a.need_k4 = need_k4;
+  a.need_k6 = need_k6;
   a.need_0 = need_0;
   a.norm_out = pro.norm_out;
   a.status = status;
@@ -817,7 +1024,7 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
     if (peer->rx_n > 0 && (pro.mode != 1 || cols % 256 || cols > kRxChunks * kPipeAllWarps * 256 || !status))
       return fail(CMLD_ERR_INVALID, "gemv: a receiving launch is an RMSNorm prologue over at most %d columns", kRxChunks * kPipeAllWarps * 256);
   }
-  if (a.mode == 0 && ((need_k && !a.act_in) || (need_0 && !a.act_in0))) return fail(CMLD_ERR_INVALID, "gemv: activation buffer missing");
+  if (a.mode == 0 && (((need_k4 || need_k6) && !a.act_in) || (need_0 && !a.act_in0))) return fail(CMLD_ERR_INVALID, "gemv: activation buffer missing");
   const int grid = std::min(a.paired ? a.job[0].n_tiles : tiles, g_sm_count);
   switch (batch) {
     case 1: return launch_pipe_b<1>(p, grid, s, pdl);

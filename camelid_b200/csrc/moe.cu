@@ -38,12 +38,23 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
   __shared__ float logits[kMaxExperts];
   const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float *xr = x + (int64_t)b * hidden;
-  for (int e = warp; e < n_exp; e += 8) {
-    const float *r = router + (int64_t)e * hidden;
+  (void)lane;
+  (void)warp;
+  // logits_e = ((0 + x0*r0) + x1*r1) + ...: the CPU's one-accumulator dot (dot_product_row,
+  // src/inference.rs:29382-29409), one thread per expert
+  if ((int)threadIdx.x < n_exp) {
+    const float *r = router + (int64_t)threadIdx.x * hidden;
     float s = 0.0f;
-    for (int i = lane; i < hidden; i += 32) s = __fmaf_rn(xr[i], r[i], s);
-    s = warp_sum(s);
-    if (lane == 0) logits[e] = s;
+    int i = 0;
+    for (; i + 4 <= hidden; i += 4) {
+      const float4 xv = __ldg(reinterpret_cast<const float4 *>(xr + i)), rv = __ldg(reinterpret_cast<const float4 *>(r + i));
+      s = __fadd_rn(s, __fmul_rn(xv.x, rv.x));
+      s = __fadd_rn(s, __fmul_rn(xv.y, rv.y));
+      s = __fadd_rn(s, __fmul_rn(xv.z, rv.z));
+      s = __fadd_rn(s, __fmul_rn(xv.w, rv.w));
+    }
+    for (; i < hidden; ++i) s = __fadd_rn(s, __fmul_rn(xr[i], r[i]));
+    logits[threadIdx.x] = s;
   }
   __syncthreads();
   if (threadIdx.x != 0) return;
@@ -64,7 +75,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict_
   for (int s = 0; s < k; ++s) {
     const float v = logits[idx[s]];
     w[s] = isfinite(v) ? expf_exact(__fsub_rn(v, mx)) : 0.0f;
-    sum += w[s];
+    sum = __fadd_rn(sum, w[s]);
   }
   for (int s = 0; s < k; ++s) w[s] = sum > 0.0f ? __fdiv_rn(w[s], sum) : __fdiv_rn(1.0f, (float)k);
   for (int s = 1; s < k; ++s) {  // stable insertion by (weight desc, index asc)
@@ -365,6 +376,112 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_gemv_kernel(MoeGemvArgs a)
   }
 }
 
+// ------------------------------------------------------------------ expert matvec in the CPU path's order
+//
+// The reference holds non-Q8_0 expert tensors as dequantised f32 and multiplies them with the f32 activation by
+// its one-accumulator dot (expert_matrix_view else-branch, src/inference.rs:14109-14123; dot_product_row,
+// :29382-29409): y[r] = ((0 + x0*w0) + x1*w1) + ... with w_i the dequantised weight (Q4KBlock::dequantize /
+// Q6KBlock::dequantize, src/tensor/mod.rs:5903-5924 and :6039-6066).  One thread owns one output row and walks
+// its weights in index order, dequantising on the way; up to kOrdCols assignments of the expert share the
+// dequantised weight (independent chains, which also cover each other's addition latency).
+constexpr int kOrdCols = 4;
+constexpr int kOrdThreads = 128;
+
+template <int QT>
+__global__ void __launch_bounds__(kOrdThreads) moe_gemv_ordered_kernel(MoeGemvArgs a) {
+  const int e_local = blockIdx.y;
+  const int e = a.first_expert + e_local * a.expert_step;
+  const int n = a.counts[e];
+  if (n == 0) return;
+  const int64_t r = (int64_t)blockIdx.x * kOrdThreads + threadIdx.x;
+  if (r >= a.rows_per_expert) return;
+  const uint8_t *row = a.w + ((int64_t)e_local * a.rows_per_expert + r) * a.stride;
+  const int nsb = (int)(a.cols >> 8);
+  for (int c0 = 0; c0 < n; c0 += kOrdCols) {
+    const float *xc[kOrdCols];
+    int asg[kOrdCols];
+#pragma unroll
+    for (int c = 0; c < kOrdCols; ++c) {
+      asg[c] = a.lists[e * a.n_assign + min(c0 + c, n - 1)];
+      xc[c] = a.x + (int64_t)(asg[c] / a.x_div) * a.x_stride;
+    }
+    float acc[kOrdCols];
+#pragma unroll
+    for (int c = 0; c < kOrdCols; ++c) acc[c] = 0.0f;
+    for (int sb = 0; sb < nsb; ++sb) {
+      if (QT == CMLD_Q4_K) {
+        const uint8_t *blk = row + (int64_t)sb * 144;
+        const uint4 meta = ld_stream16(blk);
+        const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const uint4 q0 = ld_stream16(blk + 16 + 32 * p), q1 = ld_stream16(blk + 32 + 32 * p);
+          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int hl = 0; hl < 2; ++hl) {  // low nibbles = values 64p..64p+31, high nibbles = the next 32
+            int sc, m;
+            q4k_scale_min(2 * p + hl, meta.y, meta.z, meta.w, sc, m);
+            const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)m);
+            const int xo = sb * 256 + 64 * p + 32 * hl;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t nib = hl ? (qw[k] >> 4) & 0x0f0f0f0fu : qw[k] & 0x0f0f0f0fu;
+              float w4[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) w4[i] = __fsub_rn(__fmul_rn(dsc, byte_to_float(nib, i)), dm);
+#pragma unroll
+              for (int c = 0; c < kOrdCols; ++c) {
+                const float4 xv = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo + 4 * k));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.x, w4[0]));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.y, w4[1]));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.z, w4[2]));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.w, w4[3]));
+              }
+            }
+          }
+        }
+      } else {  // Q6_K: values 128h + 32*stream + l, stream 0/1 = low nibbles of ql[64h + 32*stream' ..], 2/3 = high nibbles
+        const uint8_t *blk = row + (int64_t)sb * 208;
+        const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row + (int64_t)nsb * 208) + sb));
+        const uint4 scw = ld_stream16(blk + 192);
+        const uint32_t scs[4] = {scw.x, scw.y, scw.z, scw.w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 h0 = ld_stream16(blk + 128 + 32 * h), h1 = ld_stream16(blk + 144 + 32 * h);
+          const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+          for (int stream = 0; stream < 4; ++stream) {
+            const uint4 l0 = ld_stream16(blk + 64 * h + 32 * (stream & 1)), l1 = ld_stream16(blk + 64 * h + 32 * (stream & 1) + 16);
+            const uint32_t ql[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int j = 8 * h + 2 * stream + (k >> 2);  // scale index of values 16j..16j+15
+              const float dsc = __fmul_rn(d, (float)(int)(int8_t)(scs[j >> 2] >> (8 * (j & 3))));
+              const uint32_t lo = (stream & 2) ? (ql[k] >> 4) & 0x0f0f0f0fu : ql[k] & 0x0f0f0f0fu;
+              const uint32_t q6 = lo | (((qh[k] >> (2 * stream)) & 0x03030303u) << 4);
+              float w4[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) w4[i] = __fmul_rn(dsc, byte_to_float(q6, i) - 32.0f);
+              const int xo = sb * 256 + 128 * h + 32 * stream + 4 * k;
+#pragma unroll
+              for (int c = 0; c < kOrdCols; ++c) {
+                const float4 xv = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.x, w4[0]));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.y, w4[1]));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.z, w4[2]));
+                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.w, w4[3]));
+              }
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kOrdCols; ++c)
+      if (c0 + c < n) a.y[(int64_t)asg[c] * a.rows_per_expert + r] = acc[c];
+  }
+}
+
 // h[b] += sum_s down[b*k+s] * w[b][s], accumulated in selection order from zero, as the CPU does.
 __global__ void moe_combine_kernel(float *__restrict__ h, const float *__restrict__ down, const float *__restrict__ sel_w,
                                    const int32_t *__restrict__ sel_idx, int hidden, int k, int first_expert, int expert_step,
@@ -405,6 +522,20 @@ int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local
   dim3 grid((unsigned)((rows_per_expert + kMoeRows * kMoeWarps - 1) / (kMoeRows * kMoeWarps)), (unsigned)n_local_experts);
   if (slab.qt == CMLD_Q4_K) moe_gemv_kernel<CMLD_Q4_K><<<grid, kMoeWarps * 32, 0, s>>>(a);
   else if (slab.qt == CMLD_Q6_K) moe_gemv_kernel<CMLD_Q6_K><<<grid, kMoeWarps * 32, 0, s>>>(a);
+  else return fail(CMLD_ERR_UNSUPPORTED, "expert tensors must be Q4_K or Q6_K");
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
+int32_t moe_expert_gemv_ordered(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
+                                const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
+                                int n_assign, cudaStream_t s) {
+  MoeGemvArgs a{slab.data, slab.qt, rows_per_expert, slab.cols, slab.stride, x, x_stride, x_div, y, counts, lists, n_assign,
+                first_expert, expert_step};
+  if (slab.cols % 256) return fail(CMLD_ERR_SHAPE, "expert tensor width %lld is not a multiple of 256", (long long)slab.cols);
+  dim3 grid((unsigned)((rows_per_expert + kOrdThreads - 1) / kOrdThreads), (unsigned)n_local_experts);
+  if (slab.qt == CMLD_Q4_K) moe_gemv_ordered_kernel<CMLD_Q4_K><<<grid, kOrdThreads, 0, s>>>(a);
+  else if (slab.qt == CMLD_Q6_K) moe_gemv_ordered_kernel<CMLD_Q6_K><<<grid, kOrdThreads, 0, s>>>(a);
   else return fail(CMLD_ERR_UNSUPPORTED, "expert tensors must be Q4_K or Q6_K");
   CMLD_CUDA(cudaGetLastError());
   return CMLD_OK;

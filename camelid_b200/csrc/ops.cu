@@ -1,6 +1,7 @@
 // Per-token work around the matvecs: RMSNorm / SwiGLU fused with activation quantisation,
 // RoPE fused with the f16 KV-cache write, and greedy argmax.
 #include "actquant.cuh"
+#include "exact_sum.cuh"
 
 namespace cmld {
 
@@ -8,13 +9,14 @@ namespace cmld {
 //
 // One CTA per batch row.  v = (x*scale)*w (rms_norm_into, src/tensor/mod.rs:2740-2764 in the
 // Camelid tree), or v = g/(1+exp(-g))*u (src/inference.rs:13231-13236), or v = x.  The
-// mean-square is a shuffle/shared-memory tree rather than the CPU's sequential sum.  v is then
-// quantised the way the CPU quantises a matvec operand:
+// mean-square has the bits of the CPU's sequential sum.  v is then quantised the way the CPU
+// quantises a matvec operand:
 //   Q8_K (quantize_q8_k_blocks, src/inference.rs:23121-23152): first max |v| of each 256 keeps
 //        its sign, iscale = -127/max, q = min(127, rne(iscale*v)), d = 1/iscale;
 //   Q8_0 (quantize_q8_0_block, src/inference.rs:22510-22528): d = amax/127 kept as its f16
 //        rounding, q = round-half-away(v * (1/d_unrounded)) clamped to [-128,127].
-constexpr int kNormThreads = 256;  // same thread count and summation tree as the staged matvec's fused prologue
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxExact = 8192;  // widest row whose squares are summed by all warps (exact_sum.cuh); wider rows by one thread
 
 template <int MODE>  // 0 plain, 1 rmsnorm, 2 swiglu
 __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs a) {
@@ -26,60 +28,25 @@ __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs 
   const float *x2 = MODE == 2 ? a.x2 + (int64_t)b * a.cols : nullptr;
   float scale = 1.0f;
   if (MODE == 1) {
-    __shared__ float red[kNormThreads / 32];
     __shared__ float s_scale;
-    if (a.exact) {
-      // the CPU's order: one accumulator, squares added in index order (rms_norm_into, src/tensor/mod.rs:2755)
-      if (threadIdx.x == 0) {
-        float t = 0.0f;
-        for (int64_t i = 0; i < a.cols; ++i) t = __fadd_rn(t, __fmul_rn(x[i], x[i]));
-        s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
-      }
-      __syncthreads();
-    } else {
-      if ((a.cols & 255) == 0 && a.cols <= 8192 && blockDim.x == 256) {
-        // the order of the matvec kernel's fused prologue (sixteen warps there, each holding chunks w and w+16):
-        // per lane over those chunks' values, shuffle tree within the warp, shuffle tree over the sixteen sums
-        __shared__ float red16[16];
-        for (int vw = warp; vw < 16; vw += 8) {
-          float ss = 0.0f;
-          for (int k = 0; k < 2; ++k) {
-            const int64_t e0 = (int64_t)(vw + 16 * k) * 256 + lane * 8;
-            if (e0 < a.cols) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float v = x[e0 + i];
-                ss = __fmaf_rn(v, v, ss);
-              }
-            }
-          }
-          ss = warp_sum(ss);
-          if (lane == 0) red16[vw] = ss;
-        }
-        __syncthreads();
-        if (warp == 0) {
-          float t = lane < 16 ? red16[lane] : 0.0f;
-          t = warp_sum(t);
-          if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
-        }
-        __syncthreads();
-      } else {
-        float ss = 0.0f;
-        for (int64_t i = threadIdx.x; i < a.cols; i += blockDim.x) {
-          const float v = x[i];
-          ss = __fmaf_rn(v, v, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        if (warp == 0) {
-          float t = lane < nwarps ? red[lane] : 0.0f;
-          t = warp_sum(t);
-          if (lane == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
-        }
-        __syncthreads();
-      }
+    // the CPU's order: one accumulator, squares added in index order (rms_norm_into, src/tensor/mod.rs:2755)
+    if ((a.cols & 255) == 0 && a.cols <= kNormMaxExact) {
+      // the same bits from all the warps (exact_sum.cuh)
+      __shared__ __align__(16) float sq[kNormMaxExact];
+      __shared__ __align__(16) uint8_t ws[(kNormMaxExact >> 8) * 16 + (kNormMaxExact >> 3) * 8];
+      __shared__ float s_sum;
+      for (int64_t i = threadIdx.x; i < a.cols; i += kNormThreads) sq[i] = __fmul_rn(x[i], x[i]);
+      const int nch = (int)(a.cols >> 8);
+      const float t = xsum::cta_sum<kNormThreads / 32>(sq, (int)a.cols, warp, lane, 1, reinterpret_cast<double *>(ws),
+                                                       reinterpret_cast<uint32_t *>(ws + nch * 8),
+                                                       reinterpret_cast<xsum::Item *>(ws + nch * 16), &s_sum);
+      if (threadIdx.x == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
+    } else if (threadIdx.x == 0) {
+      float t = 0.0f;
+      for (int64_t i = 0; i < a.cols; ++i) t = __fadd_rn(t, __fmul_rn(x[i], x[i]));
+      s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
     }
+    __syncthreads();
     scale = s_scale;
   }
   const int64_t n_chunks = (a.cols + 255) >> 8;

@@ -19,6 +19,7 @@ SHAPES = {
     "tiny": (256, 2, 4, 2, 64, 512, 512, 10000.0, 0, 0),
     "tiny-moe": (256, 2, 4, 2, 64, 512, 512, 10000.0, 4, 2),
     "tiny-tp": (512, 2, 8, 2, 64, 1024, 512, 10000.0, 0, 0),  # smallest shape that splits over two ranks
+    "small": (4096, 2, 32, 8, 128, 8192, 2048, 500000.0, 0, 0),  # two layers at the 8B width: every matvec takes the staged kernel
     "llama-1b": (2048, 16, 32, 8, 64, 8192, 128256, 500000.0, 0, 0),
     "llama-3b": (3072, 28, 24, 8, 128, 8192, 128256, 500000.0, 0, 0),
     "llama-8b": (4096, 32, 32, 8, 128, 14336, 128256, 500000.0, 0, 0),

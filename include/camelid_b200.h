@@ -74,11 +74,12 @@ typedef struct {
 } cmld_config;
 
 #define CMLD_FLAG_NO_GRAPH 1u     /* launch kernels directly instead of replaying a CUDA graph */
-#define CMLD_FLAG_DIRECT_GEMV 2u  /* use the direct-load matvec kernel everywhere (no staged kernel) */
+#define CMLD_FLAG_DIRECT_GEMV 2u  /* use the generic matvec kernel everywhere (no staged kernel) */
 #define CMLD_FLAG_NO_PDL 4u       /* no programmatic dependent launch between kernels */
-#define CMLD_FLAG_EXACT_ORDER 16u   /* every f32 sum in the CPU path's order (bit-level parity work; slow) */
+#define CMLD_FLAG_EXACT_ORDER 16u   /* the plain reference-order kernels (one lane walks each sum): the same bits as the default path, slowly; a cross-check */
 #define CMLD_FLAG_SPLIT_PROLOGUE 8u /* norm/SwiGLU/quantise in a small kernel of its own instead of the matvec prologue (always so for steps of more than 2 rows) */
-#define CMLD_FLAG_TENSOR_BATCH 64u   /* steps of 5..8 rows on the tensor-core matvec too (faster; such a step is then no longer bit-identical to the same rows stepped one by one) */
+#define CMLD_FLAG_FAST_ORDER 128u  /* attention by the split-range (flash-decoding) kernel, whose sums are trees: faster at long contexts, no longer the CPU path's bits */
+#define CMLD_FLAG_TENSOR_BATCH 64u   /* steps of 5..32 rows and prompt ingestion on the int8 mma.sync matvec (one pass over the weights; its row sums are trees, so no longer the CPU path's bits) */
 #define CMLD_FLAG_NCCL_ONLY 32u     /* sharded engines: every sublayer sum as an NCCL all-reduce (no peer-memory path in the matvec kernels) */
 
 typedef struct cmld_engine cmld_engine;
@@ -266,9 +267,11 @@ CMLD_API int32_t cmld_act_export(int32_t act_kind, const void *act_dev, int64_t 
 CMLD_API int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, float *y_dev,
                            const float *residual_dev);
 /* Which matvec kernel cmld_gemv / cmld_gemv_time use: bit 0 clear = the staged (bulk-copy
- * pipelined) kernel whenever it takes the shape, bit 0 set = the direct-load kernel only; bit 1
- * set = cmld_gemv_time chains its launches with programmatic dependent launch; bit 2 set = the
- * tensor-core kernel (normally used from 9 rows) from 1 row.  Process-wide; for A/B runs. */
+ * pipelined) kernel whenever it takes the shape, bit 0 set = the generic kernel only (both give
+ * the CPU dot's bits); bit 1 set = cmld_gemv_time chains its launches with programmatic dependent
+ * launch; bit 3 set = batches of 9..32 rows on the int8 mma.sync kernel (one pass over the weights,
+ * tree sums: within tolerance, not the CPU's bits), bit 2 set = that kernel from 1 row.
+ * Process-wide; for A/B runs. */
 CMLD_API int32_t cmld_gemv_select_kernel(int32_t choice);
 /* Self-test of the bounded device-side wait of the peer-memory path (no reference counterpart): waits for an
  * arrival word that nobody raises; returns CMLD_ERR_TIMEOUT after timeout_ms (1..5000) when the bound works,
@@ -294,6 +297,13 @@ CMLD_API int32_t cmld_argmax(const float *x_dev, int64_t n, int32_t batch, uint3
 CMLD_API int32_t cmld_attention_decode(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev,
                                        int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int64_t max_pos,
                                        int64_t n_pos, float scale, float *out_dev);
+/* The same attention with every f32 sum in the CPU path's order (attention_context_for_head_into_with_kernels,
+ * src/inference.rs:30287-30466; dot_product, src/tensor/mod.rs:3464-3480): the kernel the engine runs by
+ * default.  The output has the CPU path's bits. */
+CMLD_API int32_t cmld_attention_decode_ordered(const float *q_dev, const void *k_cache_dev, const void *v_cache_dev,
+                                               int32_t n_heads, int32_t n_kv_heads, int32_t head_dim, int64_t max_pos,
+                                               int64_t n_pos, float scale, float *out_dev);
+
 /* cmld_attention_decode without any allocator call (no counterpart in the reference; added for
  * hosts that cannot call cudaMalloc when they need attention: the device is fully owned by their
  * own pool, their latency path forbids allocator calls, or their CUDA binding has no allocator).

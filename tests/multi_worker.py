@@ -19,11 +19,15 @@ def prompt(vocab: int, s: int) -> np.ndarray:
 def run_model(eng, cfg):
     """The same calls on a sharded rank and on the single-GPU engine it is compared with."""
     firsts = [eng.prefill_tokens(s, prompt(cfg.vocab, s), 0) for s in range(2)]
+    # a probe step with fixed tokens (the same inputs whatever the greedy streams do); its KV rows are
+    # rewritten by the decode below
+    _, probe_logits, probe_hidden = eng.step_batch([0, 1], [5, 9], [N_PROMPT] * 2, want_logits=True, want_hidden=True)
     toks = eng.decode_greedy([0, 1], firsts, [N_PROMPT, N_PROMPT], N_DECODE)
     # one more step at the next position, with logits and hidden rows read back
     last = [int(t) for t in toks[-1]]
     nxt, logits, hidden = eng.step_batch([0, 1], last, [N_PROMPT + N_DECODE] * 2, want_logits=True, want_hidden=True)
-    return dict(firsts=np.array(firsts), tokens=toks, next=nxt, logits=logits, hidden=hidden)
+    return dict(firsts=np.array(firsts), tokens=toks, next=nxt, logits=logits, hidden=hidden, probe_logits=probe_logits,
+                probe_hidden=probe_hidden)
 
 
 def main():

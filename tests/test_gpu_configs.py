@@ -5,20 +5,14 @@ the CPU checker holding byte-identical weights.  The larger configs are run at t
 (hidden, heads, ffn, vocab) but with fewer layers so the CPU checker finishes in seconds; the
 arithmetic of a layer does not depend on how many follow it.
 
-Two engine modes are held to different bars, and the reason is the reference's arithmetic itself:
-every matvec operand is quantised to int8, so a value 1e-6 away (one f32 reassociation) from a
-rounding boundary gets the neighbouring code, and on these seeded N(0, 0.02) models with unit norm
-weights, blocks that hold an outlier activation turn one code step into a >1e-2 step of the layer
-output.  The CPU checker fed inputs perturbed by 1e-6 jumps in the same way.
-
-* reference order (CMLD_FLAG_EXACT_ORDER): every f32 sum in the CPU path's order.  Bar: the residual
-  stream after every layer, the logits and every greedy token are BIT-IDENTICAL to the checker.
-  The acceptance gates (max-abs 2e-2 / relative 1e-2 per layer and logits, >= 32 equal greedy tokens)
-  hold with zero difference.
-* fast order (default; shuffle-tree sums): each layer, fed the checker's own input, is inside
-  the acceptance gate for most (position, layer) pairs with a median deviation of 1e-6..1e-3; pairs
-  outside it are rounding-boundary events.  Greedy streams leave the checker's where its top-2 logit
-  gap is of the size of those events; the lengths are printed, not gated.
+The reference quantises every matvec operand to int8, so a value 1e-6 away (one f32 reassociation)
+from a rounding boundary gets the neighbouring code and the layer output jumps by more than the
+acceptance gate allows; the only way to meet the gates (per-layer hidden states and logits within
+max-abs 2e-2 / relative 1e-2, at least 32 equal greedy tokens) on every input is to keep the CPU
+path's order of f32 operations.  The engine does, in its default mode — the mode the benchmark
+times — so the bar here is zero difference: the residual stream after every layer, the logits and
+every greedy token are BIT-IDENTICAL to the checker's.  CMLD_FLAG_EXACT_ORDER selects the plain
+(one lane per sum) kernels, which must give the same bits again.
 """
 import numpy as np
 import pytest
@@ -27,32 +21,7 @@ from helpers import ModelPair, greedy_match, hidden_gate
 
 pytestmark = pytest.mark.gpu
 
-
-def _per_layer(pair, orc, prompt, n_positions):
-    """Per-layer agreement with identical inputs: layer l of the engine is fed the checker's own
-    residual stream entering layer l (at every position, so its KV rows are built from the same
-    inputs too) and must return the checker's residual stream leaving it.
-
-    Why layer by layer: the reference quantises every matvec operand to int8.  A value that is
-    1e-6 away (f32 reassociation) from a rounding boundary gets the neighbouring code; in a block
-    that holds an outlier activation one code step is a large absolute step, and the checker
-    itself, fed inputs perturbed by 1e-6, jumps by >1e-2 in the same way.  Feeding each layer the
-    checker's input measures each layer's own error and keeps one such event from being counted
-    again in every later layer.  Gate per (position, layer): max-abs 2e-2 and relative 1e-2."""
-    eng, ref, cfg = pair.engine, pair.oracle, pair.cfg
-    devs = []
-    for pos in range(n_positions):
-        emb = ref.embedding(int(prompt[pos]))
-        c, s = pair.rope(pos)
-        ref_logits, ref_hidden, ref_taps = ref.forward(emb, pos, want_taps=True)
-        for layer in range(cfg.n_layers):
-            h_in = emb if layer == 0 else ref_taps[layer - 1]
-            h_out = eng.forward_layer(layer, h_in, c, s, pos, pair.scale)
-            devs.append(hidden_gate(h_out, ref_taps[layer]) + (pos, layer))
-    ok = np.array([d[0] for d in devs])
-    max_abs = np.array([d[1] for d in devs])
-    worst = max(devs, key=lambda d: d[1])
-    return float(ok.mean()), float(np.median(max_abs)), worst
+EXACT = 16  # CMLD_FLAG_EXACT_ORDER
 
 
 def _greedy(pair, orc, prompt, n_gen, seq=0):
@@ -64,22 +33,11 @@ def _greedy(pair, orc, prompt, n_gen, seq=0):
     return greedy_match(got, ref_tokens, gaps)
 
 
-def _run(pair, orc, n_prompt, n_gen, seq=0, layer_positions=6):
-    prompt = orc.synth_tokens(20261125, 5, n_prompt, pair.cfg.vocab)
-    frac_ok, median_dev, worst = _per_layer(pair, orc, prompt, min(layer_positions, n_prompt))
-    print(f"per-layer: {frac_ok:.3f} of (position, layer) pairs inside the gate, median max-abs {median_dev:.2e}, worst {worst}")
-    # fast order: most pairs inside the gate, typical deviation far below it (see the module docstring)
-    assert frac_ok >= 0.6 and median_dev < 5e-3, (frac_ok, median_dev, worst)
-    return _greedy(pair, orc, prompt, n_gen, seq)
-
-
-EXACT = 16  # CMLD_FLAG_EXACT_ORDER
-
-
 def _bit_identity(pair, orc, prompt, n_positions):
-    """Whole forward passes (no teacher forcing): residual stream after every layer, and logits."""
+    """Whole forward passes (no teacher forcing): residual stream after every layer, and logits.
+    Returns the counts of positions with identical taps / logits and the acceptance gate's verdict."""
     eng, ref, cfg = pair.engine, pair.oracle, pair.cfg
-    equal_taps = equal_logits = total = 0
+    equal_taps = equal_logits = total = gate_ok = 0
     worst = 0.0
     for pos in range(n_positions):
         emb = ref.embedding(int(prompt[pos]))
@@ -87,69 +45,70 @@ def _bit_identity(pair, orc, prompt, n_positions):
         ref_logits, _, ref_taps = ref.forward(emb, pos, want_taps=True)
         _, taps = eng.forward_token_hidden(emb, c, s, pos, pair.scale, taps=True)
         logits = eng.forward_token_logits(emb, c, s, pos, pair.scale)
-        equal_taps += int(np.array_equal(taps, ref_taps))
-        equal_logits += int(np.array_equal(logits, ref_logits))
+        equal_taps += int(np.array_equal(taps.view(np.uint32), ref_taps.view(np.uint32)))
+        equal_logits += int(np.array_equal(logits.view(np.uint32), ref_logits.view(np.uint32)))
+        gate_ok += int(all(hidden_gate(taps[l], ref_taps[l])[0] for l in range(cfg.n_layers)) and hidden_gate(logits, ref_logits)[0])
         worst = max(worst, float(np.abs(taps - ref_taps).max()), float(np.abs(logits - ref_logits).max()))
         total += 1
-    return equal_taps, equal_logits, total, worst
+    return equal_taps, equal_logits, total, worst, gate_ok
 
 
-def test_config1_llama_1b_q8_0_reference_order_is_bit_identical(cm, orc):
-    """Config 1 in full with every f32 sum in the CPU path's order: the residual stream after each
-    of the 16 layers, the logits and all 128 greedy tokens equal the CPU checker's bit for bit."""
+@pytest.mark.parametrize("flags", [0, EXACT])
+def test_config1_llama_1b_q8_0_is_bit_identical(cm, orc, flags):
+    """Config 1 in full: the residual stream after each of the 16 layers, the logits and all 128 greedy
+    tokens equal the CPU checker's bit for bit (default engine; and the plain reference-order kernels)."""
     from camelid_b200 import synth
 
-    cfg = synth.engine_config("llama-1b", max_pos=512, flags=EXACT)
+    cfg = synth.engine_config("llama-1b", max_pos=512, flags=flags)
     pair = ModelPair(cfg, "q8_0", seed=20261125)
     prompt = orc.synth_tokens(20261125, 5, 32, cfg.vocab)
-    eq_t, eq_l, total, worst = _bit_identity(pair, orc, prompt, 6)
-    print(f"reference order: taps bit-identical at {eq_t}/{total} positions, logits at {eq_l}/{total}, worst abs diff {worst:.2e}")
-    assert eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
+    eq_t, eq_l, total, worst, gate = _bit_identity(pair, orc, prompt, 6)
+    print(f"config 1 flags={flags}: taps bit-identical at {eq_t}/{total} positions, logits at {eq_l}/{total}, worst abs diff {worst:.2e}")
+    assert gate == total and eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
     n_match, gap = _greedy(pair, orc, prompt, 128)
-    print(f"config 1, reference order: {n_match}/128 greedy tokens equal")
+    print(f"config 1 flags={flags}: {n_match}/128 greedy tokens equal")
     assert n_match == 128, (n_match, gap)
 
 
-@pytest.mark.parametrize("shape,layers", [("llama-3b", 4), ("llama-8b", 3)])
-def test_k_quant_mix_reference_order_is_bit_identical(cm, orc, shape, layers):
+@pytest.mark.parametrize("shape,layers,flags", [("llama-3b", 6, 0), ("llama-8b", 8, 0), ("llama-3b", 3, EXACT), ("llama-8b", 2, EXACT)])
+def test_k_quant_mix_is_bit_identical(cm, orc, shape, layers, flags):
+    """Configs 3 and 4 (Q4_K_M mix) at their true widths: 100 % of (position, layer) pairs and the logits
+    inside the acceptance gate — with zero difference — and every greedy token equal."""
     from camelid_b200 import synth
 
-    cfg = synth.engine_config(shape, max_pos=256, n_layers=layers, flags=EXACT)
+    cfg = synth.engine_config(shape, max_pos=256, n_layers=layers, flags=flags)
     pair = ModelPair(cfg, "q4_k_m", seed=20261125)
     prompt = orc.synth_tokens(20261125, 5, 24, cfg.vocab)
-    eq_t, eq_l, total, worst = _bit_identity(pair, orc, prompt, 5)
-    print(f"{shape} reference order: taps bit-identical at {eq_t}/{total} positions, logits {eq_l}/{total}, worst {worst:.2e}")
-    assert eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
+    eq_t, eq_l, total, worst, gate = _bit_identity(pair, orc, prompt, 5)
+    print(f"{shape} x{layers} flags={flags}: taps bit-identical at {eq_t}/{total} positions, logits {eq_l}/{total}, worst {worst:.2e}")
+    assert gate == total and eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
     n_match, gap = _greedy(pair, orc, prompt, 40)
     assert n_match == 40, (n_match, gap)
 
 
-def test_config1_llama_1b_q8_0_fast_order(cm, orc):
+def test_llama_8b_long_context_stays_bit_identical(cm, orc):
+    """The attention and its exact softmax sum over a context past 1024 positions (the benchmark's prompt
+    length): KV seeded by a prompt the engine ingests itself, then greedy tokens against the checker."""
     from camelid_b200 import synth
 
-    cfg = synth.engine_config("llama-1b", max_pos=512)
-    pair = ModelPair(cfg, "q8_0", seed=20261125)
-    n_match, gap = _run(pair, orc, n_prompt=32, n_gen=128)
-    print(f"config 1, fast order: {n_match}/128 greedy tokens equal (checker top-2 gap at first difference: {gap})")
-    assert n_match == 128 or gap < 0.05, (n_match, gap)
+    cfg = synth.engine_config("llama-8b", max_pos=1280, n_layers=2)
+    pair = ModelPair(cfg, "q4_k_m", seed=7)
+    prompt = orc.synth_tokens(7, 5, 1100, cfg.vocab)
+    n_match, gap = _greedy(pair, orc, prompt, 34)
+    assert n_match == 34, (n_match, gap)
 
 
-@pytest.mark.parametrize("shape,layers", [("llama-3b", 4), ("llama-8b", 3)])
-def test_k_quant_mix_fast_order(cm, orc, shape, layers):
-    from camelid_b200 import synth
-
-    cfg = synth.engine_config(shape, max_pos=256, n_layers=layers)
-    pair = ModelPair(cfg, "q4_k_m", seed=20261125)
-    n_match, gap = _run(pair, orc, n_prompt=24, n_gen=40)
-    print(f"{shape} x{layers} layers, fast order: {n_match}/40 greedy tokens equal (gap {gap})")
-    assert n_match == 40 or gap < 0.05, (n_match, gap)
-
-
-def test_mixtral_shape_two_layers_fast_order(cm, orc):
+def test_mixtral_shape_two_layers(cm, orc):
+    """Config 5's shape (8 experts, top-2, ffn 14336, vocab 32000), two layers: the expert matvecs multiply
+    the f32 activation with dequantised weights in index order, like the reference; bit identity again."""
     from camelid_b200 import synth
 
     cfg = synth.engine_config("mixtral-8x7b", max_pos=128, n_layers=2, max_seqs=2)
     pair = ModelPair(cfg, "q4_k_m", seed=20261125)
-    n_match, gap = _run(pair, orc, n_prompt=6, n_gen=34, seq=1, layer_positions=3)
-    print(f"mixtral x2 layers, fast order: {n_match}/34 greedy tokens equal (gap {gap})")
-    assert n_match == 34 or gap < 0.05, (n_match, gap)
+    prompt = orc.synth_tokens(20261125, 5, 6, cfg.vocab)
+    eq_t, eq_l, total, worst, gate = _bit_identity(pair, orc, prompt, 3)
+    print(f"mixtral x2: taps bit-identical at {eq_t}/{total} positions, logits {eq_l}/{total}, worst {worst:.2e}")
+    assert gate == total and eq_t == total and eq_l == total, (eq_t, eq_l, total, worst)
+    n_match, gap = _greedy(pair, orc, prompt, 34, seq=1)
+    print(f"mixtral x2 layers: {n_match}/34 greedy tokens equal (gap {gap})")
+    assert n_match == 34, (n_match, gap)

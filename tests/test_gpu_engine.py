@@ -1,9 +1,10 @@
 """Engine-level parity on a B200 through the C ABI: whole decode steps against the CPU
 checker holding byte-identical weights.
 
-Acceptance gates: per-layer hidden states and logits within max-abs 2e-2 and relative
-1e-2; greedy token ids equal for at least the first 32 generated tokens; KV rows equal to
-what serial single-token calls write.
+The engine keeps every f32 operation in the CPU path's order, so for dense models the bar is
+bit identity: residual stream after every layer, logits, KV rows and every greedy token equal the
+checker's.  (Acceptance gates, for reference: per-layer hidden states and logits within max-abs
+2e-2 and relative 1e-2; greedy token ids equal for at least the first 32 generated tokens.)
 """
 import numpy as np
 import pytest
@@ -70,7 +71,7 @@ def pair(request, cm):
     return ModelPair(cfg, request.param, seed=20261125)
 
 
-def test_per_layer_hidden_and_logits_within_gate(pair, orc):
+def test_per_layer_hidden_logits_and_kv_are_bit_identical(pair, orc):
     eng, ref, cfg = pair.engine, pair.oracle, pair.cfg
     toks = orc.synth_tokens(1, 1, 12, cfg.vocab)
     for pos, t in enumerate(toks):
@@ -79,23 +80,14 @@ def test_per_layer_hidden_and_logits_within_gate(pair, orc):
         ref_logits, ref_hidden, ref_taps = ref.forward(emb, pos, want_taps=True)
         hidden, taps = eng.forward_token_hidden(emb, c, s, pos, pair.scale, taps=True)
         for layer in range(cfg.n_layers):
-            ok, max_abs, rel = hidden_gate(taps[layer], ref_taps[layer])
-            assert ok, (pos, layer, max_abs, rel)
-        assert hidden_gate(hidden, ref_hidden)[0]
+            assert np.array_equal(taps[layer].view(np.uint32), ref_taps[layer].view(np.uint32)), (pos, layer, hidden_gate(taps[layer], ref_taps[layer]))
+        assert np.array_equal(hidden.view(np.uint32), ref_hidden.view(np.uint32))
         logits = eng.forward_token_logits(emb, c, s, pos, pair.scale)
-        ok, max_abs, rel = hidden_gate(logits, ref_logits)
-        assert ok, (pos, max_abs, rel)
-        # much tighter in practice: f32 reassociation only
-        assert np.abs(logits - ref_logits).max() < 2e-3
-    # KV rows against the checker's: both hold f16-exact values; a row computed from an f32 that
-    # differs in its last bits may round to the neighbouring f16 (tolerance: one f16 ulp)
+        assert np.array_equal(logits.view(np.uint32), ref_logits.view(np.uint32)), (pos, hidden_gate(logits, ref_logits))
     for layer in range(cfg.n_layers):
         ck, cv = eng.read_kv_layer(layer, len(toks))
         rk, rv = ref.read_kv_layer(layer, len(toks))
-        for got, want in ((ck, rk), (cv, rv)):
-            assert np.array_equal(got.astype(np.float16).astype(np.float32), got)
-            assert (got == want).mean() > 0.99
-            assert np.abs(got - want).max() <= np.abs(want).max() * 2.0 ** -10
+        assert np.array_equal(ck, rk) and np.array_equal(cv, rv), layer
 
 
 def test_greedy_tokens_match_checker(pair, orc):
@@ -109,13 +101,7 @@ def test_greedy_tokens_match_checker(pair, orc):
         out = eng.decode_greedy([0], [first], [len(prompt)], n_gen - 1)
         got = np.concatenate([[first], out[:, 0]])
         runs.append(greedy_match(got, ref_tokens, gaps))
-    # This 256-wide toy model quantises its whole hidden state as ONE Q8_K superblock, so a single
-    # int8 rounding that lands on the other side of .5 moves the logits by ~1e-2 and the toy's
-    # repetitive greedy loops sit on top-2 gaps of that size.  Gate: most prompts give >= 32 equal
-    # tokens, and any earlier difference happened at a checker top-2 gap below 5e-3 (a near tie).
-    # The full-size configurations are held to >= 32 equal tokens with no such allowance.
-    assert sum(n >= 32 for n, _ in runs) >= 3, runs
-    assert all(n >= 32 or gap < 5e-3 for n, gap in runs), runs
+    assert all(n == n_gen for n, _ in runs), runs  # every token of every prompt
     ms, launches = eng.last_timing()
     assert ms > 0 and launches > 0
 
@@ -183,10 +169,11 @@ def test_error_paths_do_not_touch_the_device(pair, cm):
     assert ei.value.code == 3  # Q4_0 is outside the path
 
 
-def test_direct_and_staged_matvec_paths_agree(cm, orc):
-    """The engine built with CMLD_FLAG_DIRECT_GEMV (separate quantise kernels + direct-load matvec)
-    and the default engine (staged matvec with fused prologues) see the same quantised codes; their
-    logits agree to f32 reassociation and their greedy tokens are equal."""
+def test_generic_and_staged_matvec_paths_agree(cm, orc):
+    """The engine built with CMLD_FLAG_DIRECT_GEMV (separate quantise kernels + the generic matvec),
+    the default engine (staged matvec with fused prologues), the engine with separate preparation
+    kernels and no graphs, and the plain reference-order engine (CMLD_FLAG_EXACT_ORDER) all keep the
+    CPU path's order of operations: identical logits."""
     from camelid_b200 import synth
 
     for mix in ("q8_0", "q4_k_m"):
@@ -194,14 +181,15 @@ def test_direct_and_staged_matvec_paths_agree(cm, orc):
         a = ModelPair(cfg, mix, seed=9)
         b = ModelPair(synth.engine_config("tiny", max_pos=64, flags=2), mix, seed=9)
         c = ModelPair(synth.engine_config("tiny", max_pos=64, flags=8 | 1 | 4), mix, seed=9)  # separate prep kernels, no graph, no PDL
+        d = ModelPair(synth.engine_config("tiny", max_pos=64, flags=16), mix, seed=9)
         prompt = orc.synth_tokens(8, 1, 8, cfg.vocab)
-        fa, fb, fc = (m.engine.prefill_tokens(0, prompt, 0) for m in (a, b, c))
+        fa, fb, fc, fd = (m.engine.prefill_tokens(0, prompt, 0) for m in (a, b, c, d))
         _, la, _ = a.engine.step_batch([0], [fa], [8], want_logits=True)
         _, lb, _ = b.engine.step_batch([0], [fb], [8], want_logits=True)
         _, lc, _ = c.engine.step_batch([0], [fc], [8], want_logits=True)
-        assert fa == fb == fc
-        assert np.abs(la - lb).max() < 1e-4 * np.abs(la).max()
-        assert np.array_equal(la, lc)  # same staged kernel, same quantised codes: identical bits
+        _, ld, _ = d.engine.step_batch([0], [fd], [8], want_logits=True)
+        assert fa == fb == fc == fd
+        assert np.array_equal(la, lb) and np.array_equal(la, lc) and np.array_equal(la, ld)
         _, launches_a = a.engine.last_timing()
         _, launches_c = c.engine.last_timing()
         assert launches_a < launches_c  # fused prologues (the default): fewer kernels per step
@@ -233,19 +221,18 @@ def test_mixtral_shaped_moe_parity(cm, orc):
         ref_logits, ref_hidden, ref_taps = ref.forward(emb, pos, want_taps=True)
         hidden, taps = eng.forward_token_hidden(emb, c, s, pos, pair.scale, taps=True)
         for layer in range(cfg.n_layers):
-            ok, max_abs, rel = hidden_gate(taps[layer], ref_taps[layer])
-            assert ok, (pos, layer, max_abs, rel)
+            assert np.array_equal(taps[layer].view(np.uint32), ref_taps[layer].view(np.uint32)), (pos, layer, hidden_gate(taps[layer], ref_taps[layer]))
         logits = eng.forward_token_logits(emb, c, s, pos, pair.scale)
-        assert hidden_gate(logits, ref_logits)[0]
+        assert np.array_equal(logits.view(np.uint32), ref_logits.view(np.uint32)), hidden_gate(logits, ref_logits)
     ref_tokens, _, gaps = ref.generate(prompt, 40, want_gaps=True)
     first = eng.prefill_tokens(1, prompt, 0)
     got = np.concatenate([[first], eng.decode_greedy([1], [first], [len(prompt)], 39)[:, 0]])
     n_match, gap = greedy_match(got, ref_tokens, gaps)
-    assert n_match >= 32, (n_match, gap)
+    assert n_match == 40, (n_match, gap)
 
 
 def test_tensor_batch_flag_moves_small_batches_to_the_tensor_core_kernel(cm, orc):
-    """CMLD_FLAG_TENSOR_BATCH (64): steps of 5..8 rows use the batched tensor-core matvec.  Same integers, f32 terms
+    """CMLD_FLAG_TENSOR_BATCH (64): steps of 5..32 rows use the int8 mma.sync matvec.  Same integers, f32 terms
     added in another order: logits within the acceptance gate of the default engine's, and the rows of such a
     step do not depend on their neighbours."""
     from camelid_b200 import synth
@@ -260,8 +247,61 @@ def test_tensor_batch_flag_moves_small_batches_to_the_tensor_core_kernel(cm, orc
     _, l1, h1 = fast.step_batch(seqs, toks, [0] * 6, want_logits=True, want_hidden=True)
     ok, max_abs, rel = hidden_gate(l1, l0)
     assert ok, (max_abs, rel)
-    assert not np.array_equal(l1, l0) or True  # the order of the f32 terms differs; equality is not required
     _, l2, _ = fast.step_batch(seqs[::-1], toks[::-1], [0] * 6, want_logits=True)
     assert np.array_equal(l2[::-1], l1)
     base.close()
     fast.close()
+
+
+# Continuous batching (ContinuousBatch::run_round, src/api/continuous_batch.rs:86-104): a round is N
+# independent serial token steps, so the oracle for a 16- or 32-row step is N single-sequence runs of
+# the checker.  "small" is wide enough (hidden 4096) for every matvec to take the staged kernel.
+@pytest.mark.parametrize("shape,mix,rows", [("small", "q4_k_m", 16), ("small", "q4_k_m", 32), ("small", "q8_0", 32),
+                                             ("tiny-moe", "q4_k_m", 16), ("tiny-moe", "q4_k_m", 32)])
+def test_steps_of_16_and_32_rows_equal_independent_sequences(cm, orc, shape, mix, rows):
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config(shape, max_pos=48, max_seqs=rows)
+    pair = ModelPair(cfg, mix, seed=77)
+    eng, ref = pair.engine, pair.oracle
+    prompts = [orc.synth_tokens(50 + s, 1, 3 + s % 5, cfg.vocab) for s in range(rows)]
+    firsts = [eng.prefill_tokens(s, prompts[s], 0) for s in range(rows)]
+    # the checker, one sequence at a time: prompt, then the logits of the step that follows it
+    want_first, want_logits = [], []
+    for s in range(rows):
+        for pos, t in enumerate(prompts[s]):
+            lg, _, _ = ref.forward(ref.embedding(int(t)), pos)
+        want_first.append(orc.argmax(lg))
+        lg, _, _ = ref.forward(ref.embedding(want_first[-1]), len(prompts[s]))
+        want_logits.append(lg)
+    assert firsts == want_first
+    toks, lg, _ = eng.step_batch(list(range(rows)), firsts, [len(p) for p in prompts], want_logits=True)
+    for s in range(rows):
+        assert np.array_equal(lg[s].view(np.uint32), want_logits[s].view(np.uint32)), (s, hidden_gate(lg[s], want_logits[s]))
+        assert toks[s] == orc.argmax(want_logits[s])
+    # rows do not depend on their neighbours: the same rows in another order
+    order = list(range(rows))[::-1]
+    _, lg2, _ = eng.step_batch(order, [firsts[s] for s in order], [len(prompts[s]) for s in order], want_logits=True)
+    assert np.array_equal(lg2[::-1], lg)
+
+
+def test_prefill_chunk_of_32_rows_leaves_the_serial_kv(cm, orc):
+    """prefill_then_decode_matches_sequential (src/cuda_resident/tests.rs:3143): a 40-token prompt ingested in
+    chunks of 32 rows leaves the KV rows, and gives the next token, of token-by-token steps — which are the
+    checker's."""
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("small", max_pos=64, max_seqs=2)
+    pair = ModelPair(cfg, "q4_k_m", seed=78)
+    eng, ref = pair.engine, pair.oracle
+    prompt = orc.synth_tokens(9, 1, 40, cfg.vocab)
+    first = eng.prefill_tokens(0, prompt, 0)
+    tok = None
+    for pos, t in enumerate(prompt):  # serial steps on the second sequence
+        tok, _, _ = eng.step_batch([1], [int(t)], [pos])
+        lg, _, _ = ref.forward(ref.embedding(int(t)), pos)
+    assert first == int(tok[0]) == orc.argmax(lg)
+    for layer in range(cfg.n_layers):
+        rk, rv = ref.read_kv_layer(layer, len(prompt))
+        k0, v0 = eng.read_kv_layer(layer, len(prompt))
+        assert np.array_equal(k0, rk) and np.array_equal(v0, rv), layer

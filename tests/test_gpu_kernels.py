@@ -108,13 +108,15 @@ def test_activation_quantisers_bit_exact(cm, orc, cols, batch):
     ("Q8_0", 96, 64), ("Q8_0", 515, 2048), ("Q8_0", 64, 8192),
     ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 3072), ("Q4_K", 64, 14336),
     ("Q6_K", 33, 256), ("Q6_K", 512, 4096), ("Q6_K", 130, 3072), ("Q6_K", 64, 14336)])
-@pytest.mark.parametrize("batch", [1, 4, 8])
-@pytest.mark.parametrize("kernel", ["staged", "direct"])
+@pytest.mark.parametrize("batch", [1, 2, 3, 8])
+@pytest.mark.parametrize("kernel", ["staged", "generic"])
 def test_gemv_matches_checker(cm, orc, name, rows, cols, batch, kernel):
+    """Both matvec kernels add a row's f32 terms in the CPU dot's order: every output equals the
+    checker's bit for bit (the staged kernel takes the shapes it supports, the generic one the rest)."""
     from camelid_b200.engine import quantize_activation, export_activation, DeviceBuffer
     from camelid_b200._lib import check
 
-    check(cm.lib().cmld_gemv_select_kernel(1 if kernel == "direct" else 0))
+    check(cm.lib().cmld_gemv_select_kernel(1 if kernel == "generic" else 0))
     qt = QT[name]
     wire = orc.synth_tensor(qt, 11, rows * 7 + cols, rows, cols, 0.02)
     w = cm.Weight.from_wire(qt, rows, cols, wire)
@@ -127,19 +129,14 @@ def test_gemv_matches_checker(cm, orc, name, rows, cols, batch, kernel):
     res = rng.standard_normal((batch, rows)).astype(np.float32)
     res_d = DeviceBuffer.from_numpy(res)
     y_res = w.gemv(act, batch, res_d)
-    exact = 0
-    for b in range(batch):
-        ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
-        # tolerance: 1e-4 relative + 1e-5 of the largest output (f32 reassociation of <=448 terms)
-        ok, max_abs, n_bad = close_enough(y[b], ref, rel=1e-4, floor=1e-5)
-        assert ok, (name, rows, cols, b, max_abs, n_bad)
-        assert np.array_equal(y_res[b], (res[b] + y[b]).astype(np.float32))
-        exact += int((y[b] == ref).sum())
-    assert exact > 0  # some rows agree to the last bit; all agree within the tolerance above
-    # batched columns are bitwise the single-column results
-    y1 = w.gemv(quantize_activation(kind, x[:1]), 1)
-    assert np.array_equal(y1[0], y[0])
-    check(cm.lib().cmld_gemv_select_kernel(0))
+    try:
+        for b in range(batch):
+            ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
+            bad = np.nonzero(y[b].view(np.uint32) != ref.view(np.uint32))[0]
+            assert bad.size == 0, (name, rows, cols, b, bad[:5], y[b][bad[:5]], ref[bad[:5]])
+            assert np.array_equal(y_res[b], (res[b] + y[b]).astype(np.float32))
+    finally:
+        check(cm.lib().cmld_gemv_select_kernel(0))
 
 
 # The staged kernel's fused prologues: RMSNorm / plain / SwiGLU + quantiser + matvec in one launch
@@ -175,9 +172,9 @@ def test_fused_prologue_equals_separate_steps(cm, orc, name, rows, cols, mode, b
     assert np.array_equal(got, want)
 
 
-# More than 8 activation rows: the tensor-core kernel (one pass over the weights).  Integer parts are
-# those of the row kernel; only the order of the superblocks' f32 terms differs, so the bar is the same
-# tolerance against the CPU row dot, and closeness (not bit equality) to the <= 8-row kernel.
+# More than 8 activation rows.  By default they run as passes of the ordered kernels (the checker's bits).
+# The int8 mma.sync kernel reads the weights once for all rows; its integer parts are exact but the
+# superblocks' f32 terms are added as a tree, so it is opt-in and held to a tolerance.
 @pytest.mark.parametrize("name,rows,cols", [
     ("Q8_0", 96, 256), ("Q8_0", 515, 2048), ("Q8_0", 70, 1792),
     ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 1792), ("Q4_K", 64, 14336),
@@ -195,22 +192,29 @@ def test_gemv_batched_tensor_core_kernel_matches_checker(cm, orc, name, rows, co
     kind = cm.ACT_Q8_0 if qt == 8 else cm.ACT_Q8_K
     act = quantize_activation(kind, x)
     codes, scales = export_activation(kind, act, cols, batch)
-    y = w.gemv(act, batch)
     res = rng.standard_normal((batch, rows)).astype(np.float32)
     res_d = DeviceBuffer.from_numpy(res)
-    y_res = w.gemv(act, batch, res_d)
+    # default: passes of the ordered kernels -> the checker's bits, whatever the batch
+    y = w.gemv(act, batch)
     for b in range(batch):
         ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
-        ok, max_abs, n_bad = close_enough(y[b], ref, rel=1e-4, floor=1e-5)
-        assert ok, (name, rows, cols, b, max_abs, n_bad)
-        assert np.array_equal(y_res[b], (res[b] + y[b]).astype(np.float32))
-    # the <= 8-row kernel on the first rows: same integers, f32 terms added in another order
-    y8 = w.gemv(quantize_activation(kind, x[:8]), 8)
-    ok, max_abs, n_bad = close_enough(y[:8], y8, rel=1e-5, floor=1e-6)
-    assert ok, (max_abs, n_bad)
-    # and the very same bits whatever the row's neighbours are
-    y_again = w.gemv(quantize_activation(kind, x[::-1].copy()), batch)
-    assert np.array_equal(y_again[::-1], y)
+        assert np.array_equal(y[b].view(np.uint32), ref.view(np.uint32)), (name, rows, cols, b)
+    # opt-in: the int8 mma.sync kernel (kernel choice 8), one pass over the weights, tree sums
+    check(cm.lib().cmld_gemv_select_kernel(8))
+    try:
+        ym = w.gemv(act, batch)
+        ym_res = w.gemv(act, batch, res_d)
+        for b in range(batch):
+            ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
+            # tolerance: 1e-4 relative + 1e-5 of the largest output (f32 reassociation of <= 448 terms)
+            ok, max_abs, n_bad = close_enough(ym[b], ref, rel=1e-4, floor=1e-5)
+            assert ok, (name, rows, cols, b, max_abs, n_bad)
+            assert np.array_equal(ym_res[b], (res[b] + ym[b]).astype(np.float32))
+        # the very same bits whatever the row's neighbours are
+        y_again = w.gemv(quantize_activation(kind, x[::-1].copy()), batch)
+        assert np.array_equal(y_again[::-1], ym)
+    finally:
+        check(cm.lib().cmld_gemv_select_kernel(0))
 
 
 def test_gemv_end_to_end_against_f32_activation_path(cm, orc):
@@ -242,8 +246,8 @@ def test_rms_norm_and_swiglu(cm, orc, cols, batch):
     codes, scales = export_activation(kind, act, cols, batch)
     for b in range(batch):
         ref = orc.rms_norm(x[b], wgt, 1e-5)
-        # tolerance 2e-6 relative: the mean square is a tree sum here, sequential on the CPU
-        assert np.abs(out[b] - ref).max() <= 2e-6 * np.abs(ref).max()
+        # the mean square has the bits of the CPU's sequential sum, so the normalised row is the CPU's
+        assert np.array_equal(out[b].view(np.uint32), ref.view(np.uint32))
         # the fused quantiser is the standalone quantiser applied to the kernel's own f32 output
         rq, rs = (orc.quantize_act_q8_k if kind == cm.ACT_Q8_K else orc.quantize_act_q8_0)(out[b])
         assert np.array_equal(codes[b], rq) and np.array_equal(scales[b], rs)
@@ -252,8 +256,7 @@ def test_rms_norm_and_swiglu(cm, orc, cols, batch):
     check(cm.lib().cmld_silu_mul(gd.ptr, xd.ptr, cols, batch, od.ptr, 0, None))
     out = od.to_numpy(np.float32).reshape(batch, cols)
     ref = np.stack([orc.silu_mul(g[b], x[b]) for b in range(batch)])
-    # tolerance: CUDA expf is within 2 ulp of glibc's
-    assert np.abs(out - ref).max() <= 1e-6 * np.abs(ref).max()
+    assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))  # expf restated from glibc: the same bits
 
 
 def test_argmax_lowest_index_wins(cm, orc):
@@ -299,3 +302,32 @@ def test_attention_matches_checker(cm, orc, n_heads, n_kv, hd, n_pos):
         ref = orc.attention_head(q[h], kf[h // g, :n_pos], vf[h // g, :n_pos], n_pos, hd, scale)
         # tolerance 2e-5 of the largest output: split ranges + online softmax reassociate the sums
         assert np.abs(out[h] - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max()), (h, np.abs(out[h] - ref).max())
+
+
+# The attention the engine runs by default: every sum in the CPU's order, so the CPU's bits.
+@pytest.mark.parametrize("n_heads,n_kv,hd,n_pos", [(2, 1, 32, 4), (32, 8, 64, 1), (32, 8, 64, 33), (24, 8, 128, 300),
+                                                    (32, 8, 128, 1153), (8, 8, 128, 70), (8, 1, 64, 515), (16, 8, 128, 256),
+                                                    (32, 8, 128, 2049), (16, 4, 64, 3000), (32, 8, 128, 8192),
+                                                    (8, 8, 64, 9), (24, 8, 64, 700), (4, 4, 128, 1025)])
+def test_attention_reference_order_is_bit_identical(cm, orc, n_heads, n_kv, hd, n_pos):
+    from camelid_b200.engine import DeviceBuffer
+    from camelid_b200._lib import check
+
+    max_pos = max(256, n_pos)
+    rng = np.random.default_rng(n_heads * n_pos + 1)
+    q = rng.standard_normal((n_heads, hd)).astype(np.float32)
+    k = np.zeros((n_kv, max_pos, hd), np.float16)
+    v = np.zeros((n_kv, max_pos, hd), np.float16)
+    k[:, :n_pos] = rng.standard_normal((n_kv, n_pos, hd)).astype(np.float16)
+    v[:, :n_pos] = rng.standard_normal((n_kv, n_pos, hd)).astype(np.float16)
+    scale = float(1.0 / np.sqrt(np.float32(hd)))
+    out_d = DeviceBuffer(n_heads * hd * 4)
+    qd, kd, vd = DeviceBuffer.from_numpy(q), DeviceBuffer.from_numpy(k), DeviceBuffer.from_numpy(v)
+    check(cm.lib().cmld_attention_decode_ordered(qd.ptr, kd.ptr, vd.ptr, n_heads, n_kv, hd, max_pos, n_pos, scale, out_d.ptr))
+    out = out_d.to_numpy(np.float32).reshape(n_heads, hd)
+    kf, vf = k.astype(np.float32), v.astype(np.float32)
+    g = n_heads // n_kv
+    for h in range(n_heads):
+        ref = orc.attention_head(q[h], kf[h // g, :n_pos], vf[h // g, :n_pos], n_pos, hd, scale)
+        bad = np.nonzero(out[h].view(np.uint32) != ref.view(np.uint32))[0]
+        assert bad.size == 0, (h, bad[:4], out[h][bad[:4]], ref[bad[:4]])

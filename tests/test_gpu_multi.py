@@ -66,9 +66,14 @@ def _single(shape, mix, flags=0):
 
 def _compare(ranks, one):
     for r in ranks[1:]:
-        for k in ("firsts", "tokens", "next", "logits", "hidden"):
+        for k in ("firsts", "tokens", "next", "logits", "hidden", "probe_logits", "probe_hidden"):
             assert np.array_equal(ranks[0][k], r[k]), f"ranks disagree on {k}"
     got = ranks[0]
+    # The hard bar: a step fed fixed tokens after the same prompts.  A sharded sum adds the ranks' partial rows
+    # in rank order, which is not the single GPU's (the CPU path's) order, so the bar is the acceptance gate.
+    for k in ("probe_hidden", "probe_logits"):
+        ok, max_abs, rel = hidden_gate(got[k], one[k])
+        assert ok, (k, max_abs, rel)
     # prompt ingestion: same next token on both sequences unless a near tie
     same = int((got["tokens"] == one["tokens"]).all(axis=1).sum())
     print(f"greedy steps equal to the single-GPU engine: {same}/{one['tokens'].shape[0]}")
@@ -82,8 +87,8 @@ def _compare(ranks, one):
             if top2[s, 1] - top2[s, 0] > 1e-3:
                 assert got["next"][s] == one["next"][s]
     else:
-        # the sequences parted at a near tie; the first step (same inputs on both sides) must still agree
-        assert np.array_equal(got["firsts"], one["firsts"]) or same >= 0
+        # the greedy streams parted somewhere (a near tie on this toy model); the steps before that are equal
+        print("greedy streams of the sharded and the single-GPU engine differ after", same, "steps")
 
 
 @pytest.mark.skipif(not has_gpu() or _n_gpus() < 2, reason="needs two GPUs")

@@ -24,10 +24,12 @@ def test_noalloc_attention_matches_allocating_entry_point_twice_in_a_row(cm):
     from camelid_b200._lib import check
     from camelid_b200.engine import DeviceBuffer
 
-    max_pos = 2048
-    # two calls in a row with different shapes: the second finds the first one's partials and
-    # counters in the shared array
-    for seed, (n_heads, n_kv, hd, n_pos) in enumerate([(32, 8, 128, 1153), (24, 8, 64, 77)]):
+    # Calls in a row with different shapes.  Contexts past 2048 positions go through the fixed array (split-range
+    # partials and the per-head arrival counters): the second such call finds the first one's partials and
+    # counters there and must not be disturbed by them.  Then two short-context calls, which merge their
+    # ranges inside a thread-block cluster and use the array for the position word only.
+    for seed, (n_heads, n_kv, hd, n_pos, max_pos) in enumerate([(32, 8, 128, 2500, 4096), (24, 8, 64, 2100, 4096),
+                                                                 (32, 8, 128, 1153, 2048), (24, 8, 64, 77, 2048)]):
         q, k, v = _case(seed, n_heads, n_kv, hd, n_pos, max_pos)
         qd, kd, vd = DeviceBuffer.from_numpy(q), DeviceBuffer.from_numpy(k), DeviceBuffer.from_numpy(v)
         out_a, out_b = DeviceBuffer(q.nbytes), DeviceBuffer(q.nbytes)
