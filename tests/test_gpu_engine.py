@@ -176,12 +176,12 @@ def test_generic_and_staged_matvec_paths_agree(cm, orc):
     CPU path's order of operations: identical logits."""
     from camelid_b200 import synth
 
-    for mix in ("q8_0", "q4_k_m"):
-        cfg = synth.engine_config("tiny", max_pos=64)
+    for shape, mix in (("tiny", "q8_0"), ("tiny", "q4_k_m"), ("small", "q4_k_m")):
+        cfg = synth.engine_config(shape, max_pos=64)
         a = ModelPair(cfg, mix, seed=9)
-        b = ModelPair(synth.engine_config("tiny", max_pos=64, flags=2), mix, seed=9)
-        c = ModelPair(synth.engine_config("tiny", max_pos=64, flags=8 | 1 | 4), mix, seed=9)  # separate prep kernels, no graph, no PDL
-        d = ModelPair(synth.engine_config("tiny", max_pos=64, flags=16), mix, seed=9)
+        b = ModelPair(synth.engine_config(shape, max_pos=64, flags=2), mix, seed=9)
+        c = ModelPair(synth.engine_config(shape, max_pos=64, flags=8 | 1 | 4), mix, seed=9)  # separate prep kernels, no graph, no PDL
+        d = ModelPair(synth.engine_config(shape, max_pos=64, flags=16), mix, seed=9)
         prompt = orc.synth_tokens(8, 1, 8, cfg.vocab)
         fa, fb, fc, fd = (m.engine.prefill_tokens(0, prompt, 0) for m in (a, b, c, d))
         _, la, _ = a.engine.step_batch([0], [fa], [8], want_logits=True)
@@ -192,7 +192,10 @@ def test_generic_and_staged_matvec_paths_agree(cm, orc):
         assert np.array_equal(la, lb) and np.array_equal(la, lc) and np.array_equal(la, ld)
         _, launches_a = a.engine.last_timing()
         _, launches_c = c.engine.last_timing()
-        assert launches_a < launches_c  # fused prologues (the default): fewer kernels per step
+        if shape == "small":  # wide enough for the staged kernel, whose fused prologues (the default) save kernels
+            assert launches_a < launches_c
+        for m in (a, b, c, d):
+            m.engine.close()
 
 
 def test_wire_upload_path_equals_device_generated(cm, orc):
