@@ -505,10 +505,22 @@ int32_t cmld_attention_decode_ordered(const float *q_dev, const void *k_cache_de
   int64_t cap = 0;
   for (int64_t c : {1024, 2048, 4096, 8192})
     if (cap == 0 && n_pos <= c) cap = c;
+  // CMLD_ATTN_PHASES=1: print where the cluster kernel's time goes (CTA 0's clock at the end of each phase)
+  unsigned long long *phases = nullptr;
+  if (getenv("CMLD_ATTN_PHASES") && cudaMalloc(&phases, 64) == cudaSuccess) cudaMemset(phases, 0, 64);
+  a.phase_ns = phases;
   int32_t rc;
   if (cap > 0 && attention_ordered_fits(n_heads, n_kv_heads, head_dim, cap)) rc = launch_attention_ordered(a, cap, nullptr);
   else rc = launch_attention_exact(a, nullptr);
   if (rc == CMLD_OK) rc = sync_ok("attention_decode_ordered");
+  if (phases) {
+    unsigned long long h[8] = {0};
+    cudaMemcpy(h, phases, 64, cudaMemcpyDeviceToHost);
+    if (h[5])
+      fprintf(stderr, "attention phases (us): scores %.2f, maxima %.2f, weights %.2f, sums %.2f, scaling %.2f, chains %.2f\n", (h[1] - h[0]) * 1e-3,
+              (h[2] - h[1]) * 1e-3, (h[3] - h[2]) * 1e-3, (h[4] - h[3]) * 1e-3, (h[6] - h[4]) * 1e-3, (h[5] - h[6]) * 1e-3);
+    cudaFree(phases);
+  }
   cudaFree(pos_slot);
   return rc;
 }

@@ -14,9 +14,11 @@
 //   * softmax: range maxima meet through distributed shared memory; e_p is written straight into the
 //     shared memory of the CTAs that need it; the sum over positions is a sequential f32 sum of non-negative
 //     terms, computed with its exact bits by all warps of one CTA per head (exact_sum.cuh);
-//   * output: the G*head_dim chains over positions are spread evenly over the 8 CTAs; a warp walks 32 of
-//     them with the V slice it needs streamed through a private cp.async ring that was started when the
-//     kernel began, so V arrives while the scores are still being computed.
+//   * output: CTA r of the cluster owns dims [r*hd/8, (r+1)*hd/8) of ALL G heads (G*hd/8 chains), so a V element
+//     it loads serves G chains and the V bytes a CTA needs are 1/8 of the rows.  Producer warps form the products
+//     (e_p/S)*v_pd — V streamed through a cp.async ring that was started when the kernel began, so V arrives
+//     while the scores are still being computed — into double-buffered shared memory; a chain warp walks 32
+//     chains with one load per addition, which costs the additions' own latency (4 cycles each).
 // RoPE of q and k and the f16 KV append can be folded in (fuse_rope), as in the split-range kernel.
 #include <cooperative_groups.h>
 
@@ -28,13 +30,14 @@ namespace cmld {
 
 namespace cg = cooperative_groups;
 
-constexpr int kOaThreads = 256;
+constexpr int kOaThreads = 512;
 constexpr int kOaWarps = kOaThreads / 32;
 constexpr int kOaCluster = 8;
-constexpr int kOaKBlock = 64;   // positions per staged K block
-constexpr int kOaVChunk = 64;   // positions per V ring slot
-constexpr int kOaVDepth = 8;    // ring slots per chain warp
-constexpr int kOaVSlot = kOaVChunk * 64;  // bytes: 32 dims x f16 per position
+constexpr int kOaKBlock = 128;  // positions per staged K block (at most)
+constexpr int kOaBatch = 64;    // positions per product buffer
+// V ring slots per producer warp (one slot per batch of 64 positions): as many as shared memory allows, so that for
+// contexts of up to 2048 positions every V byte is requested when the kernel starts
+__host__ __device__ constexpr int oa_vdepth(int64_t cap) { return cap <= 2048 ? 32 : (cap <= 4096 ? 16 : 8); }
 
 __device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
@@ -67,49 +70,59 @@ __device__ __forceinline__ float oa_rope_elem(const float *x, int d, int rope_di
 struct OaLayout {
   int cap_range;   // positions a CTA's range can hold
   int cap_pad;     // positions per weight array (multiple of 256)
-  int n_warr;      // weight arrays per CTA (heads its chains touch)
-  int off_q, off_k, off_klast, off_sc, off_w, off_ws, off_mx, off_inv, off_v, total;
+  int off_q, off_sc, off_a, off_prod, off_ws, off_mx, off_inv, off_klast, off_v, total;
 };
 
+// Shared-memory map.  Region A holds the K staging buffers while the scores are computed and, after that, the
+// softmax weights of all G heads (written by the whole cluster once nobody scores any more).
 __host__ __device__ inline OaLayout oa_layout(int G, int HD, int64_t cap) {
   OaLayout L;
-  const int cpc = G * HD / kOaCluster;
+  const int dpc = HD / kOaCluster;
   L.cap_range = (int)((cap + kOaCluster - 1) / kOaCluster);
   L.cap_pad = (int)((cap + 255) / 256 * 256);
-  L.n_warr = (HD % cpc == 0) ? 1 : 2;
   int off = 0;
   L.off_q = off;
   off += G * HD * 4;
-  L.off_k = off;
-  off += 2 * kOaKBlock * (HD * 2 + 16);
-  L.off_klast = off;
-  off += HD * 2;
   L.off_sc = off;
   off += G * L.cap_range * 4;
   off = (off + 15) & ~15;
-  L.off_w = off;
-  off += L.n_warr * L.cap_pad * 4;
+  L.off_a = off;
+  {
+    const int kbytes = 2 * kOaKBlock * (HD * 2 + 16), wbytes = G * L.cap_pad * 4;
+    off += kbytes > wbytes ? kbytes : wbytes;
+  }
+  L.off_prod = off;
+  off += 2 * (kOaBatch / 4) * (G * dpc * 4 + 4) * 4;  // products: [buffer][4 positions][chain][position in the four] + 4 floats of padding
   L.off_ws = off;
-  off += (L.cap_pad >> 8) * 16 + (L.cap_pad >> 3) * 8 + 16;
+  off += xsum::workspace_bytes(L.cap_pad);
+  off = (off + 15) & ~15;
   L.off_mx = off;
   off += kOaCluster * 8 * 4;
   L.off_inv = off;
-  off += 16;
+  off += 48;
+  L.off_klast = off;
+  off += HD * 2;
   off = (off + 127) & ~127;
   L.off_v = off;
-  off += ((cpc + 31) / 32) * kOaVDepth * kOaVSlot;
+  off += (2 * (dpc / 8)) * oa_vdepth(cap) * 512;  // producer warps x slots x (32 lanes x 16 bytes)
   L.total = off;
   return L;
 }
 
-template <int G, int HD>
+template <int G, int HD, int VD>
 __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a, int64_t cap) {
   asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int CPC = G * HD / kOaCluster;   // chains of this CTA (consecutive (head, d) pairs of the kv group)
+  constexpr int DPC = HD / kOaCluster;       // dims of every head this CTA owns in the output phase
+  constexpr int CPC = G * DPC;               // its chains: (head g, dim dd) -> g * DPC + dd
+  constexpr int NP = DPC / 8;                // 16-byte pieces of a V row it needs
   constexpr int NCW = (CPC + 31) / 32;       // warps that walk chains
+  constexpr int NPW = 2 * NP;                // producer warps: each takes 32/NP positions of every 64-position batch
+  constexpr int PPB = 32 / NP;               // positions per producer warp and batch
+  constexpr int QP = CPC * 4 + 4;            // floats per group of four positions: [chain][position in the group], padded so that
+                                             // the producers' scalar stores (neighbouring positions) spread over the banks
   constexpr int KP = HD * 2 + 16;            // K row pitch in shared memory
+  static_assert(DPC % 8 == 0 && NPW >= 1 && NPW + NCW <= kOaWarps, "shape not supported");
   const OaLayout L = oa_layout(G, HD, cap);
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = (int)cluster.block_rank();
@@ -120,48 +133,70 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
   const int slot = a.slots[b];
   if (pos < 0 || pos >= a.max_pos || n_pos > cap) return;  // the same for every CTA of the cluster
   float(*s_q)[HD] = reinterpret_cast<float(*)[HD]>(smem + L.off_q);
-  uint8_t *s_k = smem + L.off_k;
-  __half *s_klast = reinterpret_cast<__half *>(smem + L.off_klast);
   float *s_sc = reinterpret_cast<float *>(smem + L.off_sc);   // [G][cap_range]
-  float *s_w = reinterpret_cast<float *>(smem + L.off_w);     // [n_warr][cap_pad]
+  uint8_t *s_k = smem + L.off_a;                              // K staging ...
+  float *s_w = reinterpret_cast<float *>(smem + L.off_a);     // ... then [G][cap_pad] weights
+  float *s_prod = reinterpret_cast<float *>(smem + L.off_prod);  // [2][kOaBatch / 4][QP]
   uint8_t *s_ws = smem + L.off_ws;
   float *s_mx = reinterpret_cast<float *>(smem + L.off_mx);   // [cluster rank][8]
-  float *s_inv = reinterpret_cast<float *>(smem + L.off_inv); // [n_warr] (+ one scratch float)
-  uint8_t *s_v = smem + L.off_v;
+  float *s_inv = reinterpret_cast<float *>(smem + L.off_inv); // [8]
+  __half *s_klast = reinterpret_cast<__half *>(smem + L.off_klast);
+  uint8_t *s_v = smem + L.off_v;                              // [producer warp][VD][32 lanes x 16 bytes]
 
+  unsigned long long *ph = (a.phase_ns && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0) ? a.phase_ns : nullptr;
+  if (ph) ph[0] = global_ns();
   __half *kbase = const_cast<__half *>(a.k_cache) + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
   __half *vbase = const_cast<__half *>(a.v_cache) + ((int64_t)slot * a.n_kv_heads + kvh) * a.max_pos * HD;
   const int n_pre = a.fuse_rope ? n_pos - 1 : n_pos;  // positions whose K/V rows are already in the cache
+  const int d0 = crank * DPC;                         // this CTA's first dim
 
-  // ---- chain bookkeeping: this CTA's chains are flat indices [c0, c0 + CPC) of (head, d) within the kv group
-  const int c0 = crank * CPC;
-  const int g_first = c0 / HD;  // first head this CTA's chains belong to
-
-  // ---- V ring of the chain warps: start it now
-  const int ch_start = c0 + warp * 32;  // first chain of this warp
-  uint8_t *vring = s_v + warp * kOaVDepth * kOaVSlot;
-  const int n_vchunks = (n_pre + kOaVChunk - 1) / kOaVChunk;
-  auto issue_v = [&](int chunk) {
-    if (chunk < n_vchunks) {
-      uint8_t *dst = vring + (chunk % kOaVDepth) * kOaVSlot;
-      const int gran = ((ch_start >> 3) + (lane & 3)) % (HD / 8);  // which 8 dims of the row this lane copies
-#pragma unroll
-      for (int i = 0; i < kOaVChunk / 8; ++i) {
-        const int pp = (lane >> 2) + 8 * i, p = chunk * kOaVChunk + pp;
-        if (p < n_pre) cp_async16(dst + pp * 64 + (lane & 3) * 16, vbase + (int64_t)p * HD + gran * 8);
+  // ---- V rings of the producer warps (the last NPW warps).  Producer warp j owns positions [j*PPB, (j+1)*PPB) of
+  // every 64-position batch; a lane copies one 16-byte piece (8 dims of one position), and later multiplies the
+  // very bytes it copied itself, so the producers never wait for each other.
+  const int pw = warp - (kOaWarps - NPW);  // producer index, < 0 for the other warps
+  const int n_batches = (n_pre + kOaBatch - 1) / kOaBatch;
+  const int v_pp = lane % PPB, v_k = lane / PPB;  // this lane's position within the warp's block, and piece
+  uint8_t *vring = s_v + (pw < 0 ? 0 : pw) * VD * 512;
+  auto issue_v = [&](int bt) {
+    if (bt < n_batches) {
+      const int p = bt * kOaBatch + pw * PPB + v_pp;
+      if (p < n_pre) cp_async16(vring + (bt % VD) * 512 + lane * 16, vbase + (int64_t)p * HD + d0 + 8 * v_k);
+    }
+    cp_async_commit();
+  };
+  // ranges: CTA r scores positions [r*len, (r+1)*len), in n_blocks blocks of bsz positions
+  const int len = (n_pos + kOaCluster - 1) / kOaCluster;
+  const int lo = crank * len, hi = min(n_pos, lo + len);
+  const int n_blocks = hi > lo ? (hi - lo + kOaKBlock - 1) / kOaKBlock : 0;
+  const int bsz = n_blocks > 0 ? (hi - lo + n_blocks - 1) / n_blocks : 0;
+  auto issue_k = [&](int blk) {
+    if (blk < n_blocks) {
+      uint8_t *dst = s_k + (blk & 1) * kOaKBlock * KP;
+      for (int i = tid; i < bsz * (HD / 8); i += kOaThreads) {
+        const int pp = i / (HD / 8), gdx = i % (HD / 8), p = lo + blk * bsz + pp;
+        if (p < hi && p < n_pre) cp_async16(dst + pp * KP + gdx * 16, kbase + (int64_t)p * HD + gdx * 8);
       }
     }
     cp_async_commit();
   };
-  if (warp < NCW) {
-    for (int c = 0; c < kOaVDepth; ++c) issue_v(c);
+  // With the KV append folded in, every row this kernel prefetches was written by an earlier step: the loads
+  // can start before the kernel waits for its predecessor (which produces q and the new k / v rows).
+  if (a.fuse_rope) {
+    issue_k(0);
+    issue_k(1);
+    if (pw >= 0)
+      for (int c = 0; c < VD; ++c) issue_v(c);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (!a.fuse_rope) {
+    issue_k(0);
+    issue_k(1);
+    if (pw >= 0)
+      for (int c = 0; c < VD; ++c) issue_v(c);
   }
 
   // ---- q (rotated), and the row's own K/V: appended to the cache, K kept for the scores
   const float *q = a.q + (int64_t)b * a.q_stride + (int64_t)kvh * G * HD;
-  // ranges: CTA r scores positions [r*len, (r+1)*len)
-  const int len = (n_pos + kOaCluster - 1) / kOaCluster;
-  const int lo = crank * len, hi = min(n_pos, lo + len);
   if (a.fuse_rope) {
     const int half = a.rope_dim >> 1;
     const float *ct = a.cos_tab + (int64_t)(a.index_by_position ? pos : b) * half;
@@ -181,30 +216,21 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
     for (int i = tid; i < G * HD; i += kOaThreads) s_q[i / HD][i % HD] = q[i];
   }
 
-  // ---- scores of this CTA's range, K staged block by block
-  const int n_blocks = (hi - lo + kOaKBlock - 1) / kOaKBlock;
-  auto issue_k = [&](int blk) {
-    if (blk < n_blocks) {
-      uint8_t *dst = s_k + (blk & 1) * kOaKBlock * KP;
-      for (int i = tid; i < kOaKBlock * (HD / 8); i += kOaThreads) {
-        const int pp = i / (HD / 8), gdx = i % (HD / 8), p = lo + blk * kOaKBlock + pp;
-        if (p < hi && p < n_pre) cp_async16(dst + pp * KP + gdx * 16, kbase + (int64_t)p * HD + gdx * 8);
-      }
-    }
-    cp_async_commit();
-  };
-  issue_k(0);
+  // ---- scores of this CTA's range, K staged block by block; a thread owns one (position, head) chain
   for (int blk = 0; blk < n_blocks; ++blk) {
-    issue_k(blk + 1);
-    cp_async_wait<1>();
+    // groups in flight, oldest first: K block blk, K block blk+1, then (producer warps) the V ring's first VD slots
+    // or, from the second pass on, nothing younger: wait until block blk has landed
+    if (blk == 0 && pw >= 0) cp_async_wait<VD + 1>();
+    else if (blk == 0) cp_async_wait<1>();
+    else cp_async_wait<1>();
     __syncthreads();  // block blk has landed for everyone (the first pass also publishes s_q and s_klast)
     const uint8_t *kb = s_k + (blk & 1) * kOaKBlock * KP;
-    for (int pair = tid; pair < kOaKBlock * G; pair += kOaThreads) {
-      const int pp = pair % kOaKBlock, g = pair / kOaKBlock, p = lo + blk * kOaKBlock + pp;
+    for (int pair = tid; pair < bsz * G; pair += kOaThreads) {
+      const int pp = pair % bsz, g = pair / bsz, p = lo + blk * bsz + pp;
       if (p < hi) {
         const uint4 *kr = p < n_pre ? reinterpret_cast<const uint4 *>(kb + pp * KP) : reinterpret_cast<const uint4 *>(s_klast);
         float s = 0.0f;
-#pragma unroll 4
+#pragma unroll
         for (int j = 0; j < HD / 8; ++j) {
           const uint4 raw = kr[j];
           const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
@@ -222,10 +248,12 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
         s_sc[g * L.cap_range + (p - lo)] = __fmul_rn(s, a.scale);
       }
     }
-    __syncthreads();  // the buffer is refilled two blocks later
+    __syncthreads();  // everyone is done with the buffer
+    issue_k(blk + 2);
   }
   if (n_blocks == 0) __syncthreads();
   cp_async_wait<0>();
+  if (ph) ph[1] = global_ns();  // scores done
 
   // ---- range maxima to every CTA
   if (warp < G) {
@@ -234,94 +262,191 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
     m = warp_max(m);
     if (lane < kOaCluster) cluster.map_shared_rank(s_mx, lane)[crank * 8 + warp] = m;
   }
-  cluster.sync();
-  // ---- e_p = expf(score - max) into the CTAs whose chains belong to the head
+  cluster.sync();  // also: nobody reads its K staging area any more, so the weights may now be written over it
+  if (ph) ph[2] = global_ns();  // maxima exchanged
+  // ---- e_p = expf(score - max) into every CTA of the cluster (each needs all heads' weights for its chains)
   for (int i = tid; i < G * (hi - lo); i += kOaThreads) {
     const int g = i / (hi - lo), pi = i % (hi - lo);
     float m = -INFINITY;
 #pragma unroll
     for (int r = 0; r < kOaCluster; ++r) m = fmaxf(m, s_mx[r * 8 + g]);
     const float e = expf_exact(__fsub_rn(s_sc[g * L.cap_range + pi], m));
-    const int r_lo = (g * HD) / CPC, r_hi = ((g + 1) * HD - 1) / CPC;
-    for (int r = r_lo; r <= r_hi; ++r) {
-      const int hl = g - (r * CPC) / HD;  // index of head g among the heads of CTA r's chains
-      cluster.map_shared_rank(s_w, r)[hl * L.cap_pad + lo + pi] = e;
-    }
-  }
-  cluster.sync();
-  // ---- S = e_0 + e_1 + ... in order, by the first CTA that holds the head's weights; 1/S to all that hold them
-  {
-    int my_head = -1;  // the head whose sum this CTA computes
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-      if ((g * HD) / CPC == crank) my_head = g;
-    if (my_head >= 0) {
-      float *w = s_w + (my_head - g_first) * L.cap_pad;
-      const int n_pad = (n_pos + 255) & ~255;
-      for (int i = n_pos + tid; i < n_pad; i += kOaThreads) w[i] = 0.0f;  // adding +0 leaves a sum as it is
-      const int nch = n_pad >> 8;
-      const float ssum = xsum::cta_sum<kOaWarps>(w, n_pad, warp, lane, 1, reinterpret_cast<double *>(s_ws),
-                                                reinterpret_cast<uint32_t *>(s_ws + nch * 8),
-                                                reinterpret_cast<xsum::Item *>(s_ws + nch * 16), s_inv + 3);
-      if (tid == 0) {
-        const float inv = __fdiv_rn(1.0f, ssum);
-        const int r_lo = (my_head * HD) / CPC, r_hi = ((my_head + 1) * HD - 1) / CPC;
-        for (int r = r_lo; r <= r_hi; ++r) cluster.map_shared_rank(s_inv, r)[my_head - (r * CPC) / HD] = inv;
-      }
-    }
+    for (int r = 0; r < kOaCluster; ++r) cluster.map_shared_rank(s_w, r)[g * L.cap_pad + lo + pi] = e;
   }
   cluster.sync();
-  // ---- prob_p = e_p * (1/S), in place
-  for (int i = tid; i < L.n_warr * n_pos; i += kOaThreads) {
-    const int hl = i / n_pos, p = i % n_pos;
-    if (g_first + hl < G) s_w[hl * L.cap_pad + p] = __fmul_rn(s_w[hl * L.cap_pad + p], s_inv[hl]);
+  if (ph) ph[3] = global_ns();  // weights delivered
+  // ---- S = e_0 + e_1 + ... in order: head g by CTA g; 1/S to all
+  if (crank < G) {
+    float *w = s_w + crank * L.cap_pad;
+    const int n_pad = (n_pos + 255) & ~255;
+    for (int i = n_pos + tid; i < n_pad; i += kOaThreads) w[i] = 0.0f;  // adding +0 leaves a sum as it is
+    const float ssum = xsum::cta_sum<kOaWarps>(w, n_pad, warp, lane, 1, s_ws);
+    if (tid < kOaCluster) cluster.map_shared_rank(s_inv, tid)[crank] = __fdiv_rn(1.0f, ssum);
+  }
+  cluster.sync();
+  if (ph) ph[4] = global_ns();  // sums done
+  // ---- prob_p = e_p * (1/S), in place (the padding of the summed head is scaled too: harmless)
+  for (int i = tid; i < G * n_pos; i += kOaThreads) {
+    const int g = i / n_pos, p = i % n_pos;
+    s_w[g * L.cap_pad + p] = __fmul_rn(s_w[g * L.cap_pad + p], s_inv[g]);
   }
   __syncthreads();
-  // ---- out_d = sum over positions, in order
-  if (warp < NCW) {
-    const int chain = warp * 32 + lane;  // within this CTA
-    const bool valid = chain < CPC;
-    const int flat = c0 + (valid ? chain : 0), g = flat / HD, d = flat % HD;
-    const float *pr = s_w + (g - g_first) * L.cap_pad;
-    float o = 0.0f;
-    for (int c = 0; c < n_vchunks; ++c) {
-      cp_async_wait<kOaVDepth - 1>();
-      __syncwarp();
-      const uint8_t *vs = vring + (c % kOaVDepth) * kOaVSlot + 2 * lane;
-      const int p0 = c * kOaVChunk, cnt = min(kOaVChunk, n_pre - p0);
-      int pp = 0;
-      for (; pp + 4 <= cnt; pp += 4) {
-        const float4 w4 = *reinterpret_cast<const float4 *>(pr + p0 + pp);
-        const float v0 = __half2float(*reinterpret_cast<const __half *>(vs + (pp + 0) * 64));
-        const float v1 = __half2float(*reinterpret_cast<const __half *>(vs + (pp + 1) * 64));
-        const float v2 = __half2float(*reinterpret_cast<const __half *>(vs + (pp + 2) * 64));
-        const float v3 = __half2float(*reinterpret_cast<const __half *>(vs + (pp + 3) * 64));
-        o = __fadd_rn(o, __fmul_rn(w4.x, v0));
-        o = __fadd_rn(o, __fmul_rn(w4.y, v1));
-        o = __fadd_rn(o, __fmul_rn(w4.z, v2));
-        o = __fadd_rn(o, __fmul_rn(w4.w, v3));
+  if (ph) ph[6] = global_ns();  // probabilities ready
+  // ---- out_d = sum over positions, in order.  Producer warps write the products (e_p/S)*v_pd of 64 positions at a
+  // time into one of two buffers, laid out [four positions][chain][position in the four]; a chain lane then gets
+  // the four next terms of its chain with one 16-byte load.  Hand-over by named barriers: 2 + b = buffer b is
+  // full, 4 + b = buffer b is free again.
+  constexpr int kHandover = (NPW + NCW) * 32;
+  if (pw >= 0) {
+    for (int bt = 0; bt < n_batches; ++bt) {
+      const int buf = bt & 1;
+      if (bt >= 2) {
+        if (buf == 0) asm volatile("bar.sync 4, %0;" ::"n"(kHandover));
+        else asm volatile("bar.sync 5, %0;" ::"n"(kHandover));
       }
-      for (; pp < cnt; ++pp) o = __fadd_rn(o, __fmul_rn(pr[p0 + pp], __half2float(*reinterpret_cast<const __half *>(vs + pp * 64))));
-      __syncwarp();
-      issue_v(c + kOaVDepth);
+      cp_async_wait<VD - 1>();  // this lane's copy for batch bt has landed (only later groups may be in flight)
+      const int pib = pw * PPB + v_pp, p = bt * kOaBatch + pib;  // position within the batch / in the context
+      const uint4 raw = *reinterpret_cast<const uint4 *>(vring + (bt % VD) * 512 + lane * 16);
+      const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+      const float2 v0 = __half22float2(h2[0]), v1 = __half22float2(h2[1]), v2 = __half22float2(h2[2]), v3 = __half22float2(h2[3]);
+      issue_v(bt + VD);  // the slot's bytes are in registers now
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float w = p < n_pre ? s_w[g * L.cap_pad + p] : 0.0f;
+        float *dst = s_prod + (buf * (kOaBatch / 4) + (pib >> 2)) * QP + (g * DPC + 8 * v_k) * 4 + (pib & 3);
+        dst[0] = __fmul_rn(w, v0.x);
+        dst[4] = __fmul_rn(w, v0.y);
+        dst[8] = __fmul_rn(w, v1.x);
+        dst[12] = __fmul_rn(w, v1.y);
+        dst[16] = __fmul_rn(w, v2.x);
+        dst[20] = __fmul_rn(w, v2.y);
+        dst[24] = __fmul_rn(w, v3.x);
+        dst[28] = __fmul_rn(w, v3.y);
+      }
+      __threadfence_block();  // the products before the hand-over
+      if (buf == 0) asm volatile("bar.arrive 2, %0;" ::"n"(kHandover) : "memory");
+      else asm volatile("bar.arrive 3, %0;" ::"n"(kHandover) : "memory");
+    }
+  } else if (warp < NCW) {
+    const int chain = warp * 32 + lane;  // within this CTA: head g, dim dd of the CTA's slice
+    const bool valid = chain < CPC;
+    const int g = (valid ? chain : 0) / DPC, d = d0 + (valid ? chain : 0) % DPC;
+    float o = 0.0f;
+    // A unit is 16 positions (four 16-byte loads): the loads of unit u+1 are issued before the 16 dependent additions
+    // of unit u.  A buffer is handed back once its last unit is in registers.
+    const int n_units = (n_pre + 15) / 16;
+    const uint32_t p_addr = (uint32_t)__cvta_generic_to_shared(s_prod + (valid ? chain : 0) * 4);
+    auto load_unit = [&](int u, float4(&T)[4]) {
+      const int bt = u >> 2, buf = bt & 1, sub = u & 3;
+      if (sub == 0) {
+        if (buf == 0) asm volatile("bar.sync 2, %0;" ::"n"(kHandover) : "memory");
+        else asm volatile("bar.sync 3, %0;" ::"n"(kHandover) : "memory");
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(T[q].x), "=f"(T[q].y), "=f"(T[q].z), "=f"(T[q].w)
+                     : "r"(p_addr + ((buf * (kOaBatch / 4) + sub * 4 + q) * QP) * 4));
+      if ((sub == 3 || u == n_units - 1) && bt + 2 < n_batches) {
+        if (buf == 0) asm volatile("bar.arrive 4, %0;" ::"n"(kHandover) : "memory");
+        else asm volatile("bar.arrive 5, %0;" ::"n"(kHandover) : "memory");
+      }
+    };
+    auto add_unit = [&](int u, const float4(&T)[4]) {
+      const int cnt = min(16, n_pre - u * 16);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (4 * q + 0 < cnt) o = __fadd_rn(o, T[q].x);
+        if (4 * q + 1 < cnt) o = __fadd_rn(o, T[q].y);
+        if (4 * q + 2 < cnt) o = __fadd_rn(o, T[q].z);
+        if (4 * q + 3 < cnt) o = __fadd_rn(o, T[q].w);
+      }
+    };
+    // Main loop: two batches (eight units) per trip, written out without a branch so that it is one basic block —
+    // only then are the next unit's loads scheduled under the current unit's additions (a conditional load, or a
+    // barrier number chosen at run time, ends the block and the loads are waited for before the additions start).
+    // It runs while the batches after the pair exist; the generic code below takes what is left.
+    float4 TA[4], TB[4];
+#define OA_LOAD(BUF, SUB, T)                                                                               \
+  do {                                                                                                     \
+    if (SUB == 0) asm volatile("bar.sync %0, %1;" ::"n"(2 + BUF), "n"(kHandover) : "memory");              \
+    _Pragma("unroll") for (int q = 0; q < 4; ++q)                                                          \
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"                                            \
+                     : "=f"(T[q].x), "=f"(T[q].y), "=f"(T[q].z), "=f"(T[q].w)                              \
+                     : "r"(p_addr + ((BUF * (kOaBatch / 4) + SUB * 4 + q) * QP) * 4));                     \
+    if (SUB == 3) asm volatile("bar.arrive %0, %1;" ::"n"(4 + BUF), "n"(kHandover) : "memory");            \
+  } while (0)
+#define OA_ADD(T)                                \
+  do {                                           \
+    _Pragma("unroll") for (int q = 0; q < 4; ++q) { \
+      o = __fadd_rn(o, T[q].x);                  \
+      o = __fadd_rn(o, T[q].y);                  \
+      o = __fadd_rn(o, T[q].z);                  \
+      o = __fadd_rn(o, T[q].w);                  \
+    }                                            \
+  } while (0)
+    int u = 0;
+    const int n_full = n_pre / kOaBatch;  // whole batches
+    int main_pairs = (n_full - 2) / 2;    // pairs (2m, 2m+1) with batches 2m+2 and 2m+3 in existence, so that every
+    if (n_batches < 4) main_pairs = 0;    // bar.arrive of the loop is one the producers wait for
+    if (main_pairs > 0) {
+      OA_LOAD(0, 0, TA);
+      for (int m = 0; m < main_pairs; ++m) {
+        OA_LOAD(0, 1, TB);
+        OA_ADD(TA);
+        OA_LOAD(0, 2, TA);
+        OA_ADD(TB);
+        OA_LOAD(0, 3, TB);
+        OA_ADD(TA);
+        OA_LOAD(1, 0, TA);
+        OA_ADD(TB);
+        OA_LOAD(1, 1, TB);
+        OA_ADD(TA);
+        OA_LOAD(1, 2, TA);
+        OA_ADD(TB);
+        OA_LOAD(1, 3, TB);
+        OA_ADD(TA);
+        OA_LOAD(0, 0, TA);
+        OA_ADD(TB);
+      }
+      u = main_pairs * 8;  // unit u is loaded in TA, not yet added
+    } else if (n_units > 0) {
+      load_unit(0, TA);
+    }
+#undef OA_LOAD
+#undef OA_ADD
+    for (; u < n_units; u += 2) {
+      if (u + 1 < n_units) load_unit(u + 1, TB);
+      add_unit(u, TA);
+      if (u + 1 < n_units) {
+        if (u + 2 < n_units) load_unit(u + 2, TA);
+        add_unit(u + 1, TB);
+      }
     }
     if (a.fuse_rope) {
       // the row's own V, rounded through f16 as the cache holds it
-      const float vn = a.v_new[(int64_t)b * a.kv_stride + (int64_t)kvh * HD + d];
-      o = __fadd_rn(o, __fmul_rn(pr[pos], __half2float(__float2half_rn(vn))));
+      const float vl = __half2float(__float2half_rn(a.v_new[(int64_t)b * a.kv_stride + (int64_t)kvh * HD + d]));
+      o = n_pos == 1 ? vl : __fadd_rn(o, __fmul_rn(s_w[g * L.cap_pad + pos], vl));
+    } else if (n_pos == 1) {
+      o = __half2float(vbase[d]);  // a single cached position: the context is a copy of V (src/inference.rs:29858-29951)
     }
-    if (valid) a.out[(int64_t)b * a.q_stride + (int64_t)kvh * G * HD + flat] = o;
+    if (valid) a.out[(int64_t)b * a.q_stride + ((int64_t)kvh * G + g) * HD + d] = o;
   }
   cp_async_wait<0>();
+  if (ph) ph[5] = global_ns();  // chains done
+  // The warps with no part in the output phase park at this CTA barrier, which costs no issue slots; waiting at the
+  // cluster barrier instead, they would poll and take the chain warps' issue slots (3x slower chains, measured).
+  __syncthreads();
   cluster.sync();  // nobody leaves while its shared memory may still be written or read
 }
 
-template <int G, int HD>
-static int32_t launch_oa(const AttnArgs &a, int64_t cap, cudaStream_t s) {
+template <int G, int HD, int VD>
+static int32_t launch_oa_vd(const AttnArgs &a, int64_t cap, cudaStream_t s) {
   const OaLayout L = oa_layout(G, HD, cap);
   static int configured = 0;
   if (L.total > configured) {
-    CMLD_CUDA(cudaFuncSetAttribute(attn_ordered_kernel<G, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
+    CMLD_CUDA(cudaFuncSetAttribute(attn_ordered_kernel<G, HD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L.total));
     configured = L.total;
   }
   cudaLaunchConfig_t cfg{};
@@ -343,8 +468,17 @@ static int32_t launch_oa(const AttnArgs &a, int64_t cap, cudaStream_t s) {
   ++n_attr;
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_ordered_kernel<G, HD>, a, cap));
+  CMLD_CUDA(cudaLaunchKernelEx(&cfg, attn_ordered_kernel<G, HD, VD>, a, cap));
   return CMLD_OK;
+}
+
+template <int G, int HD>
+static int32_t launch_oa(const AttnArgs &a, int64_t cap, cudaStream_t s) {
+  switch (oa_vdepth(cap)) {
+    case 32: return launch_oa_vd<G, HD, 32>(a, cap, s);
+    case 16: return launch_oa_vd<G, HD, 16>(a, cap, s);
+    default: return launch_oa_vd<G, HD, 8>(a, cap, s);
+  }
 }
 
 // Whether the cluster kernel takes this shape with contexts of up to `cap` positions.
@@ -352,8 +486,7 @@ bool attention_ordered_fits(int n_heads, int n_kv_heads, int head_dim, int64_t c
   if (n_kv_heads <= 0 || n_heads % n_kv_heads) return false;
   const int G = n_heads / n_kv_heads;
   if (!(G == 1 || G == 2 || G == 3 || G == 4 || G == 8)) return false;
-  if (!(head_dim == 64 || head_dim == 128)) return false;
-  if ((G * head_dim / kOaCluster) % 8) return false;
+  if (!(head_dim == 64 || head_dim == 128)) return false;  // each CTA owns head_dim/8 dims: whole 16-byte pieces
   if (cap > 8192) return false;  // the exact sum takes at most 32 chunks of 256 terms
   return oa_layout(G, head_dim, cap).total <= 226 * 1024;
 }

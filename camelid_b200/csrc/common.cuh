@@ -238,11 +238,21 @@ constexpr int kTraceRecords = 4096;
 // Stand-alone form of the receiving side: h[batch][hidden] = sum of the ranks' partials (ops.cu).
 int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, int32_t *status, bool pdl, cudaStream_t s);
 
+// Optional side job of a staged-matvec launch: pull the KV-cache rows the attention kernel that follows will
+// read into L2 (the idle lanes of the producer warp issue bulk prefetches before the kernel waits for its
+// predecessor; the rows of earlier positions do not change any more).
+struct KvPrefetch {
+  const __half *k = nullptr, *v = nullptr;  // this layer's caches, [slot][kv_head][max_pos][head_dim]
+  const int32_t *positions = nullptr, *slots = nullptr;
+  int32_t n_kv_heads = 0, head_dim = 0, batch = 0;
+  int64_t max_pos = 0;
+};
+
 // Returns CMLD_ERR_UNSUPPORTED, leaving the error message untouched, when the shape does not fit.
 // Largest batch (<= 8) the staged kernel takes for these matrices in one launch; 0 = none.
 int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired = false, bool norm = false);
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
-                         cudaStream_t s, bool pdl, const GemvPeer *peer = nullptr);
+                         cudaStream_t s, bool pdl, const GemvPeer *peer = nullptr, const KvPrefetch *pf = nullptr);
 
 // gemv_mma.cu: 9..32 activation rows in one pass over the weights (int8 tensor-core MMA)
 int64_t gemv_mma_scratch_floats(const GemvJob *jobs, int n_jobs, int32_t batch);
@@ -313,6 +323,7 @@ struct AttnArgs {
   const float *cos_tab, *sin_tab;  // [rows][rope_dim/2]
   int32_t pdl;                     // launch with programmatic stream serialisation
   int32_t cluster;                 // ranges as the CTAs of a thread-block cluster, merged through distributed shared memory
+  unsigned long long *phase_ns;    // optional (reference-order cluster kernel): %globaltimer of CTA 0 at the end of each phase
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
 // attn_ordered.cu: the reference-order cluster kernel (contexts of at most `cap` positions)

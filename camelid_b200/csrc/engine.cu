@@ -127,6 +127,7 @@ struct cmld_engine {
   float *mma_scratch = nullptr;  // per-chunk partial sums of the batched tensor-core matvec
   int64_t mma_scratch_floats = 0;
   unsigned long long *trace = nullptr;  // matvec timeline (environment CMLD_TRACE=<file>), dumped at destroy
+  unsigned long long *attn_phases = nullptr;  // with CMLD_TRACE: the last attention launch's phase clocks (8 words)
   std::string trace_path;
   std::map<int32_t, bool> peer_fit;   // rows -> every matvec of a step fits the staged kernel in one pass
   int device = 0;
@@ -339,6 +340,7 @@ static int32_t engine_init(cmld_engine *e) {
   if (const char *tp = getenv("CMLD_TRACE")) {
     e->trace_path = std::string(tp) + "." + std::to_string(e->shard_rank);
     CMLD_TRY(dev_alloc(e, &e->trace, 1 + 8 * (int64_t)kTraceRecords));
+    CMLD_TRY(dev_alloc(e, &e->attn_phases, 8));
   }
   e->history_cap = 4096;
   CMLD_TRY(dev_alloc(e, &e->d_history, e->history_cap * R));
@@ -369,6 +371,12 @@ static void drop_graphs(cmld_engine *e) {
 }
 
 static void dump_trace(cmld_engine *e) {
+  if (e->attn_phases) {
+    unsigned long long h[8] = {0};
+    if (cudaMemcpy(h, e->attn_phases, 64, cudaMemcpyDeviceToHost) == cudaSuccess && h[5])
+      fprintf(stderr, "last attention launch, phases (us): scores %.2f, maxima %.2f, weights %.2f, sums %.2f, scaling %.2f, chains %.2f\n",
+              (h[1] - h[0]) * 1e-3, (h[2] - h[1]) * 1e-3, (h[3] - h[2]) * 1e-3, (h[4] - h[3]) * 1e-3, (h[6] - h[4]) * 1e-3, (h[5] - h[6]) * 1e-3);
+  }
   if (!e->trace || e->trace_path.empty()) return;
   std::vector<unsigned long long> host(1 + 8 * (size_t)kTraceRecords);
   if (cudaMemcpy(host.data(), e->trace, host.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
@@ -378,9 +386,9 @@ static void dump_trace(cmld_engine *e) {
   fprintf(f, "start_ns,visible,arrived,prologue,rows,ticket,jobs,tx,rx,cols\n");
   for (size_t i = 0; i < n; ++i) {
     const unsigned long long *r = host.data() + 1 + i * 8;
-    fprintf(f, "%llu,%lld,%lld,%lld,%lld,%lld,%llu,%llu,%llu,%llu\n", r[0], (long long)(r[1] - r[0]), (long long)(r[2] - r[0]),
+    fprintf(f, "%llu,%lld,%lld,%lld,%lld,%lld,%llu,%llu,%llu,%llu,%lld\n", r[0], (long long)(r[1] - r[0]), (long long)(r[2] - r[0]),
             (long long)(r[3] - r[0]), (long long)(r[4] - r[0]), r[5] ? (long long)(r[5] - r[0]) : -1, r[6] & 0xff, (r[6] >> 8) & 0xff,
-            (r[6] >> 16) & 0xff, r[6] >> 32);
+            (r[6] >> 16) & 0xff, r[6] >> 32, r[7] ? (long long)(r[7] - r[0]) : -1);
   }
   fclose(f);
 }
@@ -487,7 +495,8 @@ constexpr int kFusedPrologueMaxBatch = 2;
 static int mma_min_rows(const cmld_engine *e) { return (e->cfg.flags & CMLD_FLAG_TENSOR_BATCH) ? 5 : (1 << 30); }
 
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
-                          const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr, bool pair_swiglu = false) {
+                          const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr, bool pair_swiglu = false,
+                          const KvPrefetch *pf = nullptr) {
   bool n0, nk;
   const Weight *ws[4];
   for (int i = 0; i < n; ++i) ws[i] = p[i].w;
@@ -561,7 +570,7 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
           if (peer) traced = *peer;
           traced.trace = e->trace;
         }
-        CMLD_TRY(launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, pdl, e->trace ? &traced : peer));
+        CMLD_TRY(launch_gemv_pipe(jobs, n, nb, pro, e->d_status, e->stream, pdl, e->trace ? &traced : peer, b0 == 0 ? pf : nullptr));
         e->launches += 1;
       }
       return CMLD_OK;
@@ -774,7 +783,20 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
                          {&L.proj[2], e->v, nullptr, e->kv_width}};
       GemvPeer g{};
       take_pending(g);
-      CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden, use_peer ? &g : nullptr));
+      // the attention that follows reads this layer's KV rows: have them pulled into L2 meanwhile (every row but
+      // the step's own, which the attention kernel appends itself, is final)
+      KvPrefetch pf{};
+      if (!o.shared_slots) {
+        pf.k = e->kcache + (int64_t)li * e->kv_layer_elems;
+        pf.v = e->vcache + (int64_t)li * e->kv_layer_elems;
+        pf.positions = e->d_positions;
+        pf.slots = e->d_slots;
+        pf.n_kv_heads = c.n_kv_heads;
+        pf.head_dim = c.head_dim;
+        pf.batch = B;
+        pf.max_pos = c.max_pos;
+      }
+      CMLD_TRY(gemv_fused(e, p, 3, B, 1, e->h, nullptr, L.attn_norm, c.hidden, use_peer ? &g : nullptr, false, pf.k ? &pf : nullptr));
     }
     {
       // Attention.  Default: the reference-order cluster kernel (the CPU path's bits); contexts or shapes it
@@ -838,6 +860,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
       a.pdl = !(c.flags & CMLD_FLAG_NO_PDL);
       a.cluster = o.attn_cluster && fast ? 1 : 0;
+      a.phase_ns = e->attn_phases;
       if (ordered) CMLD_TRY(launch_attention_ordered(a, o.attn_cap, e->stream));
       else if (fast) CMLD_TRY(launch_attention(a, e->stream));
       else CMLD_TRY(launch_attention_exact(a, e->stream));

@@ -13,7 +13,7 @@
 // that keeps s inside one binade acts on S as a pair of increments (d0, d1): S + d0 if S is even,
 // S + d1 if S is odd, and such pairs compose associatively.
 //
-// Procedure.  Items are groups of 8 consecutive terms.  A double-precision prefix sum predicts each
+// Procedure.  Items are groups of 8 consecutive terms.  A parallel (tree) prefix sum predicts each
 // item's binade.  Items whose predicted binade does not change across them are "fast": a lane
 // computes their (d0, d1) under that binade.  The other items (the few where the sum crosses into a
 // new binade, and the very first) are "slow".  Runs of fast items with the same binade inside a
@@ -81,15 +81,6 @@ XS_HD float mul_rn(float a, float b) {
   return r;
 #endif
 }
-XS_HD int dbl_exponent(double a) {  // unbiased exponent of a positive normal double
-#if defined(__CUDA_ARCH__)
-  return ((__double2hiint(a) >> 20) & 0x7ff) - 1023;
-#else
-  uint64_t u;
-  memcpy(&u, &a, 8);
-  return (int)((u >> 52) & 0x7ff) - 1023;
-#endif
-}
 
 // (d0, d1) of `first` followed by `second`.
 XS_HD void compose(uint32_t f0, uint32_t f1, uint32_t g0, uint32_t g1, uint32_t &h0, uint32_t &h1) {
@@ -97,26 +88,24 @@ XS_HD void compose(uint32_t f0, uint32_t f1, uint32_t g0, uint32_t g1, uint32_t 
   h1 = f1 + (((f1 + 1u) & 1u) ? g1 : g0);
 }
 
-// One item: 8 terms t[] that follow an (approximate, double) prefix sum `a_start`.  Returns the
-// biased f32 exponent of the predicted binade, or kSlow, and the item's increments.
-XS_HD uint32_t item_local(const float (&t)[kItem], double a_start, uint32_t &d0, uint32_t &d1) {
+// One item: 8 terms t[] that follow an approximate prefix sum `a_start` (a tree sum: it only has to predict
+// the binade) and end at `a_end`.  Returns the biased f32 exponent of the predicted binade, or kSlow, and
+// the item's increments.
+XS_HD uint32_t item_local(const float (&t)[kItem], float a_start, float a_end, uint32_t &d0, uint32_t &d1) {
   d0 = d1 = 0;
-  double a_end = a_start;
-  for (int i = 0; i < kItem; ++i) a_end += (double)t[i];
-  if (!(a_start > 0.0) || !(a_end < 3.0e38)) return kSlow;
-  const int eb = dbl_exponent(a_start);
-  if (eb != dbl_exponent(a_end) || eb < -100 || eb > 126) return kSlow;
+  if (!(a_start > 0.0f) || !(a_end < 3.0e38f)) return kSlow;
+  const int eb = (int)(f32_bits(a_start) >> 23) - 127;
+  if (eb != (int)(f32_bits(a_end) >> 23) - 127 || eb < -100 || eb > 126) return kSlow;
   const float scale = bits_f32((uint32_t)(23 - eb + 127) << 23);  // 2^(23-eb): term -> units of the binade's ulp
   for (int i = 0; i < kItem; ++i) {
     const float q = mul_rn(t[i], scale);  // exact (power of two) unless it underflows towards 0, where it rounds to 0 units anyway
     if (!(q < 8388608.0f)) return kSlow;  // a term as large as the binade itself (or NaN): cannot stay inside it
 #if defined(__CUDA_ARCH__)
-    const float kf = floorf(q);
+    const uint32_t k = (uint32_t)__float2int_rd(q);
 #else
-    const float kf = std::floor(q);
+    const uint32_t k = (uint32_t)std::floor(q);
 #endif
-    const float fr = q - kf;  // exact
-    const uint32_t k = (uint32_t)kf;
+    const float fr = q - (float)k;  // exact
     if (fr == 0.5f) {
       // tie: the sum moves to the even neighbour, which depends on the parity of S + k
       d0 += k + ((d0 + k) & 1u);
@@ -133,30 +122,55 @@ XS_HD uint32_t item_local(const float (&t)[kItem], double a_start, uint32_t &d0,
 
 // The walk over one chunk's events.  `sq` holds the chunk's terms (for replays), `items` its 32
 // items (already composed along runs), `events` the lanes that end a run or are slow.
+// The exact sum s is the only loop-carried value: the next event's item is fetched before the current
+// one is applied, and a slow item's eight terms are loaded before they are added.
 XS_HD float walk_chunk(float s, const float *sq, const Item *items, uint32_t events) {
-  while (events) {
+  if (!events) return s;
 #if defined(__CUDA_ARCH__)
-    const int lane = __ffs((int)events) - 1;
+  int lane = __ffs((int)events) - 1;
 #else
-    const int lane = __builtin_ctz(events);
+  int lane = __builtin_ctz(events);
 #endif
+  Item it = items[lane];
+  while (true) {
     events &= events - 1;
-    const Item it = items[lane];
-    const uint32_t e = it.w0 >> 24;
-    int first = lane;  // first lane to replay if the fast path does not apply
-    if (e != kSlow) {
-      const uint32_t sb = f32_bits(s);
-      if ((sb >> 23) == e) {
-        const uint32_t m = sb & 0x7fffffu;
-        const uint32_t d = ((m & 1u) ? it.w1 : it.w0) & 0xffffffu;
-        if (m + d < 0x800000u) {  // still inside the binade: the integer step is the f32 result
-          s = bits_f32(sb + d);
-          continue;
-        }
-      }
-      first = (int)(it.w1 >> 24);
+    int lane_n = 0;
+    Item it_n = it;
+    if (events) {
+#if defined(__CUDA_ARCH__)
+      lane_n = __ffs((int)events) - 1;
+#else
+      lane_n = __builtin_ctz(events);
+#endif
+      it_n = items[lane_n];
     }
-    for (int i = first * kItem; i < (lane + 1) * kItem; ++i) s = add_rn(s, sq[i]);
+    const uint32_t e = it.w0 >> 24;
+    if (e != kSlow) {
+      // s is in binade e iff t = bits(s) - (e << 23) < 2^23 (as unsigned); then t is its mantissa field
+      const uint32_t sb = f32_bits(s);
+      const uint32_t t = sb - (e << 23);
+      const uint32_t d = ((t & 1u) ? it.w1 : it.w0) & 0xffffffu;
+      if (t + d < 0x800000u && t < 0x800000u) {  // in the binade and still inside it afterwards: the integer step is the f32 result
+        s = bits_f32(sb + d);
+      } else {
+        const int first = (int)(it.w1 >> 24);
+        for (int i = first * kItem; i < (lane + 1) * kItem; ++i) s = add_rn(s, sq[i]);
+      }
+    } else {
+      const float *q = sq + lane * kItem;
+      const float t0 = q[0], t1 = q[1], t2 = q[2], t3 = q[3], t4 = q[4], t5 = q[5], t6 = q[6], t7 = q[7];
+      s = add_rn(s, t0);
+      s = add_rn(s, t1);
+      s = add_rn(s, t2);
+      s = add_rn(s, t3);
+      s = add_rn(s, t4);
+      s = add_rn(s, t5);
+      s = add_rn(s, t6);
+      s = add_rn(s, t7);
+    }
+    if (!events) break;
+    lane = lane_n;
+    it = it_n;
   }
   return s;
 }
@@ -166,9 +180,9 @@ XS_HD float walk_chunk(float s, const float *sq, const Item *items, uint32_t eve
 // Device side.  A warp prepares one chunk: lane l holds terms [8l, 8l+8) of the chunk in t[], and
 // a_start is the approximate prefix sum at the lane's first term.  Writes the chunk's items
 // (composed along runs) and returns the event mask (same value in every lane).
-__device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], double a_start, int lane, Item *items) {
+__device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], float a_start, float a_end, int lane, Item *items) {
   uint32_t d0, d1;
-  const uint32_t e = item_local(t, a_start, d0, d1);
+  const uint32_t e = item_local(t, a_start, a_end, d0, d1);
   const uint32_t e_prev = __shfl_up_sync(0xffffffffu, e, 1);
   const bool boundary = lane == 0 || e == kSlow || e_prev == kSlow || e != e_prev;  // a run starts here
   const uint32_t bmask = __ballot_sync(0xffffffffu, boundary);
@@ -194,56 +208,118 @@ __device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], doubl
   return __ballot_sync(0xffffffffu, e == kSlow || run_end);
 }
 
-// CTA-wide: the sequential f32 sum of sq[0..n) (n a multiple of 256, all terms >= 0), by NWARPS
-// warps that all call this with their warp / lane ids; the result is returned to every thread.
+// One event of the flat list the walker goes through: a composed run (or a slow item) and where its terms are.
+struct Event {
+  uint32_t w0, w1;   // as Item
+  uint32_t first;    // index in sq of the first term to replay if the run's step cannot be taken
+  uint32_t end;      // index in sq one past the event's last term
+};
+
+// The walk over the whole list; s is the only loop-carried value: the next event's record, and the eight
+// terms a slow event adds, are fetched one event ahead.
+__device__ __forceinline__ float walk_events(const float *sq, const Event *ev, int n_events) {
+  float s = 0.0f;
+  if (n_events <= 0) return s;
+  uint4 cur = *reinterpret_cast<const uint4 *>(ev);
+  float4 ca = *reinterpret_cast<const float4 *>(sq + cur.w - kItem), cb = *reinterpret_cast<const float4 *>(sq + cur.w - kItem + 4);
+  for (int k = 0; k < n_events; ++k) {
+    const uint4 nxt = *reinterpret_cast<const uint4 *>(ev + (k + 1 < n_events ? k + 1 : k));
+    const float4 na = *reinterpret_cast<const float4 *>(sq + nxt.w - kItem), nb = *reinterpret_cast<const float4 *>(sq + nxt.w - kItem + 4);
+    const uint32_t e = cur.x >> 24;
+    const uint32_t sb = __float_as_uint(s);
+    const uint32_t t = sb - (e << 23);  // s is in binade e iff t < 2^23 (unsigned); then t is its mantissa field
+    const uint32_t d = ((t & 1u) ? cur.y : cur.x) & 0xffffffu;
+    if (e != kSlow && t < 0x800000u && t + d < 0x800000u) {
+      s = __uint_as_float(sb + d);  // still inside the binade: the integer step is the f32 result
+    } else {
+      // a slow item (its own eight terms), or a run whose step cannot be taken: replay from cur.z
+      for (uint32_t i = cur.z; i + kItem < cur.w; ++i) s = __fadd_rn(s, sq[i]);
+      s = __fadd_rn(s, ca.x);
+      s = __fadd_rn(s, ca.y);
+      s = __fadd_rn(s, ca.z);
+      s = __fadd_rn(s, ca.w);
+      s = __fadd_rn(s, cb.x);
+      s = __fadd_rn(s, cb.y);
+      s = __fadd_rn(s, cb.z);
+      s = __fadd_rn(s, cb.w);
+    }
+    cur = nxt;
+    ca = na;
+    cb = nb;
+  }
+  return s;
+}
+
+// CTA-wide: the sequential f32 sum of sq[0..n) (n a multiple of 256, at most 8192, all terms >= 0), by
+// NWARPS warps that all call this with their warp / lane ids; the result is returned to every thread.
 // `bar` is the id of a named barrier over exactly NWARPS*32 threads that no other code uses meanwhile.
-//   ws_chunk: n/256 doubles, ws_events: n/256 words, ws_items: n/8 items, ws_out: 1 float.
+// `ws` is workspace_bytes(n) bytes of shared memory, 16-byte aligned.
 template <int NWARPS>
-__device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int lane, int bar, double *ws_chunk,
-                                         uint32_t *ws_events, Item *ws_items, float *ws_out) {
+__device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int lane, int bar, uint8_t *ws) {
   const int n_chunks = n >> 8;  // at most 32
+  float *ws_chunk = reinterpret_cast<float *>(ws);                      // [32] chunk sums (approximate)
+  uint32_t *ws_mask = reinterpret_cast<uint32_t *>(ws + 256);           // [32] event lanes per chunk
+  float *ws_out = reinterpret_cast<float *>(ws + 384);
+  Item *ws_items = reinterpret_cast<Item *>(ws + 400);                  // [n / 8]
+  Event *ws_events = reinterpret_cast<Event *>(ws + 400 + (n >> 3) * 8);  // [n / 8]
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));  // sq complete
-  // approximate prefix sums in double: per chunk first
+  // approximate prefix sums (tree sums: they only predict binades): per chunk first
   for (int ch = warp; ch < n_chunks; ch += NWARPS) {
     const float4 a = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem);
     const float4 b = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem + 4);
-    double loc = (double)a.x + (double)a.y + (double)a.z + (double)a.w + (double)b.x + (double)b.y + (double)b.z + (double)b.w;
+    float loc = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) loc += __shfl_xor_sync(0xffffffffu, loc, o);
     if (lane == 0) ws_chunk[ch] = loc;
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
   for (int ch = warp; ch < n_chunks; ch += NWARPS) {
-    double base = lane < ch ? ws_chunk[lane] : 0.0;  // n <= 8192: at most 32 chunks
+    float base = lane < ch ? ws_chunk[lane] : 0.0f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
     const float4 a = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem);
     const float4 b = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem + 4);
     const float t[kItem] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    double loc = 0.0;
-#pragma unroll
-    for (int i = 0; i < kItem; ++i) loc += (double)t[i];
-    double incl = loc;  // inclusive scan over the lanes
+    const float loc = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+    float incl = loc;  // inclusive scan over the lanes
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const double p = __shfl_up_sync(0xffffffffu, incl, o);
+      const float p = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += p;
     }
-    const uint32_t ev = prepare_chunk(t, base + (incl - loc), lane, ws_items + ch * 32);
-    if (lane == 0) ws_events[ch] = ev;
+    const uint32_t ev = prepare_chunk(t, base + (incl - loc), base + incl, lane, ws_items + ch * 32);
+    if (lane == 0) ws_mask[ch] = ev;
+  }
+  asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
+  // the events of all chunks as one list, in order
+  for (int ch = warp; ch < n_chunks; ch += NWARPS) {
+    int before = lane < ch ? __popc(ws_mask[lane]) : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
+    const uint32_t mine = ws_mask[ch];
+    if ((mine >> lane) & 1u) {
+      const Item it = ws_items[ch * 32 + lane];
+      Event e;
+      e.w0 = it.w0;
+      e.w1 = it.w1;
+      e.first = (uint32_t)(ch * kChunk + (int)(it.w1 >> 24) * kItem);
+      e.end = (uint32_t)(ch * kChunk + (lane + 1) * kItem);
+      if ((it.w0 >> 24) == kSlow) e.first = e.end - kItem;
+      ws_events[before + __popc(mine & ((1u << lane) - 1u))] = e;
+    }
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
   if (warp == 0 && lane == 0) {
-    float s = 0.0f;
-    for (int ch = 0; ch < n_chunks; ++ch) s = walk_chunk(s, sq + ch * kChunk, ws_items + ch * 32, ws_events[ch]);
-    *ws_out = s;
+    int total = 0;
+    for (int ch = 0; ch < n_chunks; ++ch) total += __popc(ws_mask[ch]);
+    *ws_out = walk_events(sq, ws_events, total);
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
   return *ws_out;
 }
 
 // Shared-memory bytes cta_sum needs besides sq itself, for n terms.
-__host__ __device__ inline int workspace_bytes(int n) { return (n >> 8) * 8 + (n >> 8) * 4 + (n >> 3) * 8 + 16; }
+__host__ __device__ inline int workspace_bytes(int n) { return 400 + (n >> 3) * 8 + (n >> 3) * 16; }
 
 #endif  // __CUDACC__
 

@@ -59,7 +59,7 @@ constexpr int kActRec6 = 528;      // 16 groups x 32 B + scale (33 x 16 B: confl
 constexpr int kRec6D = 512;
 constexpr int kTermBytes = 2048;   // per consumer warp: the terms of one pass over 32 blocks
 constexpr int kPieceBlocks = 32;   // superblocks (K-quants) per row in a piece
-constexpr int kPieceBlocks0 = 64;  // 32-value blocks (Q8_0) per row in a piece
+constexpr int kPieceBlocks0 = 256; // 32-value blocks (Q8_0) per row in a piece (rows of up to 8192 values stay whole)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -106,6 +106,7 @@ struct PipeJob {
   int32_t n_it;          // blocks (Q8_0) or superblocks (K-quants) per row
   int32_t n_pieces;      // pieces a row is cut into
   int32_t piece_blocks;  // blocks per piece (the last piece may be shorter)
+  int32_t row_mult;      // row sets a warp takes from one tile, one after another (whole-row tiles of big matrices: larger copies)
   int64_t stride;
   float *y;
   const float *residual;
@@ -128,6 +129,8 @@ struct PipeArgs {
   int32_t *status;
   GemvPeer peer;          // tensor-parallel sum folded into this launch (tx_n / rx_n = 0: none)
   int64_t peer_rank_stride;  // floats between the ranks' partials in the receive slot
+  KvPrefetch pf;
+  int32_t dbg;
 };
 
 // One Q8_K chunk (the codes of 256 values, 8 per lane, scale d) into the shared-memory operand records.
@@ -334,12 +337,15 @@ __device__ __forceinline__ bool chain_slot(int qt, int n_it, int k, int lane, in
 
 // One staged piece: rows wg*rpw .. of the tile, blocks [it0, it0+cnt_it) of each.  res[] carries the chain
 // lanes' running sums from piece to piece; `last` finishes them (Q6_K: the left-to-right sum of the eight).
+// The warp gives the stage back (one arrival on empty_bar) as soon as it has read its last byte of it — before
+// the chains, which only use the term buffer — so the producer can refill the stage while the chains run.
 // Piece layout in the stage: whole rows (stride J.stride) when the job has one piece; else per row
 // [blocks | scales]: Q4_K cnt*144; Q6_K cnt*208 then cnt f16 d; Q8_0 cnt*32 codes then cnt f16 scales.
 template <int B>
 __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, const uint8_t *tile, int nrows, int wg, int lane,
                                          int it0, int cnt_it, bool last, const uint8_t *act_k, const uint8_t *act_6,
-                                         const uint8_t *act_0, int nsb, int act0_col_stride, float *tb, float (&res)[B]) {
+                                         const uint8_t *act_0, int nsb, int act0_col_stride, float *tb, float (&res)[B],
+                                         uint64_t *empty_bar, bool release) {
   const int L = lanes_per_row(J.n_it), rpw = 32 / L;
   const int lis = lane % L, r_local = wg * rpw + lane / L;
   const bool row_ok = lane < rpw * L && r_local < nrows;
@@ -356,6 +362,10 @@ __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, co
       int S[B], P[B];
       float dw = 0.0f, dmw = 0.0f;
       if (act) sb_ints_q4k<B>(row + i * 144, act_k + (it0 + i) * kActRec, rec_col_stride, S, P, dw, dmw);
+      if (release && p0 + 32 >= cnt_it) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar);
+      }
 #pragma unroll
       for (int k = 0; k < R; ++k) {
         const int nb = (B - 4 * k) < 4 ? (B - 4 * k) : 4;
@@ -373,8 +383,20 @@ __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, co
           const int r = lane / nb, bb = lane % nb;
           if (wg * rpw + r < nrows) {
             float s = res[k];
-            for (int j = 0; j < cnt; ++j) {
-              const float4 t = t4[(r * L + j) * nb + bb];
+            const float4 *tp = t4 + r * L * nb + bb;
+            int j = 0;
+            for (; j + 8 <= cnt; j += 8) {  // eight terms loaded, then their sixteen dependent multiply-adds
+              float4 t[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) t[u] = tp[(j + u) * nb];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                s = __fmaf_rn(t[u].z, t[u].w, s);
+                s = __fmaf_rn(t[u].x, t[u].y, s);
+              }
+            }
+            for (; j < cnt; ++j) {
+              const float4 t = tp[j * nb];
               s = __fmaf_rn(t.z, t.w, s);
               s = __fmaf_rn(t.x, t.y, s);
             }
@@ -398,6 +420,10 @@ __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, co
         sb_ints_q6k<B>(row + i * 208, act_6 + (it0 + i) * kActRec6, rec6_col_stride, aux);
         dw = f16_bits_to_f32(dws[i]);
       }
+      if (release && p0 + 32 >= cnt_it) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar);
+      }
 #pragma unroll
       for (int k = 0; k < R; ++k) {
         const int nb = (B - 2 * k) < 2 ? (B - 2 * k) : 2;
@@ -420,7 +446,16 @@ __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, co
           const int l = lane & 7, r = (lane >> 3) / nb, bb = (lane >> 3) % nb;
           if (wg * rpw + r < nrows) {
             float s = res[k];
-            for (int j = 0; j < cnt; ++j) s = __fadd_rn(s, tb[((r * L + j) * nb + bb) * 8 + l]);
+            const float *tp = tb + (r * L * nb + bb) * 8 + l;
+            int j = 0;
+            for (; j + 8 <= cnt; j += 8) {
+              float t[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) t[u] = tp[(j + u) * nb * 8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) s = __fadd_rn(s, t[u]);
+            }
+            for (; j < cnt; ++j) s = __fadd_rn(s, tp[j * nb * 8]);
             res[k] = s;
           }
         }
@@ -468,11 +503,21 @@ __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, co
         }
       }
       __syncwarp();
+      if (release && p0 + 32 >= cnt_it && lane == 0) mbar_arrive(empty_bar);
       if (lane < rpw * B) {
         const int r = lane / B, bb = lane % B;
         if (wg * rpw + r < nrows) {
           float s = res[0];
-          for (int j = 0; j < cnt; ++j) s = __fadd_rn(s, tb[bb * 32 + r * L + j]);
+          const float *tp = tb + bb * 32 + r * L;
+          int j = 0;
+          for (; j + 8 <= cnt; j += 8) {
+            float t[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) t[u] = tp[j + u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) s = __fadd_rn(s, t[u]);
+          }
+          for (; j < cnt; ++j) s = __fadd_rn(s, tp[j]);
           res[0] = s;
         }
       }
@@ -544,6 +589,22 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 
   if (warp == kPipeAllWarps) {
     // ---------------- producer: weights do not depend on the previous kernel, so no wait here
+    if (lane != 0 && a.pf.k) {
+      // side job: the KV rows of the attention kernel that follows, into L2, 2 KB per request
+      constexpr int kChunk = 2048;
+      for (int b = 0; b < a.pf.batch; ++b) {
+        const int64_t row_bytes = (int64_t)a.pf.head_dim * 2, head_bytes = (int64_t)a.pf.positions[b] * row_bytes;  // rows before the new one
+        const int per_head = (int)((head_bytes + kChunk - 1) / kChunk);
+        const int total = a.pf.n_kv_heads * 2 * per_head;
+        for (int c = (int)blockIdx.x * 31 + lane - 1; c < total; c += (int)gridDim.x * 31) {
+          const int h = c / per_head, ck = c % per_head, kvh = h >> 1;
+          const __half *base = (h & 1 ? a.pf.v : a.pf.k) + (((int64_t)a.pf.slots[b] * a.pf.n_kv_heads + kvh) * a.pf.max_pos) * a.pf.head_dim;
+          const int64_t off = (int64_t)ck * kChunk;
+          const uint32_t bytes = (uint32_t)min((int64_t)kChunk, head_bytes - off);
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const uint8_t *>(base) + off), "r"(bytes) : "memory");
+        }
+      }
+    }
     if (lane == 0) {
       for (int i = 0; i < n_units; ++i) {
         int piece;
@@ -661,10 +722,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
           }
         }
       }
-      const int nch = a.cols >> 8;
-      const float ss = xsum::cta_sum<kPipeAllWarps>(sq, a.cols, warp, lane, 1, reinterpret_cast<double *>(ws),
-                                                    reinterpret_cast<uint32_t *>(ws + nch * 8),
-                                                    reinterpret_cast<xsum::Item *>(ws + nch * 16), red);
+      if (tr) tr[5] = global_ns();
+      const float ss = xsum::cta_sum<kPipeAllWarps>(sq, a.cols, warp, lane, 1, ws);
+      if (tr) tr[7] = global_ns();
       const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)a.cols), a.eps)));
 #pragma unroll
       for (int k = 0; k < kRxChunks; ++k) {
@@ -766,53 +826,62 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const int nrows = min(J.tile_rows, J.rows - row0);
     const int it0 = piece * J.piece_blocks, cnt_it = min(J.piece_blocks, J.n_it - it0);
     const bool last = piece == J.n_pieces - 1;
-    if (piece == 0) {
-#pragma unroll
-      for (int k = 0; k < B; ++k) res[k] = 0.0f;
-    }
     const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-    if (ready)
-      tile_dot<B>(a, J, ring + (int64_t)s * a.stage_bytes, nrows, wg, lane, it0, cnt_it, last, act_k, act_6, act_0, nsb,
-                  act0_col_stride, tb, res);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
-    if (!last) continue;
     const int rpw = 32 / lanes_per_row(J.n_it);
-    if (a.paired) {
-      // groups 2p (first matrix) and 2p+1 (second) hold the same rows: the second hands its results over through
-      // shared memory (double-buffered, one barrier of the two groups per pair) and the first writes
-      // SwiGLU(first, second) — the f32 operand of the down projection — so neither product goes through memory.
-      const int slot = group >> 1;
-      float *buf = pairbuf + ((slot * 2 + (done_pairs & 1)) * J.tile_rows) * B;
-      if (group & 1) {
+    for (int m = 0; m < J.row_mult; ++m) {  // row_mult > 1 only with whole-row tiles: every row set starts and ends here
+      const int wge = m * kPipeGroupWarps + wg;  // which rows of the tile this warp takes now
+      if (piece == 0) {
+#pragma unroll
+        for (int k = 0; k < B; ++k) res[k] = 0.0f;
+      }
+      const bool release = m == J.row_mult - 1;
+      if (ready && a.dbg == 1) {
+        __syncwarp();
+        if (release && lane == 0) mbar_arrive(&empty[s]);
+      } else if (ready) {
+        tile_dot<B>(a, J, ring + (int64_t)s * a.stage_bytes, nrows, wge, lane, it0, cnt_it, last, act_k, act_6, act_0, nsb,
+                    act0_col_stride, tb, res, &empty[s], release);
+      } else {
+        __syncwarp();
+        if (release && lane == 0) mbar_arrive(&empty[s]);
+      }
+      if (!last) continue;
+      if (a.paired) {
+        // groups 2p (first matrix) and 2p+1 (second) hold the same rows: the second hands its results over through
+        // shared memory (double-buffered, one barrier of the two groups per row set) and the first writes
+        // SwiGLU(first, second) — the f32 operand of the down projection — so neither product goes through memory.
+        const int slot = group >> 1;
+        float *buf = pairbuf + ((slot * 2 + (done_pairs & 1)) * kPipeGroupWarps * rpw) * B;
+        if (group & 1) {
+#pragma unroll
+          for (int k = 0; k < B; ++k) {
+            int r, b;
+            if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wge * rpw + r < nrows) buf[(wg * rpw + r) * B + b] = res[k];
+          }
+        }
+        if (slot == 0) asm volatile("bar.sync 2, %0;" ::"n"(2 * kPipeGroupWarps * 32));
+        else asm volatile("bar.sync 3, %0;" ::"n"(2 * kPipeGroupWarps * 32));
+        if (!(group & 1)) {
+#pragma unroll
+          for (int k = 0; k < B; ++k) {
+            int r, b;
+            if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wge * rpw + r < nrows)
+              a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + wge * rpw + r] = swiglu(res[k], buf[(wg * rpw + r) * B + b]);
+          }
+        }
+        ++done_pairs;
+      } else if (ready) {
 #pragma unroll
         for (int k = 0; k < B; ++k) {
           int r, b;
-          if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wg * rpw + r < nrows) buf[(wg * rpw + r) * B + b] = res[k];
-        }
-      }
-      if (slot == 0) asm volatile("bar.sync 2, %0;" ::"n"(2 * kPipeGroupWarps * 32));
-      else asm volatile("bar.sync 3, %0;" ::"n"(2 * kPipeGroupWarps * 32));
-      if (!(group & 1)) {
-#pragma unroll
-        for (int k = 0; k < B; ++k) {
-          int r, b;
-          if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wg * rpw + r < nrows)
-            a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + wg * rpw + r] = swiglu(res[k], buf[(wg * rpw + r) * B + b]);
-        }
-      }
-      ++done_pairs;
-    } else if (ready) {
-#pragma unroll
-      for (int k = 0; k < B; ++k) {
-        int r, b;
-        if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wg * rpw + r < nrows) {
-          const int64_t o = (int64_t)b * J.y_stride + row0 + wg * rpw + r;
-          const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), res[k]) : res[k];
-          if (a.peer.tx_n > 0) {
-            for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
-          } else {
-            J.y[o] = out;
+          if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wge * rpw + r < nrows) {
+            const int64_t o = (int64_t)b * J.y_stride + row0 + wge * rpw + r;
+            const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), res[k]) : res[k];
+            if (a.peer.tx_n > 0) {
+              for (int p = 0; p < a.peer.tx_n; ++p) a.peer.tx_part[p][o] = out;  // this rank's partial, onto every rank
+            } else {
+              J.y[o] = out;
+            }
           }
         }
       }
@@ -927,6 +996,18 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
       if (g.qt != CMLD_Q4_K && (n_it % 8)) return false;
       st = J.tile_rows * (int)round_up16(per_piece * blk + (g.qt == CMLD_Q4_K ? 0 : per_piece * 2));
     }
+    // Whole-row tiles of a big matrix: a warp takes two row sets per tile, so the tile is one copy of twice the
+    // bytes (copies of ~37 KB stream faster than copies of ~18 KB; smaller matrices keep the finer tiles, which
+    // spread better over the SMs).
+    J.row_mult = 1;
+    static const int force_m2 = getenv("CMLD_PIPE_M2") ? atoi(getenv("CMLD_PIPE_M2")) : 0;
+    if (np == 1 && st <= 20 * 1024 && (force_m2 || g.rows >= (int64_t)J.tile_rows * 2 * 148 * 16)) {
+      J.row_mult = 2;
+      J.tile_rows *= 2;
+      J.n_tiles = (int)((g.rows + J.tile_rows - 1) / J.tile_rows);
+      tiles += J.n_tiles - (int)((g.rows + J.tile_rows / 2 - 1) / (J.tile_rows / 2));
+      st *= 2;
+    }
     J.n_pieces = np;
     if (n_pieces < 0) n_pieces = np;
     if (np != n_pieces) return false;  // jobs of one launch are cut alike (they share cols; types may differ)
@@ -953,7 +1034,7 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
     int term = kPipeAllWarps * kTermBytes;
     // the norm prologue borrows this region for the squares and the exact sum's workspace
     if (norm && cols % 256 == 0 && cols <= kRxChunks * kPipeAllWarps * 256)
-      term = std::max(term, (int)cols * 4 + (int)(cols >> 8) * 16 + (int)(cols >> 3) * 8 + 16);
+      term = std::max(term, (int)cols * 4 + xsum::workspace_bytes((int)cols));
     off += term;
   }
   off = (off + 127) & ~127;
@@ -986,7 +1067,7 @@ int gemv_pipe_fit_batch(const GemvJob *jobs, int n_jobs, bool paired, bool norm)
 // message the caller would see) when the shape does not fit; the caller then uses the
 // generic kernel.
 int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const GemvPrologue &pro, int32_t *status,
-                         cudaStream_t s, bool pdl, const GemvPeer *peer) {
+                         cudaStream_t s, bool pdl, const GemvPeer *peer, const KvPrefetch *pf) {
   if (g_sm_count == 0) {
     int dev = 0;
     CMLD_CUDA(cudaGetDevice(&dev));
@@ -1015,6 +1096,8 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   a.need_0 = need_0;
   a.norm_out = pro.norm_out;
   a.status = status;
+  if (pf) a.pf = *pf;
+  { const char *d = getenv("CMLD_PIPE_DEBUG"); a.dbg = d ? atoi(d) : 0; }
   a.paired = pro.pair_swiglu ? 1 : 0;
   if (a.paired && peer && peer->tx_n > 0) return fail(CMLD_ERR_INVALID, "gemv: a paired launch does not send");
   if (peer) {

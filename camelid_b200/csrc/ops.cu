@@ -32,14 +32,10 @@ __global__ void __launch_bounds__(kNormThreads) norm_quant_kernel(NormQuantArgs 
     // the CPU's order: one accumulator, squares added in index order (rms_norm_into, src/tensor/mod.rs:2755)
     if ((a.cols & 255) == 0 && a.cols <= kNormMaxExact) {
       // the same bits from all the warps (exact_sum.cuh)
-      __shared__ __align__(16) float sq[kNormMaxExact];
-      __shared__ __align__(16) uint8_t ws[(kNormMaxExact >> 8) * 16 + (kNormMaxExact >> 3) * 8];
-      __shared__ float s_sum;
+      extern __shared__ __align__(16) uint8_t dyn_smem[];  // cols floats, then the exact sum's workspace
+      float *sq = reinterpret_cast<float *>(dyn_smem);
       for (int64_t i = threadIdx.x; i < a.cols; i += kNormThreads) sq[i] = __fmul_rn(x[i], x[i]);
-      const int nch = (int)(a.cols >> 8);
-      const float t = xsum::cta_sum<kNormThreads / 32>(sq, (int)a.cols, warp, lane, 1, reinterpret_cast<double *>(ws),
-                                                       reinterpret_cast<uint32_t *>(ws + nch * 8),
-                                                       reinterpret_cast<xsum::Item *>(ws + nch * 16), &s_sum);
+      const float t = xsum::cta_sum<kNormThreads / 32>(sq, (int)a.cols, warp, lane, 1, dyn_smem + a.cols * 4);
       if (threadIdx.x == 0) s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.cols), a.eps)));
     } else if (threadIdx.x == 0) {
       float t = 0.0f;
@@ -146,6 +142,7 @@ int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s) {
   cfg.gridDim = dim3((unsigned)((n_chunks + kNormThreads / 32 - 1) / (kNormThreads / 32)), (unsigned)a.batch);
   cfg.blockDim = dim3(kNormThreads);
   cfg.stream = s;
+  if (mode == 1 && a.cols % 256 == 0 && a.cols <= kNormMaxExact) cfg.dynamicSmemBytes = (size_t)a.cols * 4 + xsum::workspace_bytes((int)a.cols);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -156,6 +153,8 @@ int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s) {
     prefer_max_smem_carveout(norm_quant_kernel<0>);
     prefer_max_smem_carveout(norm_quant_kernel<1>);
     prefer_max_smem_carveout(norm_quant_kernel<2>);
+    CMLD_CUDA(cudaFuncSetAttribute(norm_quant_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kNormMaxExact * 4 + xsum::workspace_bytes(kNormMaxExact)));
     carveout_set = true;
   }
   if (mode == 0) CMLD_CUDA(cudaLaunchKernelEx(&cfg, norm_quant_kernel<0>, a));

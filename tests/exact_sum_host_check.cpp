@@ -12,19 +12,21 @@ static long g_replayed = 0, g_events = 0, g_terms = 0;
 
 static float emu(const std::vector<float> &sq) {
   const int n = (int)sq.size(), nch = n / 256;
-  std::vector<double> chunk(nch);
-  for (int c = 0; c < nch; ++c) { double s = 0; for (int i = 0; i < 256; ++i) s += sq[c * 256 + i]; chunk[c] = s; }
+  std::vector<float> chunk(nch);
+  for (int c = 0; c < nch; ++c) { float s = 0; for (int i = 0; i < 256; ++i) s += sq[c * 256 + i]; chunk[c] = s; }
   float s = 0.0f;
-  double base = 0;
+  float base = 0;
   for (int c = 0; c < nch; ++c) {
     Item items[32];
     uint32_t e[32], d0[32], d1[32];
-    double a = base;
+    float a = base;
     for (int l = 0; l < 32; ++l) {
       float t[8];
       for (int i = 0; i < 8; ++i) t[i] = sq[c * 256 + l * 8 + i];
-      e[l] = item_local(t, a, d0[l], d1[l]);
-      for (int i = 0; i < 8; ++i) a += t[i];
+      float a_end = a;
+      for (int i = 0; i < 8; ++i) a_end += t[i];
+      e[l] = item_local(t, a, a_end, d0[l], d1[l]);
+      a = a_end;
     }
     uint32_t events = 0;
     int rs = 0;
