@@ -106,7 +106,6 @@ struct PipeJob {
   int32_t n_it;          // blocks (Q8_0) or superblocks (K-quants) per row
   int32_t n_pieces;      // pieces a row is cut into
   int32_t piece_blocks;  // blocks per piece (the last piece may be shorter)
-  int32_t row_mult;      // row sets a warp takes from one tile, one after another (whole-row tiles of big matrices: larger copies)
   int64_t stride;
   float *y;
   const float *residual;
@@ -130,7 +129,6 @@ struct PipeArgs {
   GemvPeer peer;          // tensor-parallel sum folded into this launch (tx_n / rx_n = 0: none)
   int64_t peer_rank_stride;  // floats between the ranks' partials in the receive slot
   KvPrefetch pf;
-  int32_t dbg;
 };
 
 // One Q8_K chunk (the codes of 256 values, 8 per lane, scale d) into the shared-memory operand records.
@@ -313,8 +311,7 @@ __device__ __forceinline__ int lanes_per_row(int n_it) { return n_it < 32 ? n_it
 // (row of the tile, batch column) it belongs to.  Q4_K: rounds of up to 4 columns; Q8_0: one round of all
 // columns; Q6_K: rounds of 2 columns (at most two rows per warp), eight lanes per (row, column), result in the first of them.
 template <int B>
-__device__ __forceinline__ bool chain_slot(int qt, int n_it, int k, int lane, int &r, int &b) {
-  const int rpw = 32 / lanes_per_row(n_it);
+__device__ __forceinline__ bool chain_slot(int qt, int rpw, int k, int lane, int &r, int &b) {
   if (qt == CMLD_Q4_K) {
     const int nb = min(4, B - 4 * k);
     if (nb <= 0 || lane >= rpw * nb) return false;
@@ -345,9 +342,8 @@ template <int B>
 __device__ __forceinline__ void tile_dot(const PipeArgs &a, const PipeJob &J, const uint8_t *tile, int nrows, int wg, int lane,
                                          int it0, int cnt_it, bool last, const uint8_t *act_k, const uint8_t *act_6,
                                          const uint8_t *act_0, int nsb, int act0_col_stride, float *tb, float (&res)[B],
-                                         uint64_t *empty_bar, bool release) {
-  const int L = lanes_per_row(J.n_it), rpw = 32 / L;
-  const int lis = lane % L, r_local = wg * rpw + lane / L;
+                                         uint64_t *empty_bar, bool release, int L, int rpw, int lis, int rsub) {
+  const int r_local = wg * rpw + rsub;
   const bool row_ok = lane < rpw * L && r_local < nrows;
   const int rec_col_stride = nsb * kActRec, rec6_col_stride = nsb * kActRec6;
   const bool whole = J.n_pieces == 1;
@@ -808,9 +804,19 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   float *pairbuf = reinterpret_cast<float *>(smem + a.off_pair);  // paired mode: [pair slot][tile_rows][B]
   float res[B];
   int done_pairs = 0;
+  // lane geometry of the two block sizes a launch can hold (every job has the same number of columns), once:
+  // the divisions are not repeated per tile
+  const int Lk = lanes_per_row(nsb > 0 ? nsb : 1), rpwk = 32 / Lk, lisk = lane % Lk, rsubk = lane / Lk;
+  const int L0 = lanes_per_row(a.cols >> 5), rpw0 = 32 / L0, lis0 = lane % L0, rsub0 = lane / L0;
+  // unit i -> (tile tl of this CTA's list, piece): advanced without divisions; a group's units are kPipeGroups apart
+  int tl = group, piece = 0;
   for (int i = group; i < n_units; i += kPipeGroups) {
-    int piece;
-    const int tl = unit_tile(i, n_pieces, piece);
+    if (i != group) {
+      if (++piece == n_pieces) {
+        piece = 0;
+        tl += kPipeGroups;
+      }
+    }
     if (tl >= n_my_tiles) break;
     const int s = i % S;
     int j, row0;
@@ -827,20 +833,18 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const int it0 = piece * J.piece_blocks, cnt_it = min(J.piece_blocks, J.n_it - it0);
     const bool last = piece == J.n_pieces - 1;
     const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
-    const int rpw = 32 / lanes_per_row(J.n_it);
-    for (int m = 0; m < J.row_mult; ++m) {  // row_mult > 1 only with whole-row tiles: every row set starts and ends here
-      const int wge = m * kPipeGroupWarps + wg;  // which rows of the tile this warp takes now
+    const bool is0 = J.qt == CMLD_Q8_0;
+    const int L = is0 ? L0 : Lk, rpw = is0 ? rpw0 : rpwk, lis = is0 ? lis0 : lisk, rsub = is0 ? rsub0 : rsubk;
+    {
+      const int wge = wg;
       if (piece == 0) {
 #pragma unroll
         for (int k = 0; k < B; ++k) res[k] = 0.0f;
       }
-      const bool release = m == J.row_mult - 1;
-      if (ready && a.dbg == 1) {
-        __syncwarp();
-        if (release && lane == 0) mbar_arrive(&empty[s]);
-      } else if (ready) {
+      const bool release = true;
+      if (ready) {
         tile_dot<B>(a, J, ring + (int64_t)s * a.stage_bytes, nrows, wge, lane, it0, cnt_it, last, act_k, act_6, act_0, nsb,
-                    act0_col_stride, tb, res, &empty[s], release);
+                    act0_col_stride, tb, res, &empty[s], release, L, rpw, lis, rsub);
       } else {
         __syncwarp();
         if (release && lane == 0) mbar_arrive(&empty[s]);
@@ -856,7 +860,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 #pragma unroll
           for (int k = 0; k < B; ++k) {
             int r, b;
-            if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wge * rpw + r < nrows) buf[(wg * rpw + r) * B + b] = res[k];
+            if (chain_slot<B>(J.qt, rpw, k, lane, r, b) && wge * rpw + r < nrows) buf[(wg * rpw + r) * B + b] = res[k];
           }
         }
         if (slot == 0) asm volatile("bar.sync 2, %0;" ::"n"(2 * kPipeGroupWarps * 32));
@@ -865,7 +869,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 #pragma unroll
           for (int k = 0; k < B; ++k) {
             int r, b;
-            if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wge * rpw + r < nrows)
+            if (chain_slot<B>(J.qt, rpw, k, lane, r, b) && wge * rpw + r < nrows)
               a.job[0].y[(int64_t)b * a.job[0].y_stride + row0 + wge * rpw + r] = swiglu(res[k], buf[(wg * rpw + r) * B + b]);
           }
         }
@@ -874,7 +878,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 #pragma unroll
         for (int k = 0; k < B; ++k) {
           int r, b;
-          if (chain_slot<B>(J.qt, J.n_it, k, lane, r, b) && wge * rpw + r < nrows) {
+          if (chain_slot<B>(J.qt, rpw, k, lane, r, b) && wge * rpw + r < nrows) {
             const int64_t o = (int64_t)b * J.y_stride + row0 + wge * rpw + r;
             const float out = J.residual ? __fadd_rn(__ldcg(J.residual + o), res[k]) : res[k];
             if (a.peer.tx_n > 0) {
@@ -996,18 +1000,6 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
       if (g.qt != CMLD_Q4_K && (n_it % 8)) return false;
       st = J.tile_rows * (int)round_up16(per_piece * blk + (g.qt == CMLD_Q4_K ? 0 : per_piece * 2));
     }
-    // Whole-row tiles of a big matrix: a warp takes two row sets per tile, so the tile is one copy of twice the
-    // bytes (copies of ~37 KB stream faster than copies of ~18 KB; smaller matrices keep the finer tiles, which
-    // spread better over the SMs).
-    J.row_mult = 1;
-    static const int force_m2 = getenv("CMLD_PIPE_M2") ? atoi(getenv("CMLD_PIPE_M2")) : 0;
-    if (np == 1 && st <= 20 * 1024 && (force_m2 || g.rows >= (int64_t)J.tile_rows * 2 * 148 * 16)) {
-      J.row_mult = 2;
-      J.tile_rows *= 2;
-      J.n_tiles = (int)((g.rows + J.tile_rows - 1) / J.tile_rows);
-      tiles += J.n_tiles - (int)((g.rows + J.tile_rows / 2 - 1) / (J.tile_rows / 2));
-      st *= 2;
-    }
     J.n_pieces = np;
     if (n_pieces < 0) n_pieces = np;
     if (np != n_pieces) return false;  // jobs of one launch are cut alike (they share cols; types may differ)
@@ -1097,7 +1089,6 @@ int32_t launch_gemv_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, const G
   a.norm_out = pro.norm_out;
   a.status = status;
   if (pf) a.pf = *pf;
-  { const char *d = getenv("CMLD_PIPE_DEBUG"); a.dbg = d ? atoi(d) : 0; }
   a.paired = pro.pair_swiglu ? 1 : 0;
   if (a.paired && peer && peer->tx_n > 0) return fail(CMLD_ERR_INVALID, "gemv: a paired launch does not send");
   if (peer) {
