@@ -990,6 +990,22 @@ ORACLE_API int orc_model_read_kv(const orc_model *m, int32_t layer, int64_t n_po
   return 0;
 }
 
+/* The inverse of orc_model_read_kv: positions 0..n_pos-1 of one layer's cache take the given rows,
+ * rounded to f16 like rows the forward pass stores (the reference's seed_layer, src/cuda_resident.rs:17355:
+ * a test hook that plants a KV prefix before decoding). */
+ORACLE_API int orc_model_write_kv(orc_model *m, int32_t layer, int64_t n_pos, const float *ck, const float *cv) {
+  if (layer < 0 || layer >= m->n_layers || n_pos < 0 || n_pos > m->max_pos) return -1;
+  int32_t hd = m->head_dim;
+  float *kc = m->kcache + (size_t)layer * m->n_kv_heads * m->max_pos * hd;
+  float *vc = m->vcache + (size_t)layer * m->n_kv_heads * m->max_pos * hd;
+  for (int32_t kh = 0; kh < m->n_kv_heads; ++kh)
+    for (int64_t i = 0; i < n_pos * hd; ++i) {
+      kc[(size_t)kh * m->max_pos * hd + i] = kv_f16_round(ck[(size_t)kh * n_pos * hd + i]);
+      vc[(size_t)kh * m->max_pos * hd + i] = kv_f16_round(cv[(size_t)kh * n_pos * hd + i]);
+    }
+  return 0;
+}
+
 /* src/tensor/mod.rs:2899-3216 (embedding_lookup): dequantise one row. */
 ORACLE_API int orc_embedding(const orc_model *m, int32_t token, float *out) {
   if (token < 0 || token >= m->vocab || !m->token_embd.data) return -1;

@@ -75,6 +75,7 @@ def lib(path: str | os.PathLike | None = None):
         "orc_model_set_token_embd": (None, [vp, i32, vp]),
         "orc_embedding": (C.c_int, [vp, i32, vp]),
         "orc_model_read_kv": (C.c_int, [vp, i32, i64, vp, vp]),
+        "orc_model_write_kv": (C.c_int, [vp, i32, i64, vp, vp]),
         "orc_forward": (C.c_int, [vp, vp, i64, vp, vp, vp]),
         "orc_generate": (C.c_int, [vp, vp, i32, i32, i64, vp, vp]),
         "orc_generate_gaps": (C.c_int, [vp, vp, i32, i32, i64, vp, vp, vp]),
@@ -278,6 +279,12 @@ class OracleModel:
         ck, cv = np.empty(shape, np.float32), np.empty(shape, np.float32)
         assert lib().orc_model_read_kv(self._h, layer, n_positions, _p(ck), _p(cv)) == 0
         return ck, cv
+
+    def write_kv_layer(self, layer: int, ck, cv):
+        """Plants positions 0..n-1 of one layer's cache ([kv_head][n][head_dim] each), rounded to f16."""
+        ck, cv = _f32(ck), _f32(cv)
+        assert ck.shape == cv.shape and ck.shape[0] == self.cfg["n_kv_heads"] and ck.shape[2] == self.cfg["head_dim"]
+        assert lib().orc_model_write_kv(self._h, layer, ck.shape[1], _p(ck), _p(cv)) == 0
 
     def forward(self, x, position: int, want_logits=True, want_taps=False):
         x = _f32(x)

@@ -279,3 +279,22 @@ def test_expf_twin_matches_libm(orc):
     assert L.orc_expf_twin_mismatches(80.0, 95.0, 200_001) == 0          # overflow edge
     assert L.orc_expf_twin_mismatches(-1e-3, 1e-3, 200_001) == 0
     assert L.orc_expf_twin(float("-inf")) == 0.0 and L.orc_expf_twin(0.0) == 1.0
+
+
+def test_kv_prefix_written_to_the_model_reads_back_rounded_to_f16():
+    """write_kv_layer plants a KV prefix (the reference's seed_layer, src/cuda_resident.rs:17355) and
+    read_kv_layer returns it rounded to f16; a forward pass then attends over it."""
+    from oracle import oracle as orc
+
+    cfg = dict(n_layers=2, n_heads=4, n_kv_heads=2, head_dim=64, hidden=256, ffn_dim=512, rope_dim=64, max_pos=16, vocab=64,
+               eps=1e-5, rope_theta=10000.0)
+    m = orc.OracleModel(cfg)
+    rng = np.random.default_rng(3)
+    ck = rng.standard_normal((2, 5, 64)).astype(np.float32)
+    cv = rng.standard_normal((2, 5, 64)).astype(np.float32)
+    m.write_kv_layer(1, ck, cv)
+    rk, rv = m.read_kv_layer(1, 5)
+    assert np.array_equal(rk, ck.astype(np.float16).astype(np.float32))
+    assert np.array_equal(rv, cv.astype(np.float16).astype(np.float32))
+    zk, _ = m.read_kv_layer(0, 5)
+    assert not zk.any()
