@@ -69,11 +69,24 @@ static int32_t check_op_status(const char *what) {
 static int g_gemv_pdl = 0;            // cmld_gemv_time: chain its launches with programmatic dependent launch
 static int g_gemv_kernel_choice = 0;  // 0 auto (staged when the shape fits), 1 generic kernel only
 static int g_gemv_mma_min_batch = 1 << 30;  // rows from which the int8 mma.sync kernel is used (opt-in: bit 3 of the choice from 9 rows, bit 2 from 1)
+static int g_gemv_tc5_min_batch = 9;        // rows from which the tcgen05 kernel is used (bit 4 of the choice: never; bit 5: from 1 row)
 
 // One matvec launch on the default stream: staged kernel if it takes the shape, else the generic one.
 static int32_t gemv_launch(const cmld_weight *w, const uint8_t *act, int32_t batch, float *y, const float *residual,
                            cudaStream_t stream = nullptr, bool pdl = false) {
   GemvJob probe{w->data, w->qt, w->rows, w->cols, w->stride, y, residual, w->rows};
+  if (g_gemv_kernel_choice == 0 && batch >= g_gemv_tc5_min_batch && batch < g_gemv_mma_min_batch && gemv_tc5_fits(&probe, 1, std::min(batch, 32))) {
+    // several rows: one pass over the weights per 32 rows on the tcgen05 tensor cores, same bits as the one-row kernels
+    const int64_t need = gemv_tc5_pack_bytes(w->cols);
+    uint8_t *pack = reinterpret_cast<uint8_t *>(op_scratch((need + 3) / 4));
+    if (!pack) return fail(CMLD_ERR_OOM, "gemv: no room for %lld bytes of packed activations", (long long)need);
+    for (int b0 = 0; b0 < batch; b0 += 32) {
+      const int nb = std::min(32, batch - b0);
+      GemvJob j{w->data, w->qt, w->rows, w->cols, w->stride, y + (int64_t)b0 * w->rows, residual ? residual + (int64_t)b0 * w->rows : nullptr, w->rows};
+      CMLD_TRY(launch_gemv_tc5(&j, 1, act + (int64_t)b0 * act_row_stride(w->cols), nb, pack, need, op_status(), stream, nullptr));
+    }
+    return CMLD_OK;
+  }
   if (g_gemv_kernel_choice == 0 && batch >= g_gemv_mma_min_batch && batch <= 32) {
     // more than 8 rows: one pass over the weights on the tensor cores
     const int64_t need = gemv_mma_scratch_floats(&probe, 1, batch);
@@ -313,10 +326,11 @@ int32_t cmld_peer_wait_selftest(int32_t timeout_ms) {
 }
 
 int32_t cmld_gemv_select_kernel(int32_t choice) {
-  if (choice < 0 || choice > 15) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
+  if (choice < 0 || choice > 63) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
   g_gemv_kernel_choice = choice & 1;
   g_gemv_pdl = (choice >> 1) & 1;
   g_gemv_mma_min_batch = (choice & 4) ? 1 : ((choice & 8) ? 9 : (1 << 30));
+  g_gemv_tc5_min_batch = (choice & 16) ? (1 << 30) : ((choice & 32) ? 1 : 9);
   return CMLD_OK;
 }
 

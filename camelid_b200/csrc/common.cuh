@@ -259,6 +259,13 @@ int64_t gemv_mma_scratch_floats(const GemvJob *jobs, int n_jobs, int32_t batch);
 int32_t launch_gemv_mma(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, float *scratch, int64_t scratch_floats,
                         int32_t *status, cudaStream_t s, bool pdl, int64_t *launches);
 
+// gemv_tc5.cu: 9..32 activation rows in one pass over the weights on the tcgen05 tensor cores, results
+// bit-identical to the one-row kernels (reference order of f32 operations in the epilogue)
+int64_t gemv_tc5_pack_bytes(int64_t cols);
+bool gemv_tc5_fits(const GemvJob *jobs, int n_jobs, int32_t batch);
+int32_t launch_gemv_tc5(const GemvJob *jobs, int n_jobs, const uint8_t *act, int32_t batch, uint8_t *pack, int64_t pack_bytes,
+                        int32_t *status, cudaStream_t s, int64_t *launches);
+
 int64_t gemv_mma_expert_scratch_floats(const GemvJob *jobs, int n_jobs, int nt, int n_experts, int n_pass);
 int32_t launch_gemv_mma_experts(const GemvJob *jobs, int n_jobs, const uint8_t *act, int nt, int n_experts, int n_pass,
                                 const int32_t *counts, int first_expert, int expert_step, int cap, int count_mul, float *scratch,

@@ -125,6 +125,8 @@ struct cmld_engine {
     unsigned long long timeout_ns = 0;
   } peer;
   float *mma_scratch = nullptr;  // per-chunk partial sums of the batched tensor-core matvec
+  uint8_t *tc5_pack = nullptr;   // packed activation records of the tcgen05 batched matvec
+  int64_t tc5_pack_bytes = 0;
   int64_t mma_scratch_floats = 0;
   unsigned long long *trace = nullptr;  // matvec timeline (environment CMLD_TRACE=<file>), dumped at destroy
   unsigned long long *attn_phases = nullptr;  // with CMLD_TRACE: the last attention launch's phase clocks (8 words)
@@ -337,6 +339,11 @@ static int32_t engine_init(cmld_engine *e) {
     e->mma_scratch_floats = need * 32;
     CMLD_TRY(dev_alloc(e, &e->mma_scratch, e->mma_scratch_floats, false));
   }
+  {
+    const int64_t widest = std::max<int64_t>(std::max<int64_t>(c.hidden, c.ffn_dim), e->q_width);
+    e->tc5_pack_bytes = gemv_tc5_pack_bytes((widest + 255) / 256 * 256);
+    CMLD_TRY(dev_alloc(e, &e->tc5_pack, e->tc5_pack_bytes, false));
+  }
   if (const char *tp = getenv("CMLD_TRACE")) {
     e->trace_path = std::string(tp) + "." + std::to_string(e->shard_rank);
     CMLD_TRY(dev_alloc(e, &e->trace, 1 + 8 * (int64_t)kTraceRecords));
@@ -493,6 +500,11 @@ constexpr int kFusedPrologueMaxBatch = 2;
 // different order from the CPU path, so it is opt-in (CMLD_FLAG_TENSOR_BATCH); by default every step
 // goes through the staged kernel, in passes of up to 8 rows.
 static int mma_min_rows(const cmld_engine *e) { return (e->cfg.flags & CMLD_FLAG_TENSOR_BATCH) ? 5 : (1 << 30); }
+// Steps of this many rows or more (and prompt chunks) take the tcgen05 batched matvec: one pass over the weights
+// for up to 32 rows, the same bits as the one-row kernels.  Up to 8 rows the staged kernel's single pass is faster.
+static int tc5_min_rows(const cmld_engine *e) {
+  return (e->cfg.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV | CMLD_FLAG_TENSOR_BATCH)) ? (1 << 30) : 9;
+}
 
 static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, int mode, const float *x, const float *x2,
                           const float *norm_w, int64_t cols, const GemvPeer *peer = nullptr, bool pair_swiglu = false,
@@ -512,6 +524,24 @@ static int32_t gemv_fused(cmld_engine *e, const Proj *p, int n, int32_t batch, i
       e->launches += 1;
     }
     return CMLD_OK;
+  }
+  if (batch >= tc5_min_rows(e) && n <= 3 && !peer && !pair_swiglu && !(n0 && nk)) {
+    GemvJob jobs[3];
+    for (int i = 0; i < n; ++i)
+      jobs[i] = GemvJob{p[i].w->data, p[i].w->qt, p[i].w->rows, p[i].w->cols, p[i].w->stride, p[i].y, p[i].residual, p[i].y_stride};
+    if (gemv_tc5_fits(jobs, n, std::min(batch, 32)) && gemv_tc5_pack_bytes(cols) <= e->tc5_pack_bytes) {
+      CMLD_TRY(run_norm_quant(e, x, mode == 3 ? x2 : nullptr, mode == 1 ? norm_w : nullptr, cols, batch, nullptr, n0, nk));
+      for (int b0 = 0; b0 < batch; b0 += 32) {
+        const int nb = std::min(32, batch - b0);
+        for (int i = 0; i < n; ++i) {
+          jobs[i].y = p[i].y + (int64_t)b0 * p[i].y_stride;
+          jobs[i].residual = p[i].residual ? p[i].residual + (int64_t)b0 * p[i].y_stride : nullptr;
+        }
+        const uint8_t *act = (n0 ? e->act_0 : e->act_k) + (int64_t)b0 * act_row_stride(cols);
+        CMLD_TRY(launch_gemv_tc5(jobs, n, act, nb, e->tc5_pack, e->tc5_pack_bytes, e->d_status, e->stream, &e->launches));
+      }
+      return CMLD_OK;
+    }
   }
   if (!(e->cfg.flags & CMLD_FLAG_DIRECT_GEMV) && n <= 3 && batch > mma_min_rows(e) - 1 && !peer && !pair_swiglu && !(n0 && nk)) {
     // more rows than the dp4a kernel takes in one pass: one pass over the weights on the tensor cores
@@ -887,7 +917,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       take_pending(g);
       // gate and up of equal type: the staged kernel pairs their tiles and writes SwiGLU(gate, up) itself,
       // so the down projection's operand is a plain quantisation of one vector
-      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt && B < mma_min_rows(e);
+      bool pair = !(c.flags & (CMLD_FLAG_EXACT_ORDER | CMLD_FLAG_DIRECT_GEMV)) && L.proj[4].qt == L.proj[5].qt && B < mma_min_rows(e) && B < tc5_min_rows(e);
       if (pair) {
         const GemvJob pj[2] = {{L.proj[4].data, L.proj[4].qt, L.proj[4].rows, L.proj[4].cols, L.proj[4].stride, nullptr, nullptr, 0},
                                {L.proj[5].data, L.proj[5].qt, L.proj[5].rows, L.proj[5].cols, L.proj[5].stride, nullptr, nullptr, 0}};

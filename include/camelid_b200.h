@@ -271,6 +271,8 @@ CMLD_API int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t ba
  * the CPU dot's bits); bit 1 set = cmld_gemv_time chains its launches with programmatic dependent
  * launch; bit 3 set = batches of 9..32 rows on the int8 mma.sync kernel (one pass over the weights,
  * tree sums: within tolerance, not the CPU's bits), bit 2 set = that kernel from 1 row.
+ * Batches of 9 rows and more take the tcgen05 tensor-core kernel by default (one pass over the
+ * weights per 32 rows, the CPU dot's bits); bit 4 set = never, bit 5 set = from 1 row.
  * Process-wide; for A/B runs. */
 CMLD_API int32_t cmld_gemv_select_kernel(int32_t choice);
 /* Self-test of the bounded device-side wait of the peer-memory path (no reference counterpart): waits for an

@@ -109,14 +109,15 @@ def test_activation_quantisers_bit_exact(cm, orc, cols, batch):
     ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 3072), ("Q4_K", 64, 14336),
     ("Q6_K", 33, 256), ("Q6_K", 512, 4096), ("Q6_K", 130, 3072), ("Q6_K", 64, 14336)])
 @pytest.mark.parametrize("batch", [1, 2, 3, 8])
-@pytest.mark.parametrize("kernel", ["staged", "generic"])
+@pytest.mark.parametrize("kernel", ["staged", "generic", "tcgen05"])
 def test_gemv_matches_checker(cm, orc, name, rows, cols, batch, kernel):
-    """Both matvec kernels add a row's f32 terms in the CPU dot's order: every output equals the
-    checker's bit for bit (the staged kernel takes the shapes it supports, the generic one the rest)."""
+    """All matvec kernels add a row's f32 terms in the CPU dot's order: every output equals the
+    checker's bit for bit (the staged kernel takes the shapes it supports, the generic one the rest;
+    the tcgen05 kernel, forced here from one row, computes the integer parts on the tensor cores)."""
     from camelid_b200.engine import quantize_activation, export_activation, DeviceBuffer
     from camelid_b200._lib import check
 
-    check(cm.lib().cmld_gemv_select_kernel(1 if kernel == "generic" else 0))
+    check(cm.lib().cmld_gemv_select_kernel({"generic": 1, "staged": 16, "tcgen05": 32}[kernel]))
     qt = QT[name]
     wire = orc.synth_tensor(qt, 11, rows * 7 + cols, rows, cols, 0.02)
     w = cm.Weight.from_wire(qt, rows, cols, wire)
@@ -172,9 +173,10 @@ def test_fused_prologue_equals_separate_steps(cm, orc, name, rows, cols, mode, b
     assert np.array_equal(got, want)
 
 
-# More than 8 activation rows.  By default they run as passes of the ordered kernels (the checker's bits).
-# The int8 mma.sync kernel reads the weights once for all rows; its integer parts are exact but the
-# superblocks' f32 terms are added as a tree, so it is opt-in and held to a tolerance.
+# More than 8 activation rows.  By default they take the tcgen05 kernel: the weights are read once for up to
+# 32 rows, the integer parts come from the tensor cores and the f32 terms are added in the CPU dot's order
+# (the checker's bits).  The older int8 mma.sync kernel adds the superblocks' f32 terms as a tree, so it is
+# opt-in and held to a tolerance.
 @pytest.mark.parametrize("name,rows,cols", [
     ("Q8_0", 96, 256), ("Q8_0", 515, 2048), ("Q8_0", 70, 1792),
     ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 1792), ("Q4_K", 64, 14336),
@@ -194,11 +196,23 @@ def test_gemv_batched_tensor_core_kernel_matches_checker(cm, orc, name, rows, co
     codes, scales = export_activation(kind, act, cols, batch)
     res = rng.standard_normal((batch, rows)).astype(np.float32)
     res_d = DeviceBuffer.from_numpy(res)
-    # default: passes of the ordered kernels -> the checker's bits, whatever the batch
+    # default: one pass over the weights on the tcgen05 tensor cores (when the columns are a multiple of 256, else
+    # passes of the ordered kernels) -> the checker's bits, whatever the batch
     y = w.gemv(act, batch)
+    y_res = w.gemv(act, batch, res_d)
     for b in range(batch):
         ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
-        assert np.array_equal(y[b].view(np.uint32), ref.view(np.uint32)), (name, rows, cols, b)
+        bad = np.nonzero(y[b].view(np.uint32) != ref.view(np.uint32))[0]
+        assert bad.size == 0, (name, rows, cols, b, bad.size, bad[:5], y[b][bad[:5]], ref[bad[:5]])
+        assert np.array_equal(y_res[b], (res[b] + y[b]).astype(np.float32))
+    # the very same bits whatever the row's neighbours are, and from the staged kernel
+    y_rev = w.gemv(quantize_activation(kind, x[::-1].copy()), batch)
+    assert np.array_equal(y_rev[::-1].view(np.uint32), y.view(np.uint32))
+    check(cm.lib().cmld_gemv_select_kernel(16))
+    try:
+        assert np.array_equal(w.gemv(act, batch).view(np.uint32), y.view(np.uint32))
+    finally:
+        check(cm.lib().cmld_gemv_select_kernel(0))
     # opt-in: the int8 mma.sync kernel (kernel choice 8), one pass over the weights, tree sums
     check(cm.lib().cmld_gemv_select_kernel(8))
     try:
@@ -215,6 +229,29 @@ def test_gemv_batched_tensor_core_kernel_matches_checker(cm, orc, name, rows, co
         assert np.array_equal(y_again[::-1], ym)
     finally:
         check(cm.lib().cmld_gemv_select_kernel(0))
+
+
+@pytest.mark.parametrize("name,rows,cols,batch", [
+    ("Q4_K", 128 * 40 + 17, 512, 32), ("Q4_K", 128 * 170, 256, 32), ("Q4_K", 128 * 170, 256, 16),
+    ("Q6_K", 128 * 90 + 5, 512, 32), ("Q6_K", 128 * 170, 256, 11), ("Q8_0", 128 * 40, 768, 24), ("Q8_0", 128 * 170 + 64, 256, 32)])
+def test_gemv_tcgen05_many_tiles(cm, orc, name, rows, cols, batch):
+    """Launches with more tiles than SMs: a CTA walks several tiles, takes 16 or 32 activation rows at once
+    (two epilogue warp groups, two groups of columns each) and the last tile is ragged.  Bits of the checker."""
+    from camelid_b200.engine import quantize_activation, export_activation
+
+    qt = QT[name]
+    wire = orc.synth_tensor(qt, 17, rows + cols, rows, cols, 0.02)
+    w = cm.Weight.from_wire(qt, rows, cols, wire)
+    x = np.random.default_rng(rows + batch).standard_normal((batch, cols)).astype(np.float32)
+    kind = cm.ACT_Q8_0 if qt == 8 else cm.ACT_Q8_K
+    act = quantize_activation(kind, x)
+    codes, scales = export_activation(kind, act, cols, batch)
+    for rep in range(3):  # repeated: the pipeline's hand-offs are timing dependent
+        y = w.gemv(act, batch)
+        for b in range(batch):
+            ref = orc.matvec_quantised(qt, wire, rows, cols, codes[b], scales[b])
+            bad = np.nonzero(y[b].view(np.uint32) != ref.view(np.uint32))[0]
+            assert bad.size == 0, (name, rows, cols, b, rep, bad.size, bad[:5])
 
 
 def test_gemv_end_to_end_against_f32_activation_path(cm, orc):
