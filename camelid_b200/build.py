@@ -16,6 +16,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libcamelid_b200.so"
+STATIC_LIB = PKG / "libcamelid_b200.a"  # the same objects as an archive, for callers that link the engine in
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
@@ -79,6 +80,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    if jobs or not STATIC_LIB.exists():
+        # Static form: link with the CUDA runtime, e.g.
+        #   g++ app.cpp libcamelid_b200.a -L$CUDA/lib64 -lcudart_static -ldl -lpthread -lrt
+        STATIC_LIB.unlink(missing_ok=True)
+        res = subprocess.run(["ar", "rcs", str(STATIC_LIB), *[str(OBJ / (s.stem + ".o")) for s in sources]], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"ar failed:\n{res.stdout}\n{res.stderr}")
     return LIB
 
 

@@ -125,6 +125,7 @@ struct cmld_engine {
     unsigned long long timeout_ns = 0;
   } peer;
   float *mma_scratch = nullptr;  // per-chunk partial sums of the batched tensor-core matvec
+  std::vector<float> rope_freq;  // per-pair angular frequency of the engine-owned RoPE table (rope_pair_frequency)
   uint8_t *tc5_pack = nullptr;   // packed activation records of the tcgen05 batched matvec
   int64_t tc5_pack_bytes = 0;
   int64_t mma_scratch_floats = 0;
@@ -209,6 +210,23 @@ static int32_t dev_alloc(cmld_engine *e, T **p, int64_t count, bool zero = true)
   return CMLD_OK;
 }
 
+// cos/sin of position * frequency for every position and pair, by the host libm, onto the device.
+static int32_t upload_rope_tables(cmld_engine *e) {
+  const cmld_config &c = e->cfg;
+  const int half = c.rope_dim / 2;
+  std::vector<float> ct((size_t)c.max_pos * half), st((size_t)c.max_pos * half);
+  for (int64_t p = 0; p < c.max_pos; ++p)
+    for (int i = 0; i < half; ++i) {
+      const float ang = (float)p * e->rope_freq[i];
+      st[(size_t)p * half + i] = sinf(ang);
+      ct[(size_t)p * half + i] = cosf(ang);
+    }
+  CMLD_CUDA(cudaMemcpyAsync(e->cos_all, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->sin_all, st.data(), st.size() * 4, cudaMemcpyHostToDevice, e->stream));
+  CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  return CMLD_OK;
+}
+
 static int32_t validate_config(const cmld_config &c) {
   if (c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.head_dim <= 0 || c.hidden <= 0 || c.ffn_dim <= 0 ||
       c.max_pos <= 0 || c.vocab <= 0)
@@ -245,24 +263,17 @@ static int32_t engine_init(cmld_engine *e) {
   CMLD_TRY(dev_alloc(e, &e->kcache, e->kv_layer_elems * c.n_layers));
   CMLD_TRY(dev_alloc(e, &e->vcache, e->kv_layer_elems * c.n_layers));
   // RoPE tables for every position, computed with the host libm exactly as the reference's
-  // resident_decode_rope_tables does per token (src/inference/rope.rs:600-655).
+  // resident_decode_rope_tables does per token (src/inference/rope.rs:600-655).  The default per-pair
+  // frequency is freq_base^(-2i/rope_dim); cmld_engine_set_rope_frequencies replaces it (rope_freqs.weight,
+  // linear / llama3 scaling: rope_pair_frequency, src/inference/rope.rs:532-560).
   const int half = c.rope_dim / 2;
   {
-    std::vector<float> ct((size_t)c.max_pos * half), st((size_t)c.max_pos * half);
     const float base = c.rope_theta > 0.0f ? c.rope_theta : 10000.0f;
-    std::vector<float> theta(half);
-    for (int i = 0; i < half; ++i) theta[i] = powf(base, -((float)i * 2.0f) / (float)c.rope_dim);
-    for (int64_t p = 0; p < c.max_pos; ++p)
-      for (int i = 0; i < half; ++i) {
-        const float ang = (float)p * theta[i];
-        st[(size_t)p * half + i] = sinf(ang);
-        ct[(size_t)p * half + i] = cosf(ang);
-      }
+    e->rope_freq.resize(half);
+    for (int i = 0; i < half; ++i) e->rope_freq[i] = powf(base, -((float)i * 2.0f) / (float)c.rope_dim);
     CMLD_TRY(dev_alloc(e, &e->cos_all, (int64_t)c.max_pos * half, false));
     CMLD_TRY(dev_alloc(e, &e->sin_all, (int64_t)c.max_pos * half, false));
-    CMLD_CUDA(cudaMemcpyAsync(e->cos_all, ct.data(), ct.size() * 4, cudaMemcpyHostToDevice, e->stream));
-    CMLD_CUDA(cudaMemcpyAsync(e->sin_all, st.data(), st.size() * 4, cudaMemcpyHostToDevice, e->stream));
-    CMLD_CUDA(cudaStreamSynchronize(e->stream));
+    CMLD_TRY(upload_rope_tables(e));
   }
   const int64_t R = e->max_rows;
   CMLD_TRY(dev_alloc(e, &e->cos_step, R * half));
@@ -1506,15 +1517,23 @@ int32_t cmld_engine_set_filled(cmld_engine *e, int64_t filled) {
 int64_t cmld_engine_max_pos(const cmld_engine *e) { return e ? e->cfg.max_pos : 0; }
 int32_t cmld_engine_n_layers(const cmld_engine *e) { return e ? e->cfg.n_layers : 0; }
 
+int32_t cmld_engine_set_rope_frequencies(cmld_engine *e, const float *freq, int32_t n) {
+  if (!e || !freq) return fail(CMLD_ERR_INVALID, "null argument");
+  if (n != e->cfg.rope_dim / 2) return fail(CMLD_ERR_INVALID, "%d frequencies given, the engine rotates %d pairs", n, e->cfg.rope_dim / 2);
+  for (int i = 0; i < n; ++i)
+    if (!(freq[i] >= 0.0f) || !std::isfinite(freq[i])) return fail(CMLD_ERR_INVALID, "frequency %d is not a finite non-negative number", i);
+  DeviceGuard guard(e->device);
+  CMLD_CUDA(cudaStreamSynchronize(e->stream));
+  e->rope_freq.assign(freq, freq + n);
+  return upload_rope_tables(e);
+}
+
 int32_t cmld_engine_rope_row(const cmld_engine *e, int64_t position, float *cos_out, float *sin_out) {
   if (!e || !cos_out || !sin_out) return fail(CMLD_ERR_INVALID, "null argument");
   if (position < 0 || position >= e->cfg.max_pos) return fail(CMLD_ERR_INVALID, "position %lld out of range", (long long)position);
-  const cmld_config &c = e->cfg;
-  const int half = c.rope_dim / 2;
-  const float base = c.rope_theta > 0.0f ? c.rope_theta : 10000.0f;
+  const int half = e->cfg.rope_dim / 2;
   for (int i = 0; i < half; ++i) {
-    const float theta = powf(base, -((float)i * 2.0f) / (float)c.rope_dim);
-    const float ang = (float)position * theta;
+    const float ang = (float)position * e->rope_freq[i];
     sin_out[i] = sinf(ang);
     cos_out[i] = cosf(ang);
   }

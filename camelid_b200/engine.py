@@ -311,6 +311,12 @@ class ResidentDecode:
     def _f(self, a):
         return np.ascontiguousarray(a, np.float32)
 
+    def set_rope_frequencies(self, freq):
+        """Per-pair angular frequencies of the engine-owned RoPE table (``rope_pair_frequency`` of the model:
+        rope_freqs.weight and linear / llama3 scaling folded in); the table is recomputed for every position."""
+        f = self._f(freq)
+        check(lib().cmld_engine_set_rope_frequencies(self._h, _np_ptr(f), f.size))
+
     def rope_row(self, position: int):
         half = (self.cfg.rope_dim or self.cfg.head_dim) // 2
         c, s = np.empty(half, np.float32), np.empty(half, np.float32)

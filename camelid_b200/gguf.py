@@ -268,7 +268,8 @@ def model_metadata(cfg, name: str, arch: str = "llama") -> dict:
 _PROJ_NAMES = {"q": "attn_q", "k": "attn_k", "v": "attn_v", "o": "attn_output", "gate": "ffn_gate", "up": "ffn_up", "down": "ffn_down"}
 
 
-def emit_synthetic(path, shape: str, mix: str, seed: int, max_pos: int = 8192, n_layers: int | None = None, sigma: float = 0.02):
+def emit_synthetic(path, shape: str, mix: str, seed: int, max_pos: int = 8192, n_layers: int | None = None, sigma: float = 0.02,
+                   extra_metadata: dict | None = None, rope_freqs=None):
     """Writes the seeded synthetic model (the very tensors `synth.build_engine` generates) as a GGUF file.
     Tensors are generated and quantised on the current CUDA device one at a time and streamed to the file."""
     from . import synth
@@ -310,6 +311,10 @@ def emit_synthetic(path, shape: str, mix: str, seed: int, max_pos: int = 8192, n
     tensors.append(("output.weight", plan["output"], (cfg.hidden, cfg.vocab), gen(plan["output"], synth.STREAM_OUTPUT, cfg.vocab, cfg.hidden)))
     md = model_metadata(cfg, f"synthetic-{shape}-{mix}-seed{seed}")
     md["general.file_type"] = 7 if mix == "q8_0" else 15  # LLAMA_FTYPE_MOSTLY_Q8_0 / MOSTLY_Q4_K_M
+    if rope_freqs is not None:  # llama.cpp's freq_factors: one divisor per rotated pair
+        rf = np.ascontiguousarray(rope_freqs, np.float32)
+        tensors.append(("rope_freqs.weight", F32, (rf.size,), lambda: rf.view(np.uint8)))
+    md.update(extra_metadata or {})
     return write_gguf(path, md, tensors)
 
 
@@ -329,6 +334,59 @@ def engine_config_from(g: GgufFile, max_pos: int | None = None, **kw):
         rope_dim=int(md.get(f"{arch}.rope.dimension_count", head_dim)), eps=float(md.get(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5)),
         rope_theta=float(md.get(f"{arch}.rope.freq_base", 10000.0)), n_experts=int(md.get(f"{arch}.expert_count", 0)),
         n_experts_used=int(md.get(f"{arch}.expert_used_count", 0)), **kw)
+
+
+def _powf(base: float, exponent: float) -> np.float32:
+    """f32 power by the C library, which is what the reference's ``f32::powf`` and the engine's own table call
+    (numpy's float32 power differs from it in the last bit for some exponents)."""
+    import ctypes
+    import ctypes.util
+
+    global _LIBM
+    if _LIBM is None:
+        _LIBM = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+        _LIBM.powf.restype = ctypes.c_float
+        _LIBM.powf.argtypes = [ctypes.c_float, ctypes.c_float]
+    return np.float32(_LIBM.powf(float(base), float(exponent)))
+
+
+_LIBM = None
+
+
+def rope_frequencies(md: dict, rope_dim: int, rope_freqs=None) -> np.ndarray:
+    """Per-pair RoPE frequency of a model file, in f32 like ``rope_pair_frequency`` (src/inference/rope.rs:532-560
+    in the Camelid tree): freq_base^(-2i/rope_dim), divided by ``rope_freqs.weight[i]`` when the file carries that
+    tensor, then the metadata's scaling: none, "linear" (divide by the factor) or "llama3" (wavelength-dependent
+    blend, :733-757).  Any other scaling type (YaRN also rescales the rotation's magnitude) raises."""
+    arch = md["general.architecture"]
+    f32 = np.float32
+    half = rope_dim // 2
+    base = f32(md.get(f"{arch}.rope.freq_base", 10000.0))
+    kind = md.get(f"{arch}.rope.scaling.type")
+    kind = None if kind in (None, "", "none") else str(kind)
+    if kind not in (None, "linear", "llama3"):
+        raise ValueError(f"rope scaling type {kind!r} is not supported by the engine-owned RoPE table")
+    factor = f32(md.get(f"{arch}.rope.scaling.factor", 1.0))
+    out = np.empty(half, f32)
+    for i in range(half):
+        freq = _powf(base, f32(-(f32(i) * f32(2.0)) / f32(rope_dim)))
+        if rope_freqs is not None:
+            freq = f32(freq / f32(rope_freqs[i]))
+        if kind == "linear":
+            freq = f32(freq / factor)
+        elif kind == "llama3":
+            ctx = f32(md[f"{arch}.rope.scaling.original_context_length"])
+            lo, hi = f32(md[f"{arch}.rope.scaling.low_freq_factor"]), f32(md[f"{arch}.rope.scaling.high_freq_factor"])
+            wavelength = f32(f32(f32(2.0) * f32(np.pi)) / freq)
+            if wavelength < f32(ctx / hi):
+                pass
+            elif wavelength > f32(ctx / lo):
+                freq = f32(freq / factor)
+            else:
+                smooth = f32(f32(f32(ctx / wavelength) - lo) / f32(hi - lo))
+                freq = f32(f32(f32(f32(f32(1.0) - smooth) * freq) / factor) + f32(smooth * freq))
+        out[i] = freq
+    return out
 
 
 def load_engine(path, max_pos: int | None = None, **kw):
@@ -355,6 +413,14 @@ def load_engine(path, max_pos: int | None = None, **kw):
         out_name = "output.weight" if "output.weight" in g.tensors else "token_embd.weight"
         eng.set_output(f32("output_norm.weight"), (g.tensors[out_name].qt, g.data(out_name)))
         eng.set_token_embd((g.tensors["token_embd.weight"].qt, g.data("token_embd.weight")))
+        # the engine-owned RoPE table: rope_freqs.weight and the metadata's scaling, as the reference applies them
+        arch = g.metadata["general.architecture"]
+        scaled = g.metadata.get(f"{arch}.rope.scaling.type") not in (None, "", "none")
+        if "rope_freqs.weight" in g.tensors or scaled:
+            factors = f32("rope_freqs.weight") if "rope_freqs.weight" in g.tensors else None
+            if factors is not None and factors.size != cfg.rope_dim // 2:
+                raise ValueError(f"rope_freqs.weight holds {factors.size} values, {cfg.rope_dim // 2} pairs are rotated")
+            eng.set_rope_frequencies(rope_frequencies(g.metadata, cfg.rope_dim, factors))
         return eng
     finally:
         g.close()

@@ -158,6 +158,13 @@ CMLD_API int32_t cmld_engine_set_filled(cmld_engine *e, int64_t filled);
 CMLD_API int64_t cmld_engine_max_pos(const cmld_engine *e);
 CMLD_API int32_t cmld_engine_n_layers(const cmld_engine *e);
 
+/* Replaces the per-pair angular frequencies of the engine-owned RoPE table (n = rope_dim / 2) and
+ * recomputes the table for every position: what rope_pair_frequency yields for the model at hand
+ * (src/inference/rope.rs:532-560: freq_base^(-2i/rope_dim), divided by rope_freqs.weight[i], then
+ * linear / llama3 scaling).  The default after cmld_engine_create is the unscaled form.  Not to be
+ * called while a step is in flight. */
+CMLD_API int32_t cmld_engine_set_rope_frequencies(cmld_engine *e, const float *freq, int32_t n);
+
 /* The RoPE row of one position, cos_out/sin_out[rope_dim/2], as the engine's own all-position
  * table holds it: theta_i = powf(rope_theta, -2i/rope_dim), sinf/cosf of position*theta_i with the
  * host libm — what resident_decode_rope_tables computes per token (src/inference/rope.rs:600-655).

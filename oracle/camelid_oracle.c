@@ -903,6 +903,7 @@ typedef struct {
   orc_tensor token_embd, output;
   const float *final_norm;
   float *kcache, *vcache; /* [layer][kv_head][max_pos][head_dim], f16-exact f32 */
+  float *rope_freq;       /* optional per-pair frequencies (rope_pair_frequency, src/inference/rope.rs:532); NULL = base^(-2i/d) */
 } orc_model;
 
 ORACLE_API orc_model *orc_model_create(int32_t n_layers, int32_t n_heads, int32_t n_kv_heads, int32_t head_dim,
@@ -923,11 +924,31 @@ ORACLE_API orc_model *orc_model_create(int32_t n_layers, int32_t n_heads, int32_
 
 ORACLE_API void orc_model_destroy(orc_model *m) {
   if (!m) return;
-  free(m->layers); free(m->kcache); free(m->vcache); free(m);
+  free(m->layers); free(m->kcache); free(m->vcache); free(m->rope_freq); free(m);
 }
 
 static orc_tensor mk_tensor(int32_t qt, const uint8_t *data, int64_t rows, int64_t cols) {
   orc_tensor t; t.qt = qt; t.data = data; t.rows = rows; t.cols = cols; return t;
+}
+
+/* Per-pair RoPE frequencies for models with rope_freqs.weight or scaled RoPE (copied). */
+ORACLE_API int orc_model_set_rope_frequencies(orc_model *m, const float *freq, int32_t n) {
+  if (n != m->rope_dim / 2) return -1;
+  free(m->rope_freq);
+  m->rope_freq = (float *)malloc((size_t)n * 4);
+  memcpy(m->rope_freq, freq, (size_t)n * 4);
+  return 0;
+}
+
+/* The llama3 wavelength-dependent scaling of one frequency (llama3_scaled_rope_frequency, src/inference/rope.rs:733-757). */
+ORACLE_API float orc_rope_llama3_frequency(float frequency, float factor, float original_context, float low_freq_factor,
+                                           float high_freq_factor) {
+  float wavelength = (2.0f * 3.14159265358979323846f) / frequency;
+  float low_w = original_context / low_freq_factor, high_w = original_context / high_freq_factor;
+  if (wavelength < high_w) return frequency;
+  if (wavelength > low_w) return frequency / factor;
+  float smooth = (original_context / wavelength - low_freq_factor) / (high_freq_factor - low_freq_factor);
+  return ((1.0f - smooth) * frequency / factor) + (smooth * frequency);
 }
 
 /* Pointers are borrowed: the caller keeps the buffers alive. slot: 0..6 = q,k,v,o,gate,up,down. */
@@ -1062,7 +1083,16 @@ ORACLE_API int orc_forward(orc_model *m, const float *x_in, int64_t position, fl
   float *cosv = (float *)malloc((size_t)m->rope_dim * 2), *sinv = (float *)malloc((size_t)m->rope_dim * 2);
   float *scores = (float *)malloc((size_t)(position + 1) * 4);
   memcpy(h, x_in, (size_t)hidden * 4);
-  orc_rope_table(position, m->rope_dim, m->rope_base, cosv, sinv);
+  if (m->rope_freq) {
+    /* angle = position * frequency, then sin/cos (apply_rope_to_row, src/inference/rope.rs:500-502) */
+    for (int32_t i = 0; i < m->rope_dim / 2; ++i) {
+      float ang = (float)position * m->rope_freq[i];
+      sinv[i] = sinf(ang);
+      cosv[i] = cosf(ang);
+    }
+  } else {
+    orc_rope_table(position, m->rope_dim, m->rope_base, cosv, sinv);
+  }
   float scale = 1.0f / sqrtf((float)hd); /* src/inference/diagnostic_config.rs:300-317 */
   int group = m->n_heads / m->n_kv_heads;
   int rc = 0;

@@ -76,6 +76,8 @@ def lib(path: str | os.PathLike | None = None):
         "orc_embedding": (C.c_int, [vp, i32, vp]),
         "orc_model_read_kv": (C.c_int, [vp, i32, i64, vp, vp]),
         "orc_model_write_kv": (C.c_int, [vp, i32, i64, vp, vp]),
+        "orc_model_set_rope_frequencies": (C.c_int, [vp, vp, i32]),
+        "orc_rope_llama3_frequency": (f32, [f32, f32, f32, f32, f32]),
         "orc_forward": (C.c_int, [vp, vp, i64, vp, vp, vp]),
         "orc_generate": (C.c_int, [vp, vp, i32, i32, i64, vp, vp]),
         "orc_generate_gaps": (C.c_int, [vp, vp, i32, i32, i64, vp, vp, vp]),
@@ -279,6 +281,10 @@ class OracleModel:
         ck, cv = np.empty(shape, np.float32), np.empty(shape, np.float32)
         assert lib().orc_model_read_kv(self._h, layer, n_positions, _p(ck), _p(cv)) == 0
         return ck, cv
+
+    def set_rope_frequencies(self, freq):
+        f = _f32(freq)
+        assert lib().orc_model_set_rope_frequencies(self._h, _p(f), f.size) == 0
 
     def write_kv_layer(self, layer: int, ck, cv):
         """Plants positions 0..n-1 of one layer's cache ([kv_head][n][head_dim] each), rounded to f16."""

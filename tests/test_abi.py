@@ -57,3 +57,27 @@ def test_synthetic_model_byte_counts(cm):
     c = synth.engine_config("llama-8b", 8192)
     assert abs(synth.weight_bytes_per_token(c, "q4_k_m") / 1e9 - 4.8769) < 1e-3
     assert synth.kv_bytes_per_position(c) == 128 * 1024
+
+
+def test_header_compiles_as_cxx_and_links_against_the_static_archive(cm, tmp_path):
+    """include/camelid_b200.h is compiled, not only mirrored by hand in the ctypes binding: a small C++ program
+    includes it, links libcamelid_b200.a (+ the CUDA runtime) and exercises cmld_engine_create / cmld_last_error."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+
+    from camelid_b200 import build
+
+    root = Path(__file__).resolve().parent.parent
+    build.build()
+    assert build.STATIC_LIB.exists()
+    cuda = Path(shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc").resolve().parent.parent
+    if not (cuda / "lib64" / "libcudart_static.a").exists():
+        pytest.skip("the static CUDA runtime is not installed")
+    exe = tmp_path / "abi_link_check"
+    cmd = ["g++", "-std=c++17", "-Wall", "-Werror", "-I", str(root / "include"), str(root / "tests" / "abi_link_check.cpp"),
+           str(build.STATIC_LIB), "-L", str(cuda / "lib64"), "-lcudart_static", "-ldl", "-lpthread", "-lrt", "-o", str(exe)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.startswith("ok camelid_b200"), (run.returncode, run.stdout, run.stderr)

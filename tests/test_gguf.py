@@ -99,3 +99,33 @@ def test_model_metadata_keys_are_the_loader_keys():
                 "llama.expert_count", "llama.expert_used_count", "llama.vocab_size"):
         assert key in md, key
     assert md["llama.expert_count"] == 8 and md["llama.expert_used_count"] == 2 and md["llama.attention.head_count_kv"] == 8
+
+
+def test_rope_frequencies_follow_the_reference_function():
+    """gguf.rope_frequencies restates rope_pair_frequency (src/inference/rope.rs:532-560): the plain form has the C
+    library's powf bits, the llama3 form equals the checker's C restatement of llama3_scaled_rope_frequency
+    (:733-757), linear scaling and rope_freqs.weight divide, and an unknown scaling type is refused."""
+    import ctypes
+    import ctypes.util
+
+    from camelid_b200 import gguf
+    from oracle import oracle as orc
+
+    libm = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+    libm.powf.restype, libm.powf.argtypes = ctypes.c_float, [ctypes.c_float, ctypes.c_float]
+    md = {"general.architecture": "llama", "llama.rope.freq_base": 500000.0}
+    plain = gguf.rope_frequencies(md, 128)
+    want = np.array([libm.powf(500000.0, np.float32(-(np.float32(i) * np.float32(2.0)) / np.float32(128))) for i in range(64)], np.float32)
+    assert np.array_equal(plain.view(np.uint32), want.view(np.uint32))
+    l3 = dict(md, **{"llama.rope.scaling.type": "llama3", "llama.rope.scaling.factor": 32.0, "llama.rope.scaling.original_context_length": 8192,
+                     "llama.rope.scaling.low_freq_factor": 1.0, "llama.rope.scaling.high_freq_factor": 4.0})
+    got = gguf.rope_frequencies(l3, 128)
+    ref = np.array([orc.lib().orc_rope_llama3_frequency(float(f), 32.0, 8192.0, 1.0, 4.0) for f in plain], np.float32)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    assert got[0] == plain[0] and got[-1] == np.float32(plain[-1] / np.float32(32.0)) and np.any((got != plain) & (got != plain / np.float32(32.0)))
+    lin = gguf.rope_frequencies(dict(md, **{"llama.rope.scaling.type": "linear", "llama.rope.scaling.factor": 4.0}), 128)
+    assert np.array_equal(lin, (plain / np.float32(4.0)).astype(np.float32))
+    fac = (1.0 + np.arange(64, dtype=np.float32)).astype(np.float32)
+    assert np.array_equal(gguf.rope_frequencies(md, 128, fac), (plain / fac).astype(np.float32))
+    with pytest.raises(ValueError):
+        gguf.rope_frequencies(dict(md, **{"llama.rope.scaling.type": "yarn"}), 128)
