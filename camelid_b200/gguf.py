@@ -38,7 +38,7 @@ def tensor_nbytes(qt: int, dims) -> int:
     for d in dims:
         n *= int(d)
     if dims[0] % per:
-        raise ValueError(f"row length {dims[0]} is not a multiple of the {per}-value block of type {qt}")
+        raise ValueError(f"tensor first dimension {dims[0]} is not divisible by block size {per} (type {qt})")
     return n // per * size
 
 

@@ -129,3 +129,109 @@ def test_rope_frequencies_follow_the_reference_function():
     assert np.array_equal(gguf.rope_frequencies(md, 128, fac), (plain / fac).astype(np.float32))
     with pytest.raises(ValueError):
         gguf.rope_frequencies(dict(md, **{"llama.rope.scaling.type": "yarn"}), 128)
+
+
+# ---- files built the way the reference's own tests build them (tests/tensor_store.rs:1062-1090 in the Camelid
+# tree: magic, u32 version 3, i64 tensor count, i64 metadata count, one string KV, the tensor record with i64
+# dims, i32 type and u64 offset, zero padding to 32 bytes, payload) — written here field by field, not through
+# gguf.write_gguf, so the reader is pinned to the reference's byte recipe and not only to this package's writer.
+
+def _ref_style_file(path, name, type_id, dims, payload, extra_kv=()):
+    def s(v):
+        raw = v.encode()
+        return struct.pack("<Q", len(raw)) + raw
+
+    b = bytearray(b"GGUF")
+    b += struct.pack("<I", 3)
+    b += struct.pack("<q", 1)
+    b += struct.pack("<q", 1 + len(extra_kv))
+    b += s("general.architecture") + struct.pack("<i", 8) + s("llama")
+    for key, type_code, packed in extra_kv:
+        b += s(key) + struct.pack("<i", type_code) + packed
+    b += s(name) + struct.pack("<I", len(dims))
+    for d in dims:
+        b += struct.pack("<q", d)
+    b += struct.pack("<i", type_id) + struct.pack("<Q", 0)
+    while len(b) % 32:
+        b.append(0)
+    b += payload
+    path.write_bytes(bytes(b))
+
+
+def test_reader_takes_the_reference_test_files(tmp_path):
+    # loads_f32_tensor_payload (tests/tensor_store.rs:15-31)
+    p = tmp_path / "f32.gguf"
+    _ref_style_file(p, "test.weight", 0, [2], struct.pack("<ff", 1.0, 2.5))
+    g = gguf.GgufFile(p)
+    assert g.version == 3 and g.alignment == 32 and g.metadata == {"general.architecture": "llama"}
+    t = g.tensors["test.weight"]
+    assert t.dims == (2,) and t.qt == gguf.F32 and t.offset == 0 and g.data_start % 32 == 0
+    assert g.data("test.weight").view(np.float32).tolist() == [1.0, 2.5]
+    g.close()
+    # loads_q8_0_tensor_payload_as_f32 (:68-85): scale 1.0 (f16 0x3c00), codes 0..31 -> values 0..31
+    from oracle import oracle as orc
+
+    p = tmp_path / "q8.gguf"
+    payload = struct.pack("<H", 0x3C00) + bytes(range(32))
+    _ref_style_file(p, "test.weight", 8, [32], payload)
+    g = gguf.GgufFile(p)
+    t = g.tensors["test.weight"]
+    assert t.qt == gguf.Q8_0 and t.dims == (32,) and t.nbytes == 34
+    vals = orc.dequant(8, g.data("test.weight"), 32)
+    assert vals[0] == 0.0 and vals[31] == 31.0 and np.array_equal(vals, np.arange(32, dtype=np.float32))
+    g.close()
+    # K-quant superblocks and a 2-D tensor with its dims in GGUF order (innermost first)
+    rng = np.random.default_rng(11)
+    for type_id, block in ((12, 144), (14, 210)):
+        p = tmp_path / f"k{type_id}.gguf"
+        payload = rng.integers(0, 256, 3 * 2 * block, dtype=np.uint8).tobytes()
+        _ref_style_file(p, "blk.0.attn_q.weight", type_id, [512, 3], payload)
+        g = gguf.GgufFile(p)
+        t = g.tensors["blk.0.attn_q.weight"]
+        assert t.dims == (512, 3) and t.qt == type_id and t.nbytes == len(payload)
+        assert g.data("blk.0.attn_q.weight").tobytes() == payload
+        g.close()
+    # a second KV of another type before the tensor table: u32 value (type 4)
+    p = tmp_path / "kv.gguf"
+    key_val = struct.pack("<I", 16)
+    _ref_style_file(p, "test.weight", 0, [2], struct.pack("<ff", 3.0, 4.0), extra_kv=[("llama.block_count", 4, key_val)])
+    g = gguf.GgufFile(p)
+    assert g.metadata["llama.block_count"] == 16 and g.data("test.weight").view(np.float32).tolist() == [3.0, 4.0]
+    g.close()
+
+
+def test_reader_refuses_a_q8_0_tensor_that_is_not_block_aligned(tmp_path):
+    # rejects_q8_0_tensor_with_non_block_aligned_first_dimension (tests/tensor_store.rs:1023-1032)
+    p = tmp_path / "bad-q8.gguf"
+    _ref_style_file(p, "test.weight", 8, [31], b"")
+    with pytest.raises(ValueError) as ei:
+        gguf.GgufFile(p)
+    assert "first dimension 31" in str(ei.value) and "block size 32" in str(ei.value)
+
+
+def test_engine_config_reads_the_llama_keys_of_the_reference_loader(tmp_path):
+    """The metadata keys ModelConfig::from_gguf reads for a llama-architecture file (src/model.rs:320-540):
+    block_count, context_length, embedding_length, feed_forward_length, attention.head_count(_kv),
+    attention.layer_norm_rms_epsilon, rope.dimension_count, rope.freq_base, expert_count, expert_used_count,
+    vocab_size, attention.key_length — engine_config_from picks each of them up, and falls back the same way
+    (kv heads = heads, head_dim = embedding/heads, vocab from token_embd's second dim)."""
+    md = {"general.architecture": "llama", "llama.block_count": 3, "llama.context_length": 4096, "llama.embedding_length": 256,
+          "llama.feed_forward_length": 768, "llama.attention.head_count": 8, "llama.attention.head_count_kv": 2,
+          "llama.attention.layer_norm_rms_epsilon": 1e-6, "llama.rope.dimension_count": 32, "llama.rope.freq_base": 500000.0,
+          "llama.expert_count": 4, "llama.expert_used_count": 2}
+    emb = np.zeros(gguf.tensor_nbytes(gguf.F32, (256, 1000)), np.uint8)
+    path = tmp_path / "cfg.gguf"
+    gguf.write_gguf(path, md, [("token_embd.weight", gguf.F32, (256, 1000), emb)])
+    g = gguf.GgufFile(path)
+    c = gguf.engine_config_from(g)
+    g.close()
+    assert (c.n_layers, c.max_pos, c.hidden, c.ffn_dim, c.n_heads, c.n_kv_heads) == (3, 4096, 256, 768, 8, 2)
+    assert c.head_dim == 32 and c.rope_dim == 32 and c.vocab == 1000 and c.n_experts == 4 and c.n_experts_used == 2
+    assert abs(c.eps - 1e-6) < 1e-12 and c.rope_theta == 500000.0
+    for drop in ("llama.attention.head_count_kv", "llama.rope.dimension_count", "llama.expert_count", "llama.expert_used_count"):
+        md.pop(drop)
+    gguf.write_gguf(path, md, [("token_embd.weight", gguf.F32, (256, 1000), emb)])
+    g = gguf.GgufFile(path)
+    c = gguf.engine_config_from(g, max_pos=128)
+    g.close()
+    assert c.n_kv_heads == 8 and c.rope_dim == 32 and c.n_experts == 0 and c.max_pos == 128
