@@ -99,6 +99,8 @@ def lib():
         "cmld_engine_n_layers": (i32, [vp]),
         "cmld_engine_rope_row": (i32, [vp, i64, vp, vp]),
         "cmld_engine_set_rope_frequencies": (i32, [vp, vp, i32]),
+        "cmld_engine_verify_tree": (i32, [vp, vp, vp, vp, vp, vp, i32, i64, i32, f32, vp]),
+        "cmld_engine_compact_tree_kv_path": (i32, [vp, vp, i32, i64]),
         "cmld_engine_forward_token": (i32, [vp, vp, vp, vp, i64, f32, i32, P(C.c_uint32)]),
         "cmld_engine_forward_token_logits": (i32, [vp, vp, vp, vp, i64, f32, vp]),
         "cmld_engine_forward_token_hidden": (i32, [vp, vp, vp, vp, i64, f32, vp, vp]),

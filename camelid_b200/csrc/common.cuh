@@ -331,6 +331,11 @@ struct AttnArgs {
   int32_t pdl;                     // launch with programmatic stream serialisation
   int32_t cluster;                 // ranges as the CTAs of a thread-block cluster, merged through distributed shared memory
   unsigned long long *phase_ns;    // optional (reference-order cluster kernel): %globaltimer of CTA 0 at the end of each phase
+  // Tree verification (plain reference-order kernel only): cache rows tree_base.. hold the nodes of a draft tree in
+  // breadth-first order; row b attends to every position below tree_base and to node j only if bit j of its mask
+  // is set (its ancestors and itself).  Null = ordinary causal attention.
+  const uint32_t *tree_mask = nullptr;  // [batch][tree_words]
+  int32_t tree_base = 0, tree_words = 0;
 };
 int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
 // attn_ordered.cu: the reference-order cluster kernel (contexts of at most `cap` positions)

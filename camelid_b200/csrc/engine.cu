@@ -125,6 +125,7 @@ struct cmld_engine {
     unsigned long long timeout_ns = 0;
   } peer;
   float *mma_scratch = nullptr;  // per-chunk partial sums of the batched tensor-core matvec
+  uint32_t *tree_mask = nullptr;  // [kTreeMaxNodes] ancestor masks of a draft tree (one word: at most 32 nodes)
   std::vector<float> rope_freq;  // per-pair angular frequency of the engine-owned RoPE table (rope_pair_frequency)
   uint8_t *tc5_pack = nullptr;   // packed activation records of the tcgen05 batched matvec
   int64_t tc5_pack_bytes = 0;
@@ -634,6 +635,8 @@ struct StepOpts {
   int32_t layer_begin = 0, layer_end = -1;  // layers to run; -1 = through the last
   bool attn_cluster = false;  // short contexts, few rows: attention ranges as a thread-block cluster (host-side choice)
   int32_t attn_cap = 0;       // bound on the context length of every row of this step (a bucket: 1024, 2048, 4096, 8192), 0 = unknown
+  const uint32_t *tree_mask = nullptr;  // tree verification: per-row ancestor masks (device), nodes at cache rows tree_base..
+  int32_t tree_base = 0, tree_words = 0;
   bool shared_slots = false;  // several rows of this step belong to one sequence (prefill, verify): row b
                               // reads K/V that rows < b write, so the KV append must be a kernel of its own
 };
@@ -843,8 +846,8 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       // Attention.  Default: the reference-order cluster kernel (the CPU path's bits); contexts or shapes it
       // does not take, and CMLD_FLAG_EXACT_ORDER, use the plain reference-order kernel; CMLD_FLAG_FAST_ORDER
       // opts into the split-range (flash-decoding) kernel, whose sums are trees.
-      const bool fast = (c.flags & CMLD_FLAG_FAST_ORDER) && !(c.flags & CMLD_FLAG_EXACT_ORDER);
-      const bool ordered = !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && o.attn_cap > 0 &&
+      const bool fast = (c.flags & CMLD_FLAG_FAST_ORDER) && !(c.flags & CMLD_FLAG_EXACT_ORDER) && !o.tree_mask;
+      const bool ordered = !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && o.attn_cap > 0 && !o.tree_mask &&
                            attention_ordered_fits(c.n_heads, c.n_kv_heads, c.head_dim, o.attn_cap);
       const bool fuse = !o.shared_slots && (fast || ordered);
       if (!fuse) {
@@ -902,6 +905,9 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.pdl = !(c.flags & CMLD_FLAG_NO_PDL);
       a.cluster = o.attn_cluster && fast ? 1 : 0;
       a.phase_ns = e->attn_phases;
+      a.tree_mask = o.tree_mask;
+      a.tree_base = o.tree_base;
+      a.tree_words = o.tree_words;
       if (ordered) CMLD_TRY(launch_attention_ordered(a, o.attn_cap, e->stream));
       else if (fast) CMLD_TRY(launch_attention(a, e->stream));
       else CMLD_TRY(launch_attention_exact(a, e->stream));
@@ -984,7 +990,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
 // A step through a CUDA graph when possible: one graph launch replaces ~200 kernel launches, and
 // the programmatic-dependent-launch edges between the matvec kernels are kept inside the graph.
 static int32_t run_step(cmld_engine *e, const StepOpts &o) {
-  if ((e->cfg.flags & CMLD_FLAG_NO_GRAPH) || e->graphs_off) return engine_step(e, o);
+  if ((e->cfg.flags & CMLD_FLAG_NO_GRAPH) || e->graphs_off || o.tree_mask) return engine_step(e, o);
   uint32_t bits = (o.from_tokens ? 1u : 0u) | (o.rope_by_position ? 2u : 0u) | (o.logits ? 4u : 0u) | (o.argmax ? 8u : 0u) |
                   (o.feed_back ? 16u : 0u) | (o.taps ? 32u : 0u) | (o.shared_slots ? 64u : 0u) | (o.attn_cluster ? 128u : 0u) | ((uint32_t)(o.layer_begin & 0xfff) << 8) | ((uint32_t)((o.layer_end + 1) & 0xfff) << 20);
   uint32_t scale_bits;
@@ -1615,6 +1621,88 @@ int32_t cmld_engine_verify_batch(cmld_engine *e, const float *embeddings, const 
   CMLD_TRY(finish(e, "verify_batch"));
   for (int i = 0; i < k; ++i) tokens_out[i] = (uint32_t)toks[i];
   return CMLD_OK;
+}
+
+
+// verify_tree (src/cuda_resident.rs:22944): the N nodes of a draft tree (breadth-first order) in one batched pass.
+// Node i writes its K/V to cache row node_kvslot[i] (= base + i), is rotated by its own cos/sin row (position base +
+// depth) and attends to the committed prefix below base plus the nodes its ancestor mask names; tokens_out[i] is the
+// greedy token after node i along its path.  The sums run over exactly the rows a linear decode of that path would
+// see, in the same order, so the prediction is the linear decode's.
+int32_t cmld_engine_verify_tree(cmld_engine *e, const float *embeddings, const float *cos_all, const float *sin_all,
+                                const int32_t *node_kvslot, const uint32_t *ancestor_bits, int32_t words, int64_t base_position,
+                                int32_t n, float scale, uint32_t *tokens_out) {
+  CMLD_ENGINE_ENTER(e);
+  const cmld_config &c = e->cfg;
+  if (n < 1 || n > CMLD_TREE_MAX_NODES) return fail(CMLD_ERR_INVALID, "verify_tree: n=%d out of 1..=%d", n, CMLD_TREE_MAX_NODES);
+  if (!embeddings || !cos_all || !sin_all || !node_kvslot || !ancestor_bits || !tokens_out) return fail(CMLD_ERR_INVALID, "verify_tree: null argument");
+  if (words != 1) return fail(CMLD_ERR_INVALID, "verify_tree: %d mask words per node, 1 expected for at most %d nodes", words, CMLD_TREE_MAX_NODES);
+  if (base_position < 0 || base_position + n > c.max_pos) return fail(CMLD_ERR_STATE, "verify_tree: rows %lld..%lld exceed max_pos %d", (long long)base_position, (long long)(base_position + n - 1), c.max_pos);
+  if (e->tp > 1 || e->ep > 1) return fail(CMLD_ERR_UNSUPPORTED, "verify_tree: sharded engines are not supported");
+  std::vector<uint32_t> masks(n);
+  std::vector<int32_t> pos(n), slots(n, 0);
+  for (int i = 0; i < n; ++i) {
+    if (node_kvslot[i] != base_position + i) return fail(CMLD_ERR_INVALID, "verify_tree: node %d has cache row %d, base + index = %lld expected", i, node_kvslot[i], (long long)(base_position + i));
+    if (ancestor_bits[i] >> (i + 1)) return fail(CMLD_ERR_INVALID, "verify_tree: node %d names a later node as its ancestor", i);
+    masks[i] = ancestor_bits[i] | (1u << i);  // a node sees itself
+    pos[i] = (int32_t)(base_position + i);
+  }
+  CMLD_TRY(require_weights(e, true));
+  if (!e->tree_mask) CMLD_TRY(dev_alloc(e, &e->tree_mask, CMLD_TREE_MAX_NODES));
+  const int half = c.rope_dim / 2;
+  CMLD_CUDA(cudaMemcpyAsync(e->h, embeddings, (size_t)n * c.hidden * 4, cudaMemcpyDefault, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->cos_step, cos_all, (size_t)n * half * 4, cudaMemcpyDefault, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->sin_step, sin_all, (size_t)n * half * 4, cudaMemcpyDefault, e->stream));
+  CMLD_CUDA(cudaMemcpyAsync(e->tree_mask, masks.data(), (size_t)n * 4, cudaMemcpyHostToDevice, e->stream));
+  CMLD_TRY(stage_rows(e, n, nullptr, pos.data(), slots.data()));
+  StepOpts o;
+  o.batch = n;
+  o.shared_slots = true;  // every node's K/V row is appended before any node attends
+  o.from_tokens = false;
+  o.rope_by_position = false;
+  o.scale = scale;
+  o.logits = true;
+  o.argmax = true;
+  o.tree_mask = e->tree_mask;
+  o.tree_base = (int32_t)base_position;
+  o.tree_words = 1;
+  CMLD_TRY(run_step(e, o));
+  std::vector<int32_t> toks(n);
+  CMLD_TRY(settle(e));
+  CMLD_CUDA(cudaMemcpyAsync(toks.data(), e->out_idx, (size_t)n * 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "verify_tree"));
+  for (int i = 0; i < n; ++i) tokens_out[i] = (uint32_t)toks[i];
+  return CMLD_OK;
+}
+
+__global__ void kv_compact_kernel(__half *kc, __half *vc, int64_t layer_elems, int n_layers, int n_kv, int64_t max_pos, int hd, int64_t src,
+                                  int64_t dst) {
+  const int64_t total = (int64_t)n_layers * n_kv * hd;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t li = i / ((int64_t)n_kv * hd), rem = i % ((int64_t)n_kv * hd), kh = rem / hd, d = rem % hd;
+    const int64_t row = li * layer_elems + kh * max_pos * hd;
+    kc[row + dst * hd + d] = kc[row + src * hd + d];
+    vc[row + dst * hd + d] = vc[row + src * hd + d];
+  }
+}
+
+// compact_tree_kv_path (src/cuda_resident.rs:23071): the accepted path's K/V rows, at cache rows base + path[r], move
+// to the contiguous rows base + r (front to back; path[r] >= r, so a source is never overwritten before it is read).
+int32_t cmld_engine_compact_tree_kv_path(cmld_engine *e, const int32_t *path, int32_t len, int64_t base_position) {
+  CMLD_ENGINE_ENTER(e);
+  const cmld_config &c = e->cfg;
+  if (!path || len < 0 || len > CMLD_TREE_MAX_NODES) return fail(CMLD_ERR_INVALID, "compact_tree_kv_path: bad path");
+  for (int r = 0; r < len; ++r) {
+    if (path[r] < r || path[r] >= CMLD_TREE_MAX_NODES || (r > 0 && path[r] <= path[r - 1])) return fail(CMLD_ERR_INVALID, "compact_tree_kv_path: path is not an increasing sequence of node indices");
+    if (base_position + path[r] >= c.max_pos) return fail(CMLD_ERR_STATE, "compact_tree_kv_path: row beyond max_pos");
+  }
+  for (int r = 0; r < len; ++r) {
+    if (path[r] == r) continue;
+    kv_compact_kernel<<<64, 256, 0, e->stream>>>(e->kcache, e->vcache, e->kv_layer_elems, c.n_layers, c.n_kv_heads, c.max_pos, c.head_dim,
+                                                 base_position + path[r], base_position + r);
+    CMLD_CUDA(cudaGetLastError());
+  }
+  return finish(e, "compact_tree_kv_path");
 }
 
 // KV import/export, slot 0: f32 [kv_head][n_positions][head_dim] <-> f16 cache rows.

@@ -164,7 +164,19 @@ __global__ void __launch_bounds__(kExactAttnThreads) attn_exact_kernel(AttnArgs 
   const float *q = a.q + (int64_t)b * a.q_stride + (int64_t)head * hd;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) s_q[d] = q[d];
   __syncthreads();
+  // Tree verification: a position at or above tree_base takes part only if the row's mask names that node.  A
+  // position left out is skipped in every sum below, so what remains is the linear decode of the node's own path.
+  const uint32_t *mask = a.tree_mask ? a.tree_mask + (int64_t)b * a.tree_words : nullptr;
+  auto live = [&](int p) -> bool {
+    if (!mask || p < a.tree_base) return true;
+    const int j = p - a.tree_base;
+    return (mask[j >> 5] >> (j & 31)) & 1u;
+  };
   for (int p = threadIdx.x; p < n_pos; p += blockDim.x) {
+    if (!live(p)) {
+      s_sc[p] = -INFINITY;
+      continue;
+    }
     const __half *kr = kbase + (int64_t)p * hd;
     float s = 0.0f;
     for (int d = 0; d < hd; ++d) s = __fadd_rn(s, __fmul_rn(s_q[d], __half2float(kr[d])));
@@ -185,11 +197,13 @@ __global__ void __launch_bounds__(kExactAttnThreads) attn_exact_kernel(AttnArgs 
   }
   __syncthreads();
   m = s_bcast[0];
-  for (int p = threadIdx.x; p < n_pos; p += blockDim.x) s_sc[p] = expf_exact(__fsub_rn(s_sc[p], m));
+  for (int p = threadIdx.x; p < n_pos; p += blockDim.x)
+    if (live(p)) s_sc[p] = expf_exact(__fsub_rn(s_sc[p], m));
   __syncthreads();
   if (threadIdx.x == 0) {
     float sum = 0.0f;
-    for (int p = 0; p < n_pos; ++p) sum = __fadd_rn(sum, s_sc[p]);
+    for (int p = 0; p < n_pos; ++p)
+      if (live(p)) sum = __fadd_rn(sum, s_sc[p]);
     s_bcast[1] = __fdiv_rn(1.0f, sum);
   }
   __syncthreads();
@@ -197,7 +211,8 @@ __global__ void __launch_bounds__(kExactAttnThreads) attn_exact_kernel(AttnArgs 
   float *out = a.out + (int64_t)b * a.q_stride + (int64_t)head * hd;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.0f;
-    for (int p = 0; p < n_pos; ++p) o = __fadd_rn(o, __fmul_rn(__fmul_rn(s_sc[p], inv), __half2float(vbase[(int64_t)p * hd + d])));
+    for (int p = 0; p < n_pos; ++p)
+      if (live(p)) o = __fadd_rn(o, __fmul_rn(__fmul_rn(s_sc[p], inv), __half2float(vbase[(int64_t)p * hd + d])));
     out[d] = o;
   }
 }

@@ -366,6 +366,26 @@ class ResidentDecode:
         check(lib().cmld_engine_verify_batch(self._h, _np_ptr(e), _np_ptr(c), _np_ptr(s), base_position, k, scale, _np_ptr(out)))
         return out
 
+    def verify_tree(self, embeddings, cos_all, sin_all, parents, base_position: int, scale: float) -> np.ndarray:
+        """Greedy token after every node of a draft tree in one batched pass (``verify_tree``).  ``parents[i]`` is the
+        breadth-first index of node i's parent (-1 for the root, node 0); the nodes' K/V rows land at
+        base_position + i."""
+        n = len(parents)
+        bits = np.zeros(n, np.uint32)
+        for i, par in enumerate(parents):
+            if par >= 0:
+                bits[i] = bits[par] | np.uint32(1 << par)
+        e, c, s = self._f(embeddings), self._f(cos_all), self._f(sin_all)
+        slots = (base_position + np.arange(n)).astype(np.int32)
+        out = np.empty(n, np.uint32)
+        check(lib().cmld_engine_verify_tree(self._h, _np_ptr(e), _np_ptr(c), _np_ptr(s), _np_ptr(slots), _np_ptr(bits), 1,
+                                            base_position, n, scale, _np_ptr(out)))
+        return out
+
+    def compact_tree_kv_path(self, path, base_position: int):
+        p = np.ascontiguousarray(path, np.int32)
+        check(lib().cmld_engine_compact_tree_kv_path(self._h, _np_ptr(p), p.size, base_position))
+
     def seed_layer(self, layer: int, ck, cv, n_positions: int):
         ck, cv = self._f(ck), self._f(cv)
         check(lib().cmld_engine_seed_layer(self._h, layer, _np_ptr(ck), _np_ptr(cv), n_positions))

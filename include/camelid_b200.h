@@ -201,6 +201,20 @@ CMLD_API int32_t cmld_engine_prefill_from(cmld_engine *e, const float *embedding
 CMLD_API int32_t cmld_engine_verify_batch(cmld_engine *e, const float *embeddings, const float *cos_all,
                                           const float *sin_all, int64_t base_position, int32_t k, float scale,
                                           uint32_t *tokens_out);
+/* verify_tree (src/cuda_resident.rs:22944): runs the n nodes of a draft tree (breadth-first order,
+ * n <= CMLD_TREE_MAX_NODES = TREE_MAX_NODES of src/inference/spec_tree.rs:27) through the model in one
+ * batched pass.  embeddings[n][hidden]; cos_all/sin_all[n][rope_dim/2] are the nodes' own RoPE rows
+ * (position base + depth); node_kvslot[i] must be base_position + i; ancestor_bits[n][words] is the
+ * causal tree mask (bit j of node i = node j is an ancestor of i; words = 1).  tokens_out[i] = the
+ * greedy token after node i along its path: what a linear decode of that path yields.  The nodes'
+ * K/V rows stay at base_position + i; cmld_engine_compact_tree_kv_path then moves the accepted
+ * path's rows to base_position + rank (compact_tree_kv_path, :23071). */
+#define CMLD_TREE_MAX_NODES 16
+CMLD_API int32_t cmld_engine_verify_tree(cmld_engine *e, const float *embeddings, const float *cos_all, const float *sin_all,
+                                         const int32_t *node_kvslot, const uint32_t *ancestor_bits, int32_t words,
+                                         int64_t base_position, int32_t n, float scale, uint32_t *tokens_out);
+CMLD_API int32_t cmld_engine_compact_tree_kv_path(cmld_engine *e, const int32_t *path, int32_t len, int64_t base_position);
+
 /* seed_layer / read_kv_layer (src/cuda_resident.rs:17355, :17448): K and V of one layer as
  * f32 [kv_head][n_positions][head_dim] (values are f16-exact), sequence slot 0. */
 CMLD_API int32_t cmld_engine_seed_layer(cmld_engine *e, int32_t layer, const float *ck, const float *cv,

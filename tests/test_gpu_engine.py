@@ -308,3 +308,56 @@ def test_prefill_chunk_of_32_rows_leaves_the_serial_kv(cm, orc):
         rk, rv = ref.read_kv_layer(layer, len(prompt))
         k0, v0 = eng.read_kv_layer(layer, len(prompt))
         assert np.array_equal(k0, rk) and np.array_equal(v0, rv), layer
+
+
+def test_verify_tree_predicts_what_a_linear_decode_of_each_path_predicts(cm, orc):
+    """verify_tree (src/cuda_resident.rs:22944): every node of a draft tree in one batched pass.  The token predicted
+    after node i equals the CPU checker's greedy token after prompt + the tokens on the path to node i (lossless
+    speculation, :4343-4352); after compact_tree_kv_path the cache is that of a linear decode of the accepted path,
+    so decoding on gives the checker's tokens."""
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("tiny", max_pos=96)
+    pair = ModelPair(cfg, "q4_k_m", seed=41)
+    eng, ref = pair.engine, pair.oracle
+    prompt = orc.synth_tokens(41, 5, 7, cfg.vocab)
+    base = len(prompt)
+    root = eng.prefill_tokens(0, prompt, 0)
+    truth, _ = ref.generate(prompt, 8)  # the greedy continuation: truth[0] is the root token
+    assert root == truth[0]
+    # breadth-first tree: node 0 = root; one branch follows the greedy continuation for three steps, others do not
+    parents = [-1, 0, 0, 0, 1, 1, 2, 4, 4, 7, 7, 9]
+    rng = np.random.default_rng(9)
+    tokens = [int(root)] + [int(t) for t in rng.integers(0, cfg.vocab, len(parents) - 1)]
+    tokens[2] = int(truth[1])           # child of the root on the greedy path
+    tokens[6] = int(truth[2])           # its child
+    depth = [0] * len(parents)
+    for i, par in enumerate(parents):
+        if par >= 0:
+            depth[i] = depth[par] + 1
+    emb = np.stack([ref.embedding(t) for t in tokens])
+    cs = [pair.rope(base + d) for d in depth]
+    got = eng.verify_tree(emb, np.stack([c for c, _ in cs]), np.stack([s for _, s in cs]), parents, base, pair.scale)
+    for i in range(len(parents)):
+        path, j = [], i
+        while j >= 0:
+            path.append(tokens[j])
+            j = parents[j]
+        seq = np.concatenate([prompt, np.array(path[::-1], np.int32)])
+        want, _ = ref.generate(seq, 1)
+        assert got[i] == want[0], (i, got[i], want[0])
+    # accept the longest path whose tokens are the model's own predictions: 0 -> 2 -> 6
+    accepted = [0]
+    while True:
+        nxt = [j for j, par in enumerate(parents) if par == accepted[-1] and tokens[j] == got[accepted[-1]]]
+        if not nxt:
+            break
+        accepted.append(nxt[0])
+    assert accepted == [0, 2, 6]
+    eng.compact_tree_kv_path(accepted, base)
+    n_acc = len(accepted)
+    cont = eng.decode_greedy([0], [int(got[accepted[-1]])], [base + n_acc], 4)[:, 0]
+    assert int(got[accepted[-1]]) == truth[n_acc] and np.array_equal(cont, truth[n_acc + 1: n_acc + 5]), (cont, truth)
+    # argument checks: a node may not name a later node, rows must be base + index
+    with pytest.raises(cm.CmldError):
+        eng.verify_tree(emb[:2], np.stack([cs[0][0], cs[1][0]]), np.stack([cs[0][1], cs[1][1]]), [-1, 0], cfg.max_pos - 1, pair.scale)
