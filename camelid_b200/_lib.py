@@ -99,6 +99,11 @@ def lib():
         "cmld_engine_n_layers": (i32, [vp]),
         "cmld_engine_rope_row": (i32, [vp, i64, vp, vp]),
         "cmld_engine_set_rope_frequencies": (i32, [vp, vp, i32]),
+        "cmld_engine_forward_token_sample": (i32, [vp, vp, vp, vp, i64, f32, f32, f32, C.c_uint64, vp, vp]),
+        "cmld_sample_gumbel": (i32, [vp, i32, f32, C.c_uint64, vp]),
+        "cmld_sample_gumbel_filtered": (i32, [vp, i32, f32, f32, C.c_uint64, vp]),
+        "cmld_sample_min_p_mask": (i32, [vp, i32, f32, vp]),
+        "cmld_sample_uniforms": (i32, [C.c_uint64, i32, vp]),
         "cmld_engine_verify_tree": (i32, [vp, vp, vp, vp, vp, vp, i32, i64, i32, f32, vp]),
         "cmld_engine_compact_tree_kv_path": (i32, [vp, vp, i32, i64]),
         "cmld_engine_forward_token": (i32, [vp, vp, vp, vp, i64, f32, i32, P(C.c_uint32)]),

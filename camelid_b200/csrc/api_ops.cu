@@ -325,6 +325,46 @@ int32_t cmld_peer_wait_selftest(int32_t timeout_ms) {
   return fail(CMLD_ERR_STATE, "the wait did not report a timeout (status %d)", st);
 }
 
+// Sampling over a logits row on the device (sample_gumbel, sample_gumbel_filtered, sample_min_p_mask and the uniform
+// generator of src/cuda_resident/sampling.cuh), results returned to the host.
+static int32_t sample_fetch(uint32_t *dev, uint32_t *host, const char *what) {
+  CMLD_TRY(sync_ok(what));
+  CMLD_CUDA(cudaMemcpy(host, dev, 4, cudaMemcpyDeviceToHost));
+  return CMLD_OK;
+}
+int32_t cmld_sample_gumbel(const float *logits_dev, int32_t n, float inv_temp, uint64_t seed, uint32_t *token_out) {
+  if (!logits_dev || !token_out || n < 1) return fail(CMLD_ERR_INVALID, "sample_gumbel: bad arguments");
+  uint32_t *d = reinterpret_cast<uint32_t *>(op_scratch(1));
+  if (!d) return fail(CMLD_ERR_OOM, "sample_gumbel: no scratch");
+  CMLD_TRY(launch_sample_gumbel(logits_dev, n, inv_temp, seed, d, nullptr));
+  return sample_fetch(d, token_out, "sample_gumbel");
+}
+int32_t cmld_sample_gumbel_filtered(const float *logits_dev, int32_t n, float temperature, float min_p, uint64_t seed, uint32_t *token_out) {
+  if (!logits_dev || !token_out || n < 1) return fail(CMLD_ERR_INVALID, "sample_gumbel_filtered: bad arguments");
+  uint32_t *d = reinterpret_cast<uint32_t *>(op_scratch(1));
+  if (!d) return fail(CMLD_ERR_OOM, "sample_gumbel_filtered: no scratch");
+  CMLD_TRY(launch_sample_gumbel_filtered(logits_dev, n, temperature, min_p, seed, d, nullptr));
+  return sample_fetch(d, token_out, "sample_gumbel_filtered");
+}
+int32_t cmld_sample_min_p_mask(const float *logits_dev, int32_t n, float min_p, int32_t *mask_out) {
+  if (!logits_dev || !mask_out || n < 1) return fail(CMLD_ERR_INVALID, "sample_min_p_mask: bad arguments");
+  int32_t *d = reinterpret_cast<int32_t *>(op_scratch(n));
+  if (!d) return fail(CMLD_ERR_OOM, "sample_min_p_mask: no scratch");
+  CMLD_TRY(launch_min_p_mask(logits_dev, n, min_p, d, nullptr));
+  CMLD_TRY(sync_ok("sample_min_p_mask"));
+  CMLD_CUDA(cudaMemcpy(mask_out, d, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  return CMLD_OK;
+}
+int32_t cmld_sample_uniforms(uint64_t seed, int32_t n, float *out) {
+  if (!out || n < 1) return fail(CMLD_ERR_INVALID, "sample_uniforms: bad arguments");
+  float *d = op_scratch(n);
+  if (!d) return fail(CMLD_ERR_OOM, "sample_uniforms: no scratch");
+  CMLD_TRY(launch_sample_uniforms(seed, n, d, nullptr));
+  CMLD_TRY(sync_ok("sample_uniforms"));
+  CMLD_CUDA(cudaMemcpy(out, d, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  return CMLD_OK;
+}
+
 int32_t cmld_gemv_select_kernel(int32_t choice) {
   if (choice < 0 || choice > 63) return fail(CMLD_ERR_INVALID, "kernel choice %d", choice);
   g_gemv_kernel_choice = choice & 1;

@@ -351,6 +351,13 @@ int32_t comm_allreduce_sum_f32(void *comm, float *buf, int64_t count, cudaStream
 int32_t comm_allreduce_max_u64(void *comm, unsigned long long *buf, int64_t count, cudaStream_t s);
 int32_t comm_allgather_f32(void *comm, const float *send, float *recv, int64_t count_per_rank, cudaStream_t s);
 
+// sample.cu: temperature / min-p sampling over a resident logits row
+int32_t launch_sample_gumbel(const float *logits, int32_t n, float inv_temp, uint64_t seed, uint32_t *out_dev, cudaStream_t s);
+int32_t launch_sample_gumbel_filtered(const float *logits, int32_t n, float temperature, float min_p, uint64_t seed, uint32_t *out_dev,
+                                      cudaStream_t s);
+int32_t launch_min_p_mask(const float *logits, int32_t n, float min_p, int32_t *mask_dev, cudaStream_t s);
+int32_t launch_sample_uniforms(uint64_t seed, int32_t n, float *out_dev, cudaStream_t s);
+
 // ops.cu: helpers of the sharded step
 int32_t launch_residual_add(float *h, const float *delta, int64_t n, bool pdl, cudaStream_t s);
 int32_t launch_argmax_finish(const unsigned long long *keys, int32_t batch, int32_t *out_idx, int32_t *next_tokens,

@@ -1559,6 +1559,34 @@ int32_t cmld_engine_forward_token(cmld_engine *e, const float *embedding, const 
   return CMLD_OK;
 }
 
+// forward_token_sample / forward_token_sample_min_p (src/cuda_resident.rs:20163, :20197): the full forward, then the
+// draw over the resident logits.  min_p <= 0 selects the unfiltered draw (inv_temp = 1 / temperature).  With the
+// filter, *token_out = 0xffffffff means "sample this row on the CPU": logits_out (if given) then holds the row.
+int32_t cmld_engine_forward_token_sample(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
+                                         int64_t position, float scale, float temperature, float min_p, uint64_t seed,
+                                         uint32_t *token_out, float *logits_out) {
+  CMLD_ENGINE_ENTER(e);
+  if (!token_out) return fail(CMLD_ERR_INVALID, "token_out is null");
+  if (!(temperature > 0.0f) || !std::isfinite(temperature)) return fail(CMLD_ERR_INVALID, "temperature must be a finite positive number");
+  if (min_p > 0.0f && !(min_p <= 1.0f)) return fail(CMLD_ERR_INVALID, "min_p must lie in (0, 1]");
+  if (e->tp > 1) return fail(CMLD_ERR_UNSUPPORTED, "sampling on a tensor-parallel engine is not supported");
+  CMLD_TRY(forward_embedding_rows(e, embedding, cosv, sinv, position, 1, scale, true, false, false));
+  uint32_t *d_tok = reinterpret_cast<uint32_t *>(e->out_idx);
+  if (min_p > 0.0f) CMLD_TRY(launch_sample_gumbel_filtered(e->logits, e->cfg.vocab, temperature, min_p, seed, d_tok, e->stream));
+  else CMLD_TRY(launch_sample_gumbel(e->logits, e->cfg.vocab, 1.0f / temperature, seed, d_tok, e->stream));
+  e->launches += 1;
+  uint32_t tok = 0;
+  CMLD_TRY(settle(e));
+  CMLD_CUDA(cudaMemcpyAsync(&tok, d_tok, 4, cudaMemcpyDeviceToHost, e->stream));
+  CMLD_TRY(finish(e, "forward_token_sample"));
+  *token_out = tok;
+  if (tok == 0xffffffffu && logits_out) {
+    CMLD_CUDA(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->cfg.vocab * 4, cudaMemcpyDeviceToHost, e->stream));
+    CMLD_TRY(finish(e, "forward_token_sample"));
+  }
+  return CMLD_OK;
+}
+
 int32_t cmld_engine_forward_token_logits(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
                                          int64_t position, float scale, float *logits_out) {
   CMLD_ENGINE_ENTER(e);

@@ -330,6 +330,18 @@ class ResidentDecode:
                                               int(compute_logits), C.byref(tok)))
         return int(tok.value) if compute_logits else None
 
+    def forward_token_sample(self, embedding, cos, sin, position: int, scale: float, temperature: float, seed: int, min_p: float = 0.0):
+        """Forward, then a temperature draw on the device (``forward_token_sample``; with ``min_p`` the filtered draw).
+        Returns the token, or (None, logits) when the filter hands the row back to the CPU."""
+        e, c, s = self._f(embedding), self._f(cos), self._f(sin)
+        tok = C.c_uint32(0)
+        logits = np.empty(self.cfg.vocab, np.float32) if min_p > 0 else None
+        check(lib().cmld_engine_forward_token_sample(self._h, _np_ptr(e), _np_ptr(c), _np_ptr(s), position, scale, temperature, min_p,
+                                                     seed, C.byref(tok), _np_ptr(logits) if logits is not None else None))
+        if tok.value == 0xFFFFFFFF:
+            return None, logits
+        return int(tok.value)
+
     def forward_token_logits(self, embedding, cos, sin, position: int, scale: float) -> np.ndarray:
         e, c, s = self._f(embedding), self._f(cos), self._f(sin)
         out = np.empty(self.cfg.vocab, np.float32)

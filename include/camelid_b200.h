@@ -177,6 +177,16 @@ CMLD_API int32_t cmld_engine_rope_row(const cmld_engine *e, int64_t position, fl
 CMLD_API int32_t cmld_engine_forward_token(cmld_engine *e, const float *embedding, const float *cosv,
                                            const float *sinv, int64_t position, float scale,
                                            int32_t compute_logits, uint32_t *token_out);
+/* forward_token_sample / forward_token_sample_min_p (src/cuda_resident.rs:20163, :20197): the full forward, then a
+ * temperature draw over the resident logits by the Gumbel-max trick, the per-token uniforms a splitmix64 hash of
+ * (seed, index) (src/cuda_resident/sampling.cuh).  min_p <= 0: unfiltered draw at inv_temp = 1 / temperature.
+ * min_p in (0, 1]: min-p filtering precedes temperature; *token_out = 0xffffffff then means the filter could
+ * not be decided on the device (a probability ratio within 64 ulp of the cutoff, or a non-finite logit) and the
+ * caller samples on the CPU from logits_out[vocab], which is filled in that case if not NULL. */
+CMLD_API int32_t cmld_engine_forward_token_sample(cmld_engine *e, const float *embedding, const float *cosv, const float *sinv,
+                                                  int64_t position, float scale, float temperature, float min_p, uint64_t seed,
+                                                  uint32_t *token_out, float *logits_out);
+
 /* forward_token_logits (src/cuda_resident.rs:20024): logits_out[vocab]. */
 CMLD_API int32_t cmld_engine_forward_token_logits(cmld_engine *e, const float *embedding, const float *cosv,
                                                   const float *sinv, int64_t position, float scale,
@@ -287,6 +297,15 @@ CMLD_API int32_t cmld_act_export(int32_t act_kind, const void *act_dev, int64_t 
  * src/inference.rs:26166, src/diffusion_gemma/refmath.rs:504, src/inference.rs:25535). */
 CMLD_API int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, float *y_dev,
                            const float *residual_dev);
+/* The sampling kernels as operators over a device logits row of n values (src/cuda_resident/sampling.cuh:
+ * sample_gumbel, sample_gumbel_filtered, sample_min_p_mask: -1 undecided / 0 drop / 1 keep per token, and the
+ * uniform generator).  Results come back to the host. */
+CMLD_API int32_t cmld_sample_gumbel(const float *logits_dev, int32_t n, float inv_temp, uint64_t seed, uint32_t *token_out);
+CMLD_API int32_t cmld_sample_gumbel_filtered(const float *logits_dev, int32_t n, float temperature, float min_p, uint64_t seed,
+                                             uint32_t *token_out);
+CMLD_API int32_t cmld_sample_min_p_mask(const float *logits_dev, int32_t n, float min_p, int32_t *mask_out);
+CMLD_API int32_t cmld_sample_uniforms(uint64_t seed, int32_t n, float *out);
+
 /* Which matvec kernel cmld_gemv / cmld_gemv_time use: bit 0 clear = the staged (bulk-copy
  * pipelined) kernel whenever it takes the shape, bit 0 set = the generic kernel only (both give
  * the CPU dot's bits); bit 1 set = cmld_gemv_time chains its launches with programmatic dependent

@@ -878,6 +878,82 @@ ORACLE_API int orc_softmax_top_k(const float *logits, int32_t n, int32_t k, int3
   return kk;
 }
 
+/* ------------------------------------------------------------------ sampling (src/cuda_resident/sampling.cuh) */
+
+/* sampling_uniform_from_u24 + splitmix_uniform: 24 hashed bits of (seed, index) as a float in (0, 1). */
+ORACLE_API float orc_sample_uniform(uint64_t seed, uint32_t idx) {
+  uint64_t z = seed + 0x9E3779B97F4A7C15ULL * (uint64_t)(idx + 1u);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+  z = z ^ (z >> 31);
+  uint32_t m = (uint32_t)(z >> 40);
+  float u = ((float)m + 0.5f) / 16777216.0f;
+  return u < 0.999999940395355224609375f ? u : 0.999999940395355224609375f;
+}
+
+/* How many of the 2^24 mantissas the clamp of sampling_uniform_from_u24 changes (the reference's host test expects
+ * exactly one: "uniform 16777216 changed 1", src/inference/cuda_min_p_host_tests.rs:228). */
+ORACLE_API int32_t orc_sample_uniform_clamped_count(void) {
+  int32_t changed = 0;
+  for (uint32_t m = 0; m < (1u << 24); ++m) {
+    float u = ((float)m + 0.5f) / 16777216.0f;
+    if (u >= 1.0f || u != (u < 0.999999940395355224609375f ? u : 0.999999940395355224609375f)) ++changed;
+  }
+  return changed;
+}
+
+/* min_p_candidate: 1 keep, 0 drop, -1 undecided. */
+ORACLE_API int32_t orc_min_p_candidate(float logit, float max_logit, float min_p, int32_t n) {
+  if (n <= 0 || !isfinite(logit) || !isfinite(max_logit) || !isfinite(min_p) || min_p <= 0.0f || min_p >= 1.0f ||
+      min_p < (4.0f * 1.1754943508222875e-38f) * (float)n)
+    return -1;
+  float ratio = expf(logit - max_logit);
+  float margin = (64.0f * 1.1920928955078125e-7f) * min_p;
+  if (!isfinite(ratio) || fabsf(ratio - min_p) <= margin) return -1;
+  return ratio > min_p ? 1 : 0;
+}
+
+/* sample_gumbel: argmax_i(logit_i * inv_temp - log(-log(u_i))), lower index on ties.  scores (optional) receives every
+ * token's score, for tolerance checks of a device draw. */
+ORACLE_API int32_t orc_sample_gumbel(const float *logits, int32_t n, float inv_temp, uint64_t seed, float *scores) {
+  float best = -3.4e38f;
+  int32_t besti = 0;
+  for (int32_t i = 0; i < n; ++i) {
+    float g = -logf(-logf(orc_sample_uniform(seed, (uint32_t)i)));
+    float v = logits[i] * inv_temp + g;
+    if (scores) scores[i] = v;
+    if (v > best) { best = v; besti = i; }
+  }
+  return besti;
+}
+
+/* sample_gumbel_filtered: min-p filter, then the draw over the kept tokens; -1 = hand the row to the CPU sampler. */
+ORACLE_API int32_t orc_sample_gumbel_filtered(const float *logits, int32_t n, float temperature, float min_p, uint64_t seed,
+                                              float *scores) {
+  float maximum = -INFINITY;
+  int bad = n <= 0;
+  for (int32_t i = 0; i < n; ++i) {
+    if (!isfinite(logits[i])) bad = 1;
+    else if (logits[i] > maximum) maximum = logits[i];
+  }
+  if (!isfinite(temperature) || temperature <= 0.0f) bad = 1;
+  float best = -INFINITY;
+  int32_t besti = 0x7fffffff;
+  for (int32_t i = 0; i < n; ++i) {
+    if (scores) scores[i] = -INFINITY;
+    int32_t keep = orc_min_p_candidate(logits[i], maximum, min_p, n);
+    if (keep < 0) bad = 1;
+    if (keep == 1) {
+      float g = -logf(-logf(orc_sample_uniform(seed, (uint32_t)i)));
+      float score = (logits[i] / temperature) - (maximum / temperature) + g;
+      if (!isfinite(score)) bad = 1;
+      if (scores) scores[i] = score;
+      if (score > best || (score == best && i < besti)) { best = score; besti = i; }
+    }
+  }
+  return (bad || besti == 0x7fffffff) ? -1 : besti;
+}
+
 /* ------------------------------------------------------------------ model forward */
 
 typedef struct {

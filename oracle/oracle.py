@@ -76,6 +76,11 @@ def lib(path: str | os.PathLike | None = None):
         "orc_embedding": (C.c_int, [vp, i32, vp]),
         "orc_model_read_kv": (C.c_int, [vp, i32, i64, vp, vp]),
         "orc_model_write_kv": (C.c_int, [vp, i32, i64, vp, vp]),
+        "orc_sample_uniform": (f32, [C.c_uint64, C.c_uint32]),
+        "orc_sample_uniform_clamped_count": (i32, []),
+        "orc_min_p_candidate": (i32, [f32, f32, f32, i32]),
+        "orc_sample_gumbel": (i32, [vp, i32, f32, C.c_uint64, vp]),
+        "orc_sample_gumbel_filtered": (i32, [vp, i32, f32, f32, C.c_uint64, vp]),
         "orc_model_set_rope_frequencies": (C.c_int, [vp, vp, i32]),
         "orc_rope_llama3_frequency": (f32, [f32, f32, f32, f32, f32]),
         "orc_forward": (C.c_int, [vp, vp, i64, vp, vp, vp]),
@@ -217,6 +222,20 @@ def silu_mul(g, u) -> np.ndarray:
 def argmax(x) -> int:
     x = _f32(x)
     return int(lib().orc_argmax(_p(x), x.size))
+
+
+def sample_gumbel(logits, inv_temp: float, seed: int):
+    """Index and per-token scores of the temperature draw (sample_gumbel)."""
+    x = _f32(logits)
+    scores = np.empty(x.size, np.float32)
+    return int(lib().orc_sample_gumbel(_p(x), x.size, inv_temp, seed, _p(scores))), scores
+
+
+def sample_gumbel_filtered(logits, temperature: float, min_p: float, seed: int):
+    """Index (-1 = hand the row to the CPU sampler) and scores (-inf where filtered) of the min-p draw."""
+    x = _f32(logits)
+    scores = np.empty(x.size, np.float32)
+    return int(lib().orc_sample_gumbel_filtered(_p(x), x.size, temperature, min_p, seed, _p(scores))), scores
 
 
 def softmax_top_k(logits, k: int):

@@ -361,3 +361,30 @@ def test_verify_tree_predicts_what_a_linear_decode_of_each_path_predicts(cm, orc
     # argument checks: a node may not name a later node, rows must be base + index
     with pytest.raises(cm.CmldError):
         eng.verify_tree(emb[:2], np.stack([cs[0][0], cs[1][0]]), np.stack([cs[0][1], cs[1][1]]), [-1, 0], cfg.max_pos - 1, pair.scale)
+
+
+def test_forward_token_sample_draws_from_the_steps_own_logits(cm, orc):
+    """forward_token_sample (src/cuda_resident.rs:20163): the token drawn on the device is the checker's draw over the
+    logits of the very same forward pass (bit-identical to the CPU path's), with and without the min-p filter."""
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("tiny", max_pos=64)
+    pair = ModelPair(cfg, "q4_k_m", seed=3)
+    eng, ref = pair.engine, pair.oracle
+    tok = 5
+    for pos in range(6):
+        emb = ref.embedding(tok)
+        c, s = pair.rope(pos)
+        ref_logits, _, _ = ref.forward(emb, pos)
+        if pos % 2 == 0:
+            got = eng.forward_token_sample(emb, c, s, pos, pair.scale, 0.9, 1000 + pos)
+            want, scores = orc.sample_gumbel(ref_logits, np.float32(1.0) / np.float32(0.9), 1000 + pos)
+        else:
+            got = eng.forward_token_sample(emb, c, s, pos, pair.scale, 0.9, 1000 + pos, min_p=0.05)
+            want, scores = orc.sample_gumbel_filtered(ref_logits, 0.9, 0.05, 1000 + pos)
+        if isinstance(got, tuple):  # the filter handed the row back: the logits come with it, bit for bit
+            assert got[0] is None and np.array_equal(got[1].view(np.uint32), ref_logits.view(np.uint32))
+            got = want if want >= 0 else int(np.argmax(ref_logits))
+        else:
+            assert want >= 0 and (got == want or abs(float(scores[got]) - float(scores[want])) <= 1e-5 * max(1.0, abs(float(scores[want]))))
+        tok = int(got)

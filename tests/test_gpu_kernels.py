@@ -368,3 +368,62 @@ def test_attention_reference_order_is_bit_identical(cm, orc, n_heads, n_kv, hd, 
         ref = orc.attention_head(q[h], kf[h // g, :n_pos], vf[h // g, :n_pos], n_pos, hd, scale)
         bad = np.nonzero(out[h].view(np.uint32) != ref.view(np.uint32))[0]
         assert bad.size == 0, (h, bad[:4], out[h][bad[:4]], ref[bad[:4]])
+
+
+# ---- on-device sampling (src/cuda_resident/sampling.cuh): the uniforms are integer arithmetic and must equal the
+# checker's bit for bit; the Gumbel scores go through the device's logf / expf, so a draw may differ from the
+# checker's only where the two best scores lie within 1e-5 (relative) of each other — the tolerance of this test.
+def _draw_ok(tok, ref_tok, scores):
+    if tok == ref_tok:
+        return True
+    best = float(scores[ref_tok])
+    return abs(float(scores[tok]) - best) <= 1e-5 * max(1.0, abs(best))
+
+
+def test_sampling_kernels_match_the_checker(cm, orc):
+    from camelid_b200.engine import DeviceBuffer
+    from camelid_b200._lib import check
+    import ctypes as C
+
+    n = 32000
+    for seed in (0, 1, 0x915E55A9DA3C1891):
+        got = np.empty(4096, np.float32)
+        check(cm.lib().cmld_sample_uniforms(seed, 4096, got.ctypes.data_as(C.c_void_p)))
+        ref = np.array([orc.lib().orc_sample_uniform(seed, i) for i in range(4096)], np.float32)
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+    rng = np.random.default_rng(5)
+    logits = (rng.standard_normal(n) * 4).astype(np.float32)
+    dev = DeviceBuffer.from_numpy(logits)
+    tok = C.c_uint32(0)
+    same = 0
+    for seed in range(60):
+        for inv_temp in (1.0, 1.0 / 0.7):
+            check(cm.lib().cmld_sample_gumbel(dev.ptr, n, inv_temp, seed, C.byref(tok)))
+            ref_tok, scores = orc.sample_gumbel(logits, inv_temp, seed)
+            assert _draw_ok(tok.value, ref_tok, scores), (seed, inv_temp, tok.value, ref_tok)
+            same += int(tok.value == ref_tok)
+    assert same >= 115  # practically always the very same token
+    check(cm.lib().cmld_sample_gumbel(dev.ptr, n, 1.0e6, 3, C.byref(tok)))
+    assert tok.value == int(np.argmax(logits))  # a cold temperature is the greedy argmax
+    # min-p mask and filtered draw
+    mask = np.empty(n, np.int32)
+    for min_p in (0.02, 0.2):
+        check(cm.lib().cmld_sample_min_p_mask(dev.ptr, n, min_p, mask.ctypes.data_as(C.c_void_p)))
+        mx = float(logits.max())
+        ref_mask = np.array([orc.lib().orc_min_p_candidate(float(x), mx, min_p, n) for x in logits], np.int32)
+        diff = np.nonzero(mask != ref_mask)[0]
+        ratio = np.exp(logits[diff].astype(np.float64) - mx)
+        assert np.all(np.abs(ratio - min_p) <= 2 * 64 * 1.1920929e-7 * min_p), (min_p, diff[:5])
+        for seed in range(20):
+            check(cm.lib().cmld_sample_gumbel_filtered(dev.ptr, n, 0.8, min_p, seed, C.byref(tok)))
+            ref_tok, scores = orc.sample_gumbel_filtered(logits, 0.8, min_p, seed)
+            if tok.value == 0xFFFFFFFF or ref_tok < 0:
+                # a token within the margin of the cutoff sends the row to the CPU on one side or both
+                assert (mask == -1).any() or (ref_mask == -1).any()
+                continue
+            assert _draw_ok(tok.value, ref_tok, scores), (min_p, seed, tok.value, ref_tok)
+    # a non-finite logit hands the row back
+    bad = logits.copy()
+    bad[17] = np.inf
+    check(cm.lib().cmld_sample_gumbel_filtered(DeviceBuffer.from_numpy(bad).ptr, n, 0.8, 0.1, 1, C.byref(tok)))
+    assert tok.value == 0xFFFFFFFF

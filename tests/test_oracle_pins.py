@@ -298,3 +298,37 @@ def test_kv_prefix_written_to_the_model_reads_back_rounded_to_f16():
     assert np.array_equal(rv, cv.astype(np.float16).astype(np.float32))
     zk, _ = m.read_kv_layer(0, 5)
     assert not zk.any()
+
+
+def test_sampling_math_of_the_checker():
+    """The checker's restatement of src/cuda_resident/sampling.cuh: the uniform's clamp changes exactly one of the 2^24
+    mantissas (the reference's host test prints "uniform 16777216 changed 1", src/inference/cuda_min_p_host_tests.rs:228),
+    uniforms lie in (0, 1), a cold temperature collapses the Gumbel draw to the greedy argmax, and the min-p classifier
+    keeps exactly the tokens whose probability ratio to the best token exceeds min_p wherever it decides."""
+    from oracle import oracle as orc
+
+    assert orc.lib().orc_sample_uniform_clamped_count() == 1
+    us = np.array([orc.lib().orc_sample_uniform(12345, i) for i in range(2000)], np.float32)
+    assert us.min() > 0.0 and us.max() < 1.0 and abs(float(us.mean()) - 0.5) < 0.03
+    assert len(set(us.view(np.uint32).tolist())) > 1990
+    rng = np.random.default_rng(2)
+    logits = (rng.standard_normal(5000) * 3).astype(np.float32)
+    idx, _ = orc.sample_gumbel(logits, 1.0e6, 7)
+    assert idx == int(np.argmax(logits))
+    draws = [orc.sample_gumbel(logits, 1.0, seed)[0] for seed in range(200)]
+    assert len(set(draws)) > 20  # a warm temperature does spread the draws
+    mx = float(logits.max())
+    decided = 0
+    for i in range(0, 5000, 7):
+        k = orc.lib().orc_min_p_candidate(float(logits[i]), mx, 0.05, 5000)
+        ratio = math.exp(float(logits[i]) - mx)
+        if k >= 0:
+            decided += 1
+            assert k == (1 if ratio > 0.05 else 0)
+        else:
+            assert abs(ratio - 0.05) < 1e-5
+    assert decided > 700
+    assert orc.lib().orc_min_p_candidate(1.0, 2.0, 1.0, 10) == -1 and orc.lib().orc_min_p_candidate(float("nan"), 2.0, 0.1, 10) == -1
+    tok, scores = orc.sample_gumbel_filtered(logits, 0.8, 0.05, 3)
+    kept = np.isfinite(scores)
+    assert tok >= 0 and kept[tok] and scores[tok] == scores[kept].max() and 1 <= kept.sum() < 5000
