@@ -653,7 +653,7 @@ int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local
                         int n_assign, cudaStream_t s);
 int32_t moe_expert_gemv_ordered(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
                                 const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
-                                int n_assign, cudaStream_t s);
+                                int n_assign, cudaStream_t s, const Weight *slab2 = nullptr, float *y2 = nullptr);
 int32_t moe_combine(float *h, const float *down, const float *sel_w, const int32_t *sel_idx, int hidden, int k, int batch,
                     int first_expert, int expert_step, bool add_residual, cudaStream_t s);
 
@@ -715,13 +715,20 @@ static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
   }
   const int k = c.n_experts_used, na = B * k;
   const int n_local = c.n_experts / ep_size(e), first = ep_size(e) > 1 ? c.ep_rank : 0, step = ep_size(e);
-  auto expert_gemv = fast ? moe_expert_gemv : moe_expert_gemv_ordered;
   CMLD_TRY(moe_route(e->normed, L.router, c.hidden, c.n_experts, k, B, e->moe_sel_idx, e->moe_sel_w, e->moe_counts,
                      e->moe_lists, e->stream, e->moe_pos));
-  CMLD_TRY(expert_gemv(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts,
-                       e->moe_lists, na, e->stream));
-  CMLD_TRY(expert_gemv(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts,
-                       e->moe_lists, na, e->stream));
+  const bool pair = !fast && L.exps[0].qt == L.exps[1].qt && L.exps[0].stride == L.exps[1].stride;
+  if (pair) {
+    // gate and up in one launch: the rows of the few active experts are too few to fill the machine on their own
+    CMLD_TRY(moe_expert_gemv_ordered(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts,
+                                     e->moe_lists, na, e->stream, &L.exps[1], e->moe_u));
+  } else if (fast) {
+    CMLD_TRY(moe_expert_gemv(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts, e->moe_lists, na, e->stream));
+    CMLD_TRY(moe_expert_gemv(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts, e->moe_lists, na, e->stream));
+  } else {
+    CMLD_TRY(moe_expert_gemv_ordered(L.exps[0], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_g, e->moe_counts, e->moe_lists, na, e->stream));
+    CMLD_TRY(moe_expert_gemv_ordered(L.exps[1], c.ffn_dim, n_local, first, step, e->normed, c.hidden, k, e->moe_u, e->moe_counts, e->moe_lists, na, e->stream));
+  }
   NormQuantArgs a{};
   a.x = e->moe_g;
   a.x2 = e->moe_u;
@@ -729,11 +736,11 @@ static int32_t moe_ffn_step(cmld_engine *e, LayerW &L, int32_t B) {
   a.batch = na;
   a.out = e->moe_act;
   CMLD_TRY(launch_norm_quant(a, e->stream));
-  CMLD_TRY(expert_gemv(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts,
-                       e->moe_lists, na, e->stream));
+  if (fast) CMLD_TRY(moe_expert_gemv(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts, e->moe_lists, na, e->stream));
+  else CMLD_TRY(moe_expert_gemv_ordered(L.exps[2], c.hidden, n_local, first, step, e->moe_act, c.ffn_dim, 1, e->moe_down, e->moe_counts, e->moe_lists, na, e->stream));
   CMLD_TRY(moe_combine(e->h, e->moe_down, e->moe_sel_w, e->moe_sel_idx, c.hidden, k, B, first, step,
                        e->ep == 1 || e->shard_rank == 0, e->stream));
-  e->launches += 7;
+  e->launches += pair ? 6 : 7;
   if (e->ep > 1) CMLD_TRY(reduce_hidden(e, B));
   return CMLD_OK;
 }

@@ -36,25 +36,40 @@ __device__ __forceinline__ int total_key(float f) {
 __global__ void __launch_bounds__(256) moe_route_kernel(const float *__restrict__ x, const float *__restrict__ router, int hidden,
                                                         int n_exp, int k, int32_t *__restrict__ sel_idx, float *__restrict__ sel_w) {
   __shared__ float logits[kMaxExperts];
+  __shared__ __align__(16) float prod[8][1024];
   const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float *xr = x + (int64_t)b * hidden;
-  (void)lane;
-  (void)warp;
   // logits_e = ((0 + x0*r0) + x1*r1) + ...: the CPU's one-accumulator dot (dot_product_row,
-  // src/inference.rs:29382-29409), one thread per expert
-  if ((int)threadIdx.x < n_exp) {
-    const float *r = router + (int64_t)threadIdx.x * hidden;
+  // src/inference.rs:29382-29409).  One warp per expert: the products of a 1024-value chunk are formed by all lanes
+  // from coalesced loads (a product does not depend on the order), then lane 0 adds them in index order.
+  for (int e = warp; e < n_exp; e += 8) {
+    const float *r = router + (int64_t)e * hidden;
     float s = 0.0f;
-    int i = 0;
-    for (; i + 4 <= hidden; i += 4) {
-      const float4 xv = __ldg(reinterpret_cast<const float4 *>(xr + i)), rv = __ldg(reinterpret_cast<const float4 *>(r + i));
-      s = __fadd_rn(s, __fmul_rn(xv.x, rv.x));
-      s = __fadd_rn(s, __fmul_rn(xv.y, rv.y));
-      s = __fadd_rn(s, __fmul_rn(xv.z, rv.z));
-      s = __fadd_rn(s, __fmul_rn(xv.w, rv.w));
+    for (int i0 = 0; i0 < hidden; i0 += 1024) {
+      const int cnt = min(1024, hidden - i0);
+      for (int i = lane * 4; i < cnt; i += 128) {
+        if (i + 4 <= cnt && ((hidden & 3) == 0)) {
+          const float4 xv = __ldg(reinterpret_cast<const float4 *>(xr + i0 + i)), rv = __ldg(reinterpret_cast<const float4 *>(r + i0 + i));
+          *reinterpret_cast<float4 *>(&prod[warp][i]) = make_float4(__fmul_rn(xv.x, rv.x), __fmul_rn(xv.y, rv.y), __fmul_rn(xv.z, rv.z), __fmul_rn(xv.w, rv.w));
+        } else {
+          for (int j = i; j < min(i + 4, cnt); ++j) prod[warp][j] = __fmul_rn(xr[i0 + j], r[i0 + j]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        int i = 0;
+        for (; i + 4 <= cnt; i += 4) {
+          const float4 p4 = *reinterpret_cast<const float4 *>(&prod[warp][i]);
+          s = __fadd_rn(s, p4.x);
+          s = __fadd_rn(s, p4.y);
+          s = __fadd_rn(s, p4.z);
+          s = __fadd_rn(s, p4.w);
+        }
+        for (; i < cnt; ++i) s = __fadd_rn(s, prod[warp][i]);
+      }
+      __syncwarp();
     }
-    for (; i < hidden; ++i) s = __fadd_rn(s, __fmul_rn(xr[i], r[i]));
-    logits[threadIdx.x] = s;
+    if (lane == 0) logits[e] = s;
   }
   __syncthreads();
   if (threadIdx.x != 0) return;
@@ -220,6 +235,8 @@ struct MoeGemvArgs {
   const int32_t *counts, *lists;
   int32_t n_assign;
   int32_t first_expert, expert_step;  // experts held locally: first_expert + i*expert_step
+  const uint8_t *w2 = nullptr;        // ordered kernel: a second slab of the same shape and type (gate and up in one launch,
+  float *y2 = nullptr;                // grid.z = 2), results into y2
 };
 
 template <int QT>
@@ -384,101 +401,167 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_gemv_kernel(MoeGemvArgs a)
 // Q6KBlock::dequantize, src/tensor/mod.rs:5903-5924 and :6039-6066).  One thread owns one output row and walks
 // its weights in index order, dequantising on the way; up to kOrdCols assignments of the expert share the
 // dequantised weight (independent chains, which also cover each other's addition latency).
+// The weights reach a lane through a private ring in shared memory that the lane's warp fills with cp.async: the 32
+// rows of a warp are 32 separate byte ranges, and a load instruction whose lanes each touch another row costs 32
+// cache-line lookups, so the warp copies a superblock step of its 32 rows with lanes walking consecutive 16-byte
+// pieces (9 or 13 per row) and each lane then reads its own row from the ring (row pitch 144 / 208 bytes: an odd
+// number of 16-byte units, conflict-free).
 constexpr int kOrdCols = 4;
-constexpr int kOrdThreads = 128;
+constexpr int kOrdWarps = 2;   // small CTAs: the few rows of the active experts spread over all SMs
+constexpr int kOrdThreads = kOrdWarps * 32;
+constexpr int kOrdStages = 3;
 
-template <int QT>
-__global__ void __launch_bounds__(kOrdThreads) moe_gemv_ordered_kernel(MoeGemvArgs a) {
-  const int e_local = blockIdx.y;
-  const int e = a.first_expert + e_local * a.expert_step;
-  const int n = a.counts[e];
-  if (n == 0) return;
-  const int64_t r = (int64_t)blockIdx.x * kOrdThreads + threadIdx.x;
-  if (r >= a.rows_per_expert) return;
-  const uint8_t *row = a.w + ((int64_t)e_local * a.rows_per_expert + r) * a.stride;
-  const int nsb = (int)(a.cols >> 8);
-  for (int c0 = 0; c0 < n; c0 += kOrdCols) {
-    const float *xc[kOrdCols];
-    int asg[kOrdCols];
+__device__ __forceinline__ void ord_cp16(void *dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// One pass over the row for NC assignments of the expert (NC columns share each dequantised weight; their chains are
+// independent and cover each other's addition latency).
+template <int QT, int NC, class Issue>
+__device__ __forceinline__ void ord_pass(const MoeGemvArgs &a, float *yout, int e, int c0, int nsb, const uint8_t *ring, const uint8_t *row, int lane,
+                                         int64_t r, bool row_ok, Issue &&issue) {
+  constexpr int SB = QT == CMLD_Q4_K ? 144 : 208;
+  const float *xc[NC];
+  int asg[NC];
 #pragma unroll
-    for (int c = 0; c < kOrdCols; ++c) {
-      asg[c] = a.lists[e * a.n_assign + min(c0 + c, n - 1)];
-      xc[c] = a.x + (int64_t)(asg[c] / a.x_div) * a.x_stride;
-    }
-    float acc[kOrdCols];
+  for (int c = 0; c < NC; ++c) {
+    asg[c] = a.lists[e * a.n_assign + c0 + c];
+    xc[c] = a.x + (int64_t)(asg[c] / a.x_div) * a.x_stride;
+  }
+  float acc[NC];
 #pragma unroll
-    for (int c = 0; c < kOrdCols; ++c) acc[c] = 0.0f;
-    for (int sb = 0; sb < nsb; ++sb) {
-      if (QT == CMLD_Q4_K) {
-        const uint8_t *blk = row + (int64_t)sb * 144;
-        const uint4 meta = ld_stream16(blk);
-        const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
+  for (int c = 0; c < NC; ++c) acc[c] = 0.0f;
+  __syncwarp();  // the ring is free: every lane is done with the previous pass
+  for (int sb = 0; sb < kOrdStages - 1; ++sb) issue(sb);
+  for (int sb = 0; sb < nsb; ++sb) {
+    issue(sb + kOrdStages - 1);  // into the stage step sb-1 used: every lane left it at the __syncwarp below
+    asm volatile("cp.async.wait_group %0;" ::"n"(kOrdStages - 1) : "memory");
+    __syncwarp();  // the other lanes' pieces of step sb are visible
+    const uint8_t *stage = ring + (sb % kOrdStages) * (32 * SB + kOrdCols * 1024);
+    const uint8_t *blk = stage + lane * SB;
+    const float *xs = reinterpret_cast<const float *>(stage + 32 * SB);  // [assignment][256]
+    if (QT == CMLD_Q4_K) {
+      const uint4 meta = *reinterpret_cast<const uint4 *>(blk);
+      const float d = f16_bits_to_f32((uint16_t)(meta.x & 0xffff)), dmin = f16_bits_to_f32((uint16_t)(meta.x >> 16));
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-          const uint4 q0 = ld_stream16(blk + 16 + 32 * p), q1 = ld_stream16(blk + 32 + 32 * p);
-          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      for (int p = 0; p < 4; ++p) {
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(blk + 16 + 32 * p), q1 = *reinterpret_cast<const uint4 *>(blk + 32 + 32 * p);
+        const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-          for (int hl = 0; hl < 2; ++hl) {  // low nibbles = values 64p..64p+31, high nibbles = the next 32
-            int sc, m;
-            q4k_scale_min(2 * p + hl, meta.y, meta.z, meta.w, sc, m);
-            const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)m);
-            const int xo = sb * 256 + 64 * p + 32 * hl;
+        for (int hl = 0; hl < 2; ++hl) {  // low nibbles = values 64p..64p+31, high nibbles = the next 32
+          int sc, m;
+          q4k_scale_min(2 * p + hl, meta.y, meta.z, meta.w, sc, m);
+          const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)m);
+          const int xo = 64 * p + 32 * hl;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t nib = hl ? (qw[k] >> 4) & 0x0f0f0f0fu : qw[k] & 0x0f0f0f0fu;
-              float w4[4];
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t nib = hl ? (qw[k] >> 4) & 0x0f0f0f0fu : qw[k] & 0x0f0f0f0fu;
+            float w4[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) w4[i] = __fsub_rn(__fmul_rn(dsc, byte_to_float(nib, i)), dm);
+            for (int i = 0; i < 4; ++i) w4[i] = __fsub_rn(__fmul_rn(dsc, byte_to_float(nib, i)), dm);
 #pragma unroll
-              for (int c = 0; c < kOrdCols; ++c) {
-                const float4 xv = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo + 4 * k));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.x, w4[0]));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.y, w4[1]));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.z, w4[2]));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.w, w4[3]));
-              }
+            for (int c = 0; c < NC; ++c) {
+              const float4 xv = *reinterpret_cast<const float4 *>(xs + c * 256 + xo + 4 * k);
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.x, w4[0]));
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.y, w4[1]));
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.z, w4[2]));
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.w, w4[3]));
             }
           }
         }
-      } else {  // Q6_K: values 128h + 32*stream + l, stream 0/1 = low nibbles of ql[64h + 32*stream' ..], 2/3 = high nibbles
-        const uint8_t *blk = row + (int64_t)sb * 208;
-        const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row + (int64_t)nsb * 208) + sb));
-        const uint4 scw = ld_stream16(blk + 192);
-        const uint32_t scs[4] = {scw.x, scw.y, scw.z, scw.w};
+      }
+    } else {  // Q6_K: values 128h + 32*stream + l, stream 0/1 = low nibbles of ql[64h + 32*stream' ..], 2/3 = high nibbles
+      const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(row + (int64_t)nsb * 208) + sb));
+      const uint4 scw = *reinterpret_cast<const uint4 *>(blk + 192);
+      const uint32_t scs[4] = {scw.x, scw.y, scw.z, scw.w};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint4 h0 = ld_stream16(blk + 128 + 32 * h), h1 = ld_stream16(blk + 144 + 32 * h);
-          const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+      for (int h = 0; h < 2; ++h) {
+        const uint4 h0 = *reinterpret_cast<const uint4 *>(blk + 128 + 32 * h), h1 = *reinterpret_cast<const uint4 *>(blk + 144 + 32 * h);
+        const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
 #pragma unroll
-          for (int stream = 0; stream < 4; ++stream) {
-            const uint4 l0 = ld_stream16(blk + 64 * h + 32 * (stream & 1)), l1 = ld_stream16(blk + 64 * h + 32 * (stream & 1) + 16);
-            const uint32_t ql[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        for (int stream = 0; stream < 4; ++stream) {
+          const uint4 l0 = *reinterpret_cast<const uint4 *>(blk + 64 * h + 32 * (stream & 1)),
+                      l1 = *reinterpret_cast<const uint4 *>(blk + 64 * h + 32 * (stream & 1) + 16);
+          const uint32_t ql[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int j = 8 * h + 2 * stream + (k >> 2);  // scale index of values 16j..16j+15
-              const float dsc = __fmul_rn(d, (float)(int)(int8_t)(scs[j >> 2] >> (8 * (j & 3))));
-              const uint32_t lo = (stream & 2) ? (ql[k] >> 4) & 0x0f0f0f0fu : ql[k] & 0x0f0f0f0fu;
-              const uint32_t q6 = lo | (((qh[k] >> (2 * stream)) & 0x03030303u) << 4);
-              float w4[4];
+          for (int k = 0; k < 8; ++k) {
+            const int j = 8 * h + 2 * stream + (k >> 2);  // scale index of values 16j..16j+15
+            const float dsc = __fmul_rn(d, (float)(int)(int8_t)(scs[j >> 2] >> (8 * (j & 3))));
+            const uint32_t lo = (stream & 2) ? (ql[k] >> 4) & 0x0f0f0f0fu : ql[k] & 0x0f0f0f0fu;
+            const uint32_t q6 = lo | (((qh[k] >> (2 * stream)) & 0x03030303u) << 4);
+            float w4[4];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) w4[i] = __fmul_rn(dsc, byte_to_float(q6, i) - 32.0f);
-              const int xo = sb * 256 + 128 * h + 32 * stream + 4 * k;
+            for (int i = 0; i < 4; ++i) w4[i] = __fmul_rn(dsc, byte_to_float(q6, i) - 32.0f);
+            const int xo = 128 * h + 32 * stream + 4 * k;
 #pragma unroll
-              for (int c = 0; c < kOrdCols; ++c) {
-                const float4 xv = __ldg(reinterpret_cast<const float4 *>(xc[c] + xo));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.x, w4[0]));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.y, w4[1]));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.z, w4[2]));
-                acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.w, w4[3]));
-              }
+            for (int c = 0; c < NC; ++c) {
+              const float4 xv = *reinterpret_cast<const float4 *>(xs + c * 256 + xo);
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.x, w4[0]));
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.y, w4[1]));
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.z, w4[2]));
+              acc[c] = __fadd_rn(acc[c], __fmul_rn(xv.w, w4[3]));
             }
           }
         }
       }
     }
+    __syncwarp();  // every lane is done with this stage before a later copy overwrites it
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (row_ok) {
 #pragma unroll
-    for (int c = 0; c < kOrdCols; ++c)
-      if (c0 + c < n) a.y[(int64_t)asg[c] * a.rows_per_expert + r] = acc[c];
+    for (int c = 0; c < NC; ++c)
+      yout[(int64_t)asg[c] * a.rows_per_expert + r] = acc[c];
+  }
+}
+
+template <int QT>
+__global__ void __launch_bounds__(kOrdThreads) moe_gemv_ordered_kernel(MoeGemvArgs a) {
+  extern __shared__ __align__(16) uint8_t ord_smem[];
+  constexpr int SB = QT == CMLD_Q4_K ? 144 : 208, SEG = SB / 16;
+  const int e_local = blockIdx.y;
+  const int e = a.first_expert + e_local * a.expert_step;
+  const int n = a.counts[e];
+  if (n == 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r0 = ((int64_t)blockIdx.x * kOrdWarps + warp) * 32;  // this warp's first row
+  if (r0 >= a.rows_per_expert) return;
+  const int64_t r = r0 + lane;
+  const bool row_ok = r < a.rows_per_expert;
+  const uint8_t *w0 = (blockIdx.z ? a.w2 : a.w) + (int64_t)e_local * a.rows_per_expert * a.stride;
+  float *yout = blockIdx.z ? a.y2 : a.y;
+  const int nsb = (int)(a.cols >> 8);
+  constexpr int STAGE = 32 * SB + kOrdCols * 1024;  // the warp's 32 superblocks, then 256 activation values per assignment
+  uint8_t *ring = ord_smem + warp * (kOrdStages * STAGE);
+  const float *xc_issue[kOrdCols] = {nullptr, nullptr, nullptr, nullptr};
+  int nc_issue = 0;
+  // piece c of a step: row c / SEG of the warp, 16-byte unit c % SEG of that row's superblock
+  auto issue = [&](int sb) {
+    if (sb < nsb) {
+      uint8_t *dst = ring + (sb % kOrdStages) * STAGE;
+      for (int c = lane; c < nc_issue * 64; c += 32)  // the activation chunk of every live assignment: 64 pieces each
+        ord_cp16(dst + 32 * SB + c * 16, xc_issue[c >> 6] + sb * 256 + (c & 63) * 4);
+#pragma unroll
+      for (int j = 0; j < (32 * SEG + 31) / 32; ++j) {
+        const int c = lane + 32 * j;
+        if (c < 32 * SEG) {
+          const int64_t rr = min(r0 + c / SEG, a.rows_per_expert - 1);
+          ord_cp16(dst + c * 16, w0 + rr * a.stride + (int64_t)sb * SB + (c % SEG) * 16);
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const uint8_t *row = w0 + min(r, a.rows_per_expert - 1) * a.stride;  // this lane's row (Q6_K: its f16 scales behind the blocks)
+  for (int c0 = 0; c0 < n; c0 += kOrdCols) {
+    nc_issue = min(kOrdCols, n - c0);
+    for (int c = 0; c < nc_issue; ++c) xc_issue[c] = a.x + (int64_t)(a.lists[e * a.n_assign + c0 + c] / a.x_div) * a.x_stride;
+    switch (nc_issue) {
+      case 1: ord_pass<QT, 1>(a, yout, e, c0, nsb, ring, row, lane, r, row_ok, issue); break;
+      case 2: ord_pass<QT, 2>(a, yout, e, c0, nsb, ring, row, lane, r, row_ok, issue); break;
+      case 3: ord_pass<QT, 3>(a, yout, e, c0, nsb, ring, row, lane, r, row_ok, issue); break;
+      default: ord_pass<QT, 4>(a, yout, e, c0, nsb, ring, row, lane, r, row_ok, issue); break;
+    }
   }
 }
 
@@ -529,14 +612,34 @@ int32_t moe_expert_gemv(const Weight &slab, int64_t rows_per_expert, int n_local
 
 int32_t moe_expert_gemv_ordered(const Weight &slab, int64_t rows_per_expert, int n_local_experts, int first_expert, int expert_step,
                                 const float *x, int64_t x_stride, int x_div, float *y, const int32_t *counts, const int32_t *lists,
-                                int n_assign, cudaStream_t s) {
+                                int n_assign, cudaStream_t s, const Weight *slab2, float *y2) {
   MoeGemvArgs a{slab.data, slab.qt, rows_per_expert, slab.cols, slab.stride, x, x_stride, x_div, y, counts, lists, n_assign,
                 first_expert, expert_step};
+  if (slab2) {
+    if (slab2->qt != slab.qt || slab2->cols != slab.cols || slab2->stride != slab.stride || !y2) return fail(CMLD_ERR_SHAPE, "paired expert slabs differ in shape or type");
+    a.w2 = slab2->data;
+    a.y2 = y2;
+  }
   if (slab.cols % 256) return fail(CMLD_ERR_SHAPE, "expert tensor width %lld is not a multiple of 256", (long long)slab.cols);
-  dim3 grid((unsigned)((rows_per_expert + kOrdThreads - 1) / kOrdThreads), (unsigned)n_local_experts);
-  if (slab.qt == CMLD_Q4_K) moe_gemv_ordered_kernel<CMLD_Q4_K><<<grid, kOrdThreads, 0, s>>>(a);
-  else if (slab.qt == CMLD_Q6_K) moe_gemv_ordered_kernel<CMLD_Q6_K><<<grid, kOrdThreads, 0, s>>>(a);
-  else return fail(CMLD_ERR_UNSUPPORTED, "expert tensors must be Q4_K or Q6_K");
+  dim3 grid((unsigned)((rows_per_expert + kOrdThreads - 1) / kOrdThreads), (unsigned)n_local_experts, slab2 ? 2u : 1u);
+  static bool attr4 = false, attr6 = false;
+  if (slab.qt == CMLD_Q4_K) {
+    const int smem = kOrdWarps * kOrdStages * (32 * 144 + kOrdCols * 1024);
+    if (!attr4) {
+      CMLD_CUDA(cudaFuncSetAttribute(moe_gemv_ordered_kernel<CMLD_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr4 = true;
+    }
+    moe_gemv_ordered_kernel<CMLD_Q4_K><<<grid, kOrdThreads, smem, s>>>(a);
+  } else if (slab.qt == CMLD_Q6_K) {
+    const int smem = kOrdWarps * kOrdStages * (32 * 208 + kOrdCols * 1024);
+    if (!attr6) {
+      CMLD_CUDA(cudaFuncSetAttribute(moe_gemv_ordered_kernel<CMLD_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      attr6 = true;
+    }
+    moe_gemv_ordered_kernel<CMLD_Q6_K><<<grid, kOrdThreads, smem, s>>>(a);
+  } else {
+    return fail(CMLD_ERR_UNSUPPORTED, "expert tensors must be Q4_K or Q6_K");
+  }
   CMLD_CUDA(cudaGetLastError());
   return CMLD_OK;
 }
