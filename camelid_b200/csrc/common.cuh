@@ -351,6 +351,12 @@ int32_t comm_allreduce_sum_f32(void *comm, float *buf, int64_t count, cudaStream
 int32_t comm_allreduce_max_u64(void *comm, unsigned long long *buf, int64_t count, cudaStream_t s);
 int32_t comm_allgather_f32(void *comm, const float *send, float *recv, int64_t count_per_rank, cudaStream_t s);
 
+// kv_q8.cu: KV cache as Q8_0 blocks (CMLD_FLAG_KV_Q8_0)
+int64_t kv_q8_layer_bytes(int64_t seqs, int n_kv, int64_t max_pos, int hd);
+int32_t launch_rope_kv_q8(const RopeKvArgs &a, uint8_t *kq, uint8_t *vq, cudaStream_t s);
+int32_t launch_attention_q8(const AttnArgs &a, const uint8_t *kq, const uint8_t *vq, cudaStream_t s);
+int32_t launch_kv_q8_convert(uint8_t *cache, float *rows, int n_kv, int64_t max_pos, int64_t n_pos, int hd, bool to_cache, cudaStream_t s);
+
 // sample.cu: temperature / min-p sampling over a resident logits row
 int32_t launch_sample_gumbel(const float *logits, int32_t n, float inv_temp, uint64_t seed, uint32_t *out_dev, cudaStream_t s);
 int32_t launch_sample_gumbel_filtered(const float *logits, int32_t n, float temperature, float min_p, uint64_t seed, uint32_t *out_dev,

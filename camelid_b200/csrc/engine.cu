@@ -125,6 +125,8 @@ struct cmld_engine {
     unsigned long long timeout_ns = 0;
   } peer;
   float *mma_scratch = nullptr;  // per-chunk partial sums of the batched tensor-core matvec
+  uint8_t *kq8 = nullptr, *vq8 = nullptr;  // CMLD_FLAG_KV_Q8_0: the KV cache as Q8_0 blocks, [layer][slot][kv_head][max_pos][hd/32] x 34 B
+  int64_t kv_q8_bytes = 0;                 // bytes of one layer of one side
   uint32_t *tree_mask = nullptr;  // [kTreeMaxNodes] ancestor masks of a draft tree (one word: at most 32 nodes)
   std::vector<float> rope_freq;  // per-pair angular frequency of the engine-owned RoPE table (rope_pair_frequency)
   uint8_t *tc5_pack = nullptr;   // packed activation records of the tcgen05 batched matvec
@@ -261,8 +263,19 @@ static int32_t engine_init(cmld_engine *e) {
   e->layers.resize(c.n_layers);
   // KV cache: [layer][slot][kv_head][max_pos][head_dim] f16, K and V
   e->kv_layer_elems = (int64_t)seqs * c.n_kv_heads * c.max_pos * c.head_dim;
-  CMLD_TRY(dev_alloc(e, &e->kcache, e->kv_layer_elems * c.n_layers));
-  CMLD_TRY(dev_alloc(e, &e->vcache, e->kv_layer_elems * c.n_layers));
+  if (c.flags & CMLD_FLAG_KV_Q8_0) {
+    // the cache as Q8_0 blocks (src/tensor/kv_quant.rs): 34 bytes per 32 values instead of 64
+    if (c.head_dim % 32) return fail(CMLD_ERR_SHAPE, "Q8_0 KV cache: head_dim %d is not a multiple of 32", c.head_dim);
+    e->kv_q8_bytes = kv_q8_layer_bytes(seqs, c.n_kv_heads, c.max_pos, c.head_dim);
+    CMLD_TRY(dev_alloc(e, &e->kq8, e->kv_q8_bytes * c.n_layers));
+    CMLD_TRY(dev_alloc(e, &e->vq8, e->kv_q8_bytes * c.n_layers));
+    e->kv_layer_elems = 0;
+    CMLD_TRY(dev_alloc(e, &e->kcache, 8));
+    CMLD_TRY(dev_alloc(e, &e->vcache, 8));
+  } else {
+    CMLD_TRY(dev_alloc(e, &e->kcache, e->kv_layer_elems * c.n_layers));
+    CMLD_TRY(dev_alloc(e, &e->vcache, e->kv_layer_elems * c.n_layers));
+  }
   // RoPE tables for every position, computed with the host libm exactly as the reference's
   // resident_decode_rope_tables does per token (src/inference/rope.rs:600-655).  The default per-pair
   // frequency is freq_base^(-2i/rope_dim); cmld_engine_set_rope_frequencies replaces it (rope_freqs.weight,
@@ -837,7 +850,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       // the attention that follows reads this layer's KV rows: have them pulled into L2 meanwhile (every row but
       // the step's own, which the attention kernel appends itself, is final)
       KvPrefetch pf{};
-      if (!o.shared_slots) {
+      if (!o.shared_slots && !e->kq8) {
         pf.k = e->kcache + (int64_t)li * e->kv_layer_elems;
         pf.v = e->vcache + (int64_t)li * e->kv_layer_elems;
         pf.positions = e->d_positions;
@@ -853,6 +866,44 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       // Attention.  Default: the reference-order cluster kernel (the CPU path's bits); contexts or shapes it
       // does not take, and CMLD_FLAG_EXACT_ORDER, use the plain reference-order kernel; CMLD_FLAG_FAST_ORDER
       // opts into the split-range (flash-decoding) kernel, whose sums are trees.
+      if (e->kq8) {
+        // Q8_0 KV cache: append (RoPE + block quantisation) and attention over the blocks, in the CPU lane's order
+        RopeKvArgs r{};
+        r.q = e->q;
+        r.k = e->k;
+        r.v = e->v;
+        r.cos_tab = o.rope_by_position ? e->cos_all : e->cos_step;
+        r.sin_tab = o.rope_by_position ? e->sin_all : e->sin_step;
+        r.index_by_position = o.rope_by_position;
+        r.positions = e->d_positions;
+        r.slots = e->d_slots;
+        r.n_heads = c.n_heads;
+        r.n_kv_heads = c.n_kv_heads;
+        r.head_dim = c.head_dim;
+        r.rope_dim = c.rope_dim;
+        r.split_half = c.split_half_pairing;
+        r.batch = B;
+        r.max_pos = c.max_pos;
+        r.q_stride = e->q_width;
+        r.kv_stride = e->kv_width;
+        uint8_t *kq = e->kq8 + (int64_t)li * e->kv_q8_bytes, *vq = e->vq8 + (int64_t)li * e->kv_q8_bytes;
+        CMLD_TRY(launch_rope_kv_q8(r, kq, vq, e->stream));
+        AttnArgs a{};
+        a.q = e->q;
+        a.positions = e->d_positions;
+        a.slots = e->d_slots;
+        a.n_heads = c.n_heads;
+        a.n_kv_heads = c.n_kv_heads;
+        a.head_dim = c.head_dim;
+        a.batch = B;
+        a.max_pos = c.max_pos;
+        a.scale = o.scale;
+        a.out = e->attn;
+        a.q_stride = e->q_width;
+        a.tree_mask = o.tree_mask;
+        CMLD_TRY(launch_attention_q8(a, kq, vq, e->stream));
+        e->launches += 2;
+      } else {
       const bool fast = (c.flags & CMLD_FLAG_FAST_ORDER) && !(c.flags & CMLD_FLAG_EXACT_ORDER) && !o.tree_mask;
       const bool ordered = !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && o.attn_cap > 0 && !o.tree_mask &&
                            attention_ordered_fits(c.n_heads, c.n_kv_heads, c.head_dim, o.attn_cap);
@@ -919,6 +970,7 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       else if (fast) CMLD_TRY(launch_attention(a, e->stream));
       else CMLD_TRY(launch_attention_exact(a, e->stream));
       e->launches += 1;
+      }
     }
     {
       const Proj p[1] = {{&L.proj[3], e->h, (e->tp == 1 || lead) ? e->h : nullptr, c.hidden}};
@@ -1674,6 +1726,7 @@ int32_t cmld_engine_verify_tree(cmld_engine *e, const float *embeddings, const f
   if (words != 1) return fail(CMLD_ERR_INVALID, "verify_tree: %d mask words per node, 1 expected for at most %d nodes", words, CMLD_TREE_MAX_NODES);
   if (base_position < 0 || base_position + n > c.max_pos) return fail(CMLD_ERR_STATE, "verify_tree: rows %lld..%lld exceed max_pos %d", (long long)base_position, (long long)(base_position + n - 1), c.max_pos);
   if (e->tp > 1 || e->ep > 1) return fail(CMLD_ERR_UNSUPPORTED, "verify_tree: sharded engines are not supported");
+  if (e->kq8) return fail(CMLD_ERR_UNSUPPORTED, "verify_tree: not supported over a Q8_0 KV cache");
   std::vector<uint32_t> masks(n);
   std::vector<int32_t> pos(n), slots(n, 0);
   for (int i = 0; i < n; ++i) {
@@ -1727,6 +1780,7 @@ int32_t cmld_engine_compact_tree_kv_path(cmld_engine *e, const int32_t *path, in
   CMLD_ENGINE_ENTER(e);
   const cmld_config &c = e->cfg;
   if (!path || len < 0 || len > CMLD_TREE_MAX_NODES) return fail(CMLD_ERR_INVALID, "compact_tree_kv_path: bad path");
+  if (e->kq8) return fail(CMLD_ERR_UNSUPPORTED, "compact_tree_kv_path: not supported over a Q8_0 KV cache");
   for (int r = 0; r < len; ++r) {
     if (path[r] < r || path[r] >= CMLD_TREE_MAX_NODES || (r > 0 && path[r] <= path[r - 1])) return fail(CMLD_ERR_INVALID, "compact_tree_kv_path: path is not an increasing sequence of node indices");
     if (base_position + path[r] >= c.max_pos) return fail(CMLD_ERR_STATE, "compact_tree_kv_path: row beyond max_pos");
@@ -1764,6 +1818,15 @@ static int32_t kv_transfer(cmld_engine *e, int32_t layer, float *ck, float *cv, 
   int32_t rc = CMLD_OK;
   for (int side = 0; side < 2 && rc == CMLD_OK; ++side) {
     float *hostp = side == 0 ? ck : cv;
+    if (e->kq8) {
+      // Q8_0 cache: rows are quantised block by block on the way in and dequantised (code * d) on the way out
+      uint8_t *qc = (side == 0 ? e->kq8 : e->vq8) + (int64_t)layer * e->kv_q8_bytes;
+      if (to_cache && cudaMemcpyAsync(tmp, hostp, (size_t)n * 4, cudaMemcpyDefault, e->stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "KV upload failed");
+      if (rc == CMLD_OK) rc = launch_kv_q8_convert(qc, tmp, c.n_kv_heads, c.max_pos, n_pos, c.head_dim, to_cache, e->stream);
+      if (rc == CMLD_OK && !to_cache && cudaMemcpyAsync(hostp, tmp, (size_t)n * 4, cudaMemcpyDefault, e->stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "KV download failed");
+      if (rc == CMLD_OK && cudaStreamSynchronize(e->stream) != cudaSuccess) rc = fail(CMLD_ERR_CUDA, "KV transfer failed");
+      continue;
+    }
     __half *cache = (side == 0 ? e->kcache : e->vcache) + (int64_t)layer * e->kv_layer_elems;
     const unsigned blocks = (unsigned)std::min<int64_t>((n + 255) / 256, 4096);
     if (to_cache) {

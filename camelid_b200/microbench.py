@@ -49,8 +49,39 @@ def run_case(qt_name: str, rows: int, cols: int, batch: int, iters: int, warmup:
             "weight_copies": n_copies, "iters": iters}
 
 
+def run_attention(ctx: int, iters: int) -> dict:
+    """The reference-order decode attention at the Llama-3-8B shape (32 query heads, 8 KV heads, head_dim 128) over
+    `ctx` cached positions of seeded f16 K/V: wall time per call of the operator entry point (launch and
+    synchronisation included), and the KV bytes one call reads."""
+    import time
+
+    import camelid_b200 as cm
+    from camelid_b200._lib import check
+    from camelid_b200.engine import DeviceBuffer
+
+    n_heads, n_kv, hd = 32, 8, 128
+    max_pos = max(2048, 1 << (ctx - 1).bit_length())
+    rng = np.random.default_rng(1)
+    q = rng.standard_normal((n_heads, hd)).astype(np.float32)
+    k = rng.standard_normal((n_kv, max_pos, hd)).astype(np.float16)
+    v = rng.standard_normal((n_kv, max_pos, hd)).astype(np.float16)
+    out_d = DeviceBuffer(n_heads * hd * 4)
+    qd, kd, vd = DeviceBuffer.from_numpy(q), DeviceBuffer.from_numpy(k), DeviceBuffer.from_numpy(v)
+    scale = float(1 / np.sqrt(hd))
+    for _ in range(3):
+        check(cm.lib().cmld_attention_decode_ordered(qd.ptr, kd.ptr, vd.ptr, n_heads, n_kv, hd, max_pos, ctx, scale, out_d.ptr))
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        check(cm.lib().cmld_attention_decode_ordered(qd.ptr, kd.ptr, vd.ptr, n_heads, n_kv, hd, max_pos, ctx, scale, out_d.ptr))
+    dt = (time.perf_counter() - t0) / iters
+    return {"op": "attention_decode_ordered", "n_heads": n_heads, "n_kv_heads": n_kv, "head_dim": hd, "context": ctx,
+            "wall_us_per_call": dt * 1e6, "kv_bytes": 2 * n_kv * ctx * hd * 2, "iters": iters}
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--attention", type=int, default=0, metavar="CTX",
+                    help="run the reference-order decode attention at the 8B shape over CTX positions instead of the matvec cases")
     ap.add_argument("--qt", default=None, choices=sorted(BPW))
     ap.add_argument("--rows", type=int, default=0)
     ap.add_argument("--cols", type=int, default=0)
@@ -61,6 +92,9 @@ def main():
                     help="staged = bulk-copy pipelined kernel when the shape fits (default); direct = direct-load kernel")
     ap.add_argument("--pdl", action="store_true", help="chain the timed launches with programmatic dependent launch")
     a = ap.parse_args()
+    if a.attention:
+        print(json.dumps(run_attention(a.attention, max(1, a.iters))), flush=True)
+        return
     import camelid_b200 as cm
     from camelid_b200._lib import check
 

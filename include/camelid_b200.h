@@ -80,6 +80,7 @@ typedef struct {
 #define CMLD_FLAG_SPLIT_PROLOGUE 8u /* norm/SwiGLU/quantise in a small kernel of its own instead of the matvec prologue (always so for steps of more than 2 rows) */
 #define CMLD_FLAG_FAST_ORDER 128u  /* attention by the split-range (flash-decoding) kernel, whose sums are trees: faster at long contexts, no longer the CPU path's bits */
 #define CMLD_FLAG_TENSOR_BATCH 64u   /* steps of 5..32 rows and prompt ingestion on the int8 mma.sync matvec (one pass over the weights; its row sums are trees, so no longer the CPU path's bits) */
+#define CMLD_FLAG_KV_Q8_0 256u     /* KV cache as Q8_0 blocks (new_with_kv_quant, src/cuda_resident.rs:15748; src/tensor/kv_quant.rs): 34 bytes per 32 values; the arithmetic of the CPU lane's scalar path */
 #define CMLD_FLAG_NCCL_ONLY 32u     /* sharded engines: every sublayer sum as an NCCL all-reduce (no peer-memory path in the matvec kernels) */
 
 typedef struct cmld_engine cmld_engine;

@@ -878,6 +878,64 @@ ORACLE_API int orc_softmax_top_k(const float *logits, int32_t n, int32_t k, int3
   return kk;
 }
 
+/* ------------------------------------------------------------------ Q8_0 KV cache (src/tensor/kv_quant.rs, scalar path) */
+
+/* quantize_block_q8_0 (:123-143): d = amax/127, id = 1/d, q = clamp(round_half_away(x*id), -127, 127); the stored scale
+ * is f16(d).  codes[32] receive the int8 codes as floats; returns the f16-rounded scale as f32. */
+ORACLE_API float orc_kv_q8_0_quantize_block(const float *src, float *codes) {
+  float amax = 0.0f;
+  for (int i = 0; i < 32; ++i) {
+    float a = fabsf(src[i]);
+    if (a > amax) amax = a;
+  }
+  float d = amax / 127.0f;
+  float id = d != 0.0f ? 1.0f / d : 0.0f;
+  for (int i = 0; i < 32; ++i) {
+    float v = roundf(src[i] * id);
+    if (v < -127.0f) v = -127.0f;
+    if (v > 127.0f) v = 127.0f;
+    codes[i] = (float)(int8_t)v;
+  }
+  return orc_f16_bits_to_f32(orc_f32_to_f16_bits(d));
+}
+
+/* One head over a Q8_0 cache: score = (sum over blocks of (sum_i q_i * code_i) * d) * scale (vec_dot_row_q8_0, :180-201,
+ * scalar form), the softmax of attention_context_for_head (src/inference.rs:30287-30466), then per position
+ * out_i = fma(prob * d, code_i, out_i) (axpy_row_q8_0, :203-221).  kq/vq: codes as floats, rows `stride` apart;
+ * kd/vd: block scales, rows `sstride` apart. */
+ORACLE_API int orc_attention_head_q8(const float *q, const float *kq, const float *kd, const float *vq, const float *vd,
+                                     int64_t stride, int64_t sstride, int64_t n_pos, int32_t head_dim, float scale, float *out,
+                                     float *scores) {
+  int32_t nb = head_dim / 32;
+  for (int64_t p = 0; p < n_pos; ++p) {
+    float total = 0.0f;
+    for (int32_t b = 0; b < nb; ++b) {
+      float sum = 0.0f;
+      for (int32_t i = 0; i < 32; ++i) sum += q[b * 32 + i] * kq[p * stride + b * 32 + i];
+      total += sum * kd[p * sstride + b];
+    }
+    scores[p] = total * scale;
+  }
+  float mx = -INFINITY;
+  for (int64_t p = 0; p < n_pos; ++p) mx = fmaxf(mx, scores[p]);
+  float sum = 0.0f;
+  for (int64_t p = 0; p < n_pos; ++p) {
+    scores[p] = expf(scores[p] - mx);
+    sum += scores[p];
+  }
+  if (sum == 0.0f || !isfinite(sum)) return -1;
+  float inv = 1.0f / sum;
+  for (int32_t d = 0; d < head_dim; ++d) out[d] = 0.0f;
+  for (int64_t p = 0; p < n_pos; ++p) {
+    float prob = scores[p] * inv;
+    for (int32_t b = 0; b < nb; ++b) {
+      float pd = prob * vd[p * sstride + b];
+      for (int32_t i = 0; i < 32; ++i) out[b * 32 + i] = fmaf(pd, vq[p * stride + b * 32 + i], out[b * 32 + i]);
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------------ sampling (src/cuda_resident/sampling.cuh) */
 
 /* sampling_uniform_from_u24 + splitmix_uniform: 24 hashed bits of (seed, index) as a float in (0, 1). */
@@ -979,6 +1037,9 @@ typedef struct {
   orc_tensor token_embd, output;
   const float *final_norm;
   float *kcache, *vcache; /* [layer][kv_head][max_pos][head_dim], f16-exact f32 */
+  int32_t kv_q8;          /* KV cache held as Q8_0 blocks (src/tensor/kv_quant.rs): kcache/vcache then hold the int8 codes as
+                             floats and kscale/vscale the f16-rounded block scales */
+  float *kscale, *vscale; /* [layer][kv_head][max_pos][head_dim/32] */
   float *rope_freq;       /* optional per-pair frequencies (rope_pair_frequency, src/inference/rope.rs:532); NULL = base^(-2i/d) */
 } orc_model;
 
@@ -1000,11 +1061,23 @@ ORACLE_API orc_model *orc_model_create(int32_t n_layers, int32_t n_heads, int32_
 
 ORACLE_API void orc_model_destroy(orc_model *m) {
   if (!m) return;
-  free(m->layers); free(m->kcache); free(m->vcache); free(m->rope_freq); free(m);
+  free(m->layers); free(m->kcache); free(m->vcache); free(m->kscale); free(m->vscale); free(m->rope_freq); free(m);
 }
 
 static orc_tensor mk_tensor(int32_t qt, const uint8_t *data, int64_t rows, int64_t cols) {
   orc_tensor t; t.qt = qt; t.data = data; t.rows = rows; t.cols = cols; return t;
+}
+
+/* Switches the model's KV cache to Q8_0 blocks (before the first forward). */
+ORACLE_API int orc_model_set_kv_q8(orc_model *m, int32_t on) {
+  if (m->head_dim % 32) return -1;
+  m->kv_q8 = on ? 1 : 0;
+  if (on && !m->kscale) {
+    size_t n = (size_t)m->n_layers * m->n_kv_heads * m->max_pos * (m->head_dim / 32);
+    m->kscale = (float *)calloc(n, 4);
+    m->vscale = (float *)calloc(n, 4);
+  }
+  return 0;
 }
 
 /* Per-pair RoPE frequencies for models with rope_freqs.weight or scaled RoPE (copied). */
@@ -1182,12 +1255,31 @@ ORACLE_API int orc_forward(orc_model *m, const float *x_in, int64_t position, fl
     orc_rope_apply(k, m->n_kv_heads, hd, m->rope_dim, cosv, sinv, m->split_half);
     float *kc = m->kcache + (size_t)li * m->n_kv_heads * m->max_pos * hd;
     float *vc = m->vcache + (size_t)li * m->n_kv_heads * m->max_pos * hd;
+    int32_t nb = hd / 32;
+    float *ks = m->kv_q8 ? m->kscale + (size_t)li * m->n_kv_heads * m->max_pos * nb : NULL;
+    float *vs = m->kv_q8 ? m->vscale + (size_t)li * m->n_kv_heads * m->max_pos * nb : NULL;
+    if (m->kv_q8) {
+      for (int32_t kh = 0; kh < m->n_kv_heads; ++kh)
+        for (int32_t b = 0; b < nb; ++b) {
+          size_t row = (size_t)kh * m->max_pos + position;
+          ks[row * nb + b] = orc_kv_q8_0_quantize_block(k + kh * hd + b * 32, kc + row * hd + b * 32);
+          vs[row * nb + b] = orc_kv_q8_0_quantize_block(v + kh * hd + b * 32, vc + row * hd + b * 32);
+        }
+      for (int32_t hh = 0; hh < m->n_heads && rc == 0; ++hh) {
+        size_t h0 = (size_t)(hh / group) * m->max_pos;
+        rc = orc_attention_head_q8(q + hh * hd, kc + h0 * hd, ks + h0 * nb, vc + h0 * hd, vs + h0 * nb, hd, nb, position + 1, hd,
+                                   scale, ctx + hh * hd, scores);
+      }
+    } else {
     for (int32_t kh = 0; kh < m->n_kv_heads; ++kh)
       for (int32_t d = 0; d < hd; ++d) {
         kc[((size_t)kh * m->max_pos + position) * hd + d] = kv_f16_round(k[kh * hd + d]);
         vc[((size_t)kh * m->max_pos + position) * hd + d] = kv_f16_round(v[kh * hd + d]);
       }
-    if (position == 0) {
+    }
+    if (m->kv_q8) {
+      /* done above */
+    } else if (position == 0) {
       /* single cached position: the context is a copy of V (src/inference.rs:29858-29951) */
       for (int32_t hh = 0; hh < m->n_heads; ++hh)
         memcpy(ctx + hh * hd, vc + ((size_t)(hh / group) * m->max_pos) * hd, (size_t)hd * 4);

@@ -82,6 +82,9 @@ def lib(path: str | os.PathLike | None = None):
         "orc_sample_gumbel": (i32, [vp, i32, f32, C.c_uint64, vp]),
         "orc_sample_gumbel_filtered": (i32, [vp, i32, f32, f32, C.c_uint64, vp]),
         "orc_model_set_rope_frequencies": (C.c_int, [vp, vp, i32]),
+        "orc_model_set_kv_q8": (C.c_int, [vp, i32]),
+        "orc_kv_q8_0_quantize_block": (f32, [vp, vp]),
+        "orc_attention_head_q8": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i32, f32, vp, vp]),
         "orc_rope_llama3_frequency": (f32, [f32, f32, f32, f32, f32]),
         "orc_forward": (C.c_int, [vp, vp, i64, vp, vp, vp]),
         "orc_generate": (C.c_int, [vp, vp, i32, i32, i64, vp, vp]),
@@ -300,6 +303,10 @@ class OracleModel:
         ck, cv = np.empty(shape, np.float32), np.empty(shape, np.float32)
         assert lib().orc_model_read_kv(self._h, layer, n_positions, _p(ck), _p(cv)) == 0
         return ck, cv
+
+    def set_kv_q8(self, on: bool = True):
+        """Keeps the KV cache as Q8_0 blocks (src/tensor/kv_quant.rs) from the next forward on."""
+        assert lib().orc_model_set_kv_q8(self._h, int(on)) == 0
 
     def set_rope_frequencies(self, freq):
         f = _f32(freq)

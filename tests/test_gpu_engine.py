@@ -388,3 +388,54 @@ def test_forward_token_sample_draws_from_the_steps_own_logits(cm, orc):
         else:
             assert want >= 0 and (got == want or abs(float(scores[got]) - float(scores[want])) <= 1e-5 * max(1.0, abs(float(scores[want]))))
         tok = int(got)
+
+
+def test_q8_0_kv_cache_follows_the_cpu_lanes_scalar_arithmetic(cm, orc):
+    """CMLD_FLAG_KV_Q8_0 (new_with_kv_quant, src/cuda_resident.rs:15748): K and V rows are kept as Q8_0 blocks
+    (quantize_block_q8_0, src/tensor/kv_quant.rs:123) and attention runs over the blocks in the order of the CPU
+    lane's scalar path (vec_dot_row_q8_0 :180, axpy_row_q8_0 :203).  Against the checker holding its cache the same
+    way: residual stream, logits, cache rows and greedy tokens are bit-identical.  (The reference's AVX2 path adds in
+    another order; its own test holds the two to 1e-5.)"""
+    from camelid_b200 import synth
+
+    cfg = synth.engine_config("tiny", max_pos=64, flags=256)
+    pair = ModelPair(cfg, "q4_k_m", seed=19)
+    eng, ref = pair.engine, pair.oracle
+    ref.set_kv_q8(True)
+    prompt = orc.synth_tokens(19, 5, 9, cfg.vocab)
+    for pos in range(5):
+        emb = ref.embedding(int(prompt[pos]))
+        c, s = pair.rope(pos)
+        ref_logits, _, ref_taps = ref.forward(emb, pos, want_taps=True)
+        _, taps = eng.forward_token_hidden(emb, c, s, pos, pair.scale, taps=True)
+        logits = eng.forward_token_logits(emb, c, s, pos, pair.scale)
+        assert np.array_equal(taps.view(np.uint32), ref_taps.view(np.uint32)), pos
+        assert np.array_equal(logits.view(np.uint32), ref_logits.view(np.uint32)), pos
+    # the cache rows read back dequantised (code * d): what the blocks hold is what the checker's blocks hold
+    ck, cv = eng.read_kv_layer(1, 5)
+    nb = cfg.head_dim // 32
+    kq, vq = ref.read_kv_layer(1, 5)          # the checker keeps codes (as floats) ...
+    assert np.all(np.abs(kq) <= 127) and np.array_equal(kq, np.round(kq))
+    ratio = np.where(kq != 0, ck / np.where(kq != 0, kq, 1), 0).reshape(cfg.n_kv_heads, 5, nb, 32)
+    for blk in ratio.reshape(-1, 32):          # ... so every block's values are one scale times its codes
+        nz = blk[blk != 0]
+        assert nz.size == 0 or np.all(nz == nz[0])
+    # a full generation: prompt through the 32-row chunks, then greedy steps
+    ref2 = ModelPair(cfg, "q4_k_m", seed=19)
+    ref2.oracle.set_kv_q8(True)
+    want, _ = ref2.oracle.generate(prompt, 24)
+    first = ref2.engine.prefill_tokens(0, prompt, 0)
+    rest = ref2.engine.decode_greedy([0], [first], [len(prompt)], 23)[:, 0]
+    assert np.array_equal(np.concatenate([[first], rest]), want)
+    # seeding quantises rows exactly like an append does
+    rows = np.random.default_rng(2).standard_normal((cfg.n_kv_heads, 3, cfg.head_dim)).astype(np.float32)
+    eng.seed_layer(0, rows, rows * 0.5, 3)
+    back_k, back_v = eng.read_kv_layer(0, 3)
+    import ctypes as C
+    for kh in range(cfg.n_kv_heads):
+        for p in range(3):
+            for b in range(nb):
+                codes = np.empty(32, np.float32)
+                blk = np.ascontiguousarray(rows[kh, p, 32 * b: 32 * b + 32])
+                d = orc.lib().orc_kv_q8_0_quantize_block(blk.ctypes.data_as(C.c_void_p), codes.ctypes.data_as(C.c_void_p))
+                assert np.array_equal(back_k[kh, p, 32 * b: 32 * b + 32], (codes * np.float32(d)).astype(np.float32))

@@ -332,3 +332,30 @@ def test_sampling_math_of_the_checker():
     tok, scores = orc.sample_gumbel_filtered(logits, 0.8, 0.05, 3)
     kept = np.isfinite(scores)
     assert tok >= 0 and kept[tok] and scores[tok] == scores[kept].max() and 1 <= kept.sum() < 5000
+
+
+def test_q8_0_kv_block_functions_of_the_checker():
+    """The checker's restatement of src/tensor/kv_quant.rs (scalar path) on the values of the reference's own unit test
+    (q8_0_roundtrip_and_dot_match_dequantized_values, :905-933): round trip within 0.05, the block dot equals the dot
+    with the dequantised values within 1e-5, and the fused accumulation equals prob * value + out within 1e-5."""
+    import ctypes as C
+
+    from oracle import oracle as orc
+
+    original = ((np.arange(32, dtype=np.float32) - 16.0) * 0.25).astype(np.float32)
+    codes = np.empty(32, np.float32)
+    d = np.float32(orc.lib().orc_kv_q8_0_quantize_block(original.ctypes.data_as(C.c_void_p), codes.ctypes.data_as(C.c_void_p)))
+    rec = (codes * d).astype(np.float32)
+    assert np.abs(original - rec).max() < 0.05 and np.abs(codes).max() == 127
+    assert d == np.float16(np.float32(4.0) / np.float32(127.0)).astype(np.float32)
+    query = ((np.arange(32, dtype=np.float32) - 7.0) * 0.125).astype(np.float32)
+    # one position, one block: the attention helper's score is (sum q*code)*d*scale and its output prob*d*code
+    out, scores = np.empty(32, np.float32), np.empty(1, np.float32)
+    sc = np.array([d], np.float32)
+    rc = orc.lib().orc_attention_head_q8(query.ctypes.data_as(C.c_void_p), codes.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p),
+                                         codes.ctypes.data_as(C.c_void_p), sc.ctypes.data_as(C.c_void_p), 32, 1, 1, 32, 1.0,
+                                         out.ctypes.data_as(C.c_void_p), scores.ctypes.data_as(C.c_void_p))
+    assert rc == 0 and scores[0] == 1.0           # a single position has probability one
+    assert np.abs(out - rec).max() < 1e-5         # ... and the context is its dequantised value row
+    zero = np.zeros(32, np.float32)
+    assert orc.lib().orc_kv_q8_0_quantize_block(zero.ctypes.data_as(C.c_void_p), codes.ctypes.data_as(C.c_void_p)) == 0.0 and not codes.any()
