@@ -342,6 +342,10 @@ int32_t launch_attention(const AttnArgs &a, cudaStream_t s);
 bool attention_ordered_fits(int n_heads, int n_kv_heads, int head_dim, int64_t cap);
 int32_t launch_attention_ordered(const AttnArgs &a, int64_t cap, cudaStream_t s);
 
+// attn_rows.cu: the reference-order attention for steps of several rows (one CTA per (row, KV head))
+bool attention_rows_fits(int n_heads, int n_kv_heads, int head_dim, int64_t cap);
+int32_t launch_attention_rows(const AttnArgs &a, int64_t cap, cudaStream_t s);
+
 // comm.cu: NCCL collectives of the sharded engine
 int32_t comm_unique_id(uint8_t *out128);
 int32_t comm_init(void **comm_out, const uint8_t *id128, int rank, int world);

@@ -905,7 +905,10 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
         e->launches += 2;
       } else {
       const bool fast = (c.flags & CMLD_FLAG_FAST_ORDER) && !(c.flags & CMLD_FLAG_EXACT_ORDER) && !o.tree_mask;
-      const bool ordered = !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && o.attn_cap > 0 && !o.tree_mask &&
+      // steps of three rows and more: one CTA per (row, KV head) instead of a cluster of eight (same bits)
+      const bool rows = !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && B >= 3 && o.attn_cap > 0 && !o.tree_mask &&
+                        attention_rows_fits(c.n_heads, c.n_kv_heads, c.head_dim, o.attn_cap);
+      const bool ordered = !rows && !fast && !(c.flags & CMLD_FLAG_EXACT_ORDER) && o.attn_cap > 0 && !o.tree_mask &&
                            attention_ordered_fits(c.n_heads, c.n_kv_heads, c.head_dim, o.attn_cap);
       const bool fuse = !o.shared_slots && (fast || ordered);
       if (!fuse) {
@@ -966,7 +969,8 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
       a.tree_mask = o.tree_mask;
       a.tree_base = o.tree_base;
       a.tree_words = o.tree_words;
-      if (ordered) CMLD_TRY(launch_attention_ordered(a, o.attn_cap, e->stream));
+      if (rows) CMLD_TRY(launch_attention_rows(a, o.attn_cap, e->stream));
+      else if (ordered) CMLD_TRY(launch_attention_ordered(a, o.attn_cap, e->stream));
       else if (fast) CMLD_TRY(launch_attention(a, e->stream));
       else CMLD_TRY(launch_attention_exact(a, e->stream));
       e->launches += 1;
