@@ -36,11 +36,10 @@ namespace cmld {
 
 namespace {
 
-constexpr int kTcThreads = 576;
-constexpr int kTcEpiWarps = 8;
-constexpr int kTcMmaWarp = 8;
-constexpr int kTcActWarp = 9;
-constexpr int kTcUnpackWarp0 = 10;
+// Warp roles for EW epilogue warps (8: two groups of four, each with half of the CTA's activation columns; 4: one group,
+// for launches of eight columns per CTA, whose threads can then have more registers): epilogue 0..EW-1, MMA issue EW,
+// activation records EW+1, weight path EW+2..EW+9.
+constexpr int tc_threads(int ew) { return (ew + 10) * 32; }
 constexpr int kTcUnpackThreads = 256;
 constexpr int kTcRows = 128;
 constexpr int kTcRawStages = 3;
@@ -370,8 +369,9 @@ __device__ __forceinline__ void unpack_q6k(const uint8_t *raw_stage, uint8_t *a_
 // ---------------------------------------------------------------- the kernel
 
 // GW: groups of eight activation rows per epilogue warp group (1 or 2).
-template <int QT, int GW>
-__global__ void __launch_bounds__(kTcThreads, 1) gemv_tc5_kernel(const TcArgs a) {
+template <int QT, int GW, int EW>
+__global__ void __launch_bounds__(tc_threads(EW), 1) gemv_tc5_kernel(const TcArgs a) {
+  constexpr int kTcThreads = tc_threads(EW), kTcEpiWarps = EW, kTcMmaWarp = EW, kTcActWarp = EW + 1, kTcUnpackWarp0 = EW + 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   constexpr int REC = rec_bytes(QT);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + a.off_bar);
@@ -562,7 +562,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc5_kernel(const TcArgs a)
   } else {
     // ------------------------------------------------ epilogue
     const int wg = warp >> 2, quarter = warp & 3, r = quarter * 32 + lane;
-    const int n_wg = a.ng >= 2 ? 2 : 1;                // warp groups with columns of their own
+    const int n_wg = (EW == 8 && a.ng >= 2) ? 2 : 1;   // warp groups with columns of their own
     const bool has_cols = wg < n_wg;
     const int g_first = has_cols ? wg * (a.ng / n_wg) : 0;  // first group (of eight columns) of this warp group
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -652,11 +652,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc5_kernel(const TcArgs a)
           release_step(&acc_empty[sc], &b_empty[sb], lane);
           fetch_scales(q + kScaleAhead - 1);  // off the critical path
         } else if (QT == CMLD_Q6_K) {
-          int E[8][8];  // [column][l]
-          float xd[8];
           const int g = g_first;
           if (has_cols) {
             const int *ys = reinterpret_cast<const int *>(recs + g * REC + kRecB1);
+            float dd[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dd[i] = __fmul_rn(dw, reinterpret_cast<const float *>(recs + g * REC + kRecB1 + 256)[i]);  // src/inference.rs:25545
 #pragma unroll
             for (int l = 0; l < 8; l += 2) {
               int dh[8], dl[8], eh[8], el[8];
@@ -664,19 +665,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc5_kernel(const TcArgs a)
                          d0 + (2 * l + 3) * nc + g * 8, el);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
-                E[i][l] = 128 * dh[i] + dl[i] - 4096 * ys[l * 8 + i];
-                E[i][l + 1] = 128 * eh[i] + el[i] - 4096 * ys[(l + 1) * 8 + i];
+                // sums[l] += (d*xd) * (float)aux[l], each of the eight lanes on its own (independent chains)
+                acc[i][l] = __fadd_rn(acc[i][l], __fmul_rn(dd[i], (float)(128 * dh[i] + dl[i] - 4096 * ys[l * 8 + i])));
+                acc[i][l + 1] = __fadd_rn(acc[i][l + 1], __fmul_rn(dd[i], (float)(128 * eh[i] + el[i] - 4096 * ys[(l + 1) * 8 + i])));
               }
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) xd[i] = reinterpret_cast<const float *>(recs + g * REC + kRecB1 + 256)[i];
-          }
-          if (has_cols) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float dd = __fmul_rn(dw, xd[i]);  // src/inference.rs:25545
-#pragma unroll
-              for (int l = 0; l < 8; ++l) acc[i][l] = __fadd_rn(acc[i][l], __fmul_rn(dd, (float)E[i][l]));
             }
           }
           release_step(&acc_empty[sc], &b_empty[sb], lane);
@@ -759,14 +751,14 @@ bool gemv_tc5_fits(const GemvJob *jobs, int n_jobs, int32_t batch) {
   return true;
 }
 
-template <int QT, int GW>
+template <int QT, int GW, int EW>
 static int32_t launch_tc(const TcPlan &p, cudaStream_t s) {
   static bool attr = false;
   if (!attr) {
-    CMLD_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<QT, GW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    CMLD_CUDA(cudaFuncSetAttribute(gemv_tc5_kernel<QT, GW, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr = true;
   }
-  gemv_tc5_kernel<QT, GW><<<p.grid, kTcThreads, p.smem, s>>>(p.args);
+  gemv_tc5_kernel<QT, GW, EW><<<p.grid, tc_threads(EW), p.smem, s>>>(p.args);
   CMLD_CUDA(cudaGetLastError());
   return CMLD_OK;
 }
@@ -800,6 +792,11 @@ static int32_t launch_tc5_qt(const GemvJob *jobs, int n_jobs, const uint8_t *act
   const int ng_max = qt == CMLD_Q6_K ? 2 : 4;
   int ng = std::min(a.groups_total, ng_max);
   while (ng > 1 && tiles * (a.groups_total / (ng / 2)) <= g_tc_sms) ng /= 2;
+  // Q6_K keeps 64 f32 sums and 64 integers of a step per epilogue thread: with eight columns per CTA one warp group of
+  // epilogue threads is enough, and the 448-thread form of the kernel gives each thread 144 registers instead of 96
+  // (no spills).  Taken whenever the launch stays within one wave of CTAs.
+  if (qt == CMLD_Q6_K && ng == 2 && tiles * a.groups_total <= g_tc_sms) ng = 1;
+  const int ew = ng == 1 ? 4 : 8;
   a.ng = ng;
   a.n_splits = a.groups_total / ng;
   a.a_stages = qt == CMLD_Q8_0 ? 4 : 2;
@@ -811,7 +808,7 @@ static int32_t launch_tc5_qt(const GemvJob *jobs, int n_jobs, const uint8_t *act
   a.off_act = a.off_raw + raw_bytes;
   // as many activation stages as fit (the copy of a record starts when the epilogue has given its stage back and
   // takes about a microsecond: the ring must cover that)
-  const int scale_bytes = kScaleAhead * kTcEpiWarps * 32 * (qt == CMLD_Q8_0 ? 16 : 4);
+  const int scale_bytes = kScaleAhead * ew * 32 * (qt == CMLD_Q8_0 ? 16 : 4);
   a.act_stages = std::min<int>(kTcMaxActStages, (227 * 1024 - 256 - scale_bytes - a.off_act) / a.act_stage_bytes);
   if (a.act_stages < 2) return CMLD_ERR_UNSUPPORTED;
   a.off_scale = (a.off_act + a.act_stages * a.act_stage_bytes + 15) & ~15;
@@ -831,9 +828,9 @@ static int32_t launch_tc5_qt(const GemvJob *jobs, int n_jobs, const uint8_t *act
   }
   CMLD_CUDA(cudaGetLastError());
   int32_t rc;
-  if (qt == CMLD_Q4_K) rc = p.gw == 2 ? launch_tc<CMLD_Q4_K, 2>(p, s) : launch_tc<CMLD_Q4_K, 1>(p, s);
-  else if (qt == CMLD_Q6_K) rc = launch_tc<CMLD_Q6_K, 1>(p, s);
-  else rc = p.gw == 2 ? launch_tc<CMLD_Q8_0, 2>(p, s) : launch_tc<CMLD_Q8_0, 1>(p, s);
+  if (qt == CMLD_Q4_K) rc = p.gw == 2 ? launch_tc<CMLD_Q4_K, 2, 8>(p, s) : ew == 4 ? launch_tc<CMLD_Q4_K, 1, 4>(p, s) : launch_tc<CMLD_Q4_K, 1, 8>(p, s);
+  else if (qt == CMLD_Q6_K) rc = ew == 4 ? launch_tc<CMLD_Q6_K, 1, 4>(p, s) : launch_tc<CMLD_Q6_K, 1, 8>(p, s);
+  else rc = p.gw == 2 ? launch_tc<CMLD_Q8_0, 2, 8>(p, s) : ew == 4 ? launch_tc<CMLD_Q8_0, 1, 4>(p, s) : launch_tc<CMLD_Q8_0, 1, 8>(p, s);
   CMLD_TRY(rc);
   if (launches) *launches += 2;
   return CMLD_OK;
