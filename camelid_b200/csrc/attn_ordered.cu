@@ -15,10 +15,11 @@
 //     shared memory of the CTAs that need it; the sum over positions is a sequential f32 sum of non-negative
 //     terms, computed with its exact bits by all warps of one CTA per head (exact_sum.cuh);
 //   * output: CTA r of the cluster owns dims [r*hd/8, (r+1)*hd/8) of ALL G heads (G*hd/8 chains), so a V element
-//     it loads serves G chains and the V bytes a CTA needs are 1/8 of the rows.  Producer warps form the products
-//     (e_p/S)*v_pd — V streamed through a cp.async ring that was started when the kernel began, so V arrives
-//     while the scores are still being computed — into double-buffered shared memory; a chain warp walks 32
-//     chains with one load per addition, which costs the additions' own latency (4 cycles each).
+//     it loads serves G chains and the V bytes a CTA needs are 1/8 of the rows.  V is copied by cp.async into
+//     shared memory from the moment the kernel starts, so it arrives while the scores are still being computed.
+//     Contexts of up to 2048 positions keep the CTA's whole V slice there and a chain lane forms its own products
+//     (e_p/S)*v_pd; longer contexts stream V through a ring: producer warps form the products into
+//     double-buffered shared memory and a chain warp walks 32 chains with one 16-byte load per four additions.
 // RoPE of q and k and the f16 KV append can be folded in (fuse_rope), as in the split-range kernel.
 #include <cooperative_groups.h>
 
@@ -298,7 +299,78 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
   // the four next terms of its chain with one 16-byte load.  Hand-over by named barriers: 2 + b = buffer b is
   // full, 4 + b = buffer b is free again.
   constexpr int kHandover = (NPW + NCW) * 32;
-  if (pw >= 0) {
+  if (VD == 32 && warp < NCW) {
+    // Contexts of up to 2048 positions: this CTA's slice of V is wholly in shared memory by now (every ring slot was
+    // requested when the kernel started and nothing is reused), so a chain lane forms its own products: per position
+    // one 2-byte load of v, a quarter of a 16-byte load of the weights, a conversion, a multiplication and the
+    // addition — about as many issue slots as the addition's latency, with no hand-over between warps.
+    const int chain = warp * 32 + lane;
+    const bool valid = chain < CPC;
+    const int g = (valid ? chain : 0) / DPC, dd = (valid ? chain : 0) % DPC, d = d0 + dd;
+    const uint32_t v_addr0 = (uint32_t)__cvta_generic_to_shared(s_v) + (uint32_t)((dd >> 3) * PPB * 16 + (dd & 7) * 2);
+    const uint32_t w_addr0 = (uint32_t)__cvta_generic_to_shared(s_w + g * L.cap_pad);
+    // eight consecutive positions 8u..8u+7 lie in one batch and one producer warp's block: 16 bytes apart
+    auto unit_addr = [&](int u) {
+      const int p = u * 8, bt = p >> 6, r = p & 63;
+      return v_addr0 + (uint32_t)((((r / PPB) * VD + bt) * 512) + (r % PPB) * 16);
+    };
+    float o = 0.0f;
+#define OR_LOAD(U, H, WA, WB)                                                                                       \
+  do {                                                                                                              \
+    const uint32_t va_ = unit_addr(U), wa_ = w_addr0 + (uint32_t)(U) * 32u;                                         \
+    _Pragma("unroll") for (int i_ = 0; i_ < 8; ++i_)                                                                \
+        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(H[i_]) : "r"(va_ + 16u * i_));                                \
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(WA.x), "=f"(WA.y), "=f"(WA.z), "=f"(WA.w) : "r"(wa_)); \
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(WB.x), "=f"(WB.y), "=f"(WB.z), "=f"(WB.w) : "r"(wa_ + 16u)); \
+  } while (0)
+#define OR_ADD(H, WA, WB)                                                          \
+  do {                                                                             \
+    o = __fadd_rn(o, __fmul_rn(WA.x, __half2float(__ushort_as_half(H[0]))));       \
+    o = __fadd_rn(o, __fmul_rn(WA.y, __half2float(__ushort_as_half(H[1]))));       \
+    o = __fadd_rn(o, __fmul_rn(WA.z, __half2float(__ushort_as_half(H[2]))));       \
+    o = __fadd_rn(o, __fmul_rn(WA.w, __half2float(__ushort_as_half(H[3]))));       \
+    o = __fadd_rn(o, __fmul_rn(WB.x, __half2float(__ushort_as_half(H[4]))));       \
+    o = __fadd_rn(o, __fmul_rn(WB.y, __half2float(__ushort_as_half(H[5]))));       \
+    o = __fadd_rn(o, __fmul_rn(WB.z, __half2float(__ushort_as_half(H[6]))));       \
+    o = __fadd_rn(o, __fmul_rn(WB.w, __half2float(__ushort_as_half(H[7]))));       \
+  } while (0)
+    const int nu = n_pre >> 3;  // whole units of eight positions
+    if (nu > 0) {
+      unsigned short HA[8], HB[8];
+      float4 WA0, WA1, WB0, WB1;
+      OR_LOAD(0, HA, WA0, WA1);
+      int u = 0;
+      for (; u + 2 < nu; u += 2) {  // the next unit's loads are in flight under the current unit's additions
+        OR_LOAD(u + 1, HB, WB0, WB1);
+        OR_ADD(HA, WA0, WA1);
+        OR_LOAD(u + 2, HA, WA0, WA1);
+        OR_ADD(HB, WB0, WB1);
+      }
+      if (u + 1 < nu) {
+        OR_LOAD(u + 1, HB, WB0, WB1);
+        OR_ADD(HA, WA0, WA1);
+        OR_ADD(HB, WB0, WB1);
+      } else {
+        OR_ADD(HA, WA0, WA1);
+      }
+    }
+#undef OR_LOAD
+#undef OR_ADD
+    for (int p = nu * 8; p < n_pre; ++p) {
+      const int bt = p >> 6, r = p & 63;
+      const __half hv = *reinterpret_cast<const __half *>(s_v + (((r / PPB) * VD + bt) * 512) + ((dd >> 3) * PPB + (r % PPB)) * 16 + (dd & 7) * 2);
+      o = __fadd_rn(o, __fmul_rn(s_w[g * L.cap_pad + p], __half2float(hv)));
+    }
+    if (a.fuse_rope) {
+      const float vl = __half2float(__float2half_rn(a.v_new[(int64_t)b * a.kv_stride + (int64_t)kvh * HD + d]));
+      o = n_pos == 1 ? vl : __fadd_rn(o, __fmul_rn(s_w[g * L.cap_pad + pos], vl));
+    } else if (n_pos == 1) {
+      o = __half2float(vbase[d]);
+    }
+    if (valid) a.out[(int64_t)b * a.q_stride + ((int64_t)kvh * G + g) * HD + d] = o;
+  } else if (VD == 32) {
+    // the other warps have no part in the output phase of this form
+  } else if (pw >= 0) {
     for (int bt = 0; bt < n_batches; ++bt) {
       const int buf = bt & 1;
       if (bt >= 2) {

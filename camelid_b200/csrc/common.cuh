@@ -235,6 +235,7 @@ struct GemvPeer {
   unsigned long long *trace = nullptr;
 };
 constexpr int kTraceRecords = 4096;
+constexpr int kTraceCtas = 160, kTraceCtaRecords = 1024;  // per-CTA stamps of the staged matvec (same option)
 // Stand-alone form of the receiving side: h[batch][hidden] = sum of the ranks' partials (ops.cu).
 int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, int32_t *status, bool pdl, cudaStream_t s);
 

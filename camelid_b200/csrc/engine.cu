@@ -371,7 +371,7 @@ static int32_t engine_init(cmld_engine *e) {
   }
   if (const char *tp = getenv("CMLD_TRACE")) {
     e->trace_path = std::string(tp) + "." + std::to_string(e->shard_rank);
-    CMLD_TRY(dev_alloc(e, &e->trace, 1 + 8 * (int64_t)kTraceRecords));
+    CMLD_TRY(dev_alloc(e, &e->trace, 1 + 8 * (int64_t)kTraceRecords + (int64_t)kTraceCtas * (1 + 4 * (int64_t)kTraceCtaRecords)));
     CMLD_TRY(dev_alloc(e, &e->attn_phases, 8));
   }
   e->history_cap = 4096;
@@ -421,6 +421,22 @@ static void dump_trace(cmld_engine *e) {
     fprintf(f, "%llu,%lld,%lld,%lld,%lld,%lld,%llu,%llu,%llu,%llu,%lld\n", r[0], (long long)(r[1] - r[0]), (long long)(r[2] - r[0]),
             (long long)(r[3] - r[0]), (long long)(r[4] - r[0]), r[5] ? (long long)(r[5] - r[0]) : -1, r[6] & 0xff, (r[6] >> 8) & 0xff,
             (r[6] >> 16) & 0xff, r[6] >> 32, r[7] ? (long long)(r[7] - r[0]) : -1);
+  }
+  fclose(f);
+  // per-CTA stamps: one line per (CTA, launch) of the last kTraceCtaRecords launches, absolute nanoseconds
+  const size_t per = 1 + 4 * (size_t)kTraceCtaRecords;
+  std::vector<unsigned long long> cta((size_t)kTraceCtas * per);
+  if (cudaMemcpy(cta.data(), e->trace + 1 + 8 * (size_t)kTraceRecords, cta.size() * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return;
+  f = fopen((e->trace_path + ".cta").c_str(), "w");
+  if (!f) return;
+  fprintf(f, "cta,launch,start_ns,visible_ns,prologue_ns,rows_ns\n");
+  for (int b = 0; b < kTraceCtas; ++b) {
+    const unsigned long long cnt = cta[b * per];
+    const unsigned long long lo = cnt > (unsigned long long)kTraceCtaRecords ? cnt - kTraceCtaRecords : 0;
+    for (unsigned long long k = lo; k < cnt; ++k) {
+      const unsigned long long *r = cta.data() + b * per + 1 + 4 * (k % kTraceCtaRecords);
+      fprintf(f, "%d,%llu,%llu,%llu,%llu,%llu\n", b, k, r[0], r[1], r[2], r[3]);
+    }
   }
   fclose(f);
 }

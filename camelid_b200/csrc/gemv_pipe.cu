@@ -583,6 +583,16 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     }
   }
 
+  // per-CTA timeline (same option): CTA b's k-th launch -> four stamps after the per-launch records
+  unsigned long long *trc = nullptr;
+  if (a.peer.trace && tid == 0 && blockIdx.x < kTraceCtas) {
+    unsigned long long *base = a.peer.trace + 1 + 8 * (size_t)kTraceRecords + (size_t)blockIdx.x * (1 + 4 * (size_t)kTraceCtaRecords);
+    const unsigned long long k = base[0];
+    base[0] = k + 1;
+    trc = base + 1 + 4 * (k % kTraceCtaRecords);
+    trc[0] = global_ns();
+  }
+
   if (warp == kPipeAllWarps) {
     // ---------------- producer: weights do not depend on the previous kernel, so no wait here
     if (lane != 0 && a.pf.k) {
@@ -646,6 +656,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   // ---------------- consumers
   asm volatile("griddepcontrol.wait;" ::: "memory");  // inputs written by the previous kernel are now visible
   if (tr) tr[1] = global_ns();
+  if (trc) trc[1] = global_ns();
   const int nsb = a.cols >> 8;
   const int act0_col_stride = (int)round_up16(a.cols) + (int)round_up16((a.cols >> 5) * 4);
 
@@ -797,6 +808,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   }
   asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));
   if (tr) tr[3] = global_ns();
+  if (trc) trc[2] = global_ns();
 
   // Main loop over this CTA's units; group g takes units g, g + kPipeGroups, ...
   const int group = warp / kPipeGroupWarps, wg = warp % kPipeGroupWarps;
@@ -892,6 +904,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     }
   }
   if (tr) tr[4] = global_ns();
+  if (a.peer.trace) {
+    asm volatile("bar.sync 1, %0;" ::"n"(kPipeConsumers));  // the CTA's last row, not thread 0's
+    if (trc) trc[3] = global_ns();
+  }
   if (a.peer.tx_n > 0) {
     // The CTA barrier orders every consumer's stores before thread 0's system-scope fence (fences are
     // cumulative), and the fence before this CTA's ticket; the CTA that takes the last ticket has
