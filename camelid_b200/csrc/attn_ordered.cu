@@ -68,6 +68,70 @@ __device__ __forceinline__ float oa_rope_elem(const float *x, int d, int rope_di
   return first ? __fsub_rn(__fmul_rn(x[d], c), __fmul_rn(x[partner], sn)) : __fadd_rn(__fmul_rn(x[partner], sn), __fmul_rn(x[d], c));
 }
 
+__device__ __forceinline__ void cp_async4(void *dst_smem, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+
+// One output chain over a V slice that is wholly in shared memory as [dim pair][position] half2 words (va: the
+// pair's row; PAR: which half is this chain's dim) with the weights of its head at wa: out = ((0 + w_0*v_0) +
+// w_1*v_1) + ...  Eight positions per trip: four 16-byte loads, issued one trip ahead of the eight dependent
+// additions they feed, so the chain runs at the pace the warp can issue its ~3.5 instructions per position.
+template <int PAR>
+__device__ __forceinline__ float oa_resident_chain(uint32_t va, uint32_t wa, int n_pre) {
+  float o = 0.0f;
+#define OR_CV(X) (PAR ? __high2float(*reinterpret_cast<const __half2 *>(&(X))) : __low2float(*reinterpret_cast<const __half2 *>(&(X))))
+#define OR_LOAD(U, V0, V1, W0, W1)                                                                                            \
+  do {                                                                                                                        \
+    const uint32_t off_ = (uint32_t)(U) * 32u;                                                                                \
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(V0.x), "=r"(V0.y), "=r"(V0.z), "=r"(V0.w) : "r"(va + off_));        \
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(V1.x), "=r"(V1.y), "=r"(V1.z), "=r"(V1.w) : "r"(va + off_ + 16u));  \
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(W0.x), "=f"(W0.y), "=f"(W0.z), "=f"(W0.w) : "r"(wa + off_));        \
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(W1.x), "=f"(W1.y), "=f"(W1.z), "=f"(W1.w) : "r"(wa + off_ + 16u));  \
+  } while (0)
+#define OR_ADD(V0, V1, W0, W1)                          \
+  do {                                                  \
+    o = __fadd_rn(o, __fmul_rn(W0.x, OR_CV(V0.x)));     \
+    o = __fadd_rn(o, __fmul_rn(W0.y, OR_CV(V0.y)));     \
+    o = __fadd_rn(o, __fmul_rn(W0.z, OR_CV(V0.z)));     \
+    o = __fadd_rn(o, __fmul_rn(W0.w, OR_CV(V0.w)));     \
+    o = __fadd_rn(o, __fmul_rn(W1.x, OR_CV(V1.x)));     \
+    o = __fadd_rn(o, __fmul_rn(W1.y, OR_CV(V1.y)));     \
+    o = __fadd_rn(o, __fmul_rn(W1.z, OR_CV(V1.z)));     \
+    o = __fadd_rn(o, __fmul_rn(W1.w, OR_CV(V1.w)));     \
+  } while (0)
+  const int nu = n_pre >> 3;  // whole units of eight positions
+  if (nu > 0) {
+    uint4 A0, A1, B0, B1;
+    float4 WA0, WA1, WB0, WB1;
+    OR_LOAD(0, A0, A1, WA0, WA1);
+    int u = 0;
+    for (; u + 2 < nu; u += 2) {
+      OR_LOAD(u + 1, B0, B1, WB0, WB1);
+      OR_ADD(A0, A1, WA0, WA1);
+      OR_LOAD(u + 2, A0, A1, WA0, WA1);
+      OR_ADD(B0, B1, WB0, WB1);
+    }
+    if (u + 1 < nu) {
+      OR_LOAD(u + 1, B0, B1, WB0, WB1);
+      OR_ADD(A0, A1, WA0, WA1);
+      OR_ADD(B0, B1, WB0, WB1);
+    } else {
+      OR_ADD(A0, A1, WA0, WA1);
+    }
+  }
+  for (int p = nu * 8; p < n_pre; ++p) {
+    uint32_t vw;
+    float w;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(vw) : "r"(va + 4u * p));
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(w) : "r"(wa + 4u * p));
+    o = __fadd_rn(o, __fmul_rn(w, OR_CV(vw)));
+  }
+#undef OR_CV
+#undef OR_LOAD
+#undef OR_ADD
+  return o;
+}
+
 struct OaLayout {
   int cap_range;   // positions a CTA's range can hold
   int cap_pad;     // positions per weight array (multiple of 256)
@@ -92,8 +156,9 @@ __host__ __device__ inline OaLayout oa_layout(int G, int HD, int64_t cap) {
     const int kbytes = 2 * kOaKBlock * (HD * 2 + 16), wbytes = G * L.cap_pad * 4;
     off += kbytes > wbytes ? kbytes : wbytes;
   }
+  const bool resident = oa_vdepth(cap) == 32;  // the CTA's whole V slice stays in shared memory: no product buffers
   L.off_prod = off;
-  off += 2 * (kOaBatch / 4) * (G * dpc * 4 + 4) * 4;  // products: [buffer][4 positions][chain][position in the four] + 4 floats of padding
+  if (!resident) off += 2 * (kOaBatch / 4) * (G * dpc * 4 + 4) * 4;  // products: [buffer][4 positions][chain][position in the four] + 4 floats of padding
   L.off_ws = off;
   off += xsum::workspace_bytes(L.cap_pad);
   off = (off + 15) & ~15;
@@ -105,7 +170,8 @@ __host__ __device__ inline OaLayout oa_layout(int G, int HD, int64_t cap) {
   off += HD * 2;
   off = (off + 127) & ~127;
   L.off_v = off;
-  off += (2 * (dpc / 8)) * oa_vdepth(cap) * 512;  // producer warps x slots x (32 lanes x 16 bytes)
+  if (resident) off += (dpc / 2) * (L.cap_pad * 4 + 16);  // [dim pair][position] half2 words; the row pitch keeps 16-byte loads of eight rows on distinct banks
+  else off += (2 * (dpc / 8)) * oa_vdepth(cap) * 512;     // producer warps x slots x (32 lanes x 16 bytes)
   L.total = off;
   return L;
 }
@@ -165,6 +231,18 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
     }
     cp_async_commit();
   };
+  // Contexts of up to 2048 positions (VD == 32): every thread copies 4-byte pieces (two dims of one position) straight
+  // into the [dim pair][position] layout the chain lanes read, as one group.
+  constexpr bool kResident = VD == 32;
+  constexpr int HP = DPC / 2;
+  const int vt_pitch = L.cap_pad * 4 + 16;
+  auto issue_v_resident = [&]() {
+    for (int idx = tid; idx < n_pre * HP; idx += kOaThreads) {
+      const int p = idx / HP, j = idx % HP;
+      cp_async4(s_v + j * vt_pitch + p * 4, vbase + (int64_t)p * HD + d0 + 2 * j);
+    }
+    cp_async_commit();
+  };
   // ranges: CTA r scores positions [r*len, (r+1)*len), in n_blocks blocks of bsz positions
   const int len = (n_pos + kOaCluster - 1) / kOaCluster;
   const int lo = crank * len, hi = min(n_pos, lo + len);
@@ -185,14 +263,16 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
   if (a.fuse_rope) {
     issue_k(0);
     issue_k(1);
-    if (pw >= 0)
+    if (kResident) issue_v_resident();
+    else if (pw >= 0)
       for (int c = 0; c < VD; ++c) issue_v(c);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   if (!a.fuse_rope) {
     issue_k(0);
     issue_k(1);
-    if (pw >= 0)
+    if (kResident) issue_v_resident();
+    else if (pw >= 0)
       for (int c = 0; c < VD; ++c) issue_v(c);
   }
 
@@ -221,8 +301,9 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
   for (int blk = 0; blk < n_blocks; ++blk) {
     // groups in flight, oldest first: K block blk, K block blk+1, then (producer warps) the V ring's first VD slots
     // or, from the second pass on, nothing younger: wait until block blk has landed
-    if (blk == 0 && pw >= 0) cp_async_wait<VD + 1>();
-    else if (blk == 0) cp_async_wait<1>();
+    // (resident form: K block 0, K block 1, the V group, then one K group per pass)
+    if (kResident && blk < 2) cp_async_wait<2>();
+    else if (!kResident && blk == 0 && pw >= 0) cp_async_wait<VD + 1>();
     else cp_async_wait<1>();
     __syncthreads();  // block blk has landed for everyone (the first pass also publishes s_q and s_klast)
     const uint8_t *kb = s_k + (blk & 1) * kOaKBlock * KP;
@@ -299,77 +380,28 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
   // the four next terms of its chain with one 16-byte load.  Hand-over by named barriers: 2 + b = buffer b is
   // full, 4 + b = buffer b is free again.
   constexpr int kHandover = (NPW + NCW) * 32;
-  if (VD == 32 && warp < NCW) {
-    // Contexts of up to 2048 positions: this CTA's slice of V is wholly in shared memory by now (every ring slot was
-    // requested when the kernel started and nothing is reused), so a chain lane forms its own products: per position
-    // one 2-byte load of v, a quarter of a 16-byte load of the weights, a conversion, a multiplication and the
-    // addition — about as many issue slots as the addition's latency, with no hand-over between warps.
-    const int chain = warp * 32 + lane;
-    const bool valid = chain < CPC;
-    const int g = (valid ? chain : 0) / DPC, dd = (valid ? chain : 0) % DPC, d = d0 + dd;
-    const uint32_t v_addr0 = (uint32_t)__cvta_generic_to_shared(s_v) + (uint32_t)((dd >> 3) * PPB * 16 + (dd & 7) * 2);
-    const uint32_t w_addr0 = (uint32_t)__cvta_generic_to_shared(s_w + g * L.cap_pad);
-    // eight consecutive positions 8u..8u+7 lie in one batch and one producer warp's block: 16 bytes apart
-    auto unit_addr = [&](int u) {
-      const int p = u * 8, bt = p >> 6, r = p & 63;
-      return v_addr0 + (uint32_t)((((r / PPB) * VD + bt) * 512) + (r % PPB) * 16);
-    };
-    float o = 0.0f;
-#define OR_LOAD(U, H, WA, WB)                                                                                       \
-  do {                                                                                                              \
-    const uint32_t va_ = unit_addr(U), wa_ = w_addr0 + (uint32_t)(U) * 32u;                                         \
-    _Pragma("unroll") for (int i_ = 0; i_ < 8; ++i_)                                                                \
-        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(H[i_]) : "r"(va_ + 16u * i_));                                \
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(WA.x), "=f"(WA.y), "=f"(WA.z), "=f"(WA.w) : "r"(wa_)); \
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(WB.x), "=f"(WB.y), "=f"(WB.z), "=f"(WB.w) : "r"(wa_ + 16u)); \
-  } while (0)
-#define OR_ADD(H, WA, WB)                                                          \
-  do {                                                                             \
-    o = __fadd_rn(o, __fmul_rn(WA.x, __half2float(__ushort_as_half(H[0]))));       \
-    o = __fadd_rn(o, __fmul_rn(WA.y, __half2float(__ushort_as_half(H[1]))));       \
-    o = __fadd_rn(o, __fmul_rn(WA.z, __half2float(__ushort_as_half(H[2]))));       \
-    o = __fadd_rn(o, __fmul_rn(WA.w, __half2float(__ushort_as_half(H[3]))));       \
-    o = __fadd_rn(o, __fmul_rn(WB.x, __half2float(__ushort_as_half(H[4]))));       \
-    o = __fadd_rn(o, __fmul_rn(WB.y, __half2float(__ushort_as_half(H[5]))));       \
-    o = __fadd_rn(o, __fmul_rn(WB.z, __half2float(__ushort_as_half(H[6]))));       \
-    o = __fadd_rn(o, __fmul_rn(WB.w, __half2float(__ushort_as_half(H[7]))));       \
-  } while (0)
-    const int nu = n_pre >> 3;  // whole units of eight positions
-    if (nu > 0) {
-      unsigned short HA[8], HB[8];
-      float4 WA0, WA1, WB0, WB1;
-      OR_LOAD(0, HA, WA0, WA1);
-      int u = 0;
-      for (; u + 2 < nu; u += 2) {  // the next unit's loads are in flight under the current unit's additions
-        OR_LOAD(u + 1, HB, WB0, WB1);
-        OR_ADD(HA, WA0, WA1);
-        OR_LOAD(u + 2, HA, WA0, WA1);
-        OR_ADD(HB, WB0, WB1);
+  constexpr int HW = (G * HP + 31) / 32;  // resident form: chain warps per parity of the dim
+  static_assert(2 * HW <= kOaWarps, "too many chains");
+  if (kResident) {
+    // Warp w walks the chains of the even (w even) or odd dims: lane -> (head g, dim pair j); the parity being uniform
+    // in a warp, the f16 -> f32 conversion picks its half of the word without a select.
+    if (warp < 2 * HW) {
+      const int parity = warp & 1, li = (warp >> 1) * 32 + lane;
+      const bool valid = li < G * HP;
+      const int g = (valid ? li : 0) / HP, j = (valid ? li : 0) % HP, d = d0 + 2 * j + parity;
+      const uint32_t va = (uint32_t)__cvta_generic_to_shared(s_v + j * vt_pitch);
+      const uint32_t wa = (uint32_t)__cvta_generic_to_shared(s_w + g * L.cap_pad);
+      // the row's own V (rounded through f16 as the cache holds it): requested before the chain, used after it
+      const float v_own = a.fuse_rope ? __ldg(a.v_new + (int64_t)b * a.kv_stride + (int64_t)kvh * HD + d) : 0.0f;
+      float o = parity ? oa_resident_chain<1>(va, wa, n_pre) : oa_resident_chain<0>(va, wa, n_pre);
+      if (a.fuse_rope) {
+        const float vl = __half2float(__float2half_rn(v_own));
+        o = n_pos == 1 ? vl : __fadd_rn(o, __fmul_rn(s_w[g * L.cap_pad + pos], vl));
+      } else if (n_pos == 1) {
+        o = __half2float(vbase[d]);  // a single cached position: the context is a copy of V (src/inference.rs:29858-29951)
       }
-      if (u + 1 < nu) {
-        OR_LOAD(u + 1, HB, WB0, WB1);
-        OR_ADD(HA, WA0, WA1);
-        OR_ADD(HB, WB0, WB1);
-      } else {
-        OR_ADD(HA, WA0, WA1);
-      }
+      if (valid) a.out[(int64_t)b * a.q_stride + ((int64_t)kvh * G + g) * HD + d] = o;
     }
-#undef OR_LOAD
-#undef OR_ADD
-    for (int p = nu * 8; p < n_pre; ++p) {
-      const int bt = p >> 6, r = p & 63;
-      const __half hv = *reinterpret_cast<const __half *>(s_v + (((r / PPB) * VD + bt) * 512) + ((dd >> 3) * PPB + (r % PPB)) * 16 + (dd & 7) * 2);
-      o = __fadd_rn(o, __fmul_rn(s_w[g * L.cap_pad + p], __half2float(hv)));
-    }
-    if (a.fuse_rope) {
-      const float vl = __half2float(__float2half_rn(a.v_new[(int64_t)b * a.kv_stride + (int64_t)kvh * HD + d]));
-      o = n_pos == 1 ? vl : __fadd_rn(o, __fmul_rn(s_w[g * L.cap_pad + pos], vl));
-    } else if (n_pos == 1) {
-      o = __half2float(vbase[d]);
-    }
-    if (valid) a.out[(int64_t)b * a.q_stride + ((int64_t)kvh * G + g) * HD + d] = o;
-  } else if (VD == 32) {
-    // the other warps have no part in the output phase of this form
   } else if (pw >= 0) {
     for (int bt = 0; bt < n_batches; ++bt) {
       const int buf = bt & 1;

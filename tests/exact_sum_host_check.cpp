@@ -1,5 +1,5 @@
-// Host build of exact_sum.cuh: the per-item arithmetic, the composition of runs and the event walk are the
-// code the kernels run; the warp scan is replaced by a loop.  Compares with the plain sequential f32 sum
+// Host build of exact_sum.cuh: the per-item arithmetic and the checked event walk are the code the kernels
+// run; the warp scan that sums runs is replaced by a loop.  Compares with the plain sequential f32 sum
 // over thousands of seeded arrays (outliers, exact ties, zeros, powers of two, tiny and huge terms).
 #include <cstdio>
 #include <cstdlib>
@@ -18,26 +18,26 @@ static float emu(const std::vector<float> &sq) {
   float base = 0;
   for (int c = 0; c < nch; ++c) {
     Item items[32];
-    uint32_t e[32], d0[32], d1[32];
+    uint32_t e[32], d[32];
     float a = base;
     for (int l = 0; l < 32; ++l) {
       float t[8];
       for (int i = 0; i < 8; ++i) t[i] = sq[c * 256 + l * 8 + i];
       float a_end = a;
       for (int i = 0; i < 8; ++i) a_end += t[i];
-      e[l] = item_local(t, a, a_end, d0[l], d1[l]);
+      e[l] = item_local(t, a, a_end, d[l]);
       a = a_end;
     }
     uint32_t events = 0;
     int rs = 0;
-    uint32_t c0 = 0, c1 = 0;
+    uint32_t acc = 0;
     for (int l = 0; l < 32; ++l) {
       bool boundary = l == 0 || e[l] == kSlow || e[l - 1] == kSlow || e[l] != e[l - 1];
-      if (boundary) { rs = l; c0 = d0[l]; c1 = d1[l]; }
-      else { uint32_t h0, h1; compose(c0, c1, d0[l], d1[l], h0, h1); c0 = h0; c1 = h1; }
-      bool too_big = e[l] != kSlow && ((c0 | c1) >> 24);
-      items[l].w0 = (too_big ? 0xffffffu : c0) | (e[l] << 24);
-      items[l].w1 = (too_big ? 0xffffffu : c1) | ((uint32_t)rs << 24);
+      if (boundary) { rs = l; acc = d[l]; }
+      else acc += d[l];
+      bool too_big = e[l] != kSlow && (acc >> 24);
+      items[l].w0 = (too_big ? 0xffffffu : acc) | (e[l] << 24);
+      items[l].w1 = (uint32_t)rs;
       bool next_boundary = l == 31 || e[l + 1] == kSlow || e[l] == kSlow || e[l + 1] != e[l];
       if (e[l] == kSlow || next_boundary) events |= 1u << l;
     }
@@ -46,7 +46,7 @@ static float emu(const std::vector<float> &sq) {
       float s2 = s; uint32_t ev = events;
       while (ev) { int lane = __builtin_ctz(ev); ev &= ev - 1; ++g_events;
         Item it = items[lane]; uint32_t ee = it.w0 >> 24; int first = lane; bool fast = false;
-        if (ee != kSlow) { uint32_t sb = f32_bits(s2); if ((sb >> 23) == ee) { uint32_t m = sb & 0x7fffff; uint32_t d = ((m & 1) ? it.w1 : it.w0) & 0xffffff; if (m + d < 0x800000u) { s2 = bits_f32(sb + d); fast = true; } } if (!fast) first = it.w1 >> 24; }
+        if (ee != kSlow) { uint32_t sb = f32_bits(s2); if ((sb >> 23) == ee) { uint32_t m = sb & 0x7fffff; uint32_t dd = it.w0 & 0xffffff; if (m + dd < 0x800000u) { s2 = bits_f32(sb + dd); fast = true; } } if (!fast) first = it.w1; }
         if (!fast) { for (int i = first * 8; i < (lane + 1) * 8; ++i) { s2 = add_rn(s2, sq[c * 256 + i]); ++g_replayed; } }
       }
     }

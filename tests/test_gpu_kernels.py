@@ -296,6 +296,51 @@ def test_rms_norm_and_swiglu(cm, orc, cols, batch):
     assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))  # expf restated from glibc: the same bits
 
 
+# The sum of squares is evaluated in parallel with the sequential sum's bits (runs of additions inside one binade
+# applied as integer steps, ties and binade crossings replayed): rows built to hit the replay paths.
+@pytest.mark.parametrize("cols", [4096, 8192, 1024])
+def test_rms_norm_sum_of_squares_is_the_sequential_sum(cm, orc, cols):
+    from camelid_b200.engine import DeviceBuffer
+    from camelid_b200._lib import check
+
+    rng = np.random.default_rng(cols + 5)
+    rows = []
+    for mode in range(12):
+        sigma = 10.0 ** rng.integers(-6, 7)
+        x = rng.standard_normal(cols).astype(np.float32) * np.float32(sigma)
+        if mode == 1:
+            x[rng.random(cols) < 0.01] *= 100.0                      # outliers
+        if mode == 2:
+            x = (rng.integers(0, 64, cols) / 8.0).astype(np.float32)  # few mantissa bits: many ties
+        if mode == 3:
+            x[rng.random(cols) < 0.66] = 0.0                          # zeros
+        if mode == 4:
+            x = np.ldexp(rng.integers(1, 5, cols).astype(np.float32), rng.integers(-10, 10, cols)).astype(np.float32)
+        if mode == 5:
+            x[:100] = 0.0                                             # leading zeros
+        if mode == 6:
+            x[700] = 1e4                                              # one giant
+        if mode == 7:
+            x[:] = 1.0                                                # constant
+        if mode == 8:
+            x = (0.5 + rng.integers(0, 2, cols)).astype(np.float32)   # ties everywhere
+        if mode == 9:
+            x = (rng.standard_normal(cols) * 1e-18).astype(np.float32)  # squares in the subnormal range
+        if mode == 10:
+            x = (rng.standard_normal(cols) * 1e15).astype(np.float32)
+        if mode == 11:
+            x = np.sqrt((rng.integers(1, 1025, cols) * 0.5)).astype(np.float32)
+        rows.append(x.astype(np.float32))
+    x = np.stack(rows)
+    wgt = np.ones(cols, np.float32)
+    xd, wd, od = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(wgt), DeviceBuffer(x.nbytes)
+    check(cm.lib().cmld_rms_norm(xd.ptr, wd.ptr, cols, len(rows), 1e-5, od.ptr, 0, None))
+    out = od.to_numpy(np.float32).reshape(len(rows), cols)
+    for b in range(len(rows)):
+        ref = orc.rms_norm(x[b], wgt, 1e-5)
+        assert np.array_equal(out[b].view(np.uint32), ref.view(np.uint32)), b
+
+
 def test_argmax_lowest_index_wins(cm, orc):
     from camelid_b200.engine import DeviceBuffer
     from camelid_b200._lib import check
