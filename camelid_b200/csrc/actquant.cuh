@@ -16,25 +16,18 @@ namespace cmld {
 // All 32 lanes must call.  q: this lane's 8 codes; d: the chunk's scale (same in every lane).
 __device__ __forceinline__ void q8k_quantise_chunk(const float (&v)[8], int lane, int (&q)[8], float &d) {
   float amax = 0.0f, mx = 0.0f;
-  int idx = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i)
     if (fabsf(v[i]) > amax) {
       amax = fabsf(v[i]);
       mx = v[i];
-      idx = lane * 8 + i;
     }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
-    const float om = __shfl_xor_sync(0xffffffffu, mx, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (oa > amax || (oa == amax && oi < idx)) {
-      amax = oa;
-      mx = om;
-      idx = oi;
-    }
-  }
+  // the chunk's largest |v|, and among equals the first: |v| >= 0 compares like its bits, lanes hold the values in order
+  const uint32_t ab = __float_as_uint(amax);
+  const uint32_t wmax = __reduce_max_sync(0xffffffffu, ab);
+  const int src = __ffs((int)__ballot_sync(0xffffffffu, ab == wmax)) - 1;
+  mx = __shfl_sync(0xffffffffu, mx, src);
+  amax = __uint_as_float(wmax);
   d = 0.0f;
   if (amax == 0.0f) {
 #pragma unroll
@@ -61,10 +54,15 @@ __device__ __forceinline__ void q80_quantise_chunk(const float (&v)[8], int (&q)
   scale = f16_bits_to_f32(f32_to_f16_bits(du));
 }
 
+// Eight codes (each within int8) as bytes, the first lowest.
 __device__ __forceinline__ uint2 pack8(const int (&q)[8]) {
   uint2 p;
-  p.x = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((q[3] & 0xff) << 24);
-  p.y = (q[4] & 0xff) | ((q[5] & 0xff) << 8) | ((q[6] & 0xff) << 16) | ((q[7] & 0xff) << 24);
+  uint32_t t;
+  // cvt.pack d, a, b, c: d = (c << 16) | (byte(a) << 8) | byte(b)
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(q[3]), "r"(q[2]), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(p.x) : "r"(q[1]), "r"(q[0]), "r"(t));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(q[7]), "r"(q[6]), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(p.y) : "r"(q[5]), "r"(q[4]), "r"(t));
   return p;
 }
 
