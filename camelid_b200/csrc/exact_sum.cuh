@@ -162,40 +162,39 @@ __device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], float
   return __ballot_sync(0xffffffffu, e == kSlow || run_end);
 }
 
-// One event of the flat list the walker goes through: a run (or a slow item) and where its terms are.
+// One event of the flat list the walker goes through.  Every event is "one integer step, then eight f32 additions":
+// a run has its increment and eight zeros, a slow item a zero increment and its own eight terms — so the walk
+// is one straight line of code without a branch (a lone thread pays tens of cycles for every taken branch).
 struct Event {
   uint32_t d;        // the run's increment (0 for a slow item)
-  uint32_t ebits;    // the run's binade as f32 exponent bits (e << 23); kSlowBits for a slow item
-  uint32_t first;    // index in sq of the first term to replay if the run's step cannot be taken; kPadFirst: a padding event
-  uint32_t taddr;    // shared-memory address of the eight terms before the event's end (a slow item: its own terms)
+  uint32_t ebits;    // the run's binade as f32 exponent bits (e << 23)
+  uint32_t span;     // items [bits 0-10, bits 11-21) of sq that the event covers (replayed if the step cannot be taken); bit 31: a run
+  uint32_t taddr;    // shared-memory address of the eight terms to add after the step (a run, padding: eight zeros)
 };
-constexpr uint32_t kSlowBits = 0xffffffffu;
-constexpr uint32_t kPadFirst = 0xffffffffu;
+constexpr uint32_t kRunFlag = 0x80000000u;
 constexpr int kWalkUnroll = 6;  // the walk's trip: records rotate through three registers sets, terms through two
 
 // The walk, every step checked: a run whose step cannot be taken is replayed term by term.
 static __device__ __noinline__ float walk_events_checked(const float *sq, const Event *ev, int n_events) {
-  const uint32_t sq_addr = (uint32_t)__cvta_generic_to_shared(sq);
   float s = 0.0f;
   for (int k = 0; k < n_events; ++k) {
     const Event cur = ev[k];
-    if (cur.first == kPadFirst) continue;
     const uint32_t sb = __float_as_uint(s), t = sb - cur.ebits;
-    if (cur.ebits != kSlowBits && t < 0x800000u && t + cur.d < 0x800000u) {
+    if ((cur.span & kRunFlag) && t < 0x800000u && t + cur.d < 0x800000u) {
       s = __uint_as_float(sb + cur.d);
     } else {
-      const uint32_t end = ((cur.taddr - sq_addr) >> 2) + kItem;
-      for (uint32_t i = cur.first; i < end; ++i) s = __fadd_rn(s, sq[i]);
+      const uint32_t first = (cur.span & 0x7ffu) * kItem, end = ((cur.span >> 11) & 0x7ffu) * kItem;
+      for (uint32_t i = first; i < end; ++i) s = __fadd_rn(s, sq[i]);
     }
   }
   return s;
 }
 
 // The walk over the whole list (n_events a multiple of kWalkUnroll, two more readable records behind it).  s is
-// the only loop-carried value and no branch depends on it: a run is one integer addition, a slow item eight f32
-// additions; whether every run started and ended inside its binade is collected on the side.  Records are
-// fetched two events ahead and an event's terms one event ahead, into registers that rotate with the unrolled
-// trip, so the loads are never waited for and nothing is moved.  Falls back to the checked walk if a run did not fit.
+// the only loop-carried value and no branch depends on anything: whether every run started and ended inside its
+// binade is collected on the side, in the issue slots the dependent additions leave free.  Records are fetched two
+// events ahead and an event's terms one event ahead, into registers that rotate with the unrolled trip, so the
+// loads are never waited for and nothing is moved.  Falls back to the checked walk if a run did not fit.
 __device__ __forceinline__ float walk_events(const float *sq, const Event *ev, int n_events) {
   uint32_t sb = 0, bad = 0;
   uint32_t ea = (uint32_t)__cvta_generic_to_shared(ev);
@@ -207,26 +206,23 @@ __device__ __forceinline__ float walk_events(const float *sq, const Event *ev, i
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(A.x), "=f"(A.y), "=f"(A.z), "=f"(A.w) : "r"(H.w));       \
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(B.x), "=f"(B.y), "=f"(B.z), "=f"(B.w) : "r"(H.w + 16u)); \
   } while (0)
-#define XS_STEP(K, HC, HN, HNN, AC, BC, AN, BN)               \
-  do {                                                        \
-    XS_LDH(HNN, ea + 16u * ((K) + 2));                        \
-    XS_LDT(AN, BN, HN);                                       \
-    if (HC.y != kSlowBits) {                                  \
-      const uint32_t t_ = sb - HC.y;                          \
-      bad |= (t_ | (t_ + HC.x)) & 0xff800000u;                \
-      sb += HC.x;                                             \
-    } else {                                                  \
-      float s_ = __uint_as_float(sb);                         \
-      s_ = __fadd_rn(s_, AC.x);                               \
-      s_ = __fadd_rn(s_, AC.y);                               \
-      s_ = __fadd_rn(s_, AC.z);                               \
-      s_ = __fadd_rn(s_, AC.w);                               \
-      s_ = __fadd_rn(s_, BC.x);                               \
-      s_ = __fadd_rn(s_, BC.y);                               \
-      s_ = __fadd_rn(s_, BC.z);                               \
-      s_ = __fadd_rn(s_, BC.w);                               \
-      sb = __float_as_uint(s_);                               \
-    }                                                         \
+#define XS_STEP(K, HC, HN, HNN, AC, BC, AN, BN)                                        \
+  do {                                                                                 \
+    XS_LDH(HNN, ea + 16u * ((K) + 2));                                                 \
+    XS_LDT(AN, BN, HN);                                                                \
+    const uint32_t t_ = sb - HC.y;                                                     \
+    sb += HC.x;                                                                        \
+    float s_ = __uint_as_float(sb);                                                    \
+    s_ = __fadd_rn(s_, AC.x);                                                          \
+    bad |= (t_ | (t_ + HC.x)) & (uint32_t)((int32_t)HC.z >> 31); /* t >= 2^23: s is not in the binade; t + d >= 2^23: it would leave it */ \
+    s_ = __fadd_rn(s_, AC.y);                                                          \
+    s_ = __fadd_rn(s_, AC.z);                                                          \
+    s_ = __fadd_rn(s_, AC.w);                                                          \
+    s_ = __fadd_rn(s_, BC.x);                                                          \
+    s_ = __fadd_rn(s_, BC.y);                                                          \
+    s_ = __fadd_rn(s_, BC.z);                                                          \
+    s_ = __fadd_rn(s_, BC.w);                                                          \
+    sb = __float_as_uint(s_);                                                          \
   } while (0)
   XS_LDH(H0, ea);
   XS_LDH(H1, ea + 16u);
@@ -243,7 +239,7 @@ __device__ __forceinline__ float walk_events(const float *sq, const Event *ev, i
 #undef XS_LDH
 #undef XS_LDT
 #undef XS_STEP
-  if (bad) return walk_events_checked(sq, ev, n_events);
+  if (bad >> 23) return walk_events_checked(sq, ev, n_events);
   return __uint_as_float(sb);
 }
 
@@ -306,26 +302,27 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
     const uint32_t mine = ws_mask[ch];
+    const uint32_t zero_addr = (uint32_t)__cvta_generic_to_shared(ws_zero);
     if ((mine >> lane) & 1u) {
       const Item it = ws_items[ch * 32 + lane];
       const bool slow = (it.w0 >> 24) == kSlow;
-      const uint32_t end = (uint32_t)(ch * kChunk + (lane + 1) * kItem);
+      const uint32_t end_item = (uint32_t)(ch * 32 + lane + 1);
       Event e;
       e.d = slow ? 0u : (it.w0 & 0xffffffu);
-      e.ebits = slow ? kSlowBits : ((it.w0 >> 24) << 23);
-      e.first = slow ? end - kItem : (uint32_t)(ch * kChunk + (int)it.w1 * kItem);
-      e.taddr = sq_addr + (end - kItem) * 4u;
+      e.ebits = slow ? 0u : ((it.w0 >> 24) << 23);
+      e.span = slow ? ((end_item - 1) | (end_item << 11)) : ((uint32_t)(ch * 32 + (int)it.w1) | (end_item << 11) | kRunFlag);
+      e.taddr = slow ? sq_addr + (end_item - 1) * (kItem * 4u) : zero_addr;
       ws_events[before + __popc(mine & ((1u << lane) - 1u))] = e;
     }
     if (ch == n_chunks - 1) {
-      // padding: slow events that add eight zeros, up to the walk's trip and two records beyond it
+      // padding (no step, eight zeros) up to the walk's trip and two records beyond it
       const int total = before + __popc(mine);
       if (lane < kWalkUnroll + 1) {
         Event e;
         e.d = 0u;
-        e.ebits = kSlowBits;
-        e.first = kPadFirst;
-        e.taddr = (uint32_t)__cvta_generic_to_shared(ws_zero);
+        e.ebits = 0u;
+        e.span = 0u;
+        e.taddr = zero_addr;
         ws_events[total + lane] = e;
       }
       if (lane == 0) *ws_total = (total + kWalkUnroll - 1) / kWalkUnroll * kWalkUnroll;
