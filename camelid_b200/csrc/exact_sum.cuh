@@ -18,11 +18,12 @@
 // into a new binade, the rare ones with a tie, and the very first) are "slow".  Runs of fast items
 // with the same binade inside a 256-term chunk are summed with a warp scan.  Finally one thread walks
 // the events (run ends and slow items) in order with the exact s: a run is applied as one integer
-// addition, a slow item is replayed term by term with real f32 additions.  The walk first runs
-// without branching on s — it only records whether every run really started and ended inside its
-// predicted binade — and is repeated with the check in front of every step (replaying a failed run
-// term by term) in the rare case that one did not.  Every path yields the sequential sum's bits; the
-// prediction only decides how much is replayed.
+// addition, a slow item is replayed term by term with real f32 additions.  Every record of the walk
+// has the same shape — a run's integer step, then the eight terms of the slow item behind it (zeros
+// if there is none) — so the walk runs without a branch; it only records on the side whether every
+// run really started and ended inside its predicted binade, and is repeated with the check in front
+// of every step (replaying a failed run term by term) in the rare case that one did not.  Every
+// path yields the sequential sum's bits; the prediction only decides how much is replayed.
 #pragma once
 
 #include <cstdint>
@@ -139,7 +140,7 @@ XS_HD float walk_chunk(float s, const float *sq, const Item *items, uint32_t eve
 // Device side.  A warp prepares one chunk: lane l holds terms [8l, 8l+8) of the chunk in t[], and
 // a_start is the approximate prefix sum at the lane's first term.  Writes the chunk's items
 // (summed along runs) and returns the event mask (same value in every lane).
-__device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], float a_start, float a_end, int lane, Item *items) {
+__device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], float a_start, float a_end, int lane, Item *items, uint32_t &slow_mask) {
   uint32_t d;
   const uint32_t e = item_local(t, a_start, a_end, d);
   const uint32_t e_prev = __shfl_up_sync(0xffffffffu, e, 1);
@@ -159,32 +160,41 @@ __device__ __forceinline__ uint32_t prepare_chunk(const float (&t)[kItem], float
   it.w1 = (uint32_t)rs;
   items[lane] = it;
   const bool run_end = lane == 31 || ((bmask >> (lane + 1)) & 1u);
+  slow_mask = __ballot_sync(0xffffffffu, e == kSlow);
   return __ballot_sync(0xffffffffu, e == kSlow || run_end);
 }
 
 // One event of the flat list the walker goes through.  Every event is "one integer step, then eight f32 additions":
-// a run has its increment and eight zeros, a slow item a zero increment and its own eight terms — so the walk
-// is one straight line of code without a branch (a lone thread pays tens of cycles for every taken branch).
+// a run has its increment and, if the item behind it is slow, that item's eight terms (else eight zeros); a slow item
+// that follows another slow item (or nothing) has a zero increment and its own terms — so the walk is one straight
+// line of code without a branch (a lone thread pays tens of cycles for every taken branch).
 struct Event {
-  uint32_t d;        // the run's increment (0 for a slow item)
+  uint32_t d;        // the run's increment (0 without a run)
   uint32_t ebits;    // the run's binade as f32 exponent bits (e << 23)
-  uint32_t span;     // items [bits 0-10, bits 11-21) of sq that the event covers (replayed if the step cannot be taken); bit 31: a run
-  uint32_t taddr;    // shared-memory address of the eight terms to add after the step (a run, padding: eight zeros)
+  uint32_t span;     // the run: items [bits 0-10, bits 11-21) of sq (replayed if the step cannot be taken); bit 31: there is a run
+  uint32_t taddr;    // shared-memory address of the eight terms to add after the step (none: eight zeros)
 };
 constexpr uint32_t kRunFlag = 0x80000000u;
 constexpr int kWalkUnroll = 6;  // the walk's trip: records rotate through three registers sets, terms through two
 
 // The walk, every step checked: a run whose step cannot be taken is replayed term by term.
-static __device__ __noinline__ float walk_events_checked(const float *sq, const Event *ev, int n_events) {
+static __device__ __noinline__ float walk_events_checked(const float *sq, const Event *ev, int n_events, uint32_t zero_addr) {
+  const uint32_t sq_addr = (uint32_t)__cvta_generic_to_shared(sq);
   float s = 0.0f;
   for (int k = 0; k < n_events; ++k) {
     const Event cur = ev[k];
-    const uint32_t sb = __float_as_uint(s), t = sb - cur.ebits;
-    if ((cur.span & kRunFlag) && t < 0x800000u && t + cur.d < 0x800000u) {
-      s = __uint_as_float(sb + cur.d);
-    } else {
-      const uint32_t first = (cur.span & 0x7ffu) * kItem, end = ((cur.span >> 11) & 0x7ffu) * kItem;
-      for (uint32_t i = first; i < end; ++i) s = __fadd_rn(s, sq[i]);
+    if (cur.span & kRunFlag) {
+      const uint32_t sb = __float_as_uint(s), t = sb - cur.ebits;
+      if (t < 0x800000u && t + cur.d < 0x800000u) {
+        s = __uint_as_float(sb + cur.d);
+      } else {
+        const uint32_t first = (cur.span & 0x7ffu) * kItem, end = ((cur.span >> 11) & 0x7ffu) * kItem;
+        for (uint32_t i = first; i < end; ++i) s = __fadd_rn(s, sq[i]);
+      }
+    }
+    if (cur.taddr != zero_addr) {
+      const float *t = sq + ((cur.taddr - sq_addr) >> 2);
+      for (int i = 0; i < kItem; ++i) s = __fadd_rn(s, t[i]);
     }
   }
   return s;
@@ -195,7 +205,7 @@ static __device__ __noinline__ float walk_events_checked(const float *sq, const 
 // binade is collected on the side, in the issue slots the dependent additions leave free.  Records are fetched two
 // events ahead and an event's terms one event ahead, into registers that rotate with the unrolled trip, so the
 // loads are never waited for and nothing is moved.  Falls back to the checked walk if a run did not fit.
-__device__ __forceinline__ float walk_events(const float *sq, const Event *ev, int n_events) {
+__device__ __forceinline__ float walk_events(const float *sq, const Event *ev, int n_events, uint32_t zero_addr) {
   uint32_t sb = 0, bad = 0;
   uint32_t ea = (uint32_t)__cvta_generic_to_shared(ev);
   uint4 H0, H1, H2;
@@ -239,7 +249,7 @@ __device__ __forceinline__ float walk_events(const float *sq, const Event *ev, i
 #undef XS_LDH
 #undef XS_LDT
 #undef XS_STEP
-  if (bad >> 23) return walk_events_checked(sq, ev, n_events);
+  if (bad >> 23) return walk_events_checked(sq, ev, n_events, zero_addr);
   return __uint_as_float(sb);
 }
 
@@ -252,6 +262,7 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
   constexpr int kTrips = (32 + NWARPS - 1) / NWARPS;  // chunks a warp may own (chunk = warp + trip * NWARPS)
   const int n_chunks = n >> 8;  // at most 32
   float *ws_chunk = reinterpret_cast<float *>(ws);                      // [32] chunk sums (approximate)
+  uint32_t *ws_slow = reinterpret_cast<uint32_t *>(ws + 128);           // [32] slow items per chunk
   uint32_t *ws_mask = reinterpret_cast<uint32_t *>(ws + 256);           // [32] event lanes per chunk
   float *ws_out = reinterpret_cast<float *>(ws + 384);
   int *ws_total = reinterpret_cast<int *>(ws + 388);                    // number of events, padded to the walk's trip
@@ -290,33 +301,56 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
       float base = lane < ch ? ws_chunk[lane] : 0.0f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
-      const uint32_t ev = prepare_chunk(tt[trip], base + (incl_[trip] - loc_[trip]), base + incl_[trip], lane, ws_items + ch * 32);
-      if (lane == 0) ws_mask[ch] = ev;
+      uint32_t slow_mask;
+      const uint32_t ev = prepare_chunk(tt[trip], base + (incl_[trip] - loc_[trip]), base + incl_[trip], lane, ws_items + ch * 32, slow_mask);
+      if (lane == 0) {
+        ws_mask[ch] = ev;
+        ws_slow[ch] = slow_mask;
+      }
     }
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
-  // the events of all chunks as one list, in order
+  // The events of all chunks as one list, in order.  A slow item whose previous item is fast rides on that run's
+  // record (the run's step, then the item's eight terms); every other event lane owns a record.
   const uint32_t sq_addr = (uint32_t)__cvta_generic_to_shared(sq);
+  const uint32_t zero_addr = (uint32_t)__cvta_generic_to_shared(ws_zero);
+  // lanes c of a chunk's slow items that ride: slow, previous item (lane c - 1, or the previous chunk's last) fast
+  auto riders = [&](int c) {
+    const uint32_t sl = ws_slow[c];
+    const uint32_t prev_slow = (sl << 1) | (c > 0 ? (ws_slow[c - 1] >> 31) : 1u);
+    return sl & ~prev_slow;
+  };
   for (int ch = warp; ch < n_chunks; ch += NWARPS) {
-    int before = lane < ch ? __popc(ws_mask[lane]) : 0;
+    int before = lane < ch ? __popc(ws_mask[lane] & ~riders(lane)) : 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
-    const uint32_t mine = ws_mask[ch];
-    const uint32_t zero_addr = (uint32_t)__cvta_generic_to_shared(ws_zero);
+    const uint32_t mine = ws_mask[ch], slow_c = ws_slow[ch], ride = riders(ch), own = mine & ~ride;
     if ((mine >> lane) & 1u) {
       const Item it = ws_items[ch * 32 + lane];
-      const bool slow = (it.w0 >> 24) == kSlow;
       const uint32_t end_item = (uint32_t)(ch * 32 + lane + 1);
-      Event e;
-      e.d = slow ? 0u : (it.w0 & 0xffffffu);
-      e.ebits = slow ? 0u : ((it.w0 >> 24) << 23);
-      e.span = slow ? ((end_item - 1) | (end_item << 11)) : ((uint32_t)(ch * 32 + (int)it.w1) | (end_item << 11) | kRunFlag);
-      e.taddr = slow ? sq_addr + (end_item - 1) * (kItem * 4u) : zero_addr;
-      ws_events[before + __popc(mine & ((1u << lane) - 1u))] = e;
+      const uint32_t my_terms = sq_addr + (end_item - 1) * (kItem * 4u);
+      const int below = __popc(own & ((1u << lane) - 1u));
+      if ((ride >> lane) & 1u) {
+        ws_events[before + below - 1].taddr = my_terms;  // the record of the run that ends just before this item
+      } else if ((slow_c >> lane) & 1u) {
+        Event e;
+        e.d = 0u;
+        e.ebits = 0u;
+        e.span = 0u;
+        e.taddr = my_terms;
+        ws_events[before + below] = e;
+      } else {
+        const bool next_slow = lane < 31 ? ((slow_c >> (lane + 1)) & 1u) != 0 : (ch + 1 < n_chunks && (ws_slow[ch + 1] & 1u));
+        Event *e = ws_events + before + below;
+        e->d = it.w0 & 0xffffffu;
+        e->ebits = (it.w0 >> 24) << 23;
+        e->span = (uint32_t)(ch * 32 + (int)it.w1) | (end_item << 11) | kRunFlag;
+        if (!next_slow) e->taddr = zero_addr;  // else the slow item behind this run writes its terms' address here
+      }
     }
     if (ch == n_chunks - 1) {
       // padding (no step, eight zeros) up to the walk's trip and two records beyond it
-      const int total = before + __popc(mine);
+      const int total = before + __popc(own);
       if (lane < kWalkUnroll + 1) {
         Event e;
         e.d = 0u;
@@ -329,7 +363,7 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
     }
   }
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
-  if (warp == 0 && lane == 0) *ws_out = walk_events(sq, ws_events, *ws_total);
+  if (warp == 0 && lane == 0) *ws_out = walk_events(sq, ws_events, *ws_total, zero_addr);
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));
   return *ws_out;
 }
