@@ -88,7 +88,7 @@ def main():
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--kernel", default="staged", choices=["staged", "direct", "mma"],
+    ap.add_argument("--kernel", default="staged", choices=["staged", "direct", "mma", "tcgen05"],
                     help="staged = bulk-copy pipelined kernel when the shape fits (default); direct = direct-load kernel")
     ap.add_argument("--pdl", action="store_true", help="chain the timed launches with programmatic dependent launch")
     a = ap.parse_args()
@@ -98,9 +98,10 @@ def main():
     import camelid_b200 as cm
     from camelid_b200._lib import check
 
-    check(cm.lib().cmld_gemv_select_kernel({"direct": 1, "mma": 4}.get(a.kernel, 0)))
+    sel = {"direct": 1, "mma": 4, "tcgen05": 32}.get(a.kernel, 0)
+    check(cm.lib().cmld_gemv_select_kernel(sel))
     if a.pdl:
-        check(cm.lib().cmld_gemv_select_kernel({"direct": 1, "mma": 4}.get(a.kernel, 0) | 2))
+        check(cm.lib().cmld_gemv_select_kernel(sel | 2))
     qts = [a.qt] if a.qt else sorted(BPW)
     shapes = [(a.rows, a.cols)] if a.rows and a.cols else SHAPES
     batches = [a.batch] if a.batch else [1, 4, 8]
