@@ -93,17 +93,24 @@ XS_HD uint32_t item_local(const float (&t)[kItem], float a_start, float a_end, u
   const int eb = (int)(f32_bits(a_start) >> 23) - 127;
   if (eb != (int)(f32_bits(a_end) >> 23) - 127 || eb < -100 || eb > 126) return kSlow;
   const float scale = bits_f32((uint32_t)(23 - eb + 127) << 23);  // 2^(23-eb): term -> units of the binade's ulp
-  bool slow = false;
+  // q + 2^23 rounds q to an integer (ties to even); its bits minus those of 2^23 are that integer (also when the sum
+  // is 2^24).  A term as large as the binade itself (q >= 2^23) makes that difference >= 2^23, so the item's d shows
+  // it; NaN and infinity never get here (a_end is not finite then).
+  float worst = 0.0f;  // largest |q - round(q)|: 0.5 means a tie, whose result depends on the parity of S
+  uint32_t acc = 0;
   for (int i = 0; i < kItem; ++i) {
     const float q = mul_rn(t[i], scale);  // exact (power of two) unless it underflows towards 0, where it rounds to 0 units anyway
-    slow |= !(q < 8388608.0f);            // a term as large as the binade itself (or NaN): cannot stay inside it
-    // q + 2^23 rounds q to an integer (ties to even); its bits minus those of 2^23 are that integer (also when the sum is 2^24)
     const float m = add_rn(q, 8388608.0f);
     const float diff = add_rn(q, -add_rn(m, -8388608.0f));  // both subtractions are exact
-    slow |= diff == 0.5f || diff == -0.5f;                  // a tie: the result depends on the parity of S
-    d += f32_bits(m) - 0x4b000000u;
+#if defined(__CUDA_ARCH__)
+    worst = fmaxf(worst, fabsf(diff));
+#else
+    worst = std::fmax(worst, std::fabs(diff));
+#endif
+    acc += f32_bits(m);
   }
-  if (slow || (d >> 24)) return kSlow;
+  d = acc - (uint32_t)kItem * 0x4b000000u;
+  if (worst == 0.5f || (d >> 23)) return kSlow;
   return (uint32_t)(eb + 127);
 }
 

@@ -305,7 +305,13 @@ __device__ __forceinline__ void sb_ints_q6k(const uint8_t *blk, const uint8_t *r
 }
 
 // Shape of a job's lane assignment: L lanes per row, rpw rows per warp.
-__device__ __forceinline__ int lanes_per_row(int n_it) { return n_it < 32 ? n_it : 32; }
+__host__ __device__ __forceinline__ int lanes_per_row(int n_it) { return n_it < 32 ? n_it : 32; }
+// K-quant rows shorter than a few superblocks (column shards of a tensor-parallel split) keep a minimum of lanes per
+// row, the spare ones idle: the chain lanes of a warp serve at most 8 (Q4_K) / 2 (Q6_K) rows (see chain_slot).
+__host__ __device__ __forceinline__ int lanes_per_row_k(int qt, int n_it) {
+  const int L = lanes_per_row(n_it), lo = qt == CMLD_Q6_K ? 16 : 4;
+  return L < lo ? lo : L;
+}
 
 // The chain lanes.  After tile_dot, res[k] of a chain lane is a finished or running row sum; this says which
 // (row of the tile, batch column) it belongs to.  Q4_K: rounds of up to 4 columns; Q8_0: one round of all
@@ -832,7 +838,8 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   int done_pairs = 0;
   // lane geometry of the two block sizes a launch can hold (every job has the same number of columns), once:
   // the divisions are not repeated per tile
-  const int Lk = lanes_per_row(nsb > 0 ? nsb : 1), rpwk = 32 / Lk, lisk = lane % Lk, rsubk = lane / Lk;
+  const int Lk = lanes_per_row_k(CMLD_Q4_K, nsb > 0 ? nsb : 1), rpwk = 32 / Lk, lisk = lane % Lk, rsubk = lane / Lk;
+  const int L6 = lanes_per_row_k(CMLD_Q6_K, nsb > 0 ? nsb : 1), rpw6 = 32 / L6, lis6 = lane % L6, rsub6 = lane / L6;
   const int L0 = lanes_per_row(a.cols >> 5), rpw0 = 32 / L0, lis0 = lane % L0, rsub0 = lane / L0;
   // unit i -> (tile tl of this CTA's list, piece): advanced without divisions; a group's units are kPipeGroups apart
   int tl = group, piece = 0;
@@ -860,7 +867,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const bool last = piece == J.n_pieces - 1;
     const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
     const bool is0 = J.qt == CMLD_Q8_0;
-    const int L = is0 ? L0 : Lk, rpw = is0 ? rpw0 : rpwk, lis = is0 ? lis0 : lisk, rsub = is0 ? rsub0 : rsubk;
+    const bool is6 = J.qt == CMLD_Q6_K;
+    const int L = is0 ? L0 : (is6 ? L6 : Lk), rpw = is0 ? rpw0 : (is6 ? rpw6 : rpwk), lis = is0 ? lis0 : (is6 ? lis6 : lisk),
+              rsub = is0 ? rsub0 : (is6 ? rsub6 : rsubk);
     {
       const int wge = wg;
       if (piece == 0) {
@@ -987,7 +996,7 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
     const GemvJob &g = jobs[k];
     if (g.cols != cols) return false;
     const int n_it = g.qt == CMLD_Q8_0 ? (int)(cols >> 5) : (int)(cols >> 8);
-    const int L = n_it < 32 ? n_it : 32, rpw = 32 / L;
+    const int L = g.qt == CMLD_Q8_0 ? lanes_per_row(n_it) : lanes_per_row_k(g.qt, n_it), rpw = 32 / L;
     // the chain lanes of a warp must fit in it (see chain_slot)
     if (g.qt == CMLD_Q8_0) {
       need_0 = true;

@@ -107,7 +107,9 @@ def test_activation_quantisers_bit_exact(cm, orc, cols, batch):
 @pytest.mark.parametrize("name,rows,cols", [
     ("Q8_0", 96, 64), ("Q8_0", 515, 2048), ("Q8_0", 64, 8192),
     ("Q4_K", 37, 256), ("Q4_K", 512, 4096), ("Q4_K", 130, 3072), ("Q4_K", 64, 14336),
-    ("Q6_K", 33, 256), ("Q6_K", 512, 4096), ("Q6_K", 130, 3072), ("Q6_K", 64, 14336)])
+    ("Q6_K", 33, 256), ("Q6_K", 512, 4096), ("Q6_K", 130, 3072), ("Q6_K", 64, 14336),
+    # column shards of an eight-way tensor-parallel split: rows of two and seven superblocks
+    ("Q4_K", 300, 512), ("Q4_K", 300, 1792), ("Q6_K", 300, 512), ("Q6_K", 300, 1792)])
 @pytest.mark.parametrize("batch", [1, 2, 3, 8])
 @pytest.mark.parametrize("kernel", ["staged", "generic", "tcgen05"])
 def test_gemv_matches_checker(cm, orc, name, rows, cols, batch, kernel):
