@@ -278,7 +278,9 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
   Event *ws_events = reinterpret_cast<Event *>(ws + 448 + (n >> 3) * 8);  // [n / 8 + 8]
   asm volatile("bar.sync %0, %1;" ::"r"(bar), "n"(NWARPS * 32));  // sq complete
   // approximate prefix sums (tree sums: they only predict binades): inside every chunk first; the terms stay in registers
-  float tt[kTrips][kItem], incl_[kTrips], loc_[kTrips];
+  // (the first chunk's terms stay in registers across the barrier; a warp's further chunks — rows wider than
+  // NWARPS * 256 — are read again: fewer live registers in the kernels that inline this)
+  float tt[kItem], incl_[kTrips], loc_[kTrips];
   if (warp == 0 && lane < 8) ws_zero[lane] = 0.0f;
 #pragma unroll
   for (int trip = 0; trip < kTrips; ++trip) {
@@ -286,8 +288,10 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
     if (ch < n_chunks) {
       const float4 a = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem);
       const float4 b = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem + 4);
-      tt[trip][0] = a.x, tt[trip][1] = a.y, tt[trip][2] = a.z, tt[trip][3] = a.w;
-      tt[trip][4] = b.x, tt[trip][5] = b.y, tt[trip][6] = b.z, tt[trip][7] = b.w;
+      if (trip == 0) {
+        tt[0] = a.x, tt[1] = a.y, tt[2] = a.z, tt[3] = a.w;
+        tt[4] = b.x, tt[5] = b.y, tt[6] = b.z, tt[7] = b.w;
+      }
       const float loc = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
       float incl = loc;  // inclusive scan over the lanes
 #pragma unroll
@@ -308,8 +312,15 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
       float base = lane < ch ? ws_chunk[lane] : 0.0f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
-      uint32_t slow_mask;
-      const uint32_t ev = prepare_chunk(tt[trip], base + (incl_[trip] - loc_[trip]), base + incl_[trip], lane, ws_items + ch * 32, slow_mask);
+      uint32_t slow_mask, ev;
+      if (trip == 0) {
+        ev = prepare_chunk(tt, base + (incl_[trip] - loc_[trip]), base + incl_[trip], lane, ws_items + ch * 32, slow_mask);
+      } else {
+        const float4 a = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem);
+        const float4 b = *reinterpret_cast<const float4 *>(sq + ch * kChunk + lane * kItem + 4);
+        const float t2[kItem] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        ev = prepare_chunk(t2, base + (incl_[trip] - loc_[trip]), base + incl_[trip], lane, ws_items + ch * 32, slow_mask);
+      }
       if (lane == 0) {
         ws_mask[ch] = ev;
         ws_slow[ch] = slow_mask;
