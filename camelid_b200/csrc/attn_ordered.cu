@@ -246,7 +246,10 @@ __global__ void __launch_bounds__(kOaThreads, 1) attn_ordered_kernel(AttnArgs a,
   // ranges: CTA r scores positions [r*len, (r+1)*len), in n_blocks blocks of bsz positions
   const int len = (n_pos + kOaCluster - 1) / kOaCluster;
   const int lo = crank * len, hi = min(n_pos, lo + len);
-  const int n_blocks = hi > lo ? (hi - lo + kOaKBlock - 1) / kOaKBlock : 0;
+  // contexts of up to 2048 positions: a CTA's range (at most 256 positions) is one block filling both staging
+  // buffers — one wait and one pass instead of two; longer contexts: blocks of up to 128, double-buffered
+  const int kblk = kResident ? 2 * kOaKBlock : kOaKBlock;
+  const int n_blocks = hi > lo ? (hi - lo + kblk - 1) / kblk : 0;
   const int bsz = n_blocks > 0 ? (hi - lo + n_blocks - 1) / n_blocks : 0;
   auto issue_k = [&](int blk) {
     if (blk < n_blocks) {
