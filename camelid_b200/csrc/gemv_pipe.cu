@@ -547,7 +547,7 @@ __device__ __forceinline__ int tile_job(const PipeArgs &a, int t) {
 
 // ---------------------------------------------------------------- the kernel
 
-template <int B>
+template <int B, bool SHORT_ROWS>
 __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
@@ -838,8 +838,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   int done_pairs = 0;
   // lane geometry of the two block sizes a launch can hold (every job has the same number of columns), once:
   // the divisions are not repeated per tile
-  const int Lk = lanes_per_row_k(CMLD_Q4_K, nsb > 0 ? nsb : 1), rpwk = 32 / Lk, lisk = lane % Lk, rsubk = lane / Lk;
-  const int L6 = lanes_per_row_k(CMLD_Q6_K, nsb > 0 ? nsb : 1), rpw6 = 32 / L6, lis6 = lane % L6, rsub6 = lane / L6;
+  // (SHORT_ROWS: K-quant rows of fewer superblocks than 16, with a Q6_K matrix in the launch, or 4 keep that many
+  // lanes per row; a separate instantiation, so that the usual shapes run the code they always ran)
+  const int Lk = SHORT_ROWS ? max(lanes_per_row(nsb > 0 ? nsb : 1), a.need_k6 ? 16 : 4) : lanes_per_row(nsb > 0 ? nsb : 1);
+  const int rpwk = 32 / Lk, lisk = lane % Lk, rsubk = lane / Lk;
   const int L0 = lanes_per_row(a.cols >> 5), rpw0 = 32 / L0, lis0 = lane % L0, rsub0 = lane / L0;
   // unit i -> (tile tl of this CTA's list, piece): advanced without divisions; a group's units are kPipeGroups apart
   int tl = group, piece = 0;
@@ -867,9 +869,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const bool last = piece == J.n_pieces - 1;
     const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
     const bool is0 = J.qt == CMLD_Q8_0;
-    const bool is6 = J.qt == CMLD_Q6_K;
-    const int L = is0 ? L0 : (is6 ? L6 : Lk), rpw = is0 ? rpw0 : (is6 ? rpw6 : rpwk), lis = is0 ? lis0 : (is6 ? lis6 : lisk),
-              rsub = is0 ? rsub0 : (is6 ? rsub6 : rsubk);
+    const int L = is0 ? L0 : Lk, rpw = is0 ? rpw0 : rpwk, lis = is0 ? lis0 : lisk, rsub = is0 ? rsub0 : rsubk;
     {
       const int wge = wg;
       if (piece == 0) {
@@ -958,6 +958,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
 struct PipePlan {
   PipeArgs args;
   int smem_bytes;
+  bool short_rows;  // K-quant rows shorter than the lanes a row keeps: the SHORT_ROWS instantiation
 };
 
 static int g_sm_count = 0;
@@ -966,7 +967,8 @@ static bool g_attr_set[9] = {false};
 template <int B>
 static int32_t launch_pipe_b(const PipePlan &p, int grid, cudaStream_t s, bool pdl) {
   if (!g_attr_set[B]) {
-    CMLD_CUDA(cudaFuncSetAttribute(gemv_pipe_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    CMLD_CUDA(cudaFuncSetAttribute(gemv_pipe_kernel<B, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    CMLD_CUDA(cudaFuncSetAttribute(gemv_pipe_kernel<B, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     g_attr_set[B] = true;
   }
   cudaLaunchConfig_t cfg{};
@@ -979,7 +981,8 @@ static int32_t launch_pipe_b(const PipePlan &p, int grid, cudaStream_t s, bool p
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  CMLD_CUDA(cudaLaunchKernelEx(&cfg, gemv_pipe_kernel<B>, p.args));
+  if (p.short_rows) CMLD_CUDA(cudaLaunchKernelEx(&cfg, gemv_pipe_kernel<B, true>, p.args));
+  else CMLD_CUDA(cudaLaunchKernelEx(&cfg, gemv_pipe_kernel<B, false>, p.args));
   return CMLD_OK;
 }
 
@@ -992,11 +995,16 @@ static bool plan_pipe(const GemvJob *jobs, int n_jobs, int32_t batch, PipePlan &
   PipeArgs &a = p.args;
   need_k4 = need_k6 = need_0 = false;
   int stage = 0, tiles = 0, n_pieces = -1;
+  // one lane geometry for the K-quant jobs of a launch (they share the number of superblocks per row)
+  int lanes_k = 1;
+  for (int k = 0; k < n_jobs; ++k)
+    if (jobs[k].qt == CMLD_Q4_K || jobs[k].qt == CMLD_Q6_K) lanes_k = std::max(lanes_k, lanes_per_row_k(jobs[k].qt, (int)(cols >> 8)));
+  p.short_rows = lanes_k > lanes_per_row((int)(cols >> 8) > 0 ? (int)(cols >> 8) : 1);
   for (int k = 0; k < n_jobs; ++k) {
     const GemvJob &g = jobs[k];
     if (g.cols != cols) return false;
     const int n_it = g.qt == CMLD_Q8_0 ? (int)(cols >> 5) : (int)(cols >> 8);
-    const int L = g.qt == CMLD_Q8_0 ? lanes_per_row(n_it) : lanes_per_row_k(g.qt, n_it), rpw = 32 / L;
+    const int L = g.qt == CMLD_Q8_0 ? lanes_per_row(n_it) : lanes_k, rpw = 32 / L;
     // the chain lanes of a warp must fit in it (see chain_slot)
     if (g.qt == CMLD_Q8_0) {
       need_0 = true;
