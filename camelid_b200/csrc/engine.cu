@@ -858,9 +858,15 @@ static int32_t engine_step(cmld_engine *e, const StepOpts &o) {
   for (int32_t li = o.layer_begin; li < l_end; ++li) {
     LayerW &L = e->layers[li];
     {
-      const Proj p[3] = {{&L.proj[0], e->q, nullptr, e->q_width},
-                         {&L.proj[1], e->k, nullptr, e->kv_width},
-                         {&L.proj[2], e->v, nullptr, e->kv_width}};
+      // The three projections share a launch; the matrices of the type whose tiles take longest (Q6_K, then Q8_0)
+      // go first, so that a CTA's last round of tiles is made of the quick ones.
+      const Proj qkv[3] = {{&L.proj[0], e->q, nullptr, e->q_width},
+                           {&L.proj[1], e->k, nullptr, e->kv_width},
+                           {&L.proj[2], e->v, nullptr, e->kv_width}};
+      auto tile_cost = [](const Weight *w) { return w->qt == CMLD_Q6_K ? 0 : (w->qt == CMLD_Q8_0 ? 1 : 2); };
+      int order[3] = {0, 1, 2};
+      std::stable_sort(order, order + 3, [&](int x, int y) { return tile_cost(qkv[x].w) < tile_cost(qkv[y].w); });
+      const Proj p[3] = {qkv[order[0]], qkv[order[1]], qkv[order[2]]};
       GemvPeer g{};
       take_pending(g);
       // the attention that follows reads this layer's KV rows: have them pulled into L2 meanwhile (every row but
