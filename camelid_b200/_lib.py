@@ -119,6 +119,7 @@ def lib():
         "cmld_engine_step_batch": (i32, [vp, i32, vp, vp, vp, vp, vp, vp]),
         "cmld_engine_last_timing": (i32, [vp, P(f32), P(i64)]),
         "cmld_peer_wait_selftest": (i32, [i32]),
+        "cmld_exact_sum_selftest": (i32, [vp, i32, vp]),
         "cmld_weight_create": (i32, [i32, i64, i64, vp, u64, P(vp)]),
         "cmld_weight_synth": (i32, [i32, u64, u64, i64, i64, i64, f32, P(vp)]),
         "cmld_weight_shard": (i32, [vp, i64, i64, i64, i64, i64, i64, P(vp)]),

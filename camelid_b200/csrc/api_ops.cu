@@ -294,6 +294,20 @@ int32_t cmld_gemv(const cmld_weight *w, const void *act_dev, int32_t batch, floa
   return check_op_status("gemv");
 }
 
+// The parallel evaluation of the sequential f32 sum on n device-resident non-negative terms: sums_host[0] by the
+// usual path, sums_host[1] by walking the same event list with every step checked and every second run forced to
+// be replayed term by term.  Both must equal the one-accumulator loop bit for bit.
+int32_t cmld_exact_sum_selftest(const float *terms_dev, int32_t n, float *sums_host) {
+  if (!terms_dev || !sums_host) return fail(CMLD_ERR_INVALID, "exact sum self-test: null argument");
+  float *out = nullptr;
+  CMLD_CUDA(cudaMalloc(&out, 2 * sizeof(float)));
+  int32_t rc = launch_exact_sum_selftest(terms_dev, n, out, nullptr);
+  if (rc == CMLD_OK && cudaMemcpy(sums_host, out, 2 * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess)
+    rc = fail(CMLD_ERR_CUDA, "exact sum self-test: %s", cudaGetErrorString(cudaGetLastError()));
+  cudaFree(out);
+  return rc;
+}
+
 // Runs the receiving side of a peer-memory sum against an arrival word that nobody raises: the wait must run
 // out after timeout_ms, record the status word and let the kernel finish.  Returns what the status word said
 // (CMLD_ERR_TIMEOUT when the bound works); the context stays usable.

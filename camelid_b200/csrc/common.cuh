@@ -288,6 +288,7 @@ struct NormQuantArgs {
   int32_t exact;               // RMSNorm: add the squares one after another like the CPU (slow)
 };
 int32_t launch_norm_quant(const NormQuantArgs &a, cudaStream_t s);
+int32_t launch_exact_sum_selftest(const float *terms, int32_t n, float *out, cudaStream_t s);
 // key_out != null: a vocabulary shard — the final stage writes the packed (value, idx_offset + index)
 // key per row instead of the token, and leaves the feedback to launch_argmax_finish.
 int32_t launch_argmax(const float *x, int64_t n, int32_t batch, float *part_val, int32_t *part_idx,

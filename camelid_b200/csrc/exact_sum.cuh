@@ -386,6 +386,17 @@ __device__ __forceinline__ float cta_sum(const float *sq, int n, int warp, int l
   return *ws_out;
 }
 
+// For tests: the checked walk over the event list the last cta_sum call left in `ws`, with the binade of every second
+// run made wrong first, so that those runs are replayed term by term — the result must have the same bits.  One thread.
+__device__ inline float rewalk_with_forced_replays(const float *sq, int n, uint8_t *ws) {
+  Event *ev = reinterpret_cast<Event *>(ws + 448 + (n >> 3) * 8);
+  const int total = *reinterpret_cast<const int *>(ws + 388);
+  int runs = 0;
+  for (int k = 0; k < total; ++k)
+    if ((ev[k].span & kRunFlag) && (runs++ & 1)) ev[k].ebits ^= 0x00800000u;
+  return walk_events_checked(sq, ev, total, (uint32_t)__cvta_generic_to_shared(ws + 400));
+}
+
 // Shared-memory bytes cta_sum needs besides sq itself, for n terms.
 __host__ __device__ inline int workspace_bytes(int n) { return 448 + (n >> 3) * 8 + ((n >> 3) + 8) * 16; }
 

@@ -422,4 +422,36 @@ int32_t launch_peer_reduce(const GemvPeer &rx, int32_t batch, int32_t hidden, in
   return CMLD_OK;
 }
 
+
+// ---------------------------------------------------------------- self-test of the exact sum
+
+// out[0] = the sum of n non-negative terms by xsum::cta_sum; out[1] = the same event list walked again with the check
+// in front of every step and every second run forced to fail it (replayed term by term).  Both must be the
+// sequential sum's bits.
+__global__ void __launch_bounds__(kNormThreads) exact_sum_selftest_kernel(const float *terms, int n, float *out) {
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  float *sq = reinterpret_cast<float *>(dyn_smem);
+  uint8_t *ws = dyn_smem + (size_t)n * 4;
+  for (int i = threadIdx.x; i < n; i += kNormThreads) sq[i] = terms[i];
+  const float s = xsum::cta_sum<kNormThreads / 32>(sq, n, threadIdx.x >> 5, threadIdx.x & 31, 1, ws);
+  if (threadIdx.x == 0) {
+    out[0] = s;
+    out[1] = xsum::rewalk_with_forced_replays(sq, n, ws);
+  }
+}
+
+int32_t launch_exact_sum_selftest(const float *terms, int32_t n, float *out, cudaStream_t s) {
+  if (n <= 0 || n % 256 || n > kNormMaxExact) return fail(CMLD_ERR_SHAPE, "exact sum self-test: n must be a multiple of 256, at most %d", kNormMaxExact);
+  const size_t smem = (size_t)n * 4 + xsum::workspace_bytes(n);
+  static bool configured = false;
+  if (!configured) {
+    CMLD_CUDA(cudaFuncSetAttribute(exact_sum_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kNormMaxExact * 4 + xsum::workspace_bytes(kNormMaxExact)));
+    configured = true;
+  }
+  exact_sum_selftest_kernel<<<1, kNormThreads, smem, s>>>(terms, n, out);
+  CMLD_CUDA(cudaGetLastError());
+  return CMLD_OK;
+}
+
 }  // namespace cmld

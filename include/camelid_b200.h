@@ -320,6 +320,12 @@ CMLD_API int32_t cmld_gemv_select_kernel(int32_t choice);
  * arrival word that nobody raises; returns CMLD_ERR_TIMEOUT after timeout_ms (1..5000) when the bound works,
  * CMLD_ERR_STATE otherwise.  One GPU; nothing faults or hangs. */
 CMLD_API int32_t cmld_peer_wait_selftest(int32_t timeout_ms);
+/* Self-test of the parallel evaluation of the sequential f32 sum that RMSNorm (rms_norm_into,
+ * src/tensor/mod.rs:2740-2764) and the softmax of attention (src/inference.rs:30297-30466) use (no reference
+ * counterpart): n non-negative f32 terms on the device, n a multiple of 256, at most 8192.  sums_host[0] = the
+ * sum by the usual path; sums_host[1] = the same event list walked with every step checked and every second
+ * run forced to be replayed term by term.  Both must be the one-accumulator loop's bits. */
+CMLD_API int32_t cmld_exact_sum_selftest(const float *terms_dev, int32_t n, float *sums_host);
 /* The staged kernel with its fused prologue: y = W . quantise(f(x)) (+ residual), with
  * f = RMSNorm(x) * norm_w (mode 1), x (mode 2) or SwiGLU(x, x2) (mode 3); x_dev/x2_dev are f32
  * [batch][cols], batch <= 8.  One launch replaces norm/activation kernel + quantiser + matvec. */

@@ -343,6 +343,36 @@ def test_rms_norm_sum_of_squares_is_the_sequential_sum(cm, orc, cols):
         assert np.array_equal(out[b].view(np.uint32), ref.view(np.uint32)), b
 
 
+# The exact sum's two walks on the device: the usual one (integer steps, unchecked, verified on the side) and the
+# fallback (every step checked; here every second run is forced to fail its check and is replayed term by term).
+@pytest.mark.parametrize("n", [256, 1280, 4096, 8192])
+def test_exact_sum_walks_agree_with_the_sequential_sum(cm, n):
+    from camelid_b200.engine import DeviceBuffer
+    from camelid_b200._lib import check
+
+    rng = np.random.default_rng(n)
+    cases = []
+    g = rng.standard_normal(n).astype(np.float32)
+    cases.append((g * g).astype(np.float32))                                   # squares of N(0, 1)
+    cases.append(np.exp(g - 3.2).astype(np.float32))                           # softmax weights
+    cases.append((rng.integers(0, 64, n) / 8.0).astype(np.float32))            # ties
+    cases.append(np.full(n, 0.99999994, np.float32))                           # crossings at item boundaries
+    cases.append((1.0 + (rng.integers(0, 3, n) - 1) * 5.9604645e-8).astype(np.float32))
+    big = (g * g).astype(np.float32)
+    big[n // 3] = 1e4                                                          # one giant term
+    cases.append(big)
+    cases.append(np.zeros(n, np.float32))
+    for k, terms in enumerate(cases):
+        seq = np.float32(0.0)
+        for t in terms:
+            seq = np.float32(seq + t)
+        td = DeviceBuffer.from_numpy(terms)
+        out = np.zeros(2, np.float32)
+        check(cm.lib().cmld_exact_sum_selftest(td.ptr, n, out.ctypes.data))
+        assert out.view(np.uint32)[0] == np.float32(seq).view(np.uint32), (k, out[0], seq)
+        assert out.view(np.uint32)[1] == np.float32(seq).view(np.uint32), (k, out[1], seq)
+
+
 def test_argmax_lowest_index_wins(cm, orc):
     from camelid_b200.engine import DeviceBuffer
     from camelid_b200._lib import check
