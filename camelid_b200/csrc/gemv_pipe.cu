@@ -844,8 +844,11 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
   const int rpwk = 32 / Lk, lisk = lane % Lk, rsubk = lane / Lk;
   const int L0 = lanes_per_row(a.cols >> 5), rpw0 = 32 / L0, lis0 = lane % L0, rsub0 = lane / L0;
   // unit i -> (tile tl of this CTA's list, piece): advanced without divisions; a group's units are kPipeGroups apart
-  int tl = group, piece = 0;
-  for (int i = group; i < n_units; i += kPipeGroups) {
+  // likewise the unit's stage i % S and the parity (i / S) & 1 of its use of that stage: S is a multiple of the
+  // group count, so the stage advances by kPipeGroups and wraps
+  int tl = group, piece = 0, s = group;
+  uint32_t use_parity = 0;
+  for (int i = group; i < n_units; i += kPipeGroups, s += kPipeGroups, use_parity ^= (s >= S ? 1u : 0u), s -= (s >= S ? S : 0)) {
     if (i != group) {
       if (++piece == n_pieces) {
         piece = 0;
@@ -853,7 +856,6 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
       }
     }
     if (tl >= n_my_tiles) break;
-    const int s = i % S;
     int j, row0;
     if (a.paired) {
       j = tl & 1;
@@ -867,7 +869,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) gemv_pipe_kernel(const PipeAr
     const int nrows = min(J.tile_rows, J.rows - row0);
     const int it0 = piece * J.piece_blocks, cnt_it = min(J.piece_blocks, J.n_it - it0);
     const bool last = piece == J.n_pieces - 1;
-    const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], (uint32_t)((i / S) & 1), a.status));
+    const bool ready = __all_sync(0xffffffffu, mbar_wait(&full[s], use_parity, a.status));
     const bool is0 = J.qt == CMLD_Q8_0;
     const int L = is0 ? L0 : Lk, rpw = is0 ? rpw0 : rpwk, lis = is0 ? lis0 : lisk, rsub = is0 ? rsub0 : rsubk;
     {
